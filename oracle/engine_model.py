@@ -591,8 +591,9 @@ class OracleEngine:
         po.execute(descs, n, host_is_src=True)
 
     # -- introspection used by the parity tests ----------------------------------------------------
-    def block_slot_image(self, namespace, key_hash, slot) -> Optional[List[bytes]]:
-        b = self.read_cache.get((namespace, bytes(key_hash)))
+    def block_slot_image(self, instance_id, raw_hash, slot, group=0) -> Optional[List[bytes]]:
+        inst = self._instance(instance_id)
+        b = self.read_cache.get((inst.namespace, po.group_hash(bytes(raw_hash), group)))
         if b is None:
             return None
         raw = b.get_slot(slot)

@@ -1,0 +1,836 @@
+// sm_100a kernels and host-side sequencing of the transfer backend (see transfer.h).
+//
+// Kernels
+//   copy_items_ldst / copy_descs_ldst : CTA-wide 16-byte vector copy, any alignment.  Used as
+//       the HBM<->HBM gather/scatter of the staged route (bound by HBM bandwidth: every payload
+//       byte is read once and written once) and as the fallback when an address or size is
+//       not a multiple of 16.
+//   copy_items_tma / copy_descs_tma   : one thread per CTA drives a ring of bulk async copies
+//       (cp.async.bulk global->shared, then shared->global).  Used where the other side is
+//       behind PCIe or NVLink: a few CTAs keep hundreds of KiB in flight, which hides link
+//       latency without occupying the SMs a model is computing on.
+//
+// Every device-side wait is bounded; on expiry the kernel writes a code to a mapped status
+// word, drains its own stores and returns, so the context stays usable.
+#include "transfer.h"
+
+#include <algorithm>
+#include <cstring>
+
+namespace pf {
+
+#define PF_CUDA(expr)                                                                                   \
+  do {                                                                                                  \
+    cudaError_t err__ = (expr);                                                                         \
+    if (err__ != cudaSuccess)                                                                           \
+      throw Error::storage(strf("%s failed: %s (%s)", #expr, cudaGetErrorName(err__), cudaGetErrorString(err__))); \
+  } while (0)
+
+namespace {
+
+constexpr int kLdstThreads = 256;
+constexpr int kLdstUnroll = 4;
+constexpr uint32_t kPackChunk = 16384;   // bytes one CTA iteration of the ld/st kernel moves
+constexpr int kStages = 4;               // ring depth of the TMA kernels
+constexpr uint32_t kStageBytes = 32768;  // bytes per ring stage
+constexpr unsigned kStatusWaitExpired = 0x57A17u;
+
+__device__ __forceinline__ uint64_t side_addr(const Side &s, uint32_t i) {
+  if (s.table) return s.table[i];
+  uint64_t idx = s.ids ? (uint64_t)s.ids[i] : (uint64_t)i;
+  return s.base + idx * s.stride;
+}
+
+// Chunk generators: both yield (src, dst, len) triples for the calling CTA.
+struct ItemGen {
+  Side src, dst;
+  uint32_t item_bytes, chunk_bytes, chunks_per_item;
+  uint64_t cursor, total, step;
+  __device__ ItemGen(const Side &s, const Side &d, uint32_t n_items, uint32_t ib, uint32_t cb)
+      : src(s), dst(d), item_bytes(ib), chunk_bytes(cb) {
+    chunks_per_item = (ib + cb - 1) / cb;
+    total = (uint64_t)n_items * chunks_per_item;
+    cursor = blockIdx.x;
+    step = gridDim.x;
+  }
+  __device__ bool next(uint64_t &s, uint64_t &d, uint32_t &len) {
+    if (cursor >= total) return false;
+    uint32_t item = (uint32_t)(cursor / chunks_per_item);
+    uint32_t off = (uint32_t)(cursor % chunks_per_item) * chunk_bytes;
+    len = min(chunk_bytes, item_bytes - off);
+    s = side_addr(src, item) + off;
+    d = side_addr(dst, item) + off;
+    cursor += step;
+    return true;
+  }
+};
+
+// Descriptor triples [dst, src, size] as in the reference's kernel backend
+// (pegaflow-core/src/transfer/kernel.rs:21-24), sizes may differ per descriptor.
+struct DescGen {
+  const uint64_t *triples;
+  uint32_t n, chunk_bytes, i, step;
+  uint64_t off;
+  __device__ DescGen(const uint64_t *t, uint32_t n_, uint32_t cb)
+      : triples(t), n(n_), chunk_bytes(cb), i(blockIdx.x), step(gridDim.x), off(0) {}
+  __device__ bool next(uint64_t &s, uint64_t &d, uint32_t &len) {
+    while (i < n) {
+      uint64_t size = triples[3 * (uint64_t)i + 2];
+      if (off < size) {
+        uint64_t left = size - off;
+        len = left < chunk_bytes ? (uint32_t)left : chunk_bytes;
+        d = triples[3 * (uint64_t)i] + off;
+        s = triples[3 * (uint64_t)i + 1] + off;
+        off += len;
+        return true;
+      }
+      i += step;
+      off = 0;
+    }
+    return false;
+  }
+};
+
+// CTA-wide copy of one span.  16-byte vectors when source and destination share their
+// misalignment (head bytes are peeled), plain bytes otherwise.
+__device__ __forceinline__ void copy_span(uint64_t dst, uint64_t src, uint32_t len) {
+  const uint32_t tid = threadIdx.x, nthr = blockDim.x;
+  if (((dst ^ src) & 15ull) != 0) {
+    char *d = reinterpret_cast<char *>(dst);
+    const char *s = reinterpret_cast<const char *>(src);
+    for (uint32_t j = tid; j < len; j += nthr) d[j] = s[j];
+    return;
+  }
+  uint32_t head = (uint32_t)((16 - (src & 15ull)) & 15ull);
+  if (head > len) head = len;
+  if (tid < head) reinterpret_cast<char *>(dst)[tid] = reinterpret_cast<const char *>(src)[tid];
+  const int4 *s16 = reinterpret_cast<const int4 *>(src + head);
+  int4 *d16 = reinterpret_cast<int4 *>(dst + head);
+  const uint32_t body = len - head;
+  const uint32_t n16 = body >> 4;
+  for (uint32_t j = tid; j < n16; j += nthr * kLdstUnroll) {
+    int4 v[kLdstUnroll];
+#pragma unroll
+    for (int u = 0; u < kLdstUnroll; ++u) {
+      uint32_t jj = j + u * nthr;
+      if (jj < n16) {
+        asm volatile("ld.global.nc.L1::no_allocate.v4.s32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
+                     : "l"(s16 + jj));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kLdstUnroll; ++u) {
+      uint32_t jj = j + u * nthr;
+      if (jj < n16) d16[jj] = v[u];
+    }
+  }
+  const uint32_t tail_at = head + (n16 << 4);
+  for (uint32_t j = tail_at + tid; j < len; j += nthr)
+    reinterpret_cast<char *>(dst)[j] = reinterpret_cast<const char *>(src)[j];
+}
+
+__global__ void __launch_bounds__(kLdstThreads)
+copy_items_ldst(Side src, Side dst, uint32_t n_items, uint32_t item_bytes, uint32_t chunk_bytes) {
+  ItemGen gen(src, dst, n_items, item_bytes, chunk_bytes);
+  uint64_t s, d;
+  uint32_t len;
+  while (gen.next(s, d, len)) copy_span(d, s, len);
+}
+
+__global__ void __launch_bounds__(kLdstThreads)
+copy_descs_ldst(const uint64_t *__restrict__ triples, uint32_t n, uint32_t chunk_bytes) {
+  DescGen gen(triples, n, chunk_bytes);
+  uint64_t s, d;
+  uint32_t len;
+  while (gen.next(s, d, len)) copy_span(d, s, len);
+}
+
+// ---- bulk async copy (TMA) primitives ------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t *bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0,1,0,p;\n}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void bulk_g2s(void *smem_dst, uint64_t gsrc, uint32_t bytes, uint64_t *bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_s2g(uint64_t gdst, const void *smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Waits for a ring stage to fill.  Gives up after ~2 s (a link read normally takes microseconds).
+__device__ __forceinline__ bool wait_stage(uint64_t *bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t start = global_timer_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 1023u) == 0 && global_timer_ns() - start > 2000000000ull) return false;
+  }
+  return true;
+}
+
+// One thread runs the ring.  Prologue: loads 0..kStages-1 fill every stage.  Steady state, for
+// chunk k: wait for its load, issue its store, then (from k = 1 on) wait until every store but
+// the newest has finished reading shared memory and issue load k-1+kStages into the stage of
+// chunk k-1.  So kStages-1 loads are in flight while one store drains.
+template <class Gen>
+__device__ __forceinline__ void tma_ring(Gen &gen, char *ring, uint64_t *bars, uint32_t stage_bytes,
+                                         unsigned int *status) {
+  uint64_t dsts[kStages];
+  uint32_t lens[kStages];
+  for (int s = 0; s < kStages; ++s) mbar_init(&bars[s], 1);
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+
+  uint64_t produced = 0, consumed = 0;
+  bool more = true;
+  auto produce = [&]() -> bool {
+    uint64_t s, d;
+    uint32_t len;
+    if (!gen.next(s, d, len)) return false;
+    int st = (int)(produced % kStages);
+    dsts[st] = d;
+    lens[st] = len;
+    mbar_expect_tx(&bars[st], len);
+    bulk_g2s(ring + (size_t)st * stage_bytes, s, len, &bars[st]);
+    ++produced;
+    return true;
+  };
+  for (int s = 0; s < kStages && more; ++s) more = produce();
+  while (consumed < produced) {
+    const int st = (int)(consumed % kStages);
+    const uint32_t parity = (uint32_t)((consumed / kStages) & 1);
+    if (!wait_stage(&bars[st], parity)) {
+      *status = kStatusWaitExpired;
+      bulk_wait_all();
+      return;
+    }
+    bulk_s2g(dsts[st], ring + (size_t)st * stage_bytes, lens[st]);
+    bulk_commit();
+    ++consumed;
+    if (more && consumed >= 2) {
+      bulk_wait_read_1();  // every store but the newest has finished reading shared memory
+      more = produce();    // lands in the stage of chunk consumed-2
+    }
+  }
+  bulk_wait_all();
+}
+
+__global__ void __launch_bounds__(32)
+copy_items_tma(Side src, Side dst, uint32_t n_items, uint32_t item_bytes, uint32_t stage_bytes,
+               unsigned int *status) {
+  extern __shared__ __align__(128) char ring[];
+  __shared__ uint64_t bars[kStages];
+  if (threadIdx.x != 0) return;
+  ItemGen gen(src, dst, n_items, item_bytes, stage_bytes);
+  tma_ring(gen, ring, bars, stage_bytes, status);
+}
+
+__global__ void __launch_bounds__(32)
+copy_descs_tma(const uint64_t *__restrict__ triples, uint32_t n, uint32_t stage_bytes, unsigned int *status) {
+  extern __shared__ __align__(128) char ring[];
+  __shared__ uint64_t bars[kStages];
+  if (threadIdx.x != 0) return;
+  DescGen gen(triples, n, stage_bytes);
+  tma_ring(gen, ring, bars, stage_bytes, status);
+}
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace
+
+static_assert(kStages >= 2, "ring needs two stages");
+
+// ------------------------------------------------------------------------------------------------
+
+TransferBackend::TransferBackend(int device, const pf_backend_config *config) : device_(device) {
+  cfg_ = config ? *config : pf_backend_config{};
+  if (cfg_.staging_slot_bytes == 0) cfg_.staging_slot_bytes = 16u << 20;
+  if (cfg_.staging_slots <= 0) cfg_.staging_slots = 4;
+  if (cfg_.min_dma_bytes == 0) cfg_.min_dma_bytes = 256u << 10;
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0)
+    throw Error::cuda_init(strf("no CUDA device available (%s)", cudaGetErrorString(e)));
+  if (device < 0 || device >= count) throw Error::cuda_init(strf("device %d out of range (%d devices)", device, count));
+  DeviceGuard on_device(device);
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) throw Error::cuda_init("cudaGetDeviceProperties failed");
+  if (prop.major < 10)
+    throw Error::cuda_init(strf("device %d is sm_%d%d; this library carries sm_100a code only", device, prop.major,
+                                prop.minor));
+  sm_count_ = prop.multiProcessorCount;
+  if (cfg_.pack_ctas <= 0) cfg_.pack_ctas = sm_count_ * 8;
+  if (cudaStreamCreateWithFlags(&aux_, cudaStreamNonBlocking) != cudaSuccess)
+    throw Error::cuda_init("failed to create the copy stream");
+  PF_CUDA(cudaEventCreateWithFlags(&join_, cudaEventDisableTiming));
+  PF_CUDA(cudaHostAlloc(&status_host_, sizeof(unsigned int), cudaHostAllocMapped));
+  *status_host_ = 0;
+  PF_CUDA(cudaHostGetDevicePointer(&status_dev_, status_host_, 0));
+  PF_CUDA(cudaFuncSetAttribute(copy_items_tma, cudaFuncAttributeMaxDynamicSharedMemorySize, kStages * kStageBytes));
+  PF_CUDA(cudaFuncSetAttribute(copy_descs_tma, cudaFuncAttributeMaxDynamicSharedMemorySize, kStages * kStageBytes));
+  meta_grow(1u << 20);
+}
+
+TransferBackend::~TransferBackend() {
+  DeviceGuard on_device(device_);
+  if (aux_) cudaStreamSynchronize(aux_);
+  for (auto &r : meta_inflight_) cudaEventSynchronize(r.done);
+  for (auto &s : slots_) {
+    if (s.filled) cudaEventDestroy(s.filled);
+    if (s.drained) cudaEventDestroy(s.drained);
+  }
+  for (auto &r : meta_inflight_) cudaEventDestroy(r.done);
+  for (auto ev : event_pool_) cudaEventDestroy(ev);
+  for (auto &t : timed_) {
+    cudaEventDestroy(t.start);
+    cudaEventDestroy(t.stop);
+  }
+  for (auto ev : timing_event_pool_) cudaEventDestroy(ev);
+  if (staging_) cudaFree(staging_);
+  if (meta_dev_) cudaFree(meta_dev_);
+  if (meta_host_) cudaFreeHost(meta_host_);
+  if (status_host_) cudaFreeHost(status_host_);
+  if (join_) cudaEventDestroy(join_);
+  if (aux_) cudaStreamDestroy(aux_);
+}
+
+void TransferBackend::time_begin(cudaStream_t s, cudaEvent_t *start) {
+  *start = nullptr;
+  if (!cfg_.time_kernels) return;
+  if (timed_.size() > 8192) fold_timings(false);
+  auto take = [&]() {
+    if (!timing_event_pool_.empty()) {
+      cudaEvent_t ev = timing_event_pool_.back();
+      timing_event_pool_.pop_back();
+      return ev;
+    }
+    cudaEvent_t ev;
+    PF_CUDA(cudaEventCreate(&ev));
+    return ev;
+  };
+  *start = take();
+  PF_CUDA(cudaEventRecord(*start, s));
+}
+
+void TransferBackend::time_end(cudaStream_t s, cudaEvent_t start, uint64_t bytes, bool link) {
+  if (!start) return;
+  cudaEvent_t stop;
+  if (!timing_event_pool_.empty()) {
+    stop = timing_event_pool_.back();
+    timing_event_pool_.pop_back();
+  } else {
+    PF_CUDA(cudaEventCreate(&stop));
+  }
+  PF_CUDA(cudaEventRecord(stop, s));
+  timed_.push_back({start, stop, bytes, link});
+}
+
+void TransferBackend::fold_timings(bool wait) {
+  while (!timed_.empty()) {
+    TimedLaunch &t = timed_.front();
+    cudaError_t q = wait ? cudaEventSynchronize(t.stop) : cudaEventQuery(t.stop);
+    if (q != cudaSuccess) {
+      cudaGetLastError();
+      break;
+    }
+    float ms = 0;
+    if (cudaEventElapsedTime(&ms, t.start, t.stop) == cudaSuccess) {
+      if (t.link) {
+        stats_.link_kernel_ms += ms;
+        ++stats_.link_kernel_launches;
+        stats_.link_kernel_bytes += t.bytes;
+      } else {
+        stats_.pack_kernel_ms += ms;
+        ++stats_.pack_kernel_launches;
+        stats_.pack_kernel_bytes += t.bytes;
+      }
+    }
+    timing_event_pool_.push_back(t.start);
+    timing_event_pool_.push_back(t.stop);
+    timed_.pop_front();
+  }
+}
+
+void TransferBackend::stats(pf_backend_stats *out) {
+  if (cfg_.time_kernels) {
+    DeviceGuard on_device(device_);
+    fold_timings(false);
+  }
+  *out = stats_;
+  out->device_status = status_host_ ? *(volatile unsigned int *)status_host_ : 0;
+}
+
+cudaEvent_t TransferBackend::take_event() {
+  if (!event_pool_.empty()) {
+    cudaEvent_t ev = event_pool_.back();
+    event_pool_.pop_back();
+    return ev;
+  }
+  cudaEvent_t ev;
+  PF_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+  return ev;
+}
+
+void TransferBackend::meta_grow(size_t need) {
+  // Everything in flight still reads the old buffers: wait for it, then replace them.
+  for (auto &r : meta_inflight_) {
+    PF_CUDA(cudaEventSynchronize(r.done));
+    event_pool_.push_back(r.done);
+  }
+  meta_inflight_.clear();
+  size_t cap = meta_cap_ ? meta_cap_ : (1u << 20);
+  while (cap < need) cap *= 2;
+  if (meta_dev_) PF_CUDA(cudaFree(meta_dev_));
+  if (meta_host_) PF_CUDA(cudaFreeHost(meta_host_));
+  meta_dev_ = nullptr;
+  meta_host_ = nullptr;
+  PF_CUDA(cudaHostAlloc(&meta_host_, cap, cudaHostAllocDefault));
+  PF_CUDA(cudaMalloc(&meta_dev_, cap));
+  meta_cap_ = cap;
+  meta_head_ = 0;
+}
+
+size_t TransferBackend::meta_alloc(size_t bytes) {
+  bytes = align_up(std::max<size_t>(bytes, 16), 256);
+  // Drop regions whose work has already finished.
+  while (!meta_inflight_.empty() && cudaEventQuery(meta_inflight_.front().done) == cudaSuccess) {
+    event_pool_.push_back(meta_inflight_.front().done);
+    meta_inflight_.pop_front();
+  }
+  cudaGetLastError();  // cudaEventQuery reports "not ready" as an error code
+  if (bytes > meta_cap_ / 2) meta_grow(bytes * 2);
+  if (meta_head_ + bytes > meta_cap_) meta_head_ = 0;
+  const size_t begin = meta_head_, end = meta_head_ + bytes;
+  // Reclaim regions the new one overlaps (oldest first; they complete in order).
+  while (!meta_inflight_.empty()) {
+    bool overlaps = false;
+    for (auto &r : meta_inflight_)
+      if (r.begin < end && begin < r.end) overlaps = true;
+    if (!overlaps) break;
+    MetaRegion r = meta_inflight_.front();
+    meta_inflight_.pop_front();
+    PF_CUDA(cudaEventSynchronize(r.done));
+    event_pool_.push_back(r.done);
+  }
+  meta_head_ = end;
+  return begin;
+}
+
+void TransferBackend::meta_upload(size_t off, size_t bytes, cudaStream_t stream) {
+  PF_CUDA(cudaMemcpyAsync(meta_dev_ + off, meta_host_ + off, bytes, cudaMemcpyHostToDevice, stream));
+}
+
+void TransferBackend::ensure_staging() {
+  if (staging_) return;
+  PF_CUDA(cudaMalloc(&staging_, cfg_.staging_slot_bytes * (size_t)cfg_.staging_slots));
+  slots_.resize(cfg_.staging_slots);
+  for (int i = 0; i < cfg_.staging_slots; ++i) {
+    slots_[i].ptr = staging_ + (size_t)i * cfg_.staging_slot_bytes;
+    PF_CUDA(cudaEventCreateWithFlags(&slots_[i].filled, cudaEventDisableTiming));
+    PF_CUDA(cudaEventCreateWithFlags(&slots_[i].drained, cudaEventDisableTiming));
+  }
+}
+
+TransferBackend::Slot &TransferBackend::next_slot() {
+  Slot &s = slots_[slot_cursor_];
+  slot_cursor_ = (slot_cursor_ + 1) % slots_.size();
+  return s;
+}
+
+void TransferBackend::launch_pack(const Side &src, const Side &dst, size_t n_items, size_t item_bytes,
+                                  cudaStream_t s) {
+  if (n_items == 0) return;
+  const uint64_t chunks = (uint64_t)n_items * ((item_bytes + kPackChunk - 1) / kPackChunk);
+  const int grid = (int)std::min<uint64_t>(chunks, (uint64_t)cfg_.pack_ctas);
+  cudaEvent_t t0;
+  time_begin(s, &t0);
+  copy_items_ldst<<<grid, kLdstThreads, 0, s>>>(src, dst, (uint32_t)n_items, (uint32_t)item_bytes, kPackChunk);
+  PF_CUDA(cudaGetLastError());
+  time_end(s, t0, 2ull * n_items * item_bytes, false);
+  ++stats_.kernel_launches;
+}
+
+void TransferBackend::launch_link(const Side &src, const Side &dst, size_t n_items, size_t item_bytes,
+                                  cudaStream_t s, bool peer) {
+  if (n_items == 0) return;
+  // Bulk async copies need 16-byte aligned addresses and sizes.  Affine sides are checked here;
+  // whoever fills an address table clears tables_aligned_ when an entry is not aligned.
+  auto aligned16 = [](const Side &x) { return x.table != nullptr || ((x.base | x.stride) & 15ull) == 0; };
+  const bool tma_ok = aligned16(src) && aligned16(dst) && (item_bytes & 15u) == 0 && tables_aligned_;
+  int ctas = cfg_.link_ctas > 0 ? cfg_.link_ctas : (peer ? sm_count_ : 16);
+  cudaEvent_t t0;
+  time_begin(s, &t0);
+  if (tma_ok) {
+    const uint32_t stage = (uint32_t)std::min<size_t>(kStageBytes, item_bytes);
+    const uint64_t chunks = (uint64_t)n_items * ((item_bytes + stage - 1) / stage);
+    const int grid = (int)std::min<uint64_t>(chunks, (uint64_t)ctas);
+    copy_items_tma<<<grid, 32, (size_t)kStages * stage, s>>>(src, dst, (uint32_t)n_items, (uint32_t)item_bytes, stage,
+                                                             status_dev_);
+  } else {
+    const uint64_t chunks = (uint64_t)n_items * ((item_bytes + kPackChunk - 1) / kPackChunk);
+    const int grid = (int)std::min<uint64_t>(chunks, (uint64_t)std::max(ctas, sm_count_));
+    copy_items_ldst<<<grid, kLdstThreads, 0, s>>>(src, dst, (uint32_t)n_items, (uint32_t)item_bytes, kPackChunk);
+  }
+  PF_CUDA(cudaGetLastError());
+  time_end(s, t0, (uint64_t)n_items * item_bytes, true);
+  ++stats_.kernel_launches;
+}
+
+void TransferBackend::launch_descs(const uint64_t *triples_dev, size_t n, bool aligned, cudaStream_t s) {
+  if (n == 0) return;
+  int ctas = cfg_.link_ctas > 0 ? cfg_.link_ctas : 16;
+  if (aligned) {
+    const int grid = (int)std::min<size_t>(n, (size_t)ctas);
+    copy_descs_tma<<<grid, 32, (size_t)kStages * kStageBytes, s>>>(triples_dev, (uint32_t)n, kStageBytes, status_dev_);
+  } else {
+    const int grid = (int)std::min<size_t>(n, (size_t)std::max(ctas, sm_count_));
+    copy_descs_ldst<<<grid, kLdstThreads, 0, s>>>(triples_dev, (uint32_t)n, kPackChunk);
+  }
+  PF_CUDA(cudaGetLastError());
+  ++stats_.kernel_launches;
+}
+
+// Moves run.n_blocks items (`item_bytes` each) between the device side and a host run through
+// the staging ring.  `dev_side.ids` / `.table` already point at the run's first item.
+void TransferBackend::staged_run(const Side &dev_side, const pf_host_run &run, size_t /*ids_offset*/,
+                                 size_t item_bytes, bool host_is_src, cudaStream_t stream, bool *aux_touched) {
+  ensure_staging();
+  const size_t cap = cfg_.staging_slot_bytes / item_bytes;
+  char *host = static_cast<char *>(run.host);
+  const bool dense = run.stride_bytes == item_bytes;
+  for (size_t b0 = 0; b0 < run.n_blocks; b0 += cap) {
+    const size_t nb = std::min(cap, run.n_blocks - b0);
+    Side d = dev_side;
+    if (d.table) d.table += b0;
+    if (d.ids) d.ids += b0;
+    if (!d.table && !d.ids) d.base += (uint64_t)b0 * d.stride;
+    Slot &slot = next_slot();
+    const Side st{(uint64_t)(uintptr_t)slot.ptr, item_bytes, nullptr, nullptr};
+    char *h = host + b0 * run.stride_bytes;
+    if (!host_is_src) {
+      if (slot.used) PF_CUDA(cudaStreamWaitEvent(stream, slot.drained, 0));
+      launch_pack(d, st, nb, item_bytes, stream);
+      PF_CUDA(cudaEventRecord(slot.filled, stream));
+      PF_CUDA(cudaStreamWaitEvent(aux_, slot.filled, 0));
+      if (dense)
+        PF_CUDA(cudaMemcpyAsync(h, slot.ptr, nb * item_bytes, cudaMemcpyDeviceToHost, aux_));
+      else
+        PF_CUDA(cudaMemcpy2DAsync(h, run.stride_bytes, slot.ptr, item_bytes, item_bytes, nb, cudaMemcpyDeviceToHost,
+                                  aux_));
+      PF_CUDA(cudaEventRecord(slot.drained, aux_));
+    } else {
+      if (slot.used) PF_CUDA(cudaStreamWaitEvent(aux_, slot.drained, 0));
+      if (dense)
+        PF_CUDA(cudaMemcpyAsync(slot.ptr, h, nb * item_bytes, cudaMemcpyHostToDevice, aux_));
+      else
+        PF_CUDA(cudaMemcpy2DAsync(slot.ptr, item_bytes, h, run.stride_bytes, item_bytes, nb, cudaMemcpyHostToDevice,
+                                  aux_));
+      PF_CUDA(cudaEventRecord(slot.filled, aux_));
+      PF_CUDA(cudaStreamWaitEvent(stream, slot.filled, 0));
+      launch_pack(st, d, nb, item_bytes, stream);
+      PF_CUDA(cudaEventRecord(slot.drained, stream));
+    }
+    slot.used = true;
+    ++stats_.dma_copies;
+    stats_.bytes_staged += nb * item_bytes;
+    *aux_touched = true;
+  }
+}
+
+void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, bool host_is_src,
+                                  cudaStream_t stream, void *const *layer_done) {
+  DeviceGuard on_device(device_);
+  // ---- validate and plan the meta upload: block ids of every layer, plus an address table
+  // for each (layer, range) whose zero-copy part spans more than one host run.
+  struct RangePlan {
+    std::vector<size_t> zc_runs;  // indices of runs taking the zero-copy route
+    size_t zc_blocks = 0;
+    size_t table_off = 0, zc_ids_off = 0;  // valid when zc_runs.size() > 1
+  };
+  std::vector<size_t> ids_off(n_layers, 0);
+  std::vector<RangePlan> plans(n_layers * 2);
+  size_t meta_bytes = 0;
+  for (size_t li = 0; li < n_layers; ++li) {
+    const pf_layer_xfer &L = layers[li];
+    if (L.n_blocks == 0) continue;
+    if (L.n_ranges < 1 || L.n_ranges > 2) throw Error::invalid(strf("layer %zu: n_ranges must be 1 or 2", li));
+    if (L.range_bytes == 0 || L.range_bytes > 0xFFFFFFFFull)
+      throw Error::invalid(strf("layer %zu: range_bytes %zu unsupported", li, L.range_bytes));
+    if (L.n_blocks > 0xFFFFFFFFull) throw Error::invalid("too many blocks in one layer transfer");
+    if (!L.block_ids) throw Error::invalid(strf("layer %zu: block_ids is null", li));
+    ids_off[li] = meta_bytes;
+    meta_bytes += align_up(L.n_blocks * sizeof(uint32_t), 256);
+    for (uint32_t r = 0; r < L.n_ranges; ++r) {
+      RangePlan &P = plans[li * 2 + r];
+      size_t covered = 0;
+      for (size_t j = 0; j < L.n_runs[r]; ++j) {
+        const pf_host_run &run = L.runs[r][j];
+        if (run.first_block != covered)
+          throw Error::invalid(strf("layer %zu range %u: host runs must cover the blocks in order", li, r));
+        if (run.n_blocks && (!run.host || !run.host_device))
+          throw Error::invalid(strf("layer %zu range %u: host run without an address", li, r));
+        if (run.n_blocks > 1 && run.stride_bytes < L.range_bytes)
+          throw Error::invalid(strf("layer %zu range %u: host stride smaller than the range", li, r));
+        covered += run.n_blocks;
+        const size_t bytes = run.n_blocks * L.range_bytes;
+        bool staged = cfg_.route == PF_ROUTE_STAGED || (cfg_.route == PF_ROUTE_AUTO && bytes >= cfg_.min_dma_bytes);
+        if (L.range_bytes > cfg_.staging_slot_bytes) staged = false;
+        if (!staged && run.n_blocks) {
+          P.zc_runs.push_back(j);
+          P.zc_blocks += run.n_blocks;
+        }
+      }
+      if (covered != L.n_blocks)
+        throw Error::invalid(strf("layer %zu range %u: host runs cover %zu of %zu blocks", li, r, covered, L.n_blocks));
+      if (P.zc_runs.size() > 1) {
+        P.table_off = meta_bytes;
+        meta_bytes += align_up(P.zc_blocks * sizeof(uint64_t), 256);
+        P.zc_ids_off = meta_bytes;
+        meta_bytes += align_up(P.zc_blocks * sizeof(uint32_t), 256);
+      }
+    }
+  }
+  if (meta_bytes == 0) {
+    if (layer_done)
+      for (size_t li = 0; li < n_layers; ++li)
+        if (layer_done[li]) PF_CUDA(cudaEventRecord((cudaEvent_t)layer_done[li], stream));
+    return;
+  }
+  const size_t base = meta_alloc(meta_bytes);
+  tables_aligned_ = true;
+  for (size_t li = 0; li < n_layers; ++li) {
+    const pf_layer_xfer &L = layers[li];
+    if (L.n_blocks == 0) continue;
+    std::memcpy(meta_host_ + base + ids_off[li], L.block_ids, L.n_blocks * sizeof(uint32_t));
+    for (uint32_t r = 0; r < L.n_ranges; ++r) {
+      RangePlan &P = plans[li * 2 + r];
+      if (P.zc_runs.size() <= 1) continue;
+      uint64_t *table = reinterpret_cast<uint64_t *>(meta_host_ + base + P.table_off);
+      uint32_t *zids = reinterpret_cast<uint32_t *>(meta_host_ + base + P.zc_ids_off);
+      size_t k = 0;
+      for (size_t j : P.zc_runs) {
+        const pf_host_run &run = L.runs[r][j];
+        for (size_t i = 0; i < run.n_blocks; ++i, ++k) {
+          table[k] = run.host_device + (uint64_t)i * run.stride_bytes;
+          zids[k] = L.block_ids[run.first_block + i];
+          if (table[k] & 15ull) tables_aligned_ = false;
+        }
+      }
+    }
+  }
+  meta_upload(base, meta_bytes, stream);
+
+  // ---- enqueue, layer by layer.
+  bool aux_touched = false;
+  for (size_t li = 0; li < n_layers; ++li) {
+    const pf_layer_xfer &L = layers[li];
+    bool layer_aux = false, layer_stream = false;
+    if (L.n_blocks) {
+      const uint32_t *ids_dev = reinterpret_cast<const uint32_t *>(meta_dev_ + base + ids_off[li]);
+      for (uint32_t r = 0; r < L.n_ranges; ++r) {
+        RangePlan &P = plans[li * 2 + r];
+        const uint64_t dev_base = L.data_ptr + (uint64_t)r * L.kv_stride_bytes;
+        size_t zc_cursor = 0;
+        for (size_t j = 0; j < L.n_runs[r]; ++j) {
+          const pf_host_run &run = L.runs[r][j];
+          if (run.n_blocks == 0) continue;
+          const bool is_zc = zc_cursor < P.zc_runs.size() && P.zc_runs[zc_cursor] == j;
+          if (is_zc) {
+            ++zc_cursor;
+            if (P.zc_runs.size() > 1) continue;  // handled below in one table-driven launch
+            const Side dev{dev_base, L.block_stride_bytes, ids_dev + run.first_block, nullptr};
+            const Side host{run.host_device, run.stride_bytes, nullptr, nullptr};
+            if (host_is_src)
+              launch_link(host, dev, run.n_blocks, L.range_bytes, stream, false);
+            else
+              launch_link(dev, host, run.n_blocks, L.range_bytes, stream, false);
+            stats_.bytes_zero_copy += run.n_blocks * L.range_bytes;
+            layer_stream = true;
+          } else {
+            const Side dev{dev_base, L.block_stride_bytes, ids_dev + run.first_block, nullptr};
+            staged_run(dev, run, run.first_block, L.range_bytes, host_is_src, stream, &layer_aux);
+          }
+        }
+        if (P.zc_runs.size() > 1) {
+          const Side dev{dev_base, L.block_stride_bytes,
+                         reinterpret_cast<const uint32_t *>(meta_dev_ + base + P.zc_ids_off), nullptr};
+          const Side host{0, 0, nullptr, reinterpret_cast<const uint64_t *>(meta_dev_ + base + P.table_off)};
+          if (host_is_src)
+            launch_link(host, dev, P.zc_blocks, L.range_bytes, stream, false);
+          else
+            launch_link(dev, host, P.zc_blocks, L.range_bytes, stream, false);
+          stats_.bytes_zero_copy += P.zc_blocks * L.range_bytes;
+          layer_stream = true;
+        }
+      }
+    }
+    aux_touched |= layer_aux;
+    cudaEvent_t done = layer_done ? (cudaEvent_t)layer_done[li] : nullptr;
+    if (done) {
+      // A saved layer is complete when its last DMA (copy stream) and its zero-copy kernels
+      // (caller's stream) are; a loaded layer always ends with a scatter on the caller's stream.
+      if (!host_is_src && layer_aux && !layer_stream) {
+        PF_CUDA(cudaEventRecord(done, aux_));
+      } else {
+        if (!host_is_src && layer_aux) {
+          PF_CUDA(cudaEventRecord(join_, aux_));
+          PF_CUDA(cudaStreamWaitEvent(stream, join_, 0));
+        }
+        PF_CUDA(cudaEventRecord(done, stream));
+      }
+    }
+  }
+  if (aux_touched && !host_is_src) {
+    PF_CUDA(cudaEventRecord(join_, aux_));
+    PF_CUDA(cudaStreamWaitEvent(stream, join_, 0));
+  }
+  // The meta region is free once everything enqueued above has run.
+  cudaEvent_t ev = take_event();
+  PF_CUDA(cudaEventRecord(ev, stream));
+  meta_inflight_.push_back({base, base + align_up(std::max<size_t>(meta_bytes, 16), 256), ev});
+}
+
+void TransferBackend::copy_descs(const pf_copy_desc *copies, size_t n, bool host_is_src, cudaStream_t stream) {
+  if (n == 0) return;
+  DeviceGuard on_device(device_);
+  if (n > 0xFFFFFFFFull) throw Error::invalid("too many copy descriptors in one batch");
+  // Split the batch: maximal runs of equally sized descriptors whose host side is contiguous
+  // go through the staging ring (the device side may be scattered); the rest become
+  // [dst, src, size] triples for the zero-copy kernel.
+  struct Run {
+    size_t first, count;
+  };
+  std::vector<Run> staged;
+  std::vector<char> is_staged(n, 0);
+  if (cfg_.route != PF_ROUTE_ZEROCOPY) {
+    size_t i = 0;
+    while (i < n) {
+      size_t j = i + 1;
+      const size_t sz = copies[i].size;
+      while (j < n && copies[j].size == sz &&
+             (char *)copies[j].host == (char *)copies[j - 1].host + sz &&
+             copies[j].host_device == copies[j - 1].host_device + sz &&
+             copies[j].host_allocation == copies[i].host_allocation)
+        ++j;
+      const size_t bytes = (j - i) * sz;
+      const bool want = cfg_.route == PF_ROUTE_STAGED || bytes >= cfg_.min_dma_bytes;
+      if (want && sz > 0 && sz <= cfg_.staging_slot_bytes && sz <= 0xFFFFFFFFull) {
+        staged.push_back({i, j - i});
+        for (size_t k = i; k < j; ++k) is_staged[k] = 1;
+      }
+      i = j;
+    }
+  }
+  size_t n_staged = 0;
+  for (auto &r : staged) n_staged += r.count;
+  const size_t n_direct = n - n_staged;
+  const size_t table_bytes = align_up(n_staged * sizeof(uint64_t), 256);
+  const size_t triple_bytes = align_up(n_direct * 3 * sizeof(uint64_t), 256);
+  const size_t meta_bytes = table_bytes + triple_bytes;
+  const size_t base = meta_alloc(meta_bytes);
+  uint64_t *table = reinterpret_cast<uint64_t *>(meta_host_ + base);
+  uint64_t *triples = reinterpret_cast<uint64_t *>(meta_host_ + base + table_bytes);
+  bool aligned = true;
+  size_t t = 0, q = 0;
+  for (size_t i = 0; i < n; ++i) {
+    const pf_copy_desc &c = copies[i];
+    if (is_staged[i]) {
+      table[t++] = c.device;
+    } else {
+      if (c.size && (!c.device || !c.host_device)) throw Error::invalid(strf("copy descriptor %zu has a null address", i));
+      triples[3 * q + 0] = host_is_src ? c.device : c.host_device;
+      triples[3 * q + 1] = host_is_src ? c.host_device : c.device;
+      triples[3 * q + 2] = c.size;
+      if ((c.device | c.host_device | c.size) & 15ull) aligned = false;
+      stats_.bytes_zero_copy += c.size;
+      ++q;
+    }
+  }
+  meta_upload(base, meta_bytes, stream);
+  bool aux_touched = false;
+  size_t table_cursor = 0;
+  for (auto &r : staged) {
+    const pf_copy_desc &c0 = copies[r.first];
+    const Side dev{0, 0, nullptr, reinterpret_cast<const uint64_t *>(meta_dev_ + base) + table_cursor};
+    const pf_host_run run{0, r.count, c0.host, c0.host_device, c0.size};
+    staged_run(dev, run, 0, c0.size, host_is_src, stream, &aux_touched);
+    table_cursor += r.count;
+  }
+  launch_descs(reinterpret_cast<const uint64_t *>(meta_dev_ + base + table_bytes), n_direct, aligned, stream);
+  if (aux_touched && !host_is_src) {
+    PF_CUDA(cudaEventRecord(join_, aux_));
+    PF_CUDA(cudaStreamWaitEvent(stream, join_, 0));
+  }
+  cudaEvent_t ev = take_event();
+  PF_CUDA(cudaEventRecord(ev, stream));
+  meta_inflight_.push_back({base, base + align_up(std::max<size_t>(meta_bytes, 16), 256), ev});
+}
+
+void TransferBackend::peer_copy(const pf_device_layout &src, const uint32_t *src_ids, const pf_device_layout &dst,
+                                const uint32_t *dst_ids, size_t n_blocks, cudaStream_t stream) {
+  if (n_blocks == 0) return;
+  DeviceGuard on_device(device_);
+  if (src.n_ranges != dst.n_ranges || src.range_bytes != dst.range_bytes)
+    throw Error::invalid("peer copy needs the same block geometry on both sides");
+  if (src.n_ranges < 1 || src.n_ranges > 2 || src.range_bytes == 0 || src.range_bytes > 0xFFFFFFFFull)
+    throw Error::invalid("peer copy: unsupported block geometry");
+  if (n_blocks > 0xFFFFFFFFull) throw Error::invalid("peer copy: too many blocks");
+  const size_t ids_bytes = align_up(n_blocks * sizeof(uint32_t), 256);
+  const size_t base = meta_alloc(2 * ids_bytes);
+  std::memcpy(meta_host_ + base, src_ids, n_blocks * sizeof(uint32_t));
+  std::memcpy(meta_host_ + base + ids_bytes, dst_ids, n_blocks * sizeof(uint32_t));
+  meta_upload(base, 2 * ids_bytes, stream);
+  tables_aligned_ = true;
+  for (uint32_t r = 0; r < src.n_ranges; ++r) {
+    const Side s{src.data_ptr + (uint64_t)r * src.kv_stride_bytes, src.block_stride_bytes,
+                 reinterpret_cast<const uint32_t *>(meta_dev_ + base), nullptr};
+    const Side d{dst.data_ptr + (uint64_t)r * dst.kv_stride_bytes, dst.block_stride_bytes,
+                 reinterpret_cast<const uint32_t *>(meta_dev_ + base + ids_bytes), nullptr};
+    launch_link(s, d, n_blocks, src.range_bytes, stream, true);
+    stats_.bytes_peer += n_blocks * src.range_bytes;
+  }
+  cudaEvent_t ev = take_event();
+  PF_CUDA(cudaEventRecord(ev, stream));
+  meta_inflight_.push_back({base, base + 2 * ids_bytes, ev});
+}
+
+void enable_peer_access(int device, int peer) {
+  DeviceGuard on_device(device);
+  int can = 0;
+  PF_CUDA(cudaDeviceCanAccessPeer(&can, device, peer));
+  if (!can) throw Error::cuda_init(strf("device %d cannot access device %d", device, peer));
+  cudaError_t e = cudaDeviceEnablePeerAccess(peer, 0);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) {
+    cudaGetLastError();
+    return;
+  }
+  if (e != cudaSuccess) throw Error::cuda_init(strf("cudaDeviceEnablePeerAccess(%d->%d): %s", device, peer, cudaGetErrorString(e)));
+}
+
+}  // namespace pf

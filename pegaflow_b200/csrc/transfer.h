@@ -1,0 +1,138 @@
+// The transfer backend: every byte the engine moves between HBM and the pinned host pool (or
+// a peer GPU) goes through this class.  It replaces the reference's two backends
+// (pegaflow-core/src/transfer/memcpy.rs, kernel.rs) with one path that has two routes:
+//
+//   staged    scattered KV blocks are gathered by a kernel into a contiguous HBM staging ring
+//             at HBM speed, and the copy engine moves each slot to/from the pool in one large
+//             DMA (256-byte PCIe payloads).  Gather of slot i+1 overlaps the DMA of slot i.
+//   zero-copy a TMA ring kernel (a handful of CTAs, one issuing thread each) moves blocks
+//             directly between HBM and mapped pinned memory; used where the host side is
+//             irregular or the batch is too small to amortise the staging hand-off.
+//
+// All calls only enqueue work (transfer/mod.rs:51-52 contract): nothing here synchronises the
+// caller's stream.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+#include <deque>
+#include <vector>
+
+#include "common.h"
+
+namespace pf {
+
+// One side of a batch of equally sized items: item i lives at table[i], or at
+// base + (ids ? ids[i] : i) * stride.  `ids` / `table` are device pointers.
+struct Side {
+  uint64_t base;
+  uint64_t stride;
+  const uint32_t *ids;
+  const uint64_t *table;
+};
+
+class TransferBackend {
+ public:
+  TransferBackend(int device, const pf_backend_config *config);
+  ~TransferBackend();
+  TransferBackend(const TransferBackend &) = delete;
+  TransferBackend &operator=(const TransferBackend &) = delete;
+
+  int device() const { return device_; }
+  const char *name() const { return "b200"; }
+
+  void copy_descs(const pf_copy_desc *copies, size_t n, bool host_is_src, cudaStream_t stream);
+  void move_layers(const pf_layer_xfer *layers, size_t n_layers, bool host_is_src, cudaStream_t stream,
+                   void *const *layer_done);
+  void peer_copy(const pf_device_layout &src, const uint32_t *src_ids, const pf_device_layout &dst,
+                 const uint32_t *dst_ids, size_t n_blocks, cudaStream_t stream);
+  void stats(pf_backend_stats *out);
+
+ private:
+  struct Slot {
+    char *ptr = nullptr;
+    cudaEvent_t filled = nullptr;   // staging slot holds data (gather done / DMA-in done)
+    cudaEvent_t drained = nullptr;  // staging slot may be overwritten (DMA-out done / scatter done)
+    bool used = false;
+  };
+  struct MetaRegion {
+    size_t begin, end;
+    cudaEvent_t done;
+  };
+  struct TimedLaunch {
+    cudaEvent_t start, stop;
+    uint64_t bytes;
+    bool link;
+  };
+
+  // Meta ring: pinned host bytes + device mirror for block ids, address tables and descriptors.
+  size_t meta_alloc(size_t bytes);
+  void meta_upload(size_t off, size_t bytes, cudaStream_t stream);
+  void meta_grow(size_t need);
+  cudaEvent_t take_event();
+
+  Slot &next_slot();
+  void ensure_staging();
+
+  // Kernel launchers (transfer.cu).
+  void launch_pack(const Side &src, const Side &dst, size_t n_items, size_t item_bytes, cudaStream_t s);
+  void launch_link(const Side &src, const Side &dst, size_t n_items, size_t item_bytes, cudaStream_t s,
+                   bool peer);
+  void launch_descs(const uint64_t *triples_dev, size_t n, bool aligned, cudaStream_t s);
+
+  // One run of one range of one layer through the staged route.
+  void staged_run(const Side &dev_side, const pf_host_run &run, size_t ids_offset, size_t item_bytes,
+                  bool host_is_src, cudaStream_t stream, bool *aux_touched);
+
+  int device_;
+  pf_backend_config cfg_;
+  int sm_count_ = 0;
+  cudaStream_t aux_ = nullptr;  // copy-engine stream of the staged route
+  cudaEvent_t join_ = nullptr;
+  std::vector<Slot> slots_;
+  char *staging_ = nullptr;
+  size_t slot_cursor_ = 0;
+
+  char *meta_host_ = nullptr;
+  char *meta_dev_ = nullptr;
+  size_t meta_cap_ = 0, meta_head_ = 0;
+  std::deque<MetaRegion> meta_inflight_;
+  std::vector<cudaEvent_t> event_pool_;
+
+  unsigned int *status_host_ = nullptr;  // mapped pinned word kernels write when a wait expires
+  unsigned int *status_dev_ = nullptr;
+  // Kernel timing (cfg_.time_kernels): event pairs of launches not yet folded into stats_.
+  void time_begin(cudaStream_t s, cudaEvent_t *start);
+  void time_end(cudaStream_t s, cudaEvent_t start, uint64_t bytes, bool link);
+  void fold_timings(bool wait);
+  std::deque<TimedLaunch> timed_;
+  std::vector<cudaEvent_t> timing_event_pool_;
+
+  bool tables_aligned_ = true;           // set while an address table is filled
+  pf_backend_stats stats_{};
+};
+
+void enable_peer_access(int device, int peer);
+
+// Makes `device` current for the calling thread and restores the previous one on scope exit,
+// so a call through the C ABI never changes the caller's current device.
+class DeviceGuard {
+ public:
+  explicit DeviceGuard(int device) {
+    if (cudaGetDevice(&prev_) != cudaSuccess) prev_ = -1;
+    if (prev_ != device) cudaSetDevice(device);
+    else prev_ = -1;
+  }
+  ~DeviceGuard() {
+    if (prev_ >= 0) cudaSetDevice(prev_);
+  }
+  DeviceGuard(const DeviceGuard &) = delete;
+  DeviceGuard &operator=(const DeviceGuard &) = delete;
+
+ private:
+  int prev_ = -1;
+};
+
+}  // namespace pf

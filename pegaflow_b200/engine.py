@@ -1,0 +1,336 @@
+"""Python view of the engine boundary of ``libpegaflow_b200.so``.
+
+``PegaEngine`` carries the reference's method names and argument order
+(pegaflow-core/src/lib.rs:138-709, offload.rs:293-300) so that code written against the
+reference's engine reads the same.  Every call goes through the C ABI; nothing here moves
+bytes on the CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Sequence, Tuple
+
+from . import _native as N
+from ._native import PegaFlowError, PegaflowInternal, PegaflowInvalidArgument  # noqa: F401  (re-exported)
+
+TRANSFER_MODES = {"direct": 0, "kernel": 1}  # transfer/mod.rs:66-76; both run on the one B200 backend
+
+LOAD_STATE_PENDING, LOAD_STATE_SUCCESS, LOAD_STATE_ERROR = 0, 1, -1
+
+
+def _hash_arrays(hashes: Sequence[bytes]):
+    n = len(hashes)
+    bufs = [(C.c_uint8 * max(1, len(h))).from_buffer_copy(bytes(h) or b"\0") for h in hashes]
+    ptrs = (C.POINTER(C.c_uint8) * max(1, n))(*[C.cast(b, C.POINTER(C.c_uint8)) for b in bufs])
+    lens = (C.c_size_t * max(1, n))(*[len(h) for h in hashes])
+    return bufs, ptrs, lens
+
+
+class Block:
+    """Owned handle on a sealed block (``Arc<SealedBlock>`` in the reference)."""
+
+    def __init__(self, handle):
+        self._h = handle
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            N.lib.pf_block_release(self._h)
+            self._h = None
+
+    @property
+    def num_slots(self) -> int:
+        return N.lib.pf_block_num_slots(self._h)
+
+    def slot_image(self, slot: int) -> List[bytes]:
+        """Host bytes of one slot, one ``bytes`` per segment."""
+        nseg = C.c_size_t()
+        sizes = (C.c_size_t * 2)()
+        N.check(N.lib.pf_block_slot_info(self._h, slot, C.byref(nseg), sizes))
+        out = []
+        for s in range(nseg.value):
+            buf = C.create_string_buffer(sizes[s])
+            N.check(N.lib.pf_block_slot_read(self._h, slot, s, buf, sizes[s]))
+            out.append(buf.raw)
+        return out
+
+
+class Completion:
+    """Completion of an in-process load (the oneshot receiver of lib.rs:691-709)."""
+
+    def __init__(self, handle):
+        self._h = handle
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            N.lib.pf_completion_free(self._h)
+            self._h = None
+
+    def poll(self) -> int:
+        st = C.c_int()
+        N.check(N.lib.pf_completion_poll(self._h, C.byref(st)))
+        return st.value
+
+    def wait(self, timeout: float = 120.0) -> int:
+        st = C.c_int()
+        N.check(N.lib.pf_completion_wait(self._h, timeout, C.byref(st)))
+        return st.value
+
+    def error(self) -> str:
+        return N.lib.pf_completion_error(self._h).decode(errors="replace")
+
+
+class PyLoadState:
+    """Shared-memory load state (python/src/lib.rs:628-663 `PyLoadState`)."""
+
+    def __init__(self, attach_to: Optional[str] = None):
+        h = C.c_void_p()
+        if attach_to is None:
+            N.check(N.lib.pf_load_state_new(C.byref(h)))
+        else:
+            N.check(N.lib.pf_load_state_attach(attach_to.encode(), C.byref(h)))
+        self._h = h
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            N.lib.pf_load_state_free(self._h)
+            self._h = None
+
+    def shm_name(self) -> str:
+        return N.lib.pf_load_state_shm_name(self._h).decode()
+
+    def get_state(self) -> int:
+        return N.lib.pf_load_state_get(self._h)
+
+    def is_ready(self) -> bool:
+        return self.get_state() != LOAD_STATE_PENDING
+
+    def set_completed(self):
+        N.lib.pf_load_state_set_completed(self._h)
+
+    def set_error(self):
+        N.lib.pf_load_state_set_error(self._h)
+
+
+class PegaEngine:
+    def __init__(self, pool_bytes: int, use_hugepages: bool = False, *, enable_numa_affinity: bool = True,
+                 blockwise_alloc: bool = False, hint_value_size: int = 0, pool_shards: int = 1,
+                 host_alignment: int = 0, use_mmap_pool: bool = False, route: int = N.ROUTE_AUTO,
+                 staging_slot_bytes: int = 0, staging_slots: int = 0, min_dma_bytes: int = 0, link_ctas: int = 0,
+                 pack_ctas: int = 0, time_kernels: bool = False):
+        cfg = N.StorageConfig()
+        cfg.enable_numa_affinity = int(enable_numa_affinity)
+        cfg.blockwise_alloc = int(blockwise_alloc)
+        cfg.hint_value_size = hint_value_size
+        cfg.pool_shards = pool_shards
+        cfg.host_alignment = host_alignment
+        cfg.use_mmap_pool = int(use_mmap_pool)
+        cfg.backend.route = route
+        cfg.backend.staging_slot_bytes = staging_slot_bytes
+        cfg.backend.staging_slots = staging_slots
+        cfg.backend.min_dma_bytes = min_dma_bytes
+        cfg.backend.link_ctas = link_ctas
+        cfg.backend.pack_ctas = pack_ctas
+        cfg.backend.time_kernels = int(time_kernels)
+        h = C.c_void_p()
+        N.check(N.lib.pf_engine_new(pool_bytes, int(use_hugepages), C.byref(cfg), C.byref(h)))
+        self._h = h
+
+    def close(self):
+        if getattr(self, "_h", None):
+            N.lib.pf_engine_free(self._h)
+            self._h = None
+
+    __del__ = close
+
+    # lib.rs:302-322
+    def register_context_layer_batch_strided(self, instance_id, namespace, device_id, tp_rank, pp_rank, tp_size,
+                                             world_size, layer_names, data_ptrs, size_bytes, num_blocks,
+                                             bytes_per_block, kv_stride_bytes, segments, block_stride_bytes=None,
+                                             layer_group_ids=None, transfer_mode="direct", page_first=False):
+        n = len(layer_names)
+        lists = dict(data_ptrs=data_ptrs, size_bytes=size_bytes, num_blocks=num_blocks, bytes_per_block=bytes_per_block,
+                     kv_stride_bytes=kv_stride_bytes, segments=segments)
+        if any(len(v) != n for v in lists.values()):
+            # lib.rs:327-344: the C ABI takes one length, so the mismatch is caught here
+            raise PegaflowInvalidArgument(3, "invalid argument: registration metadata length mismatch: layer_names="
+                                          f"{n}, " + ", ".join(f"{k}={len(v)}" for k, v in lists.items()))
+        for key, v in (("block_stride_bytes", block_stride_bytes), ("layer_group_ids", layer_group_ids)):
+            if v is not None and len(v) != n:
+                raise PegaflowInvalidArgument(3, "invalid argument: registration metadata length mismatch: "
+                                              f"layer_names={n}, {key}={len(v)}")
+        SZ = C.c_size_t * max(1, n)
+        names = (C.c_char_p * max(1, n))(*[s.encode() for s in layer_names])
+        mode = TRANSFER_MODES[transfer_mode] if isinstance(transfer_mode, str) else int(transfer_mode)
+        N.check(N.lib.pf_engine_register_context_layer_batch_strided(
+            self._h, instance_id.encode(), namespace.encode(), device_id, tp_rank, pp_rank, tp_size, world_size, n,
+            names, (C.c_uint64 * max(1, n))(*data_ptrs), SZ(*size_bytes), SZ(*num_blocks), SZ(*bytes_per_block),
+            SZ(*kv_stride_bytes), SZ(*segments), SZ(*block_stride_bytes) if block_stride_bytes is not None else None,
+            (C.c_uint32 * max(1, n))(*layer_group_ids) if layer_group_ids is not None else None, mode,
+            int(bool(page_first))))
+
+    def unregister_instance(self, instance_id):
+        N.check(N.lib.pf_engine_unregister_instance(self._h, instance_id.encode()))
+
+    def _layer_saves(self, saves):
+        n = len(saves)
+        arr = (N.LayerSave * max(1, n))()
+        keep = []
+        marshalled = {}   # layers usually share one hash list: marshal it once
+        for i, (name, ids, hashes) in enumerate(saves):
+            if len(ids) != len(hashes):
+                raise PegaflowInvalidArgument(3, f"invalid argument: block_ids length {len(ids)} does not match "
+                                              f"block_hashes {len(hashes)} for layer {name}")
+            if id(hashes) not in marshalled:
+                marshalled[id(hashes)] = _hash_arrays(hashes)
+            bufs, ptrs, lens = marshalled[id(hashes)]
+            ids_arr = (C.c_size_t * max(1, len(ids)))(*[int(x) for x in ids])
+            keep.append((bufs, ptrs, lens, ids_arr))
+            arr[i].layer_name = name.encode()
+            arr[i].n_blocks = len(ids)
+            arr[i].block_ids = ids_arr
+            arr[i].block_hashes = ptrs
+            arr[i].block_hash_lens = lens
+        return arr, n, keep
+
+    # offload.rs:293-300
+    def prepare_saves(self, saves):
+        """Marshal `saves` once; the result can be passed to batch_save / save_layers_async
+        repeatedly (what a native caller of the C ABI would hold anyway)."""
+        return self._layer_saves(saves)
+
+    def batch_save(self, instance_id, tp_rank, pp_rank, device_id, saves):
+        """saves: [(layer_name, block_ids, block_hashes)] or the result of prepare_saves()."""
+        arr, n, _keep = saves if isinstance(saves, tuple) else self._layer_saves(saves)
+        N.check(N.lib.pf_engine_batch_save(self._h, instance_id.encode(), tp_rank, pp_rank, device_id, n, arr))
+
+    def save_layers_async(self, instance_id, tp_rank, pp_rank, device_id, saves, ready_event: int = 0):
+        """Non-blocking save that starts once ``ready_event`` (a cudaEvent_t value or 0) fired."""
+        arr, n, _keep = saves if isinstance(saves, tuple) else self._layer_saves(saves)
+        N.check(N.lib.pf_engine_save_layers_async(self._h, instance_id.encode(), tp_rank, pp_rank, device_id, n, arr,
+                                                  C.c_void_p(ready_event or None)))
+
+    def flush_saves(self):
+        N.check(N.lib.pf_engine_flush_saves(self._h))
+
+    # lib.rs:506-533
+    @staticmethod
+    def prepare_hashes(hashes: Sequence[bytes]):
+        return ("hashes", len(hashes)) + _hash_arrays(hashes)
+
+    def query_prefix(self, instance_id, hashes, req_id: str = ""):
+        if isinstance(hashes, tuple) and hashes and hashes[0] == "hashes":
+            _tag, n, _bufs, ptrs, lens = hashes
+        else:
+            n = len(hashes)
+            _bufs, ptrs, lens = _hash_arrays(hashes)
+        out = (C.c_void_p * max(1, n))()
+        hit, missing = C.c_size_t(), C.c_size_t()
+        N.check(N.lib.pf_engine_query_prefix(self._h, instance_id.encode(), req_id.encode(), n, ptrs, lens, out,
+                                             C.byref(hit), C.byref(missing)))
+        return [Block(C.c_void_p(out[i])) for i in range(hit.value)], missing.value
+
+    def query_group_membership(self, instance_id, group_id, hashes: Sequence[bytes]):
+        n = len(hashes)
+        _bufs, ptrs, lens = _hash_arrays(hashes)
+        out = (C.c_void_p * max(1, n))()
+        N.check(N.lib.pf_engine_query_group_membership(self._h, instance_id.encode(), group_id, n, ptrs, lens, out))
+        return [Block(C.c_void_p(out[i])) if out[i] else None for i in range(n)]
+
+    def create_query_lease(self, instance_id, blocks: Sequence[Block]) -> bytes:
+        n = len(blocks)
+        arr = (C.c_void_p * max(1, n))(*[b._h for b in blocks])
+        lease = (C.c_uint8 * 16)()
+        N.check(N.lib.pf_engine_create_query_lease(self._h, instance_id.encode(), n, arr, lease))
+        return bytes(lease)
+
+    def release_query_lease(self, lease: bytes) -> bool:
+        released = C.c_int()
+        N.check(N.lib.pf_engine_release_query_lease(self._h, (C.c_uint8 * 16)(*lease), C.byref(released)))
+        return bool(released.value)
+
+    def _load_args(self, layer_groups, loads):
+        flat = [nm.encode() for g in layer_groups for nm in g]
+        groups = N.LayerGroups()
+        groups.n_groups = len(layer_groups)
+        sizes = (C.c_size_t * max(1, len(layer_groups)))(*[len(g) for g in layer_groups])
+        names = (C.c_char_p * max(1, len(flat)))(*flat)
+        groups.group_sizes = sizes
+        groups.layer_names = names
+        arr = (N.LeaseLoad * max(1, len(loads)))()
+        keep = [sizes, names]
+        for i, (lease, ids_by_group) in enumerate(loads):
+            if len(ids_by_group) != len(layer_groups):
+                raise PegaflowInvalidArgument(3, f"invalid argument: load group count {len(ids_by_group)} does not "
+                                              f"match layer group count {len(layer_groups)}")
+            n_blocks = len(ids_by_group[0]) if ids_by_group else 0
+            for gi, g in enumerate(ids_by_group):
+                if len(g) != n_blocks:
+                    raise PegaflowInvalidArgument(3, "invalid argument: query lease destination lists differ in length "
+                                                  f"({n_blocks} vs {len(g)} for group {gi})")
+            rows = [(C.c_size_t * max(1, n_blocks))(*[N.PF_NO_BLOCK if v is None else int(v) for v in g])
+                    for g in ids_by_group]
+            ptrs = (C.POINTER(C.c_size_t) * max(1, len(rows)))(*[C.cast(r, C.POINTER(C.c_size_t)) for r in rows])
+            keep.extend([rows, ptrs])
+            arr[i].lease = (C.c_uint8 * 16)(*lease)
+            arr[i].n_blocks = n_blocks
+            arr[i].dst_ids = ptrs
+        return groups, arr, len(loads), keep
+
+    # lib.rs:691-709
+    def prepare_loads(self, layer_groups, loads):
+        return ("loads",) + self._load_args(layer_groups, loads)
+
+    def batch_load_async(self, instance_id, tp_rank, device_id, layer_groups, loads=None) -> Completion:
+        """`layer_groups` may be the result of prepare_loads(), in which case `loads` is unused."""
+        if isinstance(layer_groups, tuple) and layer_groups and layer_groups[0] == "loads":
+            _tag, groups, arr, n, _keep = layer_groups
+        else:
+            groups, arr, n, _keep = self._load_args(layer_groups, loads)
+        out = C.c_void_p()
+        N.check(N.lib.pf_engine_batch_load_inproc(self._h, instance_id.encode(), tp_rank, device_id, C.byref(groups),
+                                                  n, arr, C.byref(out)))
+        return Completion(out)
+
+    def batch_load(self, instance_id, tp_rank, device_id, layer_groups, loads=None, timeout: float = 120.0):
+        """Blocking convenience over batch_load_async: raises if the load fails."""
+        done = self.batch_load_async(instance_id, tp_rank, device_id, layer_groups, loads)
+        state = done.wait(timeout)
+        if state == 0:
+            raise PegaflowInternal(5, "storage error: load timed out")
+        if state < 0:
+            raise PegaflowInternal(5, done.error())
+
+    # lib.rs:654-680
+    def batch_load_shm(self, instance_id, tp_rank, device_id, load_state_shm: str, layer_groups, loads):
+        groups, arr, n, _keep = self._load_args(layer_groups, loads)
+        N.check(N.lib.pf_engine_batch_load_shm(self._h, instance_id.encode(), tp_rank, device_id,
+                                               load_state_shm.encode(), C.byref(groups), n, arr))
+
+    def layer_load_event(self, instance_id, device_id, layer_name) -> int:
+        out = C.c_void_p()
+        N.check(N.lib.pf_engine_layer_load_event(self._h, instance_id.encode(), device_id, layer_name.encode(),
+                                                 C.byref(out)))
+        return out.value or 0
+
+    @staticmethod
+    def stream_wait_event(stream: int, event: int):
+        """Order `stream` (a cudaStream_t value, 0 = default stream) after `event`."""
+        N.check(N.lib.pf_stream_wait_event(C.c_void_p(stream or None), C.c_void_p(event)))
+
+    def peer_load(self, src_instance, src_device, dst_instance, dst_device, src_block_ids, dst_block_ids):
+        n = len(src_block_ids)
+        SZ = C.c_size_t * max(1, n)
+        N.check(N.lib.pf_engine_peer_load(self._h, src_instance.encode(), src_device, dst_instance.encode(), dst_device,
+                                          n, SZ(*src_block_ids), SZ(*dst_block_ids)))
+
+    def metrics(self) -> dict:
+        m = N.EngineMetrics()
+        N.check(N.lib.pf_engine_get_metrics(self._h, C.byref(m)))
+        out = {f: getattr(m, f) for f, _ in N.EngineMetrics._fields_ if f != "transfer"}
+        out["transfer"] = {f: getattr(m.transfer, f) for f, _ in N.BackendStats._fields_}
+        return out
+
+    def block_slot_image(self, instance_id, raw_hash: bytes, slot: int, group: int = 0):
+        """Host image of one stored slot, or None when the block is not resident."""
+        (b,) = self.query_group_membership(instance_id, group, [raw_hash])
+        return None if b is None else b.slot_image(slot)

@@ -1,0 +1,360 @@
+"""Engine-level parity: the same call sequence is replayed on the CUDA engine (through the C ABI)
+and on the CPU oracle model; GPU bytes after the load, every stored block's host image and the
+error behaviour must agree.  Scenarios follow the reference's integration tests
+(pegaflow-core/tests/engine_basic.rs, prefix_semantics.rs, save_validation.rs)."""
+import numpy as np
+import pytest
+
+from oracle.engine_model import EngineError, OracleEngine
+from tests import scenarios as sc
+from tests.gpu_util import CudaMem, make_event
+
+pytestmark = pytest.mark.gpu
+
+ROUTES = {"auto": 0, "staged": 1, "zerocopy": 2}
+
+
+@pytest.fixture(scope="module")
+def pf():
+    import torch
+
+    if not torch.cuda.is_available():
+        pytest.fail("these tests need a CUDA device (there is no CPU fallback to test)")
+    import pegaflow_b200
+
+    return pegaflow_b200
+
+
+def _pair(pf, pool=64 << 20, **kw):
+    okw = {}
+    if "host_alignment" in kw:
+        okw["ssd_alignment"] = kw["host_alignment"]
+    if "blockwise_alloc" in kw:
+        okw["blockwise_alloc"] = kw["blockwise_alloc"]
+    return pf.PegaEngine(pool, **kw), CudaMem(0), OracleEngine(pool, **okw), sc.NumpyMem()
+
+
+def _compare_images(eng, ora, instance, hashes, n_slots, group=0):
+    for h in hashes:
+        for slot in range(n_slots):
+            a = eng.block_slot_image(instance, h, slot, group)
+            b = ora.block_slot_image(instance, h, slot, group)
+            assert (a is None) == (b is None)
+            if a is not None:
+                assert [bytes(x) for x in a] == [bytes(x) for x in b], f"host image of slot {slot} differs"
+
+
+def _both_roundtrip(pf, layers_spec, save_ids, load_ids, hashes, fills, *, route="auto", n_slots=None, **kw):
+    reg = {k: kw.pop(k) for k in list(kw) if k in ("page_first", "use_groups", "use_strides", "one_batch")}
+    eng, gmem, ora, nmem = _pair(pf, route=ROUTES[route], min_dma_bytes=64 << 10, **kw)
+    try:
+        gl = [sc.Layer(**s) for s in layers_spec]
+        nl = [sc.Layer(**s) for s in layers_spec]
+        got = sc.roundtrip(eng, gmem, "inst", "ns", gl, save_ids, load_ids, hashes, fills=fills, **reg)
+        want = sc.roundtrip(ora, nmem, "inst", "ns", nl, save_ids, load_ids, hashes, fills=fills, **reg)
+        for L, fill in zip(nl, fills):
+            assert np.array_equal(got[L.name], want[L.name]), f"GPU bytes of {L.name} differ from the oracle"
+            if not reg.get("page_first"):
+                assert np.array_equal(want[L.name], sc.expected_after_roundtrip(L, fill, list(save_ids), list(load_ids)))
+        slots = n_slots if n_slots is not None else (1 if reg.get("page_first") else len(gl))
+        _compare_images(eng, ora, "inst", hashes, slots)
+        m = eng.metrics()
+        assert m["load_failures"] == 0 and m["save_batches"] >= 1 and m["load_tasks"] == 1
+        return m
+    finally:
+        eng.close()
+
+
+def test_save_query_load_roundtrip(pf):
+    """engine_basic.rs:12-25."""
+    fill = sc.fill_pattern(4, 1024)
+    _both_roundtrip(pf, [dict(name="layer_0", num_blocks=4, segment_bytes=1024)], range(4), range(4),
+                    sc.make_block_hashes(4, 0), [fill])
+
+
+@pytest.mark.parametrize("route", list(ROUTES))
+def test_page_first_multi_layer_roundtrip(pf, route):
+    """engine_basic.rs:32-58: uneven page offsets 0 / 512 / 1536."""
+    spec = [dict(name="layer_a", num_blocks=4, segment_bytes=512), dict(name="layer_b", num_blocks=4, segment_bytes=1024),
+            dict(name="layer_c", num_blocks=4, segment_bytes=1536)]
+    fills = [sc.fill_pattern(4, 512), sc.fill_pattern(4, 1024, 0x40), sc.fill_pattern(4, 1536, 0x80)]
+    _both_roundtrip(pf, spec, range(4), [3, 1, 0, 2], sc.make_block_hashes(4, 0xAB), fills, route=route,
+                    page_first=True)
+
+
+@pytest.mark.parametrize("seg,kv_stride,nblocks", [(512, 4096, 4), (4096, 16384, 2)])
+def test_split_storage_roundtrip(pf, seg, kv_stride, nblocks):
+    """engine_basic.rs:217-252 (both the direct- and the kernel-mode shapes)."""
+    L = sc.Layer("layer_0", nblocks, seg, segments=2, kv_stride=kv_stride)
+    fill = sc.seeded_bytes(L.region_bytes, 7)
+    ids = list(range(nblocks))
+    _both_roundtrip(pf, [dict(name="layer_0", num_blocks=nblocks, segment_bytes=seg, segments=2, kv_stride=kv_stride)],
+                    ids, ids[::-1], sc.make_block_hashes(nblocks, 1), [fill])
+
+
+@pytest.mark.parametrize("route", list(ROUTES))
+def test_qwen3_kv_layout_roundtrip(pf, route):
+    """Qwen3-0.6B shape at reduced layer count: 8 KV heads x 128 x bf16 x 16 tokens = 32 KiB K and V
+    regions per layer, 256 GPU blocks, save 64 random ids, load into another random 64."""
+    rng = np.random.default_rng(43)
+    n_layers, num_blocks, seg = 6, 256, 32768
+    spec = [dict(name=f"model.layers.{i}.self_attn.attn", num_blocks=num_blocks, segment_bytes=seg, segments=2,
+                 kv_stride=num_blocks * seg) for i in range(n_layers)]
+    fills = [rng.standard_normal(2 * num_blocks * seg // 2).astype(np.float16).view(np.uint8) for _ in range(n_layers)]
+    save_ids = (rng.permutation(num_blocks - 1)[:64] + 1).tolist()
+    load_ids = (rng.permutation(num_blocks - 1)[:64] + 1).tolist()
+    m = _both_roundtrip(pf, spec, save_ids, load_ids, sc.make_block_hashes(64, 9), fills, route=route,
+                        pool=256 << 20)
+    assert m["save_bytes"] == n_layers * 64 * 2 * seg and m["load_bytes"] == m["save_bytes"]
+
+
+@pytest.mark.parametrize("dtype_bytes", [2, 1])
+def test_mla_latent_page_first_roundtrip(pf, dtype_bytes):
+    """DeepSeek-style latent cache [num_blocks, 64, 576] (bf16 and fp8 byte widths), page-first pages."""
+    rng = np.random.default_rng(44 + dtype_bytes)
+    n_layers, num_blocks, seg = 5, 40, 64 * 576 * dtype_bytes
+    spec = [dict(name=f"model.layers.{i}.mla", num_blocks=num_blocks, segment_bytes=seg) for i in range(n_layers)]
+    fills = [sc.seeded_bytes(num_blocks * seg, 100 + i) for i in range(n_layers)]
+    save_ids = (rng.permutation(num_blocks)[:16]).tolist()
+    load_ids = (rng.permutation(num_blocks)[:16]).tolist()
+    _both_roundtrip(pf, spec, save_ids, load_ids, sc.make_block_hashes(16, 3), fills, page_first=True,
+                    pool=128 << 20)
+
+
+def test_padded_host_strides_and_blockwise_alloc(pf):
+    """Host strides padded to 512 bytes (lib.rs:379-388) and one pool allocation per block
+    (offload.rs:454-456): the images keep their padding tails untouched."""
+    spec = [dict(name="l0", num_blocks=12, segment_bytes=8848), dict(name="l1", num_blocks=12, segment_bytes=1000,
+                                                                      segments=2, kv_stride=12 * 1000 + 24)]
+    fills = [sc.seeded_bytes(sc.Layer(**s).region_bytes, 3 + i) for i, s in enumerate(spec)]
+    ids = [5, 0, 11, 7]
+    _both_roundtrip(pf, spec, ids, [1, 2, 3, 4], sc.make_block_hashes(4, 5), fills, host_alignment=512)
+    _both_roundtrip(pf, spec, ids, [1, 2, 3, 4], sc.make_block_hashes(4, 5), fills, blockwise_alloc=True)
+
+
+def test_fused_buffer_block_stride(pf):
+    """One layer's view into a buffer that holds all layers of a block (layout.rs:140-153)."""
+    spec = [dict(name="fused", num_blocks=8, segment_bytes=8192, block_stride=16384)]
+    fill = sc.seeded_bytes(sc.Layer(**spec[0]).region_bytes, 21)
+    _both_roundtrip(pf, spec, [7, 2, 5], [0, 1, 6], sc.make_block_hashes(3, 8), [fill], use_strides=True)
+
+
+def test_hybrid_groups_load_to_distinct_block_ids(pf, kats):
+    """engine_basic.rs:62-124 with its spelled-out expected images."""
+    eng, mem, _, _ = _pair(pf)
+    try:
+        layers = [sc.Layer("full_attention", 4, 1024), sc.Layer("gdn", 4, 1024)]
+        sc.register(eng, mem, "hyb", "ns", layers, use_groups=True)
+        mem.write(layers[0].buf, sc.fill_pattern(4, 1024))
+        mem.write(layers[1].buf, sc.fill_pattern(4, 1024, 0x40))
+        hashes = sc.make_block_hashes(2, 0xAC)
+        eng.batch_save("hyb", 0, 0, 0, [("full_attention", [0, 1], hashes), ("gdn", [2, 3], hashes)])
+        eng.flush_saves()
+        for L in layers:
+            mem.zero(L.buf)
+        blocks, missing = eng.query_prefix("hyb", hashes)
+        assert missing == 0
+        lease = eng.create_query_lease("hyb", blocks)
+        eng.batch_load("hyb", 0, 0, [["full_attention"], [], ["gdn"]], [(lease, [[2, 3], [None, None], [None, 0]])])
+        full = np.zeros(4096, dtype=np.uint8)
+        full[2048:3072] = 1
+        full[3072:4096] = 2
+        gdn = np.zeros(4096, dtype=np.uint8)
+        gdn[0:1024] = kats["engine_roundtrips"]["hybrid_expected"]["gdn"]["0"]
+        assert np.array_equal(mem.read(layers[0].buf), full)
+        assert np.array_equal(mem.read(layers[1].buf), gdn)
+    finally:
+        eng.close()
+
+
+def test_prefix_dedup_and_partial_layer_semantics(pf):
+    """engine_basic.rs:165-208 + prefix_semantics.rs."""
+    eng, mem, _, _ = _pair(pf)
+    try:
+        layers = [sc.Layer("layer_0", 4, 1024), sc.Layer("layer_1", 4, 1024)]
+        sc.register(eng, mem, "ml", "ns", layers)
+        hashes = sc.make_block_hashes(4, 55)
+        eng.batch_save("ml", 0, 0, 0, [("layer_0", [0, 1, 2, 3], hashes)])
+        eng.flush_saves()
+        assert len(eng.query_prefix("ml", hashes)[0]) == 0, "partial save must not expose as hit"
+        eng.batch_save("ml", 0, 0, 0, [("layer_1", [0, 1, 2, 3], hashes)])
+        eng.flush_saves()
+        assert len(eng.query_prefix("ml", hashes)[0]) == 4
+        used_before = eng.metrics()["pool_used_bytes"]
+        eng.batch_save("ml", 0, 0, 0, [("layer_0", [0, 1, 2, 3], hashes), ("layer_1", [0, 1, 2, 3], hashes)])
+        eng.flush_saves()
+        assert eng.metrics()["pool_used_bytes"] == used_before, "a save of resident blocks must not allocate"
+        # gap breaks the prefix
+        sc.register(eng, mem, "gap", "ns2", [sc.Layer("layer_0", 3, 1024)])
+        allh = sc.make_block_hashes(4, 20)
+        eng.batch_save("gap", 0, 0, 0, [("layer_0", [0, 1, 2], [allh[0], allh[2], allh[3]])])
+        eng.flush_saves()
+        blocks, missing = eng.query_prefix("gap", allh)
+        assert (len(blocks), missing) == (1, 3)
+        # namespace isolation (engine_basic.rs:255-272)
+        assert eng.query_prefix("gap", hashes) == ([], 4)
+    finally:
+        eng.close()
+
+
+def test_error_behaviour_matches_the_oracle(pf):
+    """The same invalid calls fail with the same variant and text on both engines."""
+    eng, gmem, ora, nmem = _pair(pf)
+    try:
+        def both(fn, match):
+            with pytest.raises(pf.PegaFlowError) as e1:
+                fn(eng, gmem)
+            with pytest.raises(EngineError) as e2:
+                fn(ora, nmem)
+            assert e1.value.kind == e2.value.kind
+            assert match in str(e1.value) and match in str(e2.value)
+
+        both(lambda e, m: e.batch_save("nope", 0, 0, 0, []), "instance nope not found")
+        both(lambda e, m: sc.register(e, m, "bad", "ns", [sc.Layer("l", 4, 1024, segments=2, kv_stride=512)]),
+             "overlap")
+        both(lambda e, m: sc.register(e, m, "bad2", "ns", [sc.Layer("l", 10, 1024, region_bytes=5120)]), "too small")
+        for e, m in ((eng, gmem), (ora, nmem)):
+            sc.register(e, m, "v", "ns", [sc.Layer("layer_0", 4, 1024), sc.Layer("layer_1", 4, 1024)])
+        both(lambda e, m: sc.register(e, m, "v", "ns", [sc.Layer("layer_0", 4, 1024)]), "already exists")
+        both(lambda e, m: sc.register(e, m, "v", "ns", [sc.Layer("layer_0", 4, 1024)], device_id=1),
+             "already fully registered")
+        both(lambda e, m: sc.register(e, m, "v", "ns", [sc.Layer("layer_0", 4, 1024)], tp_size=2), "topology mismatch")
+        both(lambda e, m: e.batch_save("v", 0, 0, 0, [("layer_0", [4], [b"h"])]), "block_id 4 out of range")
+        both(lambda e, m: e.batch_save("v", 0, 0, 0, [("layer_0", [1, 2], [b"h"])]), "does not match block_hashes")
+        both(lambda e, m: e.batch_save("v", 0, 0, 9, [("layer_0", [1], [b"h"])]), "device 9 not found")
+        both(lambda e, m: e.batch_save("v", 1, 0, 0, [("layer_0", [1], [b"h"])]), "but save requested")
+        both(lambda e, m: e.batch_save("v", 0, 0, 0, [("layer_x", [1], [b"h"])]), "layer layer_x is not registered")
+        both(lambda e, m: e.create_query_lease("v", []), "requires at least one block")
+        both(lambda e, m: e.batch_load("v", 0, 0, [], []), "at least one layer group")
+        both(lambda e, m: e.batch_load("v", 0, 0, [["layer_0"], ["layer_0"]], []), "unique across groups")
+        both(lambda e, m: e.batch_load("v", 0, 0, [["layer_0"]], [(b"\0" * 16, [[0]])]), "unknown or expired")
+        # page-first partial save (engine_basic.rs:131-158)
+        for e, m in ((eng, gmem), (ora, nmem)):
+            sc.register(e, m, "pf", "ns3", [sc.Layer(n, 4, 512) for n in ("layer_a", "layer_b", "layer_c")],
+                        page_first=True)
+        both(lambda e, m: e.batch_save("pf", 0, 0, 0, [("layer_a", [0, 1, 2, 3], sc.make_block_hashes(4, 0xCD))]),
+             "must cover all")
+        # lease accounting: world_size consumers, then gone (lease.rs:98-133)
+        h = sc.make_block_hashes(2, 77)
+        for e in (eng, ora):
+            e.batch_save("v", 0, 0, 0, [("layer_0", [0, 1], h), ("layer_1", [0, 1], h)])
+            e.flush_saves()
+            blocks, missing = e.query_prefix("v", h)
+            assert missing == 0
+            lease = e.create_query_lease("v", blocks)
+            e.batch_load("v", 0, 0, [["layer_0", "layer_1"]], [(lease, [[2, 3]])])
+            assert e.release_query_lease(lease) is False
+            lease2 = e.create_query_lease("v", blocks)
+            assert e.release_query_lease(lease2) is True
+        both(lambda e, m: e.unregister_instance("ghost"), "instance ghost not found")
+    finally:
+        eng.close()
+
+
+def test_pool_exhaustion_evicts_lru_then_fails(pf):
+    """storage/mod.rs:294-330: a full pool evicts least recently used blocks; a request larger
+    than the pool fails with the reference's message and counts an allocation failure."""
+    eng = pf.PegaEngine(1 << 20)
+    mem = CudaMem(0)
+    try:
+        L = sc.Layer("layer_0", 64, 65536)
+        sc.register(eng, mem, "ev", "ns", [L])
+        mem.write(L.buf, sc.seeded_bytes(L.region_bytes, 1))
+        first = sc.make_block_hashes(8, 1)
+        eng.batch_save("ev", 0, 0, 0, [("layer_0", list(range(8)), first)])     # 512 KiB
+        eng.flush_saves()
+        second = sc.make_block_hashes(12, 2)
+        eng.batch_save("ev", 0, 0, 0, [("layer_0", list(range(8, 20)), second)])  # 768 KiB: must evict
+        eng.flush_saves()
+        m = eng.metrics()
+        assert m["evicted_blocks"] >= 8 and len(eng.query_prefix("ev", second)[0]) == 12
+        assert len(eng.query_prefix("ev", first)[0]) == 0
+        with pytest.raises(pf.PegaflowInternal, match="pinned pool exhausted while allocating block buffer"):
+            eng.batch_save("ev", 0, 0, 0, [("layer_0", list(range(20, 40)), sc.make_block_hashes(20, 3))])
+        assert eng.metrics()["pool_alloc_failures"] == 1
+    finally:
+        eng.close()
+
+
+def test_load_state_shm_completion_and_failure(pf):
+    """lib.rs:654-680 + sync_state.rs: a cross-process style load completes through the
+    shared-memory word; a pre-submit error flips it to ERROR."""
+    import time
+
+    eng = pf.PegaEngine(16 << 20)
+    mem = CudaMem(0)
+    try:
+        L = sc.Layer("layer_0", 8, 4096)
+        sc.register(eng, mem, "shm", "ns", [L])
+        fill = sc.seeded_bytes(L.region_bytes, 9)
+        mem.write(L.buf, fill)
+        h = sc.make_block_hashes(8, 4)
+        eng.batch_save("shm", 0, 0, 0, [("layer_0", list(range(8)), h)])
+        eng.flush_saves()
+        mem.zero(L.buf)
+        blocks, _ = eng.query_prefix("shm", h)
+        state = pf.PyLoadState()
+        assert state.get_state() == 0 and state.shm_name().startswith("pega_load_")
+        eng.batch_load_shm("shm", 0, 0, state.shm_name(), [["layer_0"]],
+                           [(eng.create_query_lease("shm", blocks), [list(range(8))])])
+        deadline = time.time() + 5
+        while not state.is_ready() and time.time() < deadline:
+            time.sleep(0.001)
+        assert state.get_state() == 1
+        assert np.array_equal(mem.read(L.buf), fill)
+        bad = pf.PyLoadState()
+        with pytest.raises(pf.PegaFlowError):
+            eng.batch_load_shm("shm", 0, 0, bad.shm_name(), [["layer_0"]], [(b"\1" * 16, [[0]])])
+        assert bad.get_state() == -1
+        with pytest.raises(pf.PegaflowInternal, match="LoadState"):
+            eng.batch_load_shm("shm", 0, 0, "pega_load_does_not_exist", [["layer_0"]], [])
+    finally:
+        eng.close()
+
+
+def test_layerwise_async_save_and_per_layer_load_events(pf):
+    """Layer-wise pipeline: layers saved one by one as a compute stream produces them, and a
+    consumer stream that waits on each layer's load event before touching the layer."""
+    import torch
+
+    eng = pf.PegaEngine(64 << 20, min_dma_bytes=64 << 10)
+    mem = CudaMem(0)
+    try:
+        n_layers, num_blocks, seg = 4, 32, 16384
+        layers = [sc.Layer(f"l{i}", num_blocks, seg, segments=2, kv_stride=num_blocks * seg) for i in range(n_layers)]
+        sc.register(eng, mem, "lw", "ns", layers)
+        compute = torch.cuda.Stream()
+        ids = list(range(1, 17))
+        h = sc.make_block_hashes(16, 6)
+        fills, ready_events = [], []
+        for i, L in enumerate(layers):
+            fill = torch.from_numpy(sc.seeded_bytes(L.region_bytes, 50 + i)).pin_memory()
+            fills.append(fill)
+            with torch.cuda.stream(compute):
+                L.buf.copy_(fill, non_blocking=True)      # stands in for the layer's attention writing its KV
+                ready = make_event(torch)
+                ready.record(compute)
+            ready_events.append(ready)                    # must outlive the save that waits on it
+            eng.save_layers_async("lw", 0, 0, 0, [(L.name, ids, h)], ready.cuda_event)
+        eng.flush_saves()
+        blocks, missing = eng.query_prefix("lw", h)
+        assert missing == 0
+        compute.synchronize()
+        for L in layers:
+            mem.zero(L.buf)
+        dst = list(range(16, 32))
+        done = eng.batch_load_async("lw", 0, 0, [[L.name for L in layers]],
+                                    [(eng.create_query_lease("lw", blocks), [dst])])
+        outs = []
+        for L in layers:
+            ev = eng.layer_load_event("lw", 0, L.name)
+            eng.stream_wait_event(compute.cuda_stream, ev)
+            with torch.cuda.stream(compute):
+                outs.append(L.buf.clone())               # the layer's consumer
+        compute.synchronize()
+        assert done.wait(10) == 1
+        for L, fill, out in zip(layers, fills, outs):
+            want = sc.expected_after_roundtrip(L, fill.numpy(), ids, dst)
+            assert np.array_equal(out.cpu().numpy(), want), "consumer ran before the layer's bytes had landed"
+    finally:
+        eng.close()

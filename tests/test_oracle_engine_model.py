@@ -30,7 +30,7 @@ def test_page_first_multi_layer_roundtrip_uneven_offsets():
     for L, f in zip(layers, fills):
         assert np.array_equal(out[L.name], f)
     # the stored page of block 2 is layer_a | layer_b | layer_c at offsets 0, 512, 1536
-    img = eng.block_slot_image("test-ns", hashes[2], 0)
+    img = eng.block_slot_image("test-page-first", hashes[2], 0)
     assert len(img) == 1 and len(img[0]) == 3072
     assert img[0][:512] == bytes([3]) * 512 and img[0][512:1536] == bytes([3 + 0x40]) * 1024
     assert img[0][1536:] == bytes([3 + 0x80]) * 1536
