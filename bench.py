@@ -389,13 +389,17 @@ def run_b200(args, rank, world, local):
     spec = workloads()[args.workload]
     wl = Workload(spec, device, 42 + 2 + rank)
     L, seg, per, n_req = spec["layers"], spec["seg_bytes"], spec["blocks"], spec["requests"]
+    if args.contiguous_ids:
+        wl.save_ids = [np.arange(1 + r * per, 1 + (r + 1) * per, dtype=np.uint32) for r in range(n_req)]
+        wl.load_ids = list(wl.save_ids)
     route = {"auto": 0, "staged": 1, "zerocopy": 2}[args.route]
 
     # ---------------- transfer-only arm: backend + pool, KV resident in HBM -------------------
     pool = pf.PinnedPool(wl.payload + (64 << 20), numa_node=-1)
     allocs = [[(pool.alloc(per * seg), pool.alloc(per * seg)) for _ in range(L)] for _ in range(n_req)]
-    be = pf.TransferBackend(local, route=route, time_kernels=True, link_ctas=args.link_ctas,
-                            staging_slot_bytes=args.slot_mib << 20, staging_slots=args.slots)
+    be = pf.TransferBackend(local, route=route, time_kernels=not args.no_kernel_timing, link_ctas=args.link_ctas,
+                            staging_slot_bytes=args.slot_mib << 20, staging_slots=args.slots,
+                            copy_streams=args.copy_streams, pack_ctas=args.pack_ctas)
     save_x = make_layer_xfers(pf, wl, allocs, wl.save_ids)
     load_x = make_layer_xfers(pf, wl, allocs, wl.load_ids)
     stream = torch.cuda.Stream()
@@ -536,7 +540,8 @@ def run_e2e(args, pf, wl, rank, world, local, route):
     steps_total = args.steps + max(1, args.warmup)
     # room for two steps' blocks: older steps are evicted (LRU) while a new one is being saved
     eng = pf.PegaEngine(2 * wl.payload + (256 << 20), route=route, link_ctas=args.link_ctas,
-                        staging_slot_bytes=args.slot_mib << 20, staging_slots=args.slots)
+                        staging_slot_bytes=args.slot_mib << 20, staging_slots=args.slots,
+                        copy_streams=args.copy_streams)
     names = [f"model.layers.{l}.self_attn.attn" for l in range(L)]
     region = 2 * spec["gpu_blocks"] * seg
     eng.register_context_layer_batch_strided(
@@ -596,6 +601,10 @@ def main():
     ap.add_argument("--link-ctas", type=int, default=0)
     ap.add_argument("--slot-mib", type=int, default=0)
     ap.add_argument("--slots", type=int, default=0)
+    ap.add_argument("--copy-streams", type=int, default=0)
+    ap.add_argument("--pack-ctas", type=int, default=0)
+    ap.add_argument("--no-kernel-timing", action="store_true", help="diagnostic: no event pairs around kernels")
+    ap.add_argument("--contiguous-ids", action="store_true", help="diagnostic: block ids in ascending order")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--allow-short-warmup", action="store_true", help="profiling runs only")

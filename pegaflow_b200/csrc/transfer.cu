@@ -15,6 +15,7 @@
 #include "transfer.h"
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 
 namespace pf {
@@ -91,9 +92,26 @@ struct DescGen {
   }
 };
 
+// L2 policies for the staged route: the KV side is streamed (evict first), the staging side is
+// kept (evict last) so that the copy engine finds a gathered slot in L2 and a scattered slot is
+// read back from L2, not HBM.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+
 // CTA-wide copy of one span.  16-byte vectors when source and destination share their
-// misalignment (head bytes are peeled), plain bytes otherwise.
-__device__ __forceinline__ void copy_span(uint64_t dst, uint64_t src, uint32_t len) {
+// misalignment (head bytes are peeled), plain bytes otherwise.  kHints: 0 none, 1 source is
+// streamed / destination kept in L2 (gather into staging), 2 the reverse (scatter from staging).
+template <int kHints>
+__device__ __forceinline__ void copy_span(uint64_t dst, uint64_t src, uint32_t len, uint64_t pol_src,
+                                          uint64_t pol_dst) {
   const uint32_t tid = threadIdx.x, nthr = blockDim.x;
   if (((dst ^ src) & 15ull) != 0) {
     char *d = reinterpret_cast<char *>(dst);
@@ -114,15 +132,27 @@ __device__ __forceinline__ void copy_span(uint64_t dst, uint64_t src, uint32_t l
     for (int u = 0; u < kLdstUnroll; ++u) {
       uint32_t jj = j + u * nthr;
       if (jj < n16) {
-        asm volatile("ld.global.nc.L1::no_allocate.v4.s32 {%0,%1,%2,%3}, [%4];"
-                     : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
-                     : "l"(s16 + jj));
+        if (kHints)
+          asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.s32 {%0,%1,%2,%3}, [%4], %5;"
+                       : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
+                       : "l"(s16 + jj), "l"(pol_src));
+        else
+          asm volatile("ld.global.nc.L1::no_allocate.v4.s32 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
+                       : "l"(s16 + jj));
       }
     }
 #pragma unroll
     for (int u = 0; u < kLdstUnroll; ++u) {
       uint32_t jj = j + u * nthr;
-      if (jj < n16) d16[jj] = v[u];
+      if (jj < n16) {
+        if (kHints)
+          asm volatile("st.global.L2::cache_hint.v4.s32 [%0], {%1,%2,%3,%4}, %5;" ::"l"(d16 + jj), "r"(v[u].x),
+                       "r"(v[u].y), "r"(v[u].z), "r"(v[u].w), "l"(pol_dst)
+                       : "memory");
+        else
+          d16[jj] = v[u];
+      }
     }
   }
   const uint32_t tail_at = head + (n16 << 4);
@@ -130,12 +160,20 @@ __device__ __forceinline__ void copy_span(uint64_t dst, uint64_t src, uint32_t l
     reinterpret_cast<char *>(dst)[j] = reinterpret_cast<const char *>(src)[j];
 }
 
+template <int kHints>
 __global__ void __launch_bounds__(kLdstThreads)
 copy_items_ldst(Side src, Side dst, uint32_t n_items, uint32_t item_bytes, uint32_t chunk_bytes) {
   ItemGen gen(src, dst, n_items, item_bytes, chunk_bytes);
-  uint64_t s, d;
+  uint64_t s, d, pol_src = 0, pol_dst = 0;
+  if (kHints == 1) {
+    pol_src = l2_policy_evict_first();
+    pol_dst = l2_policy_evict_last();
+  } else if (kHints == 2) {
+    pol_src = l2_policy_evict_first();  // a staging slot is dead once it has been scattered
+    pol_dst = l2_policy_evict_first();
+  }
   uint32_t len;
-  while (gen.next(s, d, len)) copy_span(d, s, len);
+  while (gen.next(s, d, len)) copy_span<kHints>(d, s, len, pol_src, pol_dst);
 }
 
 __global__ void __launch_bounds__(kLdstThreads)
@@ -143,7 +181,7 @@ copy_descs_ldst(const uint64_t *__restrict__ triples, uint32_t n, uint32_t chunk
   DescGen gen(triples, n, chunk_bytes);
   uint64_t s, d;
   uint32_t len;
-  while (gen.next(s, d, len)) copy_span(d, s, len);
+  while (gen.next(s, d, len)) copy_span<0>(d, s, len, 0, 0);
 }
 
 // ---- bulk async copy (TMA) primitives ------------------------------------------------------
@@ -270,8 +308,10 @@ static_assert(kStages >= 2, "ring needs two stages");
 
 TransferBackend::TransferBackend(int device, const pf_backend_config *config) : device_(device) {
   cfg_ = config ? *config : pf_backend_config{};
-  if (cfg_.staging_slot_bytes == 0) cfg_.staging_slot_bytes = 16u << 20;
+  if (cfg_.staging_slot_bytes == 0) cfg_.staging_slot_bytes = 32u << 20;
   if (cfg_.staging_slots <= 0) cfg_.staging_slots = 4;
+  if (cfg_.copy_streams <= 0) cfg_.copy_streams = 2;
+  if (cfg_.copy_streams > 8) cfg_.copy_streams = 8;
   if (cfg_.min_dma_bytes == 0) cfg_.min_dma_bytes = 256u << 10;
   int count = 0;
   cudaError_t e = cudaGetDeviceCount(&count);
@@ -286,9 +326,16 @@ TransferBackend::TransferBackend(int device, const pf_backend_config *config) : 
                                 prop.minor));
   sm_count_ = prop.multiProcessorCount;
   if (cfg_.pack_ctas <= 0) cfg_.pack_ctas = sm_count_ * 8;
-  if (cudaStreamCreateWithFlags(&aux_, cudaStreamNonBlocking) != cudaSuccess)
-    throw Error::cuda_init("failed to create the copy stream");
-  PF_CUDA(cudaEventCreateWithFlags(&join_, cudaEventDisableTiming));
+  if (const char *e = getenv("PF_EXP_PACK_HINTS")) pack_hints_ = atoi(e) != 0;
+  aux_.resize(cfg_.copy_streams, nullptr);
+  aux_join_.resize(cfg_.copy_streams, nullptr);
+  aux_layer_dirty_.assign(cfg_.copy_streams, 0);
+  aux_task_dirty_.assign(cfg_.copy_streams, 0);
+  for (int i = 0; i < cfg_.copy_streams; ++i) {
+    if (cudaStreamCreateWithFlags(&aux_[i], cudaStreamNonBlocking) != cudaSuccess)
+      throw Error::cuda_init("failed to create a copy stream");
+    PF_CUDA(cudaEventCreateWithFlags(&aux_join_[i], cudaEventDisableTiming));
+  }
   PF_CUDA(cudaHostAlloc(&status_host_, sizeof(unsigned int), cudaHostAllocMapped));
   *status_host_ = 0;
   PF_CUDA(cudaHostGetDevicePointer(&status_dev_, status_host_, 0));
@@ -299,7 +346,8 @@ TransferBackend::TransferBackend(int device, const pf_backend_config *config) : 
 
 TransferBackend::~TransferBackend() {
   DeviceGuard on_device(device_);
-  if (aux_) cudaStreamSynchronize(aux_);
+  for (auto st : aux_)
+    if (st) cudaStreamSynchronize(st);
   for (auto &r : meta_inflight_) cudaEventSynchronize(r.done);
   for (auto &s : slots_) {
     if (s.filled) cudaEventDestroy(s.filled);
@@ -316,8 +364,10 @@ TransferBackend::~TransferBackend() {
   if (meta_dev_) cudaFree(meta_dev_);
   if (meta_host_) cudaFreeHost(meta_host_);
   if (status_host_) cudaFreeHost(status_host_);
-  if (join_) cudaEventDestroy(join_);
-  if (aux_) cudaStreamDestroy(aux_);
+  for (auto ev : aux_join_)
+    if (ev) cudaEventDestroy(ev);
+  for (auto st : aux_)
+    if (st) cudaStreamDestroy(st);
 }
 
 void TransferBackend::time_begin(cudaStream_t s, cudaEvent_t *start) {
@@ -464,13 +514,18 @@ TransferBackend::Slot &TransferBackend::next_slot() {
 }
 
 void TransferBackend::launch_pack(const Side &src, const Side &dst, size_t n_items, size_t item_bytes,
-                                  cudaStream_t s) {
+                                  cudaStream_t s, bool into_staging) {
   if (n_items == 0) return;
   const uint64_t chunks = (uint64_t)n_items * ((item_bytes + kPackChunk - 1) / kPackChunk);
   const int grid = (int)std::min<uint64_t>(chunks, (uint64_t)cfg_.pack_ctas);
   cudaEvent_t t0;
   time_begin(s, &t0);
-  copy_items_ldst<<<grid, kLdstThreads, 0, s>>>(src, dst, (uint32_t)n_items, (uint32_t)item_bytes, kPackChunk);
+  if (!pack_hints_)
+    copy_items_ldst<0><<<grid, kLdstThreads, 0, s>>>(src, dst, (uint32_t)n_items, (uint32_t)item_bytes, kPackChunk);
+  else if (into_staging)
+    copy_items_ldst<1><<<grid, kLdstThreads, 0, s>>>(src, dst, (uint32_t)n_items, (uint32_t)item_bytes, kPackChunk);
+  else
+    copy_items_ldst<2><<<grid, kLdstThreads, 0, s>>>(src, dst, (uint32_t)n_items, (uint32_t)item_bytes, kPackChunk);
   PF_CUDA(cudaGetLastError());
   time_end(s, t0, 2ull * n_items * item_bytes, false);
   ++stats_.kernel_launches;
@@ -495,7 +550,7 @@ void TransferBackend::launch_link(const Side &src, const Side &dst, size_t n_ite
   } else {
     const uint64_t chunks = (uint64_t)n_items * ((item_bytes + kPackChunk - 1) / kPackChunk);
     const int grid = (int)std::min<uint64_t>(chunks, (uint64_t)std::max(ctas, sm_count_));
-    copy_items_ldst<<<grid, kLdstThreads, 0, s>>>(src, dst, (uint32_t)n_items, (uint32_t)item_bytes, kPackChunk);
+    copy_items_ldst<0><<<grid, kLdstThreads, 0, s>>>(src, dst, (uint32_t)n_items, (uint32_t)item_bytes, kPackChunk);
   }
   PF_CUDA(cudaGetLastError());
   time_end(s, t0, (uint64_t)n_items * item_bytes, true);
@@ -516,16 +571,39 @@ void TransferBackend::launch_descs(const uint64_t *triples_dev, size_t n, bool a
   ++stats_.kernel_launches;
 }
 
+// Copy streams take the DMAs of consecutive staging slots in turn, so that the fixed cost at
+// the start and end of one DMA overlaps the body of the next.
+int TransferBackend::next_aux() {
+  const int i = (int)(aux_cursor_++ % aux_.size());
+  aux_layer_dirty_[i] = 1;
+  aux_task_dirty_[i] = 1;
+  aux_last_ = i;
+  return i;
+}
+
+// Makes `target` wait for everything enqueued so far on the copy streams flagged in `dirty`
+// (except `skip`, for the case where target is that copy stream itself).
+void TransferBackend::join_copy_streams(cudaStream_t target, std::vector<char> &dirty, int skip) {
+  for (size_t i = 0; i < aux_.size(); ++i) {
+    if (!dirty[i] || (int)i == skip) continue;
+    PF_CUDA(cudaEventRecord(aux_join_[i], aux_[i]));
+    PF_CUDA(cudaStreamWaitEvent(target, aux_join_[i], 0));
+  }
+}
+
 // Moves run.n_blocks items (`item_bytes` each) between the device side and a host run through
 // the staging ring.  `dev_side.ids` / `.table` already point at the run's first item.
-void TransferBackend::staged_run(const Side &dev_side, const pf_host_run &run, size_t /*ids_offset*/,
-                                 size_t item_bytes, bool host_is_src, cudaStream_t stream, bool *aux_touched) {
+void TransferBackend::staged_run(const Side &dev_side, const pf_host_run &run, size_t item_bytes, bool host_is_src,
+                                 cudaStream_t stream) {
   ensure_staging();
   const size_t cap = cfg_.staging_slot_bytes / item_bytes;
+  // Equal chunks: a run that needs k slots is cut into k pieces of (almost) the same size.
+  const size_t n_chunks = (run.n_blocks + cap - 1) / cap;
+  const size_t per_chunk = (run.n_blocks + n_chunks - 1) / n_chunks;
   char *host = static_cast<char *>(run.host);
   const bool dense = run.stride_bytes == item_bytes;
-  for (size_t b0 = 0; b0 < run.n_blocks; b0 += cap) {
-    const size_t nb = std::min(cap, run.n_blocks - b0);
+  for (size_t b0 = 0; b0 < run.n_blocks; b0 += per_chunk) {
+    const size_t nb = std::min(per_chunk, run.n_blocks - b0);
     Side d = dev_side;
     if (d.table) d.table += b0;
     if (d.ids) d.ids += b0;
@@ -533,33 +611,33 @@ void TransferBackend::staged_run(const Side &dev_side, const pf_host_run &run, s
     Slot &slot = next_slot();
     const Side st{(uint64_t)(uintptr_t)slot.ptr, item_bytes, nullptr, nullptr};
     char *h = host + b0 * run.stride_bytes;
+    cudaStream_t copy = aux_[next_aux()];
     if (!host_is_src) {
       if (slot.used) PF_CUDA(cudaStreamWaitEvent(stream, slot.drained, 0));
-      launch_pack(d, st, nb, item_bytes, stream);
+      launch_pack(d, st, nb, item_bytes, stream, true);
       PF_CUDA(cudaEventRecord(slot.filled, stream));
-      PF_CUDA(cudaStreamWaitEvent(aux_, slot.filled, 0));
+      PF_CUDA(cudaStreamWaitEvent(copy, slot.filled, 0));
       if (dense)
-        PF_CUDA(cudaMemcpyAsync(h, slot.ptr, nb * item_bytes, cudaMemcpyDeviceToHost, aux_));
+        PF_CUDA(cudaMemcpyAsync(h, slot.ptr, nb * item_bytes, cudaMemcpyDeviceToHost, copy));
       else
         PF_CUDA(cudaMemcpy2DAsync(h, run.stride_bytes, slot.ptr, item_bytes, item_bytes, nb, cudaMemcpyDeviceToHost,
-                                  aux_));
-      PF_CUDA(cudaEventRecord(slot.drained, aux_));
+                                  copy));
+      PF_CUDA(cudaEventRecord(slot.drained, copy));
     } else {
-      if (slot.used) PF_CUDA(cudaStreamWaitEvent(aux_, slot.drained, 0));
+      if (slot.used) PF_CUDA(cudaStreamWaitEvent(copy, slot.drained, 0));
       if (dense)
-        PF_CUDA(cudaMemcpyAsync(slot.ptr, h, nb * item_bytes, cudaMemcpyHostToDevice, aux_));
+        PF_CUDA(cudaMemcpyAsync(slot.ptr, h, nb * item_bytes, cudaMemcpyHostToDevice, copy));
       else
         PF_CUDA(cudaMemcpy2DAsync(slot.ptr, item_bytes, h, run.stride_bytes, item_bytes, nb, cudaMemcpyHostToDevice,
-                                  aux_));
-      PF_CUDA(cudaEventRecord(slot.filled, aux_));
+                                  copy));
+      PF_CUDA(cudaEventRecord(slot.filled, copy));
       PF_CUDA(cudaStreamWaitEvent(stream, slot.filled, 0));
-      launch_pack(st, d, nb, item_bytes, stream);
+      launch_pack(st, d, nb, item_bytes, stream, false);
       PF_CUDA(cudaEventRecord(slot.drained, stream));
     }
     slot.used = true;
     ++stats_.dma_copies;
     stats_.bytes_staged += nb * item_bytes;
-    *aux_touched = true;
   }
 }
 
@@ -647,10 +725,11 @@ void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, 
   meta_upload(base, meta_bytes, stream);
 
   // ---- enqueue, layer by layer.
-  bool aux_touched = false;
+  std::fill(aux_task_dirty_.begin(), aux_task_dirty_.end(), 0);
   for (size_t li = 0; li < n_layers; ++li) {
     const pf_layer_xfer &L = layers[li];
-    bool layer_aux = false, layer_stream = false;
+    bool layer_stream = false;
+    std::fill(aux_layer_dirty_.begin(), aux_layer_dirty_.end(), 0);
     if (L.n_blocks) {
       const uint32_t *ids_dev = reinterpret_cast<const uint32_t *>(meta_dev_ + base + ids_off[li]);
       for (uint32_t r = 0; r < L.n_ranges; ++r) {
@@ -674,7 +753,7 @@ void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, 
             layer_stream = true;
           } else {
             const Side dev{dev_base, L.block_stride_bytes, ids_dev + run.first_block, nullptr};
-            staged_run(dev, run, run.first_block, L.range_bytes, host_is_src, stream, &layer_aux);
+            staged_run(dev, run, L.range_bytes, host_is_src, stream);
           }
         }
         if (P.zc_runs.size() > 1) {
@@ -690,26 +769,22 @@ void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, 
         }
       }
     }
-    aux_touched |= layer_aux;
     cudaEvent_t done = layer_done ? (cudaEvent_t)layer_done[li] : nullptr;
     if (done) {
-      // A saved layer is complete when its last DMA (copy stream) and its zero-copy kernels
+      // A saved layer is complete when its DMAs (copy streams) and its zero-copy kernels
       // (caller's stream) are; a loaded layer always ends with a scatter on the caller's stream.
+      const bool layer_aux = std::find(aux_layer_dirty_.begin(), aux_layer_dirty_.end(), 1) != aux_layer_dirty_.end();
       if (!host_is_src && layer_aux && !layer_stream) {
-        PF_CUDA(cudaEventRecord(done, aux_));
+        // Signal from the copy stream that took the layer's last DMA, after the others.
+        join_copy_streams(aux_[aux_last_], aux_layer_dirty_, aux_last_);
+        PF_CUDA(cudaEventRecord(done, aux_[aux_last_]));
       } else {
-        if (!host_is_src && layer_aux) {
-          PF_CUDA(cudaEventRecord(join_, aux_));
-          PF_CUDA(cudaStreamWaitEvent(stream, join_, 0));
-        }
+        if (!host_is_src && layer_aux) join_copy_streams(stream, aux_layer_dirty_, -1);
         PF_CUDA(cudaEventRecord(done, stream));
       }
     }
   }
-  if (aux_touched && !host_is_src) {
-    PF_CUDA(cudaEventRecord(join_, aux_));
-    PF_CUDA(cudaStreamWaitEvent(stream, join_, 0));
-  }
+  if (!host_is_src) join_copy_streams(stream, aux_task_dirty_, -1);
   // The meta region is free once everything enqueued above has run.
   cudaEvent_t ev = take_event();
   PF_CUDA(cudaEventRecord(ev, stream));
@@ -773,20 +848,17 @@ void TransferBackend::copy_descs(const pf_copy_desc *copies, size_t n, bool host
     }
   }
   meta_upload(base, meta_bytes, stream);
-  bool aux_touched = false;
+  std::fill(aux_task_dirty_.begin(), aux_task_dirty_.end(), 0);
   size_t table_cursor = 0;
   for (auto &r : staged) {
     const pf_copy_desc &c0 = copies[r.first];
     const Side dev{0, 0, nullptr, reinterpret_cast<const uint64_t *>(meta_dev_ + base) + table_cursor};
     const pf_host_run run{0, r.count, c0.host, c0.host_device, c0.size};
-    staged_run(dev, run, 0, c0.size, host_is_src, stream, &aux_touched);
+    staged_run(dev, run, c0.size, host_is_src, stream);
     table_cursor += r.count;
   }
   launch_descs(reinterpret_cast<const uint64_t *>(meta_dev_ + base + table_bytes), n_direct, aligned, stream);
-  if (aux_touched && !host_is_src) {
-    PF_CUDA(cudaEventRecord(join_, aux_));
-    PF_CUDA(cudaStreamWaitEvent(stream, join_, 0));
-  }
+  if (!host_is_src) join_copy_streams(stream, aux_task_dirty_, -1);
   cudaEvent_t ev = take_event();
   PF_CUDA(cudaEventRecord(ev, stream));
   meta_inflight_.push_back({base, base + align_up(std::max<size_t>(meta_bytes, 16), 256), ev});

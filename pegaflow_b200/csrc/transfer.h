@@ -77,20 +77,26 @@ class TransferBackend {
   void ensure_staging();
 
   // Kernel launchers (transfer.cu).
-  void launch_pack(const Side &src, const Side &dst, size_t n_items, size_t item_bytes, cudaStream_t s);
+  void launch_pack(const Side &src, const Side &dst, size_t n_items, size_t item_bytes, cudaStream_t s,
+                   bool into_staging);
   void launch_link(const Side &src, const Side &dst, size_t n_items, size_t item_bytes, cudaStream_t s,
                    bool peer);
   void launch_descs(const uint64_t *triples_dev, size_t n, bool aligned, cudaStream_t s);
 
   // One run of one range of one layer through the staged route.
-  void staged_run(const Side &dev_side, const pf_host_run &run, size_t ids_offset, size_t item_bytes,
-                  bool host_is_src, cudaStream_t stream, bool *aux_touched);
+  void staged_run(const Side &dev_side, const pf_host_run &run, size_t item_bytes, bool host_is_src,
+                  cudaStream_t stream);
+  int next_aux();
+  void join_copy_streams(cudaStream_t target, std::vector<char> &dirty, int skip);
 
   int device_;
   pf_backend_config cfg_;
   int sm_count_ = 0;
-  cudaStream_t aux_ = nullptr;  // copy-engine stream of the staged route
-  cudaEvent_t join_ = nullptr;
+  std::vector<cudaStream_t> aux_;      // copy-engine streams of the staged route
+  std::vector<cudaEvent_t> aux_join_;  // one per copy stream, for joining it into another stream
+  std::vector<char> aux_layer_dirty_, aux_task_dirty_;  // copy streams used by the current layer / call
+  size_t aux_cursor_ = 0;
+  int aux_last_ = 0;
   std::vector<Slot> slots_;
   char *staging_ = nullptr;
   size_t slot_cursor_ = 0;
@@ -110,6 +116,7 @@ class TransferBackend {
   std::deque<TimedLaunch> timed_;
   std::vector<cudaEvent_t> timing_event_pool_;
 
+  bool pack_hints_ = false;              // L2 eviction hints in the gather/scatter kernel
   bool tables_aligned_ = true;           // set while an address table is filled
   pf_backend_stats stats_{};
 };

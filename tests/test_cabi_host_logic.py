@@ -1,0 +1,163 @@
+"""CPU-only checks of the product library: it loads, exports every symbol the header declares,
+and its pure host logic (layout arithmetic, page layout, allocator unit, LoadState) agrees with
+the reference's known-answer tests and with the oracle.  No compute call needs a GPU here."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+import pegaflow_b200 as pf
+from pegaflow_b200 import _native as N
+from oracle import pf_oracle as po
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "pegaflow_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(pf_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    names = _declared_symbols()
+    assert len(names) >= 50
+    for name in names:
+        assert hasattr(N.lib, name), f"{name} is declared in include/pegaflow_b200.h but not exported"
+    assert N.lib.pf_abi_version() == 1
+
+
+def _layout(case):
+    out = N.Layout()
+    a = case["new"]
+    st = N.lib.pf_layout_init(C.byref(out), a[0], a[1], a[2], a[3], a[4], a[5], case.get("block_stride", 0),
+                              case.get("ssd_padding", 0))
+    return st, out
+
+
+def test_layout_known_answers_through_the_c_abi(kats):
+    for case in kats["layout"]["ok"]:
+        st, lay = _layout(case)
+        assert st == 0, (case["name"], N.lib.pf_last_error())
+        if "split" in case:
+            assert bool(lay.split) == case["split"]
+        for idx, want in case.get("copies", {}).items():
+            addr, nbytes, n = (C.c_uint64 * 2)(), (C.c_size_t * 2)(), C.c_int()
+            assert N.lib.pf_layout_block_copies(C.byref(lay), int(idx), addr, nbytes, C.byref(n)) == 0
+            assert [[addr[i], nbytes[i]] for i in range(n.value)] == want, case["name"]
+        for idx in case.get("out_of_range", []):
+            addr, nbytes, n = (C.c_uint64 * 2)(), (C.c_size_t * 2)(), C.c_int()
+            assert N.lib.pf_layout_block_copies(C.byref(lay), idx, addr, nbytes, C.byref(n)) == 3
+            assert b"out of range" in N.lib.pf_last_error()
+        if "padded_segment_bytes" in case:
+            assert lay.padded_segment_bytes == case["padded_segment_bytes"]
+            assert lay.padded_segment_bytes * lay.segments == case["padded_block_bytes"]
+    for case in kats["layout"]["reject"]:
+        st, _ = _layout(case)
+        assert st == 3, case["name"]
+        msg = N.lib.pf_last_error().decode()
+        assert case["contains"] in msg and msg.startswith("invalid argument: "), (case["name"], msg)
+
+
+def test_layout_matches_oracle_on_random_geometries():
+    import numpy as np
+
+    rng = np.random.default_rng(3)
+    agree = 0
+    for _ in range(3000):
+        seg = int(rng.choice([64, 100, 512, 1024, 4096, 8848]))
+        nb = int(rng.integers(1, 40))
+        segs = int(rng.choice([1, 2, 2, 3]))
+        kv = int(rng.choice([0, seg // 2, seg, seg * 2, seg * nb, seg * nb + 48, seg * (nb // 2) + 7]))
+        stride = int(rng.choice([0, 0, seg, seg * 2, seg * segs, seg * segs + 16, seg - 1]))
+        size = int(rng.choice([seg * segs * nb, seg * segs * nb * 3, 1 << 30, seg]))
+        args = (0x7000, size, nb, seg, kv, segs)
+        out = N.Layout()
+        st = N.lib.pf_layout_init(C.byref(out), *args, stride, 512)
+        try:
+            o = po.KVCacheLayout(*args)
+            if stride:
+                o.with_block_stride(stride)
+            o.with_ssd_padding(512)
+            err = None
+        except po.OracleError as e:
+            err = str(e)
+        if err is None:
+            assert st == 0, (args, stride, N.lib.pf_last_error())
+            for f in ("block_stride_bytes", "segment_bytes", "segments", "padded_segment_bytes", "split", "kv_stride_bytes"):
+                assert getattr(out, f) == getattr(o.c, f), (f, args, stride)
+            agree += 1
+        else:
+            assert st == 3 and N.lib.pf_last_error().decode() == "invalid argument: " + err, (args, stride, err)
+    assert agree > 200
+
+
+def test_page_layout_and_unit_size_through_the_c_abi(kats):
+    SZ = C.c_size_t
+    for case in kats["page_layout"]["ok"] + kats["page_layout"]["reject"]:
+        sets = case["sets"]
+        offs, items = [0], []
+        for s in sets:
+            items += s
+            offs.append(len(items))
+        n = case["n_layers"]
+        shard, loff, lbytes, pages, nsh = (SZ * n)(), (SZ * n)(), (SZ * n)(), (SZ * len(sets))(), SZ()
+        st = N.lib.pf_build_page_layout((SZ * len(offs))(*offs), (SZ * len(items))(*items), len(sets), n,
+                                        (SZ * n)(*case["padded"]), shard, loff, lbytes, pages, C.byref(nsh))
+        if "contains" in case:
+            assert st == 3 and case["contains"] in N.lib.pf_last_error().decode()
+        else:
+            assert st == 0
+            assert list(shard) == case["layer_shard"] and list(loff) == case["layer_offsets"]
+            assert list(lbytes) == case["layer_bytes"] and list(pages[: nsh.value]) == case["shard_page_sizes"]
+    for case in kats["allocator"]["unit_size"]:
+        assert N.lib.pf_pool_unit_size(case["pool"], case["hint"]) == case["unit"]
+
+
+def test_load_state_segment_is_bit_compatible(kats):
+    ls = kats["load_state"]
+    state = pf.PyLoadState()
+    name = state.shm_name()
+    assert name.startswith(ls["name_prefix"]) and len(name) == len(ls["name_prefix"]) + 32
+    raw = open("/dev/shm/" + name, "rb").read()
+    assert raw == po.load_state_image(0) and len(raw) == ls["mapping_bytes"]
+    other = pf.PyLoadState(attach_to=name)
+    state.set_completed()
+    assert other.get_state() == ls["success"] and po.parse_load_state(open("/dev/shm/" + name, "rb").read()) == 1
+    other.set_error()
+    assert state.get_state() == ls["error"]
+    # an image written by the other side (the oracle stands in for the reference) attaches as well
+    foreign = "pega_load_" + "0" * 31 + "f"
+    with open("/dev/shm/" + foreign, "wb") as f:
+        f.write(po.load_state_image(1))
+    try:
+        assert pf.PyLoadState(attach_to=foreign).get_state() == 1
+        with open("/dev/shm/" + foreign, "wb") as f:
+            f.write(b"\0")
+        with pytest.raises(pf.PegaflowInternal, match="too small"):
+            pf.PyLoadState(attach_to=foreign)
+        bad = bytearray(po.load_state_image(0))
+        bad[8:12] = (0xDEADBEEF).to_bytes(4, "little")
+        with open("/dev/shm/" + foreign, "wb") as f:
+            f.write(bytes(bad))
+        with pytest.raises(pf.PegaflowInternal, match="invalid LoadState header"):
+            pf.PyLoadState(attach_to=foreign)
+    finally:
+        os.unlink("/dev/shm/" + foreign)
+    del other
+    del state
+    assert not os.path.exists("/dev/shm/" + name), "the creator unlinks its segment"
+    with pytest.raises(pf.PegaflowInternal, match="failed to open shared memory"):
+        pf.PyLoadState(attach_to="pega_load_missing")
+
+
+def test_no_gpu_means_loud_failure_not_a_fallback():
+    """Without a CUDA device nothing pretends to work: engine, backend and pool refuse to start."""
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    for make in (lambda: pf.PegaEngine(1 << 20), lambda: pf.TransferBackend(0), lambda: pf.PinnedPool(1 << 20)):
+        with pytest.raises(pf.PegaFlowError):
+            make()
