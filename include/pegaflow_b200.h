@@ -198,6 +198,10 @@ typedef struct pf_backend_stats {
   double link_kernel_ms;
   uint64_t link_kernel_launches;
   uint64_t link_kernel_bytes;
+  /* The gather/scatter kernel's own clock (%globaltimer, first CTA start to last CTA end) for the
+   * first 65536 timed launches: an event pair around a ~10 us kernel measures mostly the pair. */
+  double pack_kernel_device_ms;
+  uint64_t pack_kernel_device_launches;
 } pf_backend_stats;
 int pf_backend_get_stats(pf_backend *backend, pf_backend_stats *out);
 

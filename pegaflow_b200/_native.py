@@ -65,7 +65,8 @@ class BackendStats(C.Structure):
     _fields_ = [("kernel_launches", u64), ("dma_copies", u64), ("bytes_staged", u64), ("bytes_zero_copy", u64),
                 ("bytes_peer", u64), ("device_status", u32), ("pack_kernel_ms", C.c_double),
                 ("pack_kernel_launches", u64), ("pack_kernel_bytes", u64), ("link_kernel_ms", C.c_double),
-                ("link_kernel_launches", u64), ("link_kernel_bytes", u64)]
+                ("link_kernel_launches", u64), ("link_kernel_bytes", u64), ("pack_kernel_device_ms", C.c_double),
+                ("pack_kernel_device_launches", u64)]
 
 
 class PoolConfig(C.Structure):

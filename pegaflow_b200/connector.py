@@ -1,0 +1,317 @@
+"""Host-side mirror of the reference's worker connector surface for the save/load path.
+
+* ``infer_kv_cache_registration`` — what ``_infer_kv_cache_registration`` derives from a vLLM KV
+  tensor (python/pegaflow/connector/worker.py:65-151).
+* ``InProcEngineClient`` — the method names and argument order of the reference's
+  ``EngineRpcClient`` (python/src/lib.rs:205-617, stubs in python/pegaflow/pegaflow.pyi), served
+  by an engine in the same process through the C ABI instead of gRPC + CUDA IPC.
+* ``PegaWorkerConnector`` — the worker-side hooks of ``PegaKVConnector``
+  (python/pegaflow/connector/worker.py:261-929) that touch the transfer path, including real
+  bodies for vLLM's per-layer hooks, which the reference leaves empty
+  (worker.py:712-713,755-765).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple, Union
+
+from . import _native as N
+from .engine import Completion, PegaEngine, PyLoadState
+
+CROSS_LAYER_KEY = "ALL_LAYERS"  # worker.py:32
+
+
+@dataclass(frozen=True)
+class KVCacheRegistrationInfo:
+    layout: str  # "KV-first" | "blocks-first"
+    num_blocks: int
+    bytes_per_block: int
+    kv_stride_bytes: int
+    segments: int
+    physical_blocks_per_logical_block: int
+
+
+def infer_kv_cache_registration(kv_cache, logical_block_size: int, *, is_mla: bool = False,
+                                is_recurrent_state: bool = False) -> KVCacheRegistrationInfo:
+    """Registration of one layer from its KV tensor's shape / stride / element size.
+
+    Non-MLA tensors whose first dimension is 2 are "KV-first" (K and V regions, two segments per
+    block); everything else is "blocks-first" (one segment per block).  MLA caches group the
+    kernel's physical rows into scheduler-sized logical blocks.  Errors carry the reference's text.
+    """
+    shape = tuple(kv_cache.shape)
+    stride = tuple(kv_cache.stride())
+    es = kv_cache.element_size()
+    if logical_block_size <= 0:
+        raise ValueError(f"logical block size must be > 0, got {logical_block_size}")
+    if is_recurrent_state or not is_mla:
+        kv_first = (not is_recurrent_state) and len(shape) >= 2 and shape[0] == 2
+        block_dim = 1 if kv_first else 0
+        num_blocks = shape[block_dim]
+        bytes_per_block = stride[block_dim] * es
+        if num_blocks <= 0:
+            raise ValueError(f"physical block count must be > 0, got {num_blocks}")
+        if bytes_per_block == 0:
+            raise ValueError(f"Invalid bytes_per_block: shape={shape} stride={stride}")
+        return KVCacheRegistrationInfo("KV-first" if kv_first else "blocks-first", num_blocks, bytes_per_block,
+                                       stride[0] * es if kv_first else 0, 2 if kv_first else 1, 1)
+    rows = shape[0]
+    row_tokens = shape[1] if len(shape) >= 2 else logical_block_size
+    if rows <= 0:
+        raise ValueError(f"physical block count must be > 0, got {rows}")
+    if row_tokens <= 0:
+        raise ValueError(f"physical block size must be > 0, got {row_tokens}")
+    if logical_block_size % row_tokens:
+        raise ValueError("logical block size must be a multiple of physical block size "
+                         f"(logical={logical_block_size}, physical={row_tokens})")
+    ratio = logical_block_size // row_tokens
+    if rows % ratio:
+        raise ValueError("physical block count must be divisible by physical/logical split ratio "
+                         f"(physical_blocks={rows}, ratio={ratio})")
+    bytes_per_block = stride[0] * es * ratio
+    if bytes_per_block == 0:
+        raise ValueError(f"Invalid bytes_per_block: shape={shape} stride={stride}")
+    return KVCacheRegistrationInfo("blocks-first", rows // ratio, bytes_per_block, 0, 1, ratio)
+
+
+def resolve_transfer_backend(is_mla: bool, override: Optional[str]) -> str:
+    """python/pegaflow/connector/common.py:577-594: "kernel" for MLA, "direct" otherwise, unless
+    overridden.  Both names select the one backend this library has."""
+    allowed = ("direct", "kernel")
+    if override is not None:
+        if override not in allowed:
+            raise ValueError(f"Unsupported pegaflow.transfer_backend {override!r}; expected one of: "
+                             + ", ".join(allowed))
+        return override
+    return "kernel" if is_mla else "direct"
+
+
+class QueryLoading:
+    """A backing-store fetch is in progress (never returned here: there is no SSD/RDMA tier)."""
+
+
+@dataclass
+class QueryReady:
+    num_hit_blocks: int
+    lease: bytes
+    hit_positions: List[int] = field(default_factory=list)
+
+
+def _region_of(obj) -> Tuple[int, int]:
+    """(data_ptr, nbytes) of what a worker registers for one layer: a CUDA tensor (its whole
+    storage, like the reference's IPC wrapper, ipc_wrapper.py:101-163) or an explicit pair."""
+    if isinstance(obj, tuple):
+        return int(obj[0]), int(obj[1])
+    if obj.storage_offset() != 0:
+        raise ValueError("KV cache tensor must have zero storage offset")
+    return obj.data_ptr(), obj.untyped_storage().nbytes()
+
+
+class InProcEngineClient:
+    """``EngineRpcClient`` without the wire: same methods, same argument order, ``(ok, message)``
+    results; invalid requests raise ``ValueError`` as the reference's bindings do."""
+
+    def __init__(self, engine: PegaEngine):
+        self._engine = engine
+
+    def endpoint(self) -> str:
+        return "inproc://pegaflow_b200"
+
+    def health(self) -> Tuple[bool, str]:
+        return True, "ok"
+
+    @staticmethod
+    def _reply(fn) -> Tuple[bool, str]:
+        try:
+            fn()
+            return True, ""
+        except N.PegaflowInvalidArgument:
+            raise
+        except N.PegaFlowError as e:
+            return False, str(e)
+
+    def register_context_batch(self, instance_id, namespace, tp_rank, pp_rank, tp_size, world_size, device_id,
+                               layer_names, tensors, num_blocks_list, bytes_per_block_list, kv_stride_bytes_list,
+                               segments_list, transfer_backend, page_first, layer_group_ids=None):
+        if transfer_backend not in ("direct", "kernel"):
+            raise ValueError(f"unknown transfer_backend {transfer_backend!r}")
+        regions = [_region_of(t) for t in tensors]
+        return self._reply(lambda: self._engine.register_context_layer_batch_strided(
+            instance_id, namespace, device_id, tp_rank, pp_rank, tp_size, world_size, list(layer_names),
+            [r[0] for r in regions], [r[1] for r in regions], list(num_blocks_list), list(bytes_per_block_list),
+            list(kv_stride_bytes_list), list(segments_list), None,
+            list(layer_group_ids) if layer_group_ids is not None else None, transfer_backend, page_first))
+
+    def unregister_context(self, instance_id):
+        return self._reply(lambda: self._engine.unregister_instance(instance_id))
+
+    def save(self, instance_id, tp_rank, pp_rank, device_id, saves):
+        return self._reply(lambda: self._engine.batch_save(instance_id, tp_rank, pp_rank, device_id, saves))
+
+    def save_async(self, instance_id, tp_rank, pp_rank, device_id, saves, ready_event: int = 0):
+        """Additive: returns once the save is queued; it starts when ``ready_event`` has fired."""
+        return self._reply(lambda: self._engine.save_layers_async(instance_id, tp_rank, pp_rank, device_id, saves,
+                                                                  ready_event))
+
+    def flush_saves(self):
+        return self._reply(self._engine.flush_saves)
+
+    def load(self, instance_id, tp_rank, device_id, load_state_shm, layer_groups, loads):
+        return self._reply(lambda: self._engine.batch_load_shm(instance_id, tp_rank, device_id, load_state_shm,
+                                                               layer_groups, loads))
+
+    def query_prefetch(self, instance_id, block_hashes, req_id, wait_for_full_prefix=False, group_id=0):
+        if not req_id:
+            raise ValueError("req_id must be non-empty")
+        if group_id == 0:
+            blocks, _missing = self._engine.query_prefix(instance_id, block_hashes, req_id)
+            positions = list(range(len(blocks)))
+        else:
+            found = self._engine.query_group_membership(instance_id, group_id, block_hashes)
+            positions = [i for i, b in enumerate(found) if b is not None]
+            blocks = [found[i] for i in positions]
+        if not blocks:
+            return QueryReady(0, b"", [])
+        lease = self._engine.create_query_lease(instance_id, blocks)
+        return QueryReady(len(blocks), lease, positions)
+
+    def release(self, lease: bytes) -> None:
+        if lease:
+            self._engine.release_query_lease(lease)
+
+    def shutdown(self):
+        return True, ""
+
+
+@dataclass
+class _PendingLoad:
+    state: PyLoadState
+    request_ids: List[str]
+    block_ids: List[int]
+
+
+class PegaWorkerConnector:
+    """Worker-side hooks on the transfer path for one GPU of one instance."""
+
+    def __init__(self, client: InProcEngineClient, engine: PegaEngine, *, instance_id: str, namespace: str,
+                 device_id: int, block_size: int, tp_rank: int = 0, pp_rank: int = 0, tp_size: int = 1,
+                 world_size: int = 1, is_mla: bool = False, transfer_backend: Optional[str] = None,
+                 page_first: Optional[bool] = None):
+        self.client, self.engine = client, engine
+        self.instance_id, self.namespace, self.device_id = instance_id, namespace, device_id
+        self.block_size, self.is_mla = block_size, is_mla
+        self.tp_rank, self.pp_rank, self.tp_size, self.world_size = tp_rank, pp_rank, tp_size, world_size
+        self.transfer_backend = resolve_transfer_backend(is_mla, transfer_backend)
+        self.page_first = is_mla if page_first is None else page_first
+        self.registered_layers: List[str] = []
+        self.registrations: Dict[str, KVCacheRegistrationInfo] = {}
+        self._pending_loads: List[_PendingLoad] = []
+        self._load_errors: set = set()
+        self._saves_in_flight = 0
+
+    # worker.py:261-412
+    def register_kv_caches(self, kv_caches: Dict[str, object]):
+        if not kv_caches:
+            raise RuntimeError("No KV cache layers were selected for registration")
+        names, tensors, nb, bpb, kvs, segs = [], [], [], [], [], []
+        for name, t in kv_caches.items():
+            info = infer_kv_cache_registration(t, self.block_size, is_mla=self.is_mla)
+            self.registrations[name] = info
+            names.append(name)
+            tensors.append(t)
+            nb.append(info.num_blocks)
+            bpb.append(info.bytes_per_block)
+            kvs.append(info.kv_stride_bytes)
+            segs.append(info.segments)
+        ok, msg = self.client.register_context_batch(self.instance_id, self.namespace, self.tp_rank, self.pp_rank,
+                                                     self.tp_size, self.world_size, self.device_id, names, tensors,
+                                                     nb, bpb, kvs, segs, self.transfer_backend, self.page_first)
+        if not ok:
+            raise RuntimeError(f"Register context batch failed for layers {names}: {msg}")
+        self.registered_layers = names
+
+    # worker.py:414-420
+    def register_cross_layers_kv_cache(self, kv_cache):
+        key = f"{CROSS_LAYER_KEY}_pp{self.pp_rank}" if self.world_size > self.tp_size else CROSS_LAYER_KEY
+        self.register_kv_caches({key: kv_cache})
+
+    def unregister(self):
+        if self.registered_layers:
+            self.client.unregister_context(self.instance_id)
+            self.registered_layers = []
+
+    # worker.py:549-710
+    def start_load_kv(self, loads: Sequence[Tuple[str, bytes, Sequence[Optional[int]]]]):
+        """loads: (request_id, lease, destination block ids) per request; one load task for all."""
+        if not loads:
+            return
+        state = PyLoadState()
+        pending = _PendingLoad(state, [r for r, _, _ in loads], [b for _, _, ids in loads for b in ids if b is not None])
+        try:
+            ok, msg = self.client.load(self.instance_id, self.tp_rank, self.device_id, state.shm_name(),
+                                       [list(self.registered_layers)], [(lease, [list(ids)]) for _, lease, ids in loads])
+        except ValueError as e:
+            ok, msg = False, str(e)
+        if not ok:
+            for _, lease, _ in loads:
+                self.client.release(lease)          # worker.py:650-684
+            self._load_errors.update(pending.block_ids)
+            return
+        self._pending_loads.append(pending)
+
+    # worker.py:712-713 is empty in the reference
+    def wait_for_layer_load(self, layer_name: str, stream: int = 0):
+        """Order `stream` after the arrival of `layer_name`'s bytes of the pending load."""
+        if not self._pending_loads:
+            return
+        ev = self.engine.layer_load_event(self.instance_id, self.device_id, layer_name)
+        self.engine.stream_wait_event(stream, ev)
+
+    # worker.py:755-765 is a stub in the reference
+    def save_kv_layer(self, layer_name: str, block_ids: Sequence[int], block_hashes: Sequence[bytes],
+                      ready_event: int = 0):
+        keep = [(b, h) for b, h in zip(block_ids, block_hashes) if b != 0]   # block 0 is vLLM's null block
+        if not keep:
+            return
+        ok, msg = self.client.save_async(self.instance_id, self.tp_rank, self.pp_rank, self.device_id,
+                                         [(layer_name, [b for b, _ in keep], [h for _, h in keep])], ready_event)
+        if not ok:
+            raise RuntimeError(f"layer save failed: {msg}")
+        self._saves_in_flight += 1
+
+    # worker.py:767-929
+    def wait_for_save(self, saves: Optional[Sequence[Tuple[str, Sequence[int], Sequence[bytes]]]] = None):
+        """Blocking batch save of `saves` (all layers, one GPU batch), then a flush that also
+        covers layer saves queued by save_kv_layer."""
+        if saves:
+            cleaned = []
+            for name, ids, hashes in saves:
+                keep = [(b, h) for b, h in zip(ids, hashes) if b != 0]
+                cleaned.append((name, [b for b, _ in keep], [h for _, h in keep]))
+            ok, msg = self.client.save(self.instance_id, self.tp_rank, self.pp_rank, self.device_id, cleaned)
+            if not ok:
+                raise RuntimeError(f"save failed: {msg}")
+        ok, msg = self.client.flush_saves()
+        self._saves_in_flight = 0
+        if not ok:
+            raise RuntimeError(f"save failed: {msg}")
+
+    # worker.py:422-547
+    def get_finished(self) -> Tuple[List[str], List[str]]:
+        """(request ids whose load finished, request ids whose load failed)."""
+        done, failed, still = [], [], []
+        for p in self._pending_loads:
+            st = p.state.get_state()
+            if st == 0:
+                still.append(p)
+            elif st == 1:
+                done.extend(p.request_ids)
+            else:
+                failed.extend(p.request_ids)
+                self._load_errors.update(p.block_ids)
+        self._pending_loads = still
+        return done, failed
+
+    def get_block_ids_with_load_errors(self) -> set:
+        out, self._load_errors = self._load_errors, set()
+        return out

@@ -1188,6 +1188,8 @@ void Engine::metrics(pf_engine_metrics *out) {
         t.link_kernel_ms += s.link_kernel_ms;
         t.link_kernel_launches += s.link_kernel_launches;
         t.link_kernel_bytes += s.link_kernel_bytes;
+        t.pack_kernel_device_ms += s.pack_kernel_device_ms;
+        t.pack_kernel_device_launches += s.pack_kernel_device_launches;
       }
     }
   }

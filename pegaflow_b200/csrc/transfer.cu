@@ -36,6 +36,12 @@ constexpr int kStages = 4;               // ring depth of the TMA kernels
 constexpr uint32_t kStageBytes = 32768;  // bytes per ring stage
 constexpr unsigned kStatusWaitExpired = 0x57A17u;
 
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
 __device__ __forceinline__ uint64_t side_addr(const Side &s, uint32_t i) {
   if (s.table) return s.table[i];
   uint64_t idx = s.ids ? (uint64_t)s.ids[i] : (uint64_t)i;
@@ -160,9 +166,13 @@ __device__ __forceinline__ void copy_span(uint64_t dst, uint64_t src, uint32_t l
     reinterpret_cast<char *>(dst)[j] = reinterpret_cast<const char *>(src)[j];
 }
 
+// `stamp` (optional) points at {first start, last end} in %globaltimer nanoseconds, pre-set to
+// {UINT64_MAX, 0}: a device-side measure of the launch that needs no event around it.
 template <int kHints>
 __global__ void __launch_bounds__(kLdstThreads)
-copy_items_ldst(Side src, Side dst, uint32_t n_items, uint32_t item_bytes, uint32_t chunk_bytes) {
+copy_items_ldst(Side src, Side dst, uint32_t n_items, uint32_t item_bytes, uint32_t chunk_bytes,
+                unsigned long long *stamp) {
+  if (stamp && threadIdx.x == 0) atomicMin(&stamp[0], (unsigned long long)global_timer_ns());
   ItemGen gen(src, dst, n_items, item_bytes, chunk_bytes);
   uint64_t s, d, pol_src = 0, pol_dst = 0;
   if (kHints == 1) {
@@ -174,6 +184,10 @@ copy_items_ldst(Side src, Side dst, uint32_t n_items, uint32_t item_bytes, uint3
   }
   uint32_t len;
   while (gen.next(s, d, len)) copy_span<kHints>(d, s, len, pol_src, pol_dst);
+  if (stamp) {
+    __syncthreads();
+    if (threadIdx.x == 0) atomicMax(&stamp[1], (unsigned long long)global_timer_ns());
+  }
 }
 
 __global__ void __launch_bounds__(kLdstThreads)
@@ -215,11 +229,6 @@ __device__ __forceinline__ void bulk_s2g(uint64_t gdst, const void *smem_src, ui
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ uint64_t global_timer_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
 
 // Waits for a ring stage to fill.  Gives up after ~2 s (a link read normally takes microseconds).
 __device__ __forceinline__ bool wait_stage(uint64_t *bar, uint32_t parity) {
@@ -342,6 +351,13 @@ TransferBackend::TransferBackend(int device, const pf_backend_config *config) : 
   PF_CUDA(cudaFuncSetAttribute(copy_items_tma, cudaFuncAttributeMaxDynamicSharedMemorySize, kStages * kStageBytes));
   PF_CUDA(cudaFuncSetAttribute(copy_descs_tma, cudaFuncAttributeMaxDynamicSharedMemorySize, kStages * kStageBytes));
   meta_grow(1u << 20);
+  if (cfg_.time_kernels) {
+    stamps_host_.assign(2 * (size_t)kStampRing, 0);
+    for (size_t i = 0; i < (size_t)kStampRing; ++i) stamps_host_[2 * i] = ~0ull;
+    PF_CUDA(cudaMalloc(&stamps_dev_, stamps_host_.size() * sizeof(unsigned long long)));
+    PF_CUDA(cudaMemcpy(stamps_dev_, stamps_host_.data(), stamps_host_.size() * sizeof(unsigned long long),
+                       cudaMemcpyHostToDevice));
+  }
 }
 
 TransferBackend::~TransferBackend() {
@@ -361,6 +377,7 @@ TransferBackend::~TransferBackend() {
   }
   for (auto ev : timing_event_pool_) cudaEventDestroy(ev);
   if (staging_) cudaFree(staging_);
+  if (stamps_dev_) cudaFree(stamps_dev_);
   if (meta_dev_) cudaFree(meta_dev_);
   if (meta_host_) cudaFreeHost(meta_host_);
   if (status_host_) cudaFreeHost(status_host_);
@@ -388,7 +405,7 @@ void TransferBackend::time_begin(cudaStream_t s, cudaEvent_t *start) {
   PF_CUDA(cudaEventRecord(*start, s));
 }
 
-void TransferBackend::time_end(cudaStream_t s, cudaEvent_t start, uint64_t bytes, bool link) {
+void TransferBackend::time_end(cudaStream_t s, cudaEvent_t start, uint64_t bytes, bool link, int stamp_idx) {
   if (!start) return;
   cudaEvent_t stop;
   if (!timing_event_pool_.empty()) {
@@ -398,10 +415,11 @@ void TransferBackend::time_end(cudaStream_t s, cudaEvent_t start, uint64_t bytes
     PF_CUDA(cudaEventCreate(&stop));
   }
   PF_CUDA(cudaEventRecord(stop, s));
-  timed_.push_back({start, stop, bytes, link});
+  timed_.push_back({start, stop, bytes, link, stamp_idx});
 }
 
 void TransferBackend::fold_timings(bool wait) {
+  bool stamps_fetched = false;
   while (!timed_.empty()) {
     TimedLaunch &t = timed_.front();
     cudaError_t q = wait ? cudaEventSynchronize(t.stop) : cudaEventQuery(t.stop);
@@ -419,6 +437,19 @@ void TransferBackend::fold_timings(bool wait) {
         stats_.pack_kernel_ms += ms;
         ++stats_.pack_kernel_launches;
         stats_.pack_kernel_bytes += t.bytes;
+        if (t.stamp_idx >= 0) {
+          if (!stamps_fetched) {
+            // finished launches have written their stamps; one copy serves the whole fold
+            if (cudaMemcpy(stamps_host_.data(), stamps_dev_, stamps_used_ * 2 * sizeof(unsigned long long),
+                           cudaMemcpyDeviceToHost) == cudaSuccess)
+              stamps_fetched = true;
+          }
+          const unsigned long long a = stamps_host_[2 * (size_t)t.stamp_idx], b = stamps_host_[2 * (size_t)t.stamp_idx + 1];
+          if (stamps_fetched && b > a && a != ~0ull) {
+            stats_.pack_kernel_device_ms += (double)(b - a) * 1e-6;
+            ++stats_.pack_kernel_device_launches;
+          }
+        }
       }
     }
     timing_event_pool_.push_back(t.start);
@@ -520,14 +551,21 @@ void TransferBackend::launch_pack(const Side &src, const Side &dst, size_t n_ite
   const int grid = (int)std::min<uint64_t>(chunks, (uint64_t)cfg_.pack_ctas);
   cudaEvent_t t0;
   time_begin(s, &t0);
+  unsigned long long *stamp = nullptr;
+  int stamp_idx = -1;
+  if (t0 && stamps_dev_ && stamps_used_ < kStampRing) {
+    stamp_idx = (int)stamps_used_++;
+    stamp = stamps_dev_ + 2 * (size_t)stamp_idx;
+  }
+  const uint32_t n = (uint32_t)n_items, ib = (uint32_t)item_bytes;
   if (!pack_hints_)
-    copy_items_ldst<0><<<grid, kLdstThreads, 0, s>>>(src, dst, (uint32_t)n_items, (uint32_t)item_bytes, kPackChunk);
+    copy_items_ldst<0><<<grid, kLdstThreads, 0, s>>>(src, dst, n, ib, kPackChunk, stamp);
   else if (into_staging)
-    copy_items_ldst<1><<<grid, kLdstThreads, 0, s>>>(src, dst, (uint32_t)n_items, (uint32_t)item_bytes, kPackChunk);
+    copy_items_ldst<1><<<grid, kLdstThreads, 0, s>>>(src, dst, n, ib, kPackChunk, stamp);
   else
-    copy_items_ldst<2><<<grid, kLdstThreads, 0, s>>>(src, dst, (uint32_t)n_items, (uint32_t)item_bytes, kPackChunk);
+    copy_items_ldst<2><<<grid, kLdstThreads, 0, s>>>(src, dst, n, ib, kPackChunk, stamp);
   PF_CUDA(cudaGetLastError());
-  time_end(s, t0, 2ull * n_items * item_bytes, false);
+  time_end(s, t0, 2ull * n_items * item_bytes, false, stamp_idx);
   ++stats_.kernel_launches;
 }
 
@@ -550,10 +588,11 @@ void TransferBackend::launch_link(const Side &src, const Side &dst, size_t n_ite
   } else {
     const uint64_t chunks = (uint64_t)n_items * ((item_bytes + kPackChunk - 1) / kPackChunk);
     const int grid = (int)std::min<uint64_t>(chunks, (uint64_t)std::max(ctas, sm_count_));
-    copy_items_ldst<0><<<grid, kLdstThreads, 0, s>>>(src, dst, (uint32_t)n_items, (uint32_t)item_bytes, kPackChunk);
+    copy_items_ldst<0><<<grid, kLdstThreads, 0, s>>>(src, dst, (uint32_t)n_items, (uint32_t)item_bytes, kPackChunk,
+                                                     nullptr);
   }
   PF_CUDA(cudaGetLastError());
-  time_end(s, t0, (uint64_t)n_items * item_bytes, true);
+  time_end(s, t0, (uint64_t)n_items * item_bytes, true, -1);
   ++stats_.kernel_launches;
 }
 

@@ -65,6 +65,7 @@ class TransferBackend {
     cudaEvent_t start, stop;
     uint64_t bytes;
     bool link;
+    int stamp_idx;  // slot of the kernel's own {start, end} stamps, -1 if none
   };
 
   // Meta ring: pinned host bytes + device mirror for block ids, address tables and descriptors.
@@ -111,10 +112,16 @@ class TransferBackend {
   unsigned int *status_dev_ = nullptr;
   // Kernel timing (cfg_.time_kernels): event pairs of launches not yet folded into stats_.
   void time_begin(cudaStream_t s, cudaEvent_t *start);
-  void time_end(cudaStream_t s, cudaEvent_t start, uint64_t bytes, bool link);
+  void time_end(cudaStream_t s, cudaEvent_t start, uint64_t bytes, bool link, int stamp_idx);
   void fold_timings(bool wait);
   std::deque<TimedLaunch> timed_;
   std::vector<cudaEvent_t> timing_event_pool_;
+  // Device-clock stamps written by the gather/scatter kernel itself (first CTA start, last CTA
+  // end): up to kStampRing launches per backend are stamped.
+  static constexpr int kStampRing = 1 << 16;
+  unsigned long long *stamps_dev_ = nullptr;
+  std::vector<unsigned long long> stamps_host_;
+  size_t stamps_used_ = 0;
 
   bool pack_hints_ = false;              // L2 eviction hints in the gather/scatter kernel
   bool tables_aligned_ = true;           // set while an address table is filled

@@ -161,3 +161,37 @@ def test_no_gpu_means_loud_failure_not_a_fallback():
     for make in (lambda: pf.PegaEngine(1 << 20), lambda: pf.TransferBackend(0), lambda: pf.PinnedPool(1 << 20)):
         with pytest.raises(pf.PegaFlowError):
             make()
+
+
+def test_connector_layout_inference_matches_reference_fixture():
+    """The product's host mirror of worker.py:65-151 against outputs of the reference itself."""
+    import json
+
+    from pegaflow_b200.connector import infer_kv_cache_registration, resolve_transfer_backend
+
+    class T:
+        def __init__(self, shape, stride, es):
+            self.shape, self._stride, self._es = tuple(shape), tuple(stride), es
+
+        def stride(self):
+            return self._stride
+
+        def element_size(self):
+            return self._es
+
+    with open(os.path.join(ROOT, "tests", "golden", "kv_layout_inference.json")) as f:
+        cases = json.load(f)["cases"]
+    for c in cases:
+        t = T(c["shape"], c["stride"], c["element_size"])
+        kw = dict(is_mla=c["is_mla"], is_recurrent_state=c["is_recurrent_state"])
+        if "error" in c:
+            with pytest.raises(ValueError) as ei:
+                infer_kv_cache_registration(t, c["logical_block_size"], **kw)
+            assert str(ei.value) == c["error"]
+        else:
+            info = infer_kv_cache_registration(t, c["logical_block_size"], **kw)
+            assert {k: getattr(info, k) for k in c["result"]} == c["result"], c
+    assert resolve_transfer_backend(True, None) == "kernel" and resolve_transfer_backend(False, None) == "direct"
+    assert resolve_transfer_backend(True, "direct") == "direct"
+    with pytest.raises(ValueError, match="Unsupported pegaflow.transfer_backend"):
+        resolve_transfer_backend(False, "nvlink")
