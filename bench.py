@@ -111,14 +111,11 @@ def dist_setup(n_gpus):
 
 def barrier_and_max(value, world, device):
     """Barrier, then the max of `value` over ranks (device-side all-reduce)."""
-    import torch
-    import torch.distributed as dist
-
     if world == 1:
         return value
-    t = torch.tensor([value], dtype=torch.float64, device=device)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return float(t.item())
+    from pegaflow_b200 import sharding
+
+    return sharding.barrier_and_max(value, device=device)
 
 
 def barrier(world):
