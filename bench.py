@@ -37,9 +37,17 @@ PCIE_GEN5_X16_GBS = 32e9 * 16 * (128 / 130) / 8 / 1e9   # 63.0 GB/s per directio
 
 def workloads():
     # name -> dict(layers, seg_bytes (K or V of one block), gpu_blocks, requests, blocks_per_request)
+    # segments: 2 = K and V regions per layer (KV-first registration, one pool allocation per layer and
+    # segment); 1 = one segment per block with page-first host pages (one page per block holding every layer).
     return {
-        "llama3.1-8b": dict(layers=32, seg_bytes=16 * 8 * 128 * 2, gpu_blocks=8192, requests=8, blocks=640),
-        "small": dict(layers=4, seg_bytes=16 * 8 * 128 * 2, gpu_blocks=2048, requests=2, blocks=256),
+        "llama3.1-8b": dict(layers=32, seg_bytes=16 * 8 * 128 * 2, gpu_blocks=8192, requests=8, blocks=640, segments=2),
+        "small": dict(layers=4, seg_bytes=16 * 8 * 128 * 2, gpu_blocks=2048, requests=2, blocks=256, segments=2),
+        # one rank of Llama-3.1-70B TP=8: 1 KV head per rank -> 4 KiB segments, 4 prompts of 32768 tokens
+        "llama70b-tp8-rank": dict(layers=80, seg_bytes=16 * 1 * 128 * 2, gpu_blocks=16384, requests=4, blocks=2048,
+                                  segments=2),
+        # DeepSeek-V3-style latent cache [num_blocks, 64, 576], bf16 and fp8 byte widths
+        "mla-bf16": dict(layers=61, seg_bytes=64 * 576 * 2, gpu_blocks=1024, requests=1, blocks=256, segments=1),
+        "mla-fp8": dict(layers=61, seg_bytes=64 * 576 * 1, gpu_blocks=1024, requests=1, blocks=256, segments=1),
     }
 
 
@@ -134,21 +142,23 @@ class Workload:
         self.spec = spec
         self.device = device
         L, seg, nb = spec["layers"], spec["seg_bytes"], spec["gpu_blocks"]
+        self.segments = spec["segments"]
         g = torch.Generator(device=device)
         g.manual_seed(seed)
-        # per layer one tensor [2, num_blocks, seg] bytes: K region then V region (KV-first registration)
+        # per layer one tensor [2, num_blocks, seg] bytes (K region then V region, KV-first registration)
+        # or [1, num_blocks, seg] for single-segment caches
         self.kv = []
         for _ in range(L):
-            t = torch.empty((2, nb, seg // 2), dtype=torch.bfloat16, device=device)
+            t = torch.empty((self.segments, nb, seg // 2), dtype=torch.bfloat16, device=device)
             t.normal_(0.0, 1.0, generator=g)
-            self.kv.append(t.view(torch.uint8).view(2, nb, seg))
+            self.kv.append(t.view(torch.uint8).view(self.segments, nb, seg))
         rng = np.random.default_rng(seed)
         n_req, per = spec["requests"], spec["blocks"]
         ids = rng.permutation(nb - 1)[: n_req * per] + 1          # id 0 is vLLM's null block
         self.save_ids = [ids[r * per:(r + 1) * per].astype(np.uint32) for r in range(n_req)]
         dst = rng.permutation(nb - 1)[: n_req * per] + 1
         self.load_ids = [dst[r * per:(r + 1) * per].astype(np.uint32) for r in range(n_req)]
-        self.payload_per_request = L * per * 2 * seg
+        self.payload_per_request = L * per * self.segments * seg
         self.payload = self.payload_per_request * n_req
 
     def layer_ptr(self, layer):
@@ -156,7 +166,32 @@ class Workload:
 
     @property
     def kv_stride(self):
-        return self.spec["gpu_blocks"] * self.spec["seg_bytes"]
+        return self.spec["gpu_blocks"] * self.spec["seg_bytes"] if self.segments == 2 else 0
+
+    @property
+    def page_bytes(self):
+        """Host page of one block when page-first: every layer's block back to back."""
+        return self.spec["layers"] * self.spec["seg_bytes"]
+
+
+def alloc_host_images(pool, wl):
+    """Pool placement the engine would choose: split caches get one allocation per (request, layer,
+    segment) with blocks back to back (offload.rs:477-508); single-segment caches get page-first pages,
+    one per block, layer l at offset l * seg (offload.rs:182-282).  Returns per request, per layer, per
+    range: (host, host_device, stride)."""
+    L, seg, per = wl.spec["layers"], wl.spec["seg_bytes"], wl.spec["blocks"]
+    out = []
+    for _ in range(wl.spec["requests"]):
+        if wl.segments == 2:
+            req = []
+            for _l in range(L):
+                k, v = pool.alloc(per * seg), pool.alloc(per * seg)
+                req.append([(k[0], k[1], seg), (v[0], v[1], seg)])
+        else:
+            pages = pool.alloc(per * wl.page_bytes)
+            req = [[(pages[0] + l * seg, pages[1] + l * seg, wl.page_bytes)] for l in range(L)]
+        out.append(req)
+    return out
 
 
 def make_layer_xfers(pf, wl, pool_allocs, ids_per_request):
@@ -166,10 +201,9 @@ def make_layer_xfers(pf, wl, pool_allocs, ids_per_request):
     for r, ids in enumerate(ids_per_request):
         layers = []
         for l in range(wl.spec["layers"]):
-            k, v = pool_allocs[r][l]
             n = len(ids)
-            layers.append(pf.LayerXfer(wl.layer_ptr(l), seg, wl.kv_stride, seg, 2, ids,
-                                       [[pf.HostRun(0, n, k[0], k[1], seg)], [pf.HostRun(0, n, v[0], v[1], seg)]]))
+            runs = [[pf.HostRun(0, n, h, d, stride)] for (h, d, stride) in pool_allocs[r][l]]
+            layers.append(pf.LayerXfer(wl.layer_ptr(l), seg, wl.kv_stride, seg, wl.segments, ids, runs))
         out.append(pf.TransferBackend.make_layers(layers))
     return out
 
@@ -212,13 +246,14 @@ def cpu_baseline(wl, seconds_budget=8.0):
     ids = np.concatenate(wl.save_ids).astype(np.uint64)
     n = len(ids)
     rng = np.random.default_rng(1)
-    shadow = [rng.integers(0, 256, size=2 * nb * seg, dtype=np.uint8) for _ in range(n_layers)]
-    host = [np.zeros(2 * n * seg, dtype=np.uint8) for _ in range(n_layers)]
+    nseg = spec["segments"]
+    shadow = [rng.integers(0, 256, size=nseg * nb * seg, dtype=np.uint8) for _ in range(n_layers)]
+    host = [np.zeros(nseg * n * seg, dtype=np.uint8) for _ in range(n_layers)]
     layers = (ref_layer_type() * n_layers)()
     for l in range(n_layers):
-        lay = po.KVCacheLayout(shadow[l].ctypes.data, 2 * nb * seg, nb, seg, nb * seg, 2)
+        lay = po.KVCacheLayout(shadow[l].ctypes.data, nseg * nb * seg, nb, seg, nb * seg if nseg == 2 else 0, nseg)
         layers[l].layout = lay.c
-        for s in range(2):
+        for s in range(nseg):
             layers[l].host_base[s] = host[l].ctypes.data + s * n * seg
             layers[l].host_dev_base[s] = host[l].ctypes.data + s * n * seg
             layers[l].allocation[s] = 2 * l + s + 1
@@ -227,7 +262,7 @@ def cpu_baseline(wl, seconds_budget=8.0):
     ids_c = (C.c_size_t * n)(*[int(x) for x in ids])
     descs = lib.pfr_build(layers, n_layers, ids_c, n, C.byref(nd), C.byref(secs))
     descs_p = C.cast(descs, C.POINTER(po.CopyDesc))
-    payload = n_layers * n * 2 * seg
+    payload = n_layers * n * nseg * seg
     cores = os.cpu_count() or 1
     out = {}
     for threads in (1, cores):
@@ -245,7 +280,7 @@ def cpu_baseline(wl, seconds_budget=8.0):
     lib.pfr_free(descs)
     return {"value": round(out[cores][0], 2), "unit": "GB/s", "cores": cores, "kind": "port",
             "single_core_value": round(out[1][0], 2), "descriptor_build_seconds_per_M": round(secs.value / nd.value * 1e6, 3),
-            "sample": f"{n_layers} of {spec['layers']} layers x {n} blocks (all requests), K and V, "
+            "sample": f"{n_layers} of {spec['layers']} layers x {n} blocks (all requests), {nseg} segment(s) per block, "
                       f"{payload / 2**20:.0f} MiB per pass, {out[cores][1]} passes, gather from a host shadow of the KV "
                       "cache into the pool layout with memcpy (save direction)"}
 
@@ -290,18 +325,20 @@ def run_reference(args, rank, world, local, launched_world=1):
     seg, L = spec["seg_bytes"], spec["layers"]
     per = spec["blocks"]
     pool = pf.PinnedPool(wl.payload + (64 << 20))
+    images = alloc_host_images(pool, wl)
     stream = torch.cuda.Stream()
     tasks = []
     for r in range(spec["requests"]):
         layers = (ref_layer_type() * L)()
         for l in range(L):
-            lay = po.KVCacheLayout(wl.layer_ptr(l), 2 * spec["gpu_blocks"] * seg, spec["gpu_blocks"], seg, wl.kv_stride, 2)
+            lay = po.KVCacheLayout(wl.layer_ptr(l), wl.segments * spec["gpu_blocks"] * seg, spec["gpu_blocks"], seg,
+                                   wl.kv_stride, wl.segments)
             layers[l].layout = lay.c
-            for s in range(2):
-                h, d, _ = pool.alloc(per * seg)
+            for s, (h, d, stride) in enumerate(images[r][l]):
                 layers[l].host_base[s], layers[l].host_dev_base[s] = h, d
-                layers[l].allocation[s] = (r * L + l) * 2 + s + 1
-            layers[l].host_stride = seg
+                # page-first pages of one request come from one allocation; split layers from one each
+                layers[l].allocation[s] = (r * L + l) * 2 + s + 1 if wl.segments == 2 else r + 1
+                layers[l].host_stride = stride
         sids = (C.c_size_t * per)(*[int(x) for x in wl.save_ids[r]])
         lids = (C.c_size_t * per)(*[int(x) for x in wl.load_ids[r]])
         tasks.append((layers, sids, lids))
@@ -330,8 +367,11 @@ def run_reference(args, rank, world, local, launched_world=1):
             task(layers, lids, 1, kernel)
         return t1 - t0, time.perf_counter() - t1
 
+    # the reference picks its kernel backend for MLA models and the direct one otherwise
+    # (python/pegaflow/connector/common.py:577-594)
+    use_kernel = wl.segments == 1 and bool(lib.pfr_has_reference_kernel())
     for _ in range(args.warmup):
-        step()
+        step(use_kernel)
     torch.cuda.synchronize()
     barrier(world)
     stats["calls"], stats["build_s"] = 0, 0.0
@@ -341,7 +381,7 @@ def run_reference(args, rank, world, local, launched_world=1):
     t_save = t_load = 0.0
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        a, b = step()
+        a, b = step(use_kernel)
         t_save += a
         t_load += b
     torch.cuda.synchronize()
@@ -349,11 +389,15 @@ def run_reference(args, rank, world, local, launched_world=1):
     clocks = sampler.stop() if rank == 0 else None
     extra = {}
     if lib.pfr_has_reference_kernel() and world == 1:
-        ks, kl = step(kernel=True)
-        ks, kl = step(kernel=True)
-        extra["reference_kernel_backend"] = {"save_gbs": round(wl.payload / ks / 1e9, 2), "load_gbs": round(wl.payload / kl / 1e9, 2),
-                                             "note": "the reference's own NVRTC kernel source compiled unchanged, "
-                                                     "1 CTA x 256 threads per fragment, pageable descriptor upload"}
+        ks, kl = step(kernel=not use_kernel)
+        ks, kl = step(kernel=not use_kernel)
+        other = {"save_gbs": round(wl.payload / ks / 1e9, 2), "load_gbs": round(wl.payload / kl / 1e9, 2)}
+        if use_kernel:
+            extra["reference_direct_backend"] = other
+        else:
+            other["note"] = ("the reference's own NVRTC kernel source compiled unchanged, 1 CTA x 256 threads per "
+                             "fragment, pageable descriptor upload")
+            extra["reference_kernel_backend"] = other
     if rank != 0:
         return
     value = 2 * wl.payload * args.steps * world / elapsed / 1e9
@@ -363,8 +407,11 @@ def run_reference(args, rank, world, local, launched_world=1):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(elapsed / args.steps * 1e3, 3),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
         "config": {"workload": args.workload, **spec, "between_iterations": "inputs (10 GiB per direction) far exceed the 126 MB L2",
-                   "path": "reference direct backend restated: CPU descriptor build + merge + one cudaMemcpyAsync per "
-                           "fragment + one sync per task (gpu_worker.rs:428-523, transfer/memcpy.rs:25-97)"},
+                   "path": ("reference kernel backend (its default for MLA): CPU descriptor build + pageable descriptor "
+                            "upload + its own kernel + one sync per task (gpu_worker.rs:428-523, transfer/kernel.rs:79-135)")
+                   if use_kernel else
+                   ("reference direct backend restated: CPU descriptor build + merge + one cudaMemcpyAsync per "
+                    "fragment + one sync per task (gpu_worker.rs:428-523, transfer/memcpy.rs:25-97)")},
         "save_gbs": round(wl.payload * args.steps / t_save / 1e9, 3), "load_gbs": round(wl.payload * args.steps / t_load / 1e9, 3),
         "frac_pcie_gen5_x16": round(value / world / PCIE_GEN5_X16_GBS, 4),
         "memcpy_calls_per_step": stats["calls"] // max(1, args.steps),
@@ -393,7 +440,7 @@ def run_b200(args, rank, world, local):
 
     # ---------------- transfer-only arm: backend + pool, KV resident in HBM -------------------
     pool = pf.PinnedPool(wl.payload + (64 << 20), numa_node=-1)
-    allocs = [[(pool.alloc(per * seg), pool.alloc(per * seg)) for _ in range(L)] for _ in range(n_req)]
+    allocs = alloc_host_images(pool, wl)
     be = pf.TransferBackend(local, route=route, time_kernels=not args.no_kernel_timing, link_ctas=args.link_ctas,
                             staging_slot_bytes=args.slot_mib << 20, staging_slots=args.slots,
                             copy_streams=args.copy_streams, pack_ctas=args.pack_ctas)
@@ -454,7 +501,7 @@ def run_b200(args, rank, world, local):
     stream.synchronize()
     torch.cuda.synchronize()
     per_layer = [lev[i].elapsed_time(lev[i + 1]) for i in range(L)]
-    layer_bytes = per * 2 * seg
+    layer_bytes = per * wl.segments * seg
     per_layer_gbs = sorted(layer_bytes / 1e6 / max(t, 1e-6) for t in per_layer[1:])   # layer 0 includes the ramp-up
     st2 = be.stats()
     del save_x, load_x
@@ -550,10 +597,11 @@ def run_e2e(args, pf, wl, rank, world, local, route):
                         staging_slot_bytes=args.slot_mib << 20, staging_slots=args.slots,
                         copy_streams=args.copy_streams)
     names = [f"model.layers.{l}.self_attn.attn" for l in range(L)]
-    region = 2 * spec["gpu_blocks"] * seg
+    region = wl.segments * spec["gpu_blocks"] * seg
     eng.register_context_layer_batch_strided(
-        "bench", "llama", local, 0, 0, 1, 1, names, [wl.layer_ptr(l) for l in range(L)], [region] * L,
-        [spec["gpu_blocks"]] * L, [seg] * L, [wl.kv_stride] * L, [2] * L, None, None, "direct", False)
+        "bench", "bench-ns", local, 0, 0, 1, 1, names, [wl.layer_ptr(l) for l in range(L)], [region] * L,
+        [spec["gpu_blocks"]] * L, [seg] * L, [wl.kv_stride] * L, [wl.segments] * L, None, None,
+        "direct" if wl.segments == 2 else "kernel", wl.segments == 1)
     prepared = []
     for k in range(steps_total):
         reqs = []

@@ -320,6 +320,8 @@ class PegaEngine:
 
     def peer_load(self, src_instance, src_device, dst_instance, dst_device, src_block_ids, dst_block_ids):
         n = len(src_block_ids)
+        if len(dst_block_ids) != n:
+            raise PegaflowInvalidArgument(3, "invalid argument: peer load needs one destination per source block")
         SZ = C.c_size_t * max(1, n)
         N.check(N.lib.pf_engine_peer_load(self._h, src_instance.encode(), src_device, dst_instance.encode(), dst_device,
                                           n, SZ(*src_block_ids), SZ(*dst_block_ids)))
