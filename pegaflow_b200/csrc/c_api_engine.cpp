@@ -2,6 +2,7 @@
 // sections 2-4).
 #include <chrono>
 #include <cstring>
+#include <map>
 
 #include "common.h"
 #include "engine.h"
@@ -43,12 +44,19 @@ std::vector<std::string> to_hashes(size_t n, const uint8_t *const *hashes, const
 
 std::vector<LayerSaveIn> to_saves(size_t n_layers, const pf_layer_save *saves) {
   std::vector<LayerSaveIn> out(n_layers);
+  // Layers that point at the same hash array share one copy of it.
+  std::map<std::pair<const void *, size_t>, HashList> seen;
   for (size_t i = 0; i < n_layers; ++i) {
     const pf_layer_save &s = saves[i];
     if (!s.layer_name) throw Error::invalid("layer_name is null");
     out[i].layer_name = s.layer_name;
     out[i].block_ids.assign(s.block_ids, s.block_ids + s.n_blocks);
-    out[i].block_hashes = to_hashes(s.n_blocks, s.block_hashes, s.block_hash_lens);
+    auto key = std::make_pair((const void *)s.block_hashes, s.n_blocks);
+    auto it = seen.find(key);
+    if (it == seen.end())
+      it = seen.emplace(key, std::make_shared<const std::vector<std::string>>(
+                                 to_hashes(s.n_blocks, s.block_hashes, s.block_hash_lens))).first;
+    out[i].block_hashes = it->second;
   }
   return out;
 }

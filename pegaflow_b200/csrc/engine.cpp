@@ -50,6 +50,16 @@ bool ReadCache::insert(const BlockKey &key, BlockRef block) {
   return true;
 }
 
+void ReadCache::contains_many(const std::string &ns, const std::vector<std::string> &hashes, std::vector<char> *out) {
+  out->assign(hashes.size(), 0);
+  BlockKey key{ns, ""};
+  std::lock_guard<std::mutex> g(mu_);
+  for (size_t i = 0; i < hashes.size(); ++i) {
+    key.hash = hashes[i];
+    (*out)[i] = map_.count(key) ? 1 : 0;
+  }
+}
+
 size_t ReadCache::evict_lru(size_t n) {
   std::vector<BlockRef> dropped;  // destroyed outside the lock (frees pool memory)
   {
@@ -237,6 +247,7 @@ Engine::Engine(size_t pool_bytes, bool use_hugepages, const pf_storage_config *c
                                     : cfg_.use_mmap_pool ? PinnedMemory::Strategy::MmapRegister
                                                          : PinnedMemory::Strategy::CudaHostAlloc;
   allocator_ = std::make_unique<PinnedAllocator>(pool_bytes, nodes, cfg_.pool_shards, strategy, cfg_.hint_value_size);
+  if (const char *e = getenv("PEGAFLOW_B200_TRACE")) trace_ = atoi(e) != 0;
   insert_thread_ = std::thread(&Engine::insert_loop, this);
 }
 
@@ -528,14 +539,15 @@ void Engine::batch_save(const std::string &instance_id, size_t tp_rank, size_t p
     size_t slot;
     uint32_t group;
     std::vector<size_t> ids;
-    std::vector<std::string> hashes;
+    HashList hashes;  // phase 0: as given; after phase 1: group-encoded and filtered
     std::vector<RawBlock> raw;
   };
   std::vector<Ctx> ctxs;
   for (auto &s : saves) {
-    if (s.block_ids.size() != s.block_hashes.size())
+    const size_t n_hashes = s.block_hashes ? s.block_hashes->size() : 0;
+    if (s.block_ids.size() != n_hashes)
       throw Error::invalid(strf("block_ids length %zu does not match block_hashes %zu for layer %s", s.block_ids.size(),
-                                s.block_hashes.size(), s.layer_name.c_str()));
+                                n_hashes, s.layer_name.c_str()));
     const size_t layer_id = topo->layer_id(s.layer_name);
     auto lit = gpu->layouts.find(s.layer_name);
     if (lit == gpu->layouts.end()) throw Error::invalid("layer " + s.layer_name + " not registered on device");
@@ -546,40 +558,74 @@ void Engine::batch_save(const std::string &instance_id, size_t tp_rank, size_t p
         throw Error::invalid(strf("block_id %zu out of range (num_blocks=%zu) for layer %s", id,
                                   lit->second.num_blocks(), s.layer_name.c_str()));
     if (s.block_ids.empty()) continue;
-    ctxs.push_back(Ctx{s.layer_name, &lit->second, slot, group, std::move(s.block_ids), std::move(s.block_hashes), {}});
+    ctxs.push_back(Ctx{s.layer_name, &lit->second, slot, group, std::move(s.block_ids), s.block_hashes, {}});
   }
   if (ctxs.empty()) return;
+  const auto t1 = std::chrono::steady_clock::now();
 
-  // ---- phase 1: drop blocks whose (group, hash) is already resident (offload.rs:393-424)
+  // ---- phase 1: drop blocks whose (group, hash) is already resident (offload.rs:393-424).
+  // Layers of one save normally share one hash list: each distinct (list, group) is encoded and
+  // looked up once and the result is shared.
   {
-    std::unordered_map<std::string, bool> needed;  // group-encoded hash -> must save
+    struct Filtered {
+      HashList hashes;                 // group-encoded, resident ones removed
+      std::vector<uint32_t> kept;      // positions that survive (empty + all_kept: every position)
+      bool all_kept = false;
+    };
+    std::map<std::pair<const void *, uint32_t>, Filtered> memo;
     size_t total = 0;
     for (auto &c : ctxs) {
-      std::vector<size_t> ids;
-      std::vector<std::string> hashes;
-      for (size_t i = 0; i < c.ids.size(); ++i) {
-        std::string enc = group_hash(c.hashes[i], c.group);
-        auto it = needed.find(enc);
-        if (it == needed.end()) it = needed.emplace(enc, !cache_.contains(BlockKey{inst->ns, enc})).first;
-        if (it->second) {
-          ids.push_back(c.ids[i]);
-          hashes.push_back(std::move(c.hashes[i]));
+      auto key = std::make_pair((const void *)c.hashes.get(), c.group);
+      auto it = memo.find(key);
+      if (it == memo.end()) {
+        auto encoded = std::make_shared<std::vector<std::string>>();
+        encoded->reserve(c.hashes->size());
+        for (auto &h : *c.hashes) encoded->push_back(group_hash(h, c.group));
+        std::vector<char> resident;
+        cache_.contains_many(inst->ns, *encoded, &resident);
+        Filtered f;
+        if (std::find(resident.begin(), resident.end(), 1) == resident.end()) {
+          f.all_kept = true;
+          f.hashes = std::move(encoded);
+        } else {
+          auto survivors = std::make_shared<std::vector<std::string>>();
+          for (size_t i = 0; i < encoded->size(); ++i)
+            if (!resident[i]) {
+              f.kept.push_back((uint32_t)i);
+              survivors->push_back(std::move((*encoded)[i]));
+            }
+          f.hashes = std::move(survivors);
         }
+        it = memo.emplace(key, std::move(f)).first;
       }
-      c.ids.swap(ids);
-      c.hashes.swap(hashes);
+      const Filtered &f = it->second;
+      if (!f.all_kept) {
+        std::vector<size_t> ids;
+        ids.reserve(f.kept.size());
+        for (uint32_t i : f.kept) ids.push_back(c.ids[i]);
+        c.ids.swap(ids);
+      }
+      c.hashes = f.hashes;
       total += c.ids.size();
     }
     ctxs.erase(std::remove_if(ctxs.begin(), ctxs.end(), [](const Ctx &c) { return c.ids.empty(); }), ctxs.end());
     if (total == 0 || ctxs.empty()) return;
   }
+  const auto t2 = std::chrono::steady_clock::now();
 
-  // ---- phase 2: host placement (offload.rs:428-527, 182-282)
+  // ---- phase 2: host placement (offload.rs:428-527, 182-282).  Only what the GPU copy needs is
+  // built here (allocations, block ids, host runs); the per-block bookkeeping for the cache is
+  // built after the copy has been submitted, while it runs.
   const int numa_node = gpu->numa_node;
   const bool page_first = topo->page.has_value();
+  const bool blockwise = cfg_.blockwise_alloc != 0 && !page_first;
   auto work = std::make_shared<std::vector<LayerWork>>();
+  auto all_allocs = std::make_shared<std::vector<std::shared_ptr<PinnedAllocation>>>();
   std::vector<std::shared_ptr<PinnedAllocation>> pages;
+  // allocs[c][a] = (K-or-whole, V) allocation a of layer context c
+  std::vector<std::vector<std::array<std::shared_ptr<PinnedAllocation>, 2>>> layer_allocs(ctxs.size());
   size_t padded_total = 0;
+  work->reserve(ctxs.size());
   if (page_first) {
     const size_t shard = ctxs[0].slot;
     const size_t page_size = topo->page->shard_page_sizes[shard];
@@ -589,7 +635,7 @@ void Engine::batch_save(const std::string &instance_id, size_t tp_rank, size_t p
         throw Error::invalid("page-first save does not support split K/V (layer " + c.name + ")");
       if (c.slot != shard)
         throw Error::invalid("page-first save spans multiple shards (one writer must save one shard)");
-      if (c.ids != ctxs[0].ids || c.hashes != ctxs[0].hashes)
+      if (c.ids != ctxs[0].ids || (c.hashes != ctxs[0].hashes && *c.hashes != *ctxs[0].hashes))
         throw Error::invalid("page-first save requires the same block set across all layers");
       layer_ids.insert(topo->layer_id(c.name));
     }
@@ -599,6 +645,7 @@ void Engine::batch_save(const std::string &instance_id, size_t tp_rank, size_t p
                                 "must write a shard's entire page)",
                                 shard_layers, shard, layer_ids.size()));
     if (page_size == 0) throw Error::storage("page size is zero");
+    pages.reserve(ctxs[0].ids.size());
     for (size_t i = 0; i < ctxs[0].ids.size(); ++i) pages.push_back(allocate(page_size, numa_node, "page"));
     for (auto &c : ctxs) {
       const size_t layer_id = topo->layer_id(c.name);
@@ -606,6 +653,7 @@ void Engine::batch_save(const std::string &instance_id, size_t tp_rank, size_t p
       LayerWork w;
       w.layer_name = c.name;
       w.layout = *c.layout;
+      w.block_ids.reserve(c.ids.size());
       RunBuilder rb(c.layout->range_bytes());
       for (size_t i = 0; i < c.ids.size(); ++i) {
         w.block_ids.push_back((uint32_t)c.ids[i]);
@@ -616,95 +664,62 @@ void Engine::batch_save(const std::string &instance_id, size_t tp_rank, size_t p
     }
     padded_total = page_size * pages.size();
   } else {
-    const bool blockwise = cfg_.blockwise_alloc != 0;
-    for (auto &c : ctxs) {
+    for (size_t ci = 0; ci < ctxs.size(); ++ci) {
+      Ctx &c = ctxs[ci];
       const KVCacheLayout &layout = *c.layout;
       const size_t n = c.ids.size();
       const size_t n_allocs = blockwise ? n : 1, per = blockwise ? 1 : n;
       LayerWork w;
       w.layer_name = c.name;
       w.layout = layout;
+      w.block_ids.reserve(n);
       for (size_t id : c.ids) w.block_ids.push_back((uint32_t)id);
-      RunBuilder rb0(layout.range_bytes()), rb1(layout.range_bytes());
-      c.raw.reserve(n);
+      const bool split = layout.is_split();
+      const size_t stride = split ? layout.padded_segment_bytes() : layout.padded_block_bytes();
+      layer_allocs[ci].reserve(n_allocs);
       for (size_t a = 0; a < n_allocs; ++a) {
-        if (layout.is_split()) {
-          const size_t stride = layout.padded_segment_bytes();
-          auto k = allocate(stride * per, numa_node, "K segment buffer");
-          auto v = allocate(stride * per, numa_node, "V segment buffer");
-          for (size_t i = 0; i < per; ++i) {
-            RawBlock rbk;
-            rbk.n_segments = 2;
-            rbk.seg[0] = Segment{k->host() + i * stride, k->device() + i * stride, stride, k};
-            rbk.seg[1] = Segment{v->host() + i * stride, v->device() + i * stride, stride, v};
-            rb0.add(rbk.seg[0].host, rbk.seg[0].device);
-            rb1.add(rbk.seg[1].host, rbk.seg[1].device);
-            c.raw.push_back(std::move(rbk));
-          }
-        } else {
-          const size_t stride = layout.padded_block_bytes();
-          auto b = allocate(stride * per, numa_node, "block buffer");
-          for (size_t i = 0; i < per; ++i) {
-            RawBlock rbk;
-            rbk.n_segments = 1;
-            rbk.seg[0] = Segment{b->host() + i * stride, b->device() + i * stride, stride, b};
-            rb0.add(rbk.seg[0].host, rbk.seg[0].device);
-            c.raw.push_back(std::move(rbk));
-          }
+        std::array<std::shared_ptr<PinnedAllocation>, 2> pair;
+        pair[0] = allocate(stride * per, numa_node, split ? "K segment buffer" : "block buffer");
+        if (split) pair[1] = allocate(stride * per, numa_node, "V segment buffer");
+        for (int r = 0; r < (split ? 2 : 1); ++r) {
+          // one run per allocation; neighbouring allocations that happen to continue it are merged
+          auto &runs = w.runs[r];
+          if (!runs.empty() && (char *)runs.back().host + runs.back().n_blocks * runs.back().stride_bytes == pair[r]->host() &&
+              runs.back().host_device + runs.back().n_blocks * runs.back().stride_bytes == pair[r]->device() &&
+              runs.back().stride_bytes == stride)
+            runs.back().n_blocks += per;
+          else
+            runs.push_back(pf_host_run{a * per, per, pair[r]->host(), pair[r]->device(), stride});
         }
+        if (!blockwise) {
+          all_allocs->push_back(pair[0]);
+          if (split) all_allocs->push_back(pair[1]);
+        }
+        layer_allocs[ci].push_back(std::move(pair));
       }
-      w.runs[0] = rb0.take();
-      if (layout.is_split()) w.runs[1] = rb1.take();
       padded_total += layout.padded_block_bytes() * n;
       work->push_back(std::move(w));
     }
   }
-
-  // ---- phase 4 input, built now so that the worker can hand it over by itself when async
-  auto batches = std::make_shared<std::vector<RawSaveBatch>>();
-  if (page_first) {
-    const size_t slot = ctxs[0].slot;
-    const size_t page_size = topo->page->shard_page_sizes[slot];
-    RawSaveLayer layer;
-    layer.slot_id = slot;
-    layer.hashes = ctxs[0].hashes;
-    for (auto &page : pages) {
-      RawBlock rbk;
-      rbk.n_segments = 1;
-      rbk.seg[0] = Segment{page->host(), page->device(), page_size, page};
-      layer.blocks.push_back(std::move(rbk));
-    }
-    RawSaveBatch b{inst->ns, topo->total_slots(), {}};
-    b.layers.push_back(std::move(layer));
-    batches->push_back(std::move(b));
-  } else {
-    std::map<uint32_t, RawSaveBatch> by_group;
-    for (auto &c : ctxs) {
-      auto it = by_group.find(c.group);
-      if (it == by_group.end())
-        it = by_group.emplace(c.group, RawSaveBatch{inst->ns, topo->group_total_slots(c.group), {}}).first;
-      RawSaveLayer layer;
-      layer.slot_id = c.slot;
-      layer.blocks = std::move(c.raw);
-      for (auto &h : c.hashes) layer.hashes.push_back(group_hash(h, c.group));
-      it->second.layers.push_back(std::move(layer));
-    }
-    for (auto &kv : by_group) batches->push_back(std::move(kv.second));
-  }
+  const auto t3 = std::chrono::steady_clock::now();
 
   // ---- phase 3: one GPU batch (offload.rs:532-536 -> gpu_worker.rs:482-523)
   auto done = std::make_shared<std::promise<void>>();
   std::future<void> finished = done->get_future();
+  auto batches_ready = std::make_shared<std::promise<std::shared_ptr<std::vector<RawSaveBatch>>>>();
+  auto batches_future = batches_ready->get_future().share();
   {
     std::lock_guard<std::mutex> g(insert_mu_);
     ++insert_pending_;  // until the batches have been handed to the insert worker
   }
-  auto hand_over = [this, batches] {
+  auto hand_over = [this, batches_future] {
+    auto batches = batches_future.get();
     std::lock_guard<std::mutex> g(insert_mu_);
-    for (auto &b : *batches) {
-      insert_queue_.push_back(std::move(b));
-      ++insert_pending_;
-    }
+    if (batches)
+      for (auto &b : *batches) {
+        insert_queue_.push_back(std::move(b));
+        ++insert_pending_;
+      }
     --insert_pending_;
     insert_cv_.notify_all();
     insert_idle_cv_.notify_all();
@@ -717,18 +732,15 @@ void Engine::batch_save(const std::string &instance_id, size_t tp_rank, size_t p
   gpu->save_worker->submit([=](TransferBackend &backend, cudaStream_t stream) {
     try {
       std::vector<pf_layer_xfer> xf(work->size());
-      size_t bytes = 0;
       for (size_t i = 0; i < work->size(); ++i) {
         LayerWork &w = (*work)[i];
         xf[i] = pf_layer_xfer{w.layout.data_ptr(), w.layout.block_stride_bytes(), w.layout.kv_stride_bytes(),
                               w.layout.range_bytes(), w.layout.n_ranges(), w.block_ids.size(), w.block_ids.data(),
                               {w.runs[0].size(), w.runs[1].size()}, {w.runs[0].data(), w.runs[1].data()}};
-        bytes += w.payload_bytes();
       }
       if (ready_event) cuda_or_storage(cudaStreamWaitEvent(stream, ready_event, 0), "cudaStreamWaitEvent");
       backend.move_layers(xf.data(), xf.size(), false, stream, nullptr);
       cuda_or_storage(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
-      (void)bytes;
       if (async) hand_over();
       done->set_value();
     } catch (const std::exception &e) {
@@ -743,6 +755,72 @@ void Engine::batch_save(const std::string &instance_id, size_t tp_rank, size_t p
       done->set_exception(std::current_exception());
     }
   });
+
+  // ---- phase 4 input, built while the copy runs: one RawBlock per (layer, block) and the
+  // batches the insert worker will seal (offload.rs:594-656).
+  try {
+    auto batches = std::make_shared<std::vector<RawSaveBatch>>();
+    if (page_first) {
+      const size_t slot = ctxs[0].slot;
+      const size_t page_size = topo->page->shard_page_sizes[slot];
+      RawSaveLayer layer;
+      layer.slot_id = slot;
+      layer.hashes = ctxs[0].hashes;
+      layer.blocks.reserve(pages.size());
+      for (auto &page : pages) {
+        RawBlock rbk;
+        rbk.n_segments = 1;
+        rbk.seg[0] = Segment{page->host(), page->device(), page_size};
+        rbk.owner = page;  // a page lives and dies with its block
+        layer.blocks.push_back(std::move(rbk));
+      }
+      RawSaveBatch b{inst->ns, topo->total_slots(), {}, nullptr};
+      b.layers.push_back(std::move(layer));
+      batches->push_back(std::move(b));
+    } else {
+      std::map<uint32_t, RawSaveBatch> by_group;
+      const Owner batch_owner = blockwise ? Owner() : Owner(all_allocs);
+      for (size_t ci = 0; ci < ctxs.size(); ++ci) {
+        Ctx &c = ctxs[ci];
+        auto it = by_group.find(c.group);
+        if (it == by_group.end())
+          it = by_group.emplace(c.group, RawSaveBatch{inst->ns, topo->group_total_slots(c.group), {}, batch_owner}).first;
+        const bool split = c.layout->is_split();
+        const size_t stride = split ? c.layout->padded_segment_bytes() : c.layout->padded_block_bytes();
+        const size_t per = blockwise ? 1 : c.ids.size();
+        RawSaveLayer layer;
+        layer.slot_id = c.slot;
+        layer.hashes = c.hashes;  // already group-encoded
+        layer.blocks.resize(c.ids.size());
+        for (size_t a = 0; a < layer_allocs[ci].size(); ++a) {
+          auto &pair = layer_allocs[ci][a];
+          Owner own;
+          if (blockwise) own = split ? Owner(std::make_shared<std::array<std::shared_ptr<PinnedAllocation>, 2>>(pair))
+                                     : Owner(pair[0]);
+          for (size_t i = 0; i < per; ++i) {
+            RawBlock &rbk = layer.blocks[a * per + i];
+            rbk.n_segments = split ? 2 : 1;
+            rbk.seg[0] = Segment{pair[0]->host() + i * stride, pair[0]->device() + i * stride, stride};
+            if (split) rbk.seg[1] = Segment{pair[1]->host() + i * stride, pair[1]->device() + i * stride, stride};
+            rbk.owner = own;
+          }
+        }
+        it->second.layers.push_back(std::move(layer));
+      }
+      for (auto &kv : by_group) batches->push_back(std::move(kv.second));
+    }
+    batches_ready->set_value(std::move(batches));
+  } catch (...) {
+    batches_ready->set_value(nullptr);
+    if (!async) {
+      try {
+        finished.get();
+      } catch (...) {
+      }
+      abandon();
+    }
+    throw;
+  }
   if (async) {
     save_bytes_.fetch_add(padded_total);
     save_batches_.fetch_add(1);
@@ -756,9 +834,14 @@ void Engine::batch_save(const std::string &instance_id, size_t tp_rank, size_t p
   }
   save_bytes_.fetch_add(padded_total);
   save_batches_.fetch_add(1);
-  save_nanos_.fetch_add(
-      (uint64_t)std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now() - t0).count());
+  const auto t4 = std::chrono::steady_clock::now();
+  save_nanos_.fetch_add((uint64_t)std::chrono::duration_cast<std::chrono::nanoseconds>(t4 - t0).count());
   hand_over();
+  if (trace_) {
+    auto ms = [](auto a, auto b) { return std::chrono::duration<double, std::milli>(b - a).count(); };
+    fprintf(stderr, "[pegaflow_b200] save %s: resolve %.2f ms, hash_filter %.2f ms, pinned_alloc %.2f ms, gpu_copy %.2f ms\n",
+            instance_id.c_str(), ms(t0, t1), ms(t1, t2), ms(t2, t3), ms(t3, t4));
+  }
 }
 
 void Engine::flush_saves() {
@@ -796,7 +879,7 @@ void Engine::process_insert(RawSaveBatch &batch) {
   if (batch.layers.empty()) return;
   bool same_order = true;
   for (auto &l : batch.layers)
-    if (l.hashes != batch.layers[0].hashes) same_order = false;
+    if (l.hashes != batch.layers[0].hashes && *l.hashes != *batch.layers[0].hashes) same_order = false;
   if (same_order && batch.layers.size() == batch.total_slots) {
     // Every layer carries the same hashes in the same order and together they fill every
     // slot: seal block by block without touching the inflight map.
@@ -809,15 +892,16 @@ void Engine::process_insert(RawSaveBatch &batch) {
       else seen[slot_of[l]] = 1;
     }
     if (distinct) {
-      const auto &hashes = batch.layers[0].hashes;
+      const auto &hashes = *batch.layers[0].hashes;
       for (size_t b = 0; b < hashes.size(); ++b) {
         BlockKey key{batch.ns, hashes[b]};
         if (cache_.contains(key) || inflight_.count(key)) {
           for (size_t l = 0; l < batch.layers.size(); ++l)
-            insert_slot(key, slot_of[l], std::move(batch.layers[l].blocks[b]), batch.total_slots);
+            insert_slot(key, slot_of[l], std::move(batch.layers[l].blocks[b]), batch.total_slots, batch.owner);
           continue;
         }
         auto sealed = std::make_shared<SealedBlock>();
+        sealed->owner = batch.owner;
         sealed->slots.resize(batch.total_slots);
         for (size_t l = 0; l < batch.layers.size(); ++l) {
           sealed->footprint += batch.layers[l].blocks[b].total_size();
@@ -829,12 +913,14 @@ void Engine::process_insert(RawSaveBatch &batch) {
     }
   }
   for (auto &l : batch.layers)
-    for (size_t b = 0; b < l.hashes.size(); ++b)
-      insert_slot(BlockKey{batch.ns, l.hashes[b]}, l.slot_id, std::move(l.blocks[b]), batch.total_slots);
+    for (size_t b = 0; b < l.hashes->size(); ++b)
+      insert_slot(BlockKey{batch.ns, (*l.hashes)[b]}, l.slot_id, std::move(l.blocks[b]), batch.total_slots, batch.owner);
 }
 
-void Engine::insert_slot(const BlockKey &key, size_t slot, RawBlock block, size_t total_slots) {
+void Engine::insert_slot(const BlockKey &key, size_t slot, RawBlock block, size_t total_slots,
+                         const Owner &batch_owner) {
   if (cache_.contains(key)) return;  // late duplicate of a resident block
+  if (!block.owner) block.owner = batch_owner;  // slots of one block may come from different saves
   auto it = inflight_.find(key);
   if (it == inflight_.end()) {
     Inflight fresh;
@@ -938,6 +1024,7 @@ void Engine::batch_load(const std::string &instance_id, size_t tp_rank, int devi
     else if (ok) shm_state->set_completed();
     else shm_state->set_error();
   };
+  const auto t_begin = std::chrono::steady_clock::now();
   try {
     auto inst = get_instance(instance_id);
     auto topo = sealed_topology(*inst);
@@ -1044,6 +1131,9 @@ void Engine::batch_load(const std::string &instance_id, size_t tp_rank, int devi
     }
     auto keep_alive = std::make_shared<std::vector<BlockRef>>(std::move(block_cache));
     GpuContext *gpu_raw = gpu.get();
+    if (trace_)
+      fprintf(stderr, "[pegaflow_b200] load %s: build_tasks %.2f ms\n", instance_id.c_str(),
+              std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t_begin).count());
     gpu->load_worker->submit([=](TransferBackend &backend, cudaStream_t stream) {
       const auto t0 = std::chrono::steady_clock::now();
       try {

@@ -39,18 +39,25 @@ struct Segment {
   char *host = nullptr;
   uint64_t device = 0;
   size_t size = 0;
-  std::shared_ptr<PinnedAllocation> allocation;
 };
 
-// One slot of a block: one segment (contiguous / page) or two (K and V).
+// Keeps pool memory alive: a pinned allocation, or the set of allocations of one save call.
+using Owner = std::shared_ptr<const void>;
+
+// One slot of a block: one segment (contiguous / page) or two (K and V).  The reference ties
+// every segment to its allocation (`Arc<PinnedAllocation>` per Segment, block.rs:64-71); a layer
+// batch allocation is shared by all blocks of the save, so here the owner is kept once per save
+// where possible (on the sealed block, else on the slot) instead of twice per slot.
 struct RawBlock {
   Segment seg[2];
   int n_segments = 0;
+  Owner owner;  // null when the enclosing SealedBlock / RawSaveBatch owns the memory
   size_t total_size() const { return seg[0].size + (n_segments > 1 ? seg[1].size : 0); }
 };
 
 struct SealedBlock {
   std::vector<RawBlock> slots;
+  Owner owner;  // covers every slot whose own owner is null
   size_t footprint = 0;
 };
 using BlockRef = std::shared_ptr<SealedBlock>;
@@ -73,6 +80,7 @@ std::string group_hash(const std::string &hash, uint32_t group);
 class ReadCache {
  public:
   bool contains(const BlockKey &key);
+  void contains_many(const std::string &ns, const std::vector<std::string> &hashes, std::vector<char> *out);
   BlockRef get(const BlockKey &key, bool touch);
   // Returns false (and drops `block`) when the key is already resident.
   bool insert(const BlockKey &key, BlockRef block);
@@ -197,10 +205,13 @@ struct Completion {
   void signal(bool ok, const std::string &msg);
 };
 
+// A list of block hashes, shared between the layers of a save that carry the same list.
+using HashList = std::shared_ptr<const std::vector<std::string>>;
+
 struct LayerSaveIn {
   std::string layer_name;
   std::vector<size_t> block_ids;
-  std::vector<std::string> block_hashes;
+  HashList block_hashes;
 };
 
 struct LeaseLoadIn {
@@ -248,12 +259,13 @@ class Engine {
   struct RawSaveLayer {
     size_t slot_id;
     std::vector<RawBlock> blocks;
-    std::vector<std::string> hashes;  // already group-encoded
+    std::shared_ptr<const std::vector<std::string>> hashes;  // already group-encoded
   };
   struct RawSaveBatch {
     std::string ns;
     size_t total_slots;
     std::vector<RawSaveLayer> layers;
+    Owner owner;  // all pool allocations of the save call (null when the slots carry their own)
   };
   struct Inflight {
     size_t total_slots;
@@ -282,7 +294,7 @@ class Engine {
   void send_raw_insert(RawSaveBatch batch);
   void insert_loop();
   void process_insert(RawSaveBatch &batch);
-  void insert_slot(const BlockKey &key, size_t slot, RawBlock block, size_t total_slots);
+  void insert_slot(const BlockKey &key, size_t slot, RawBlock block, size_t total_slots, const Owner &batch_owner);
   std::vector<BlockRef> consume_lease(const std::string &instance_id, const std::array<uint8_t, 16> &lease);
   void sweep_leases();
 
@@ -302,6 +314,7 @@ class Engine {
   std::deque<RawSaveBatch> insert_queue_;
   size_t insert_pending_ = 0;  // queued + in progress + async saves not yet handed over
   bool insert_stop_ = false;
+  bool trace_ = false;       // PEGAFLOW_B200_TRACE=1: per-save phase timings on stderr
   std::string async_error_;  // first failure of an asynchronous save since the last flush
   std::unordered_map<BlockKey, Inflight, BlockKeyHash> inflight_;
 
