@@ -181,6 +181,30 @@ int pf_backend_peer_copy(pf_backend *backend, const pf_device_layout *src, const
 /* Make `peer_device`'s memory addressable from `device_id` (cudaDeviceEnablePeerAccess). */
 int pf_enable_peer_access(int device_id, int peer_device);
 
+/* Allocation-free save of a small batch of blocks.  It has no counterpart in the reference.
+ *
+ * Meant for callers that cannot allocate device memory when they need blocks copied out: a
+ * serving process whose free HBM has all gone to the KV cache, a thread that cannot afford the
+ * device-wide synchronisation of cudaMalloc/cudaFree, or code running while a stream is being
+ * captured elsewhere in the process.  Blocks block_ids[0..n_blocks) of `layout` (memory of
+ * `device_id`) are gathered into a staging area that is part of the library image and copied to
+ * host_dst, which must be page-locked for the copy to be asynchronous: range 0 of every block
+ * back to back, then range 1 of every block (the image pf_backend_save_layers writes for one
+ * dense host run per range).  Everything is enqueued on `stream`; nothing is synchronised.
+ *
+ * No cudaMalloc, cudaFree, stream, event or other allocating call is made.  Limits: at most
+ * PF_NOALLOC_MAX_BLOCKS blocks and PF_NOALLOC_MAX_PAYLOAD_BYTES bytes per call, otherwise
+ * PF_INVALID_ARGUMENT.  The staging area (PF_NOALLOC_MAX_PAYLOAD_BYTES plus 4 bytes per block
+ * id) is static device memory: each GPU that loads the library holds it until the process
+ * ends.  The first call on a device looks the area's address up (cudaGetSymbolAddress with
+ * that device current), so make that first call before any stream capture starts.  All calls
+ * on one device share the area and it keeps the previous call's bytes; nothing in it needs
+ * clearing between calls, but two calls whose GPU work overlaps (different streams) race. */
+#define PF_NOALLOC_MAX_PAYLOAD_BYTES (8u << 20)
+#define PF_NOALLOC_MAX_BLOCKS 16384
+int pf_save_blocks_noalloc(int device_id, const pf_device_layout *layout, const uint32_t *block_ids,
+                           size_t n_blocks, void *host_dst, size_t host_dst_bytes, void *stream);
+
 /* Counters of one backend since creation (what was launched, which route bytes took). */
 typedef struct pf_backend_stats {
   uint64_t kernel_launches;

@@ -5,5 +5,6 @@ The package is a thin Python layer over ``libpegaflow_b200.so`` (C ABI in
 CPU fallback.
 """
 from ._native import PegaFlowError, PegaflowInternal, PegaflowInvalidArgument  # noqa: F401
-from .backend import HostRun, LayerXfer, PinnedPool, TransferBackend, enable_peer_access  # noqa: F401
+from .backend import (HostRun, LayerXfer, PinnedPool, TransferBackend, enable_peer_access,  # noqa: F401
+                      save_blocks_noalloc)
 from .engine import Block, Completion, PegaEngine, PyLoadState  # noqa: F401

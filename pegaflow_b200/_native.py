@@ -22,6 +22,8 @@ STATUS_NAMES = {1: "InstanceMissing", 2: "WorkerMissing", 3: "InvalidArgument", 
                 6: "Poisoned", 7: "TopologyMismatch"}
 PF_NO_BLOCK = C.c_size_t(-1).value
 ROUTE_AUTO, ROUTE_STAGED, ROUTE_ZEROCOPY = 0, 1, 2
+NOALLOC_MAX_PAYLOAD_BYTES = 8 << 20
+NOALLOC_MAX_BLOCKS = 16384
 
 sz = C.c_size_t
 u64 = C.c_uint64
@@ -124,6 +126,7 @@ _sig("pf_backend_save_layers", C.c_int, vp, P(LayerXfer), sz, vp, P(vp))
 _sig("pf_backend_load_layers", C.c_int, vp, P(LayerXfer), sz, vp, P(vp))
 _sig("pf_backend_peer_copy", C.c_int, vp, P(DeviceLayout), P(u32), P(DeviceLayout), P(u32), sz, vp)
 _sig("pf_enable_peer_access", C.c_int, C.c_int, C.c_int)
+_sig("pf_save_blocks_noalloc", C.c_int, C.c_int, P(DeviceLayout), P(u32), sz, vp, sz, vp)
 _sig("pf_backend_get_stats", C.c_int, vp, P(BackendStats))
 _sig("pf_pool_new", C.c_int, sz, P(PoolConfig), P(vp))
 _sig("pf_pool_free", None, vp)

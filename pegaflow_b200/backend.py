@@ -152,3 +152,20 @@ class TransferBackend:
 
 def enable_peer_access(device_id: int, peer_device: int):
     N.check(N.lib.pf_enable_peer_access(device_id, peer_device))
+
+
+def save_blocks_noalloc(device_id: int, layout, block_ids, host_dst: int, host_dst_bytes: int, stream: int = 0):
+    """Allocation-free save of a small batch (``pf_save_blocks_noalloc``).
+
+    For callers that must not allocate device memory at that moment (no free HBM left, no
+    tolerance for cudaMalloc's device-wide synchronisation, a stream capture in progress).  The
+    staging area lives inside the library image; at most ``NOALLOC_MAX_BLOCKS`` blocks and
+    ``NOALLOC_MAX_PAYLOAD_BYTES`` bytes per call.  ``layout`` is (data_ptr, block_stride_bytes,
+    kv_stride_bytes, range_bytes, n_ranges); ``host_dst`` should be page-locked.  Calls on one device
+    share the staging area: do not let their GPU work overlap.  Make the first call on a device
+    before any stream capture."""
+    n = len(block_ids)
+    ids = (C.c_uint32 * max(1, n))(*[int(b) for b in block_ids])
+    lay = N.DeviceLayout(*layout)
+    N.check(N.lib.pf_save_blocks_noalloc(device_id, C.byref(lay), ids, n, C.c_void_p(host_dst), host_dst_bytes,
+                                         C.c_void_p(stream or None)))

@@ -17,6 +17,7 @@
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 namespace pf {
 
@@ -945,3 +946,91 @@ void enable_peer_access(int device, int peer) {
 }
 
 }  // namespace pf
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free save of a few blocks.
+//
+// Some callers of this library must not allocate device memory at the moment they want KV
+// blocks copied out: a serving process that has handed all free HBM to its KV cache (a late
+// cudaMalloc simply fails there), a latency-critical scheduler thread (cudaMalloc and cudaFree
+// synchronise the whole device), or code that runs while another thread is capturing a stream.
+// For them the gather -> staging -> DMA sequence of the staged route is offered with the
+// staging area (and the block-id table) inside the library image instead of on the heap.
+//
+// The array below is file-scope device memory: every GPU that loads the library carries it
+// until the process exits.  In host code its name is only a handle for the runtime, not an
+// address a kernel could use, so each device's address is looked up once with
+// cudaGetSymbolAddress while that device is current.
+namespace pf {
+namespace {
+constexpr size_t kNoAllocPayload = PF_NOALLOC_MAX_PAYLOAD_BYTES;
+constexpr size_t kNoAllocIds = (size_t)PF_NOALLOC_MAX_BLOCKS * sizeof(uint32_t);
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocPayload + kNoAllocIds];
+
+struct NoAllocDevice {
+  unsigned char *scratch = nullptr;  // device address of g_noalloc_scratch on this GPU
+  int sm_count = 0;
+};
+std::mutex g_noalloc_mu;
+NoAllocDevice g_noalloc_devices[64];
+
+// First use on a device: resolve the symbol with that device current.
+const NoAllocDevice &noalloc_device(int device) {
+  if (device < 0 || device >= 64) throw Error::invalid(strf("device %d out of range", device));
+  std::lock_guard<std::mutex> g(g_noalloc_mu);
+  NoAllocDevice &d = g_noalloc_devices[device];
+  if (!d.scratch) {
+    void *ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+    if (e != cudaSuccess || !ptr)
+      throw Error::cuda_init(strf("cudaGetSymbolAddress for the built-in staging area failed on device %d: %s", device,
+                                  cudaGetErrorString(e)));
+    int sms = 0;
+    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    if (e != cudaSuccess || sms <= 0) throw Error::cuda_init("cudaDeviceGetAttribute(multiProcessorCount) failed");
+    d.sm_count = sms;
+    d.scratch = static_cast<unsigned char *>(ptr);
+  }
+  return d;
+}
+}  // namespace
+}  // namespace pf
+
+extern "C" int pf_save_blocks_noalloc(int device_id, const pf_device_layout *layout, const uint32_t *block_ids,
+                                      size_t n_blocks, void *host_dst, size_t host_dst_bytes, void *stream) {
+  using namespace pf;
+  return guarded([&] {
+    if (!layout || (!block_ids && n_blocks) || (!host_dst && n_blocks)) throw Error::invalid("null argument");
+    if (layout->n_ranges < 1 || layout->n_ranges > 2 || layout->range_bytes == 0)
+      throw Error::invalid("unsupported block geometry");
+    if (n_blocks == 0) return;
+    if (n_blocks > PF_NOALLOC_MAX_BLOCKS)
+      throw Error::invalid(strf("%zu blocks exceed the built-in staging area's limit of %d blocks; use "
+                                "pf_backend_save_layers for larger batches",
+                                n_blocks, PF_NOALLOC_MAX_BLOCKS));
+    const size_t per_range = n_blocks * layout->range_bytes;
+    const size_t total = per_range * layout->n_ranges;
+    if (layout->range_bytes > 0xFFFFFFFFull || total > kNoAllocPayload)
+      throw Error::invalid(strf("%zu bytes exceed the built-in staging area of %zu bytes; use pf_backend_save_layers "
+                                "for larger batches",
+                                total, kNoAllocPayload));
+    if (host_dst_bytes < total)
+      throw Error::invalid(strf("destination holds %zu bytes, the blocks need %zu", host_dst_bytes, total));
+    DeviceGuard on_device(device_id);
+    const NoAllocDevice &dev = noalloc_device(device_id);
+    cudaStream_t s = (cudaStream_t)stream;
+    uint32_t *ids_dev = reinterpret_cast<uint32_t *>(dev.scratch + kNoAllocPayload);
+    PF_CUDA(cudaMemcpyAsync(ids_dev, block_ids, n_blocks * sizeof(uint32_t), cudaMemcpyHostToDevice, s));
+    for (uint32_t r = 0; r < layout->n_ranges; ++r) {
+      const Side src{layout->data_ptr + (uint64_t)r * layout->kv_stride_bytes, layout->block_stride_bytes, ids_dev,
+                     nullptr};
+      const Side dst{(uint64_t)(uintptr_t)(dev.scratch + r * per_range), layout->range_bytes, nullptr, nullptr};
+      const uint64_t chunks = (uint64_t)n_blocks * ((layout->range_bytes + kPackChunk - 1) / kPackChunk);
+      const int grid = (int)std::min<uint64_t>(chunks, (uint64_t)dev.sm_count * 8);
+      copy_items_ldst<0><<<grid, kLdstThreads, 0, s>>>(src, dst, (uint32_t)n_blocks, (uint32_t)layout->range_bytes,
+                                                       kPackChunk, nullptr);
+      PF_CUDA(cudaGetLastError());
+    }
+    PF_CUDA(cudaMemcpyAsync(host_dst, dev.scratch, total, cudaMemcpyDeviceToHost, s));
+  });
+}
