@@ -113,7 +113,10 @@ def dist_setup(n_gpus):
     torch.cuda.set_device(local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        import datetime
+
+        # a rank that fails must not leave the others waiting for long
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=180))
     return rank, world, local
 
 
@@ -684,11 +687,19 @@ def main():
     rank, world, local = dist_setup(args.gpus)
     try:
         run_b200(args, rank, world, local)
-    finally:
-        if world > 1:
-            import torch.distributed as dist
+    except BaseException:
+        # Leave at once: a clean process-group shutdown would wait for the other ranks, and the
+        # launcher only stops them when it sees this rank die.
+        import traceback
 
-            dist.destroy_process_group()
+        traceback.print_exc()
+        sys.stderr.flush()
+        sys.stdout.flush()
+        os._exit(1)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

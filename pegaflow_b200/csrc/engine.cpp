@@ -181,6 +181,9 @@ void GpuWorker::loop(int device, int numa_node, pf_backend_config cfg, std::prom
   std::unique_ptr<TransferBackend> backend;
   cudaStream_t stream = nullptr;
   try {
+    // This thread works on one device for its whole life (gpu_worker.rs:278-283).
+    if (cudaSetDevice(device) != cudaSuccess)
+      throw Error::cuda_init(strf("Failed to create CUDA context: cudaSetDevice(%d) failed", device));
     backend = std::make_unique<TransferBackend>(device, &cfg);
     if (cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking) != cudaSuccess)
       throw Error::cuda_init("Failed to create CUDA stream");
