@@ -107,8 +107,11 @@ class TransferBackend:
         arr = (N.LayerXfer * max(1, len(layers)))()
         keep = []
         for i, L in enumerate(layers):
-            ids = (C.c_uint32 * max(1, len(L.block_ids)))(*[int(b) for b in L.block_ids])
-            keep.append(ids)
+            import numpy as np
+
+            ids_np = np.ascontiguousarray(L.block_ids, dtype=np.uint32)
+            ids = ids_np.ctypes.data_as(C.POINTER(C.c_uint32))
+            keep.append(ids_np)
             a = arr[i]
             a.data_ptr, a.block_stride_bytes, a.kv_stride_bytes = L.data_ptr, L.block_stride_bytes, L.kv_stride_bytes
             a.range_bytes, a.n_ranges, a.n_blocks = L.range_bytes, L.n_ranges, len(L.block_ids)
@@ -138,10 +141,16 @@ class TransferBackend:
 
     def peer_copy(self, src_layout, src_ids, dst_layout, dst_ids, stream: int = 0):
         """layouts: (data_ptr, block_stride_bytes, kv_stride_bytes, range_bytes, n_ranges)."""
+        import numpy as np
+
         n = len(src_ids)
-        U = C.c_uint32 * max(1, n)
+        if len(dst_ids) != n:
+            raise N.PegaflowInvalidArgument(3, "invalid argument: peer copy needs one destination per source block")
+        sa = np.ascontiguousarray(src_ids, dtype=np.uint32)
+        da = np.ascontiguousarray(dst_ids, dtype=np.uint32)
         s, d = N.DeviceLayout(*src_layout), N.DeviceLayout(*dst_layout)
-        N.check(N.lib.pf_backend_peer_copy(self._h, C.byref(s), U(*src_ids), C.byref(d), U(*dst_ids), n,
+        U = C.POINTER(C.c_uint32)
+        N.check(N.lib.pf_backend_peer_copy(self._h, C.byref(s), sa.ctypes.data_as(U), C.byref(d), da.ctypes.data_as(U), n,
                                            C.c_void_p(stream or None)))
 
     def stats(self) -> dict:

@@ -337,6 +337,7 @@ TransferBackend::TransferBackend(int device, const pf_backend_config *config) : 
   sm_count_ = prop.multiProcessorCount;
   if (cfg_.pack_ctas <= 0) cfg_.pack_ctas = sm_count_ * 8;
   if (const char *e = getenv("PF_EXP_PACK_HINTS")) pack_hints_ = atoi(e) != 0;
+  if (const char *e = getenv("PF_EXP_PEER_LDST")) peer_ldst_ = atoi(e) != 0;
   aux_.resize(cfg_.copy_streams, nullptr);
   aux_join_.resize(cfg_.copy_streams, nullptr);
   aux_layer_dirty_.assign(cfg_.copy_streams, 0);
@@ -576,8 +577,9 @@ void TransferBackend::launch_link(const Side &src, const Side &dst, size_t n_ite
   // Bulk async copies need 16-byte aligned addresses and sizes.  Affine sides are checked here;
   // whoever fills an address table clears tables_aligned_ when an entry is not aligned.
   auto aligned16 = [](const Side &x) { return x.table != nullptr || ((x.base | x.stride) & 15ull) == 0; };
-  const bool tma_ok = aligned16(src) && aligned16(dst) && (item_bytes & 15u) == 0 && tables_aligned_;
-  int ctas = cfg_.link_ctas > 0 ? cfg_.link_ctas : (peer ? sm_count_ : 16);
+  bool tma_ok = aligned16(src) && aligned16(dst) && (item_bytes & 15u) == 0 && tables_aligned_;
+  if (peer && peer_ldst_) tma_ok = false;
+  int ctas = cfg_.link_ctas > 0 ? cfg_.link_ctas : (peer ? 2 * sm_count_ : 16);
   cudaEvent_t t0;
   time_begin(s, &t0);
   if (tma_ok) {
@@ -588,7 +590,7 @@ void TransferBackend::launch_link(const Side &src, const Side &dst, size_t n_ite
                                                              status_dev_);
   } else {
     const uint64_t chunks = (uint64_t)n_items * ((item_bytes + kPackChunk - 1) / kPackChunk);
-    const int grid = (int)std::min<uint64_t>(chunks, (uint64_t)std::max(ctas, sm_count_));
+    const int grid = (int)std::min<uint64_t>(chunks, (uint64_t)(peer ? std::max(ctas, cfg_.pack_ctas) : std::max(ctas, sm_count_)));
     copy_items_ldst<0><<<grid, kLdstThreads, 0, s>>>(src, dst, (uint32_t)n_items, (uint32_t)item_bytes, kPackChunk,
                                                      nullptr);
   }
