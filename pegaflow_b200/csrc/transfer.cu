@@ -36,6 +36,7 @@ constexpr uint32_t kPackChunk = 16384;   // bytes one CTA iteration of the ld/st
 constexpr int kStages = 4;               // ring depth of the TMA kernels
 constexpr uint32_t kStageBytes = 32768;  // bytes per ring stage
 constexpr unsigned kStatusWaitExpired = 0x57A17u;
+constexpr size_t kSmallTaskBytes = 2u << 20;  // multi-layer tasks up to this size take one launch
 
 __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t t;
@@ -741,6 +742,49 @@ void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, 
       for (size_t li = 0; li < n_layers; ++li)
         if (layer_done[li]) PF_CUDA(cudaEventRecord((cudaEvent_t)layer_done[li], stream));
     return;
+  }
+  // ---- small tasks (a few blocks of every layer, e.g. the tail blocks saved while decoding):
+  // launches, not bytes, are what they cost.  Everything goes into one descriptor-driven
+  // zero-copy launch, whatever the number of layers.
+  {
+    size_t total_bytes = 0, total_items = 0;
+    for (size_t li = 0; li < n_layers; ++li) {
+      total_bytes += layers[li].n_blocks * layers[li].range_bytes * layers[li].n_ranges;
+      total_items += layers[li].n_blocks * layers[li].n_ranges;
+    }
+    if (cfg_.route != PF_ROUTE_STAGED && n_layers > 1 && total_bytes <= kSmallTaskBytes && total_items <= 65536) {
+      const size_t tb = align_up(total_items * 3 * sizeof(uint64_t), 256);
+      const size_t tbase = meta_alloc(tb);
+      uint64_t *triples = reinterpret_cast<uint64_t *>(meta_host_ + tbase);
+      bool aligned = true;
+      size_t q = 0;
+      for (size_t li = 0; li < n_layers; ++li) {
+        const pf_layer_xfer &L = layers[li];
+        for (uint32_t r = 0; r < (L.n_blocks ? L.n_ranges : 0); ++r)
+          for (size_t j = 0; j < L.n_runs[r]; ++j) {
+            const pf_host_run &run = L.runs[r][j];
+            for (size_t i = 0; i < run.n_blocks; ++i, ++q) {
+              const uint64_t dev = L.data_ptr + (uint64_t)L.block_ids[run.first_block + i] * L.block_stride_bytes +
+                                   (uint64_t)r * L.kv_stride_bytes;
+              const uint64_t host = run.host_device + (uint64_t)i * run.stride_bytes;
+              triples[3 * q] = host_is_src ? dev : host;
+              triples[3 * q + 1] = host_is_src ? host : dev;
+              triples[3 * q + 2] = L.range_bytes;
+              if ((dev | host | L.range_bytes) & 15ull) aligned = false;
+            }
+          }
+      }
+      meta_upload(tbase, tb, stream);
+      launch_descs(reinterpret_cast<const uint64_t *>(meta_dev_ + tbase), q, aligned, stream);
+      stats_.bytes_zero_copy += total_bytes;
+      if (layer_done)
+        for (size_t li = 0; li < n_layers; ++li)
+          if (layer_done[li]) PF_CUDA(cudaEventRecord((cudaEvent_t)layer_done[li], stream));
+      cudaEvent_t ev = take_event();
+      PF_CUDA(cudaEventRecord(ev, stream));
+      meta_inflight_.push_back({tbase, tbase + tb, ev});
+      return;
+    }
   }
   const size_t base = meta_alloc(meta_bytes);
   tables_aligned_ = true;

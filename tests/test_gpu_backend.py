@@ -289,3 +289,51 @@ def test_pool_allocator_rules(env, kats):
     with pytest.raises(pf.PegaflowInternal, match="exhausted"):
         p.alloc(2 << 20)
     p.close()
+
+
+def test_small_multi_layer_task_takes_one_launch(env):
+    """A few blocks of many layers (the tail blocks saved while decoding) cost one kernel launch in
+    each direction, and the per-layer events still fire."""
+    pf, mem, pool, torch = env
+    rng = np.random.default_rng(77)
+    n_layers, num_blocks, seg = 12, 64, 8192
+    be = pf.TransferBackend(0)
+    devs, inits, layers = [], [], []
+    ids = [5, 63, 1]
+    slab, slab_dev, handle = pool.alloc(n_layers * 2 * len(ids) * seg)
+    for li in range(n_layers):
+        dev = mem.alloc(2 * num_blocks * seg)
+        init = rng.integers(0, 256, size=2 * num_blocks * seg, dtype=np.uint8)
+        mem.write(dev, init)
+        off = li * 2 * len(ids) * seg
+        runs = [[pf.HostRun(0, 3, slab + off + r * 3 * seg, slab_dev + off + r * 3 * seg, seg)] for r in range(2)]
+        layers.append(pf.LayerXfer(dev.data_ptr(), seg, num_blocks * seg, seg, 2, ids, runs))
+        devs.append(dev)
+        inits.append(init)
+    events = [make_event(torch) for _ in range(n_layers)]
+    before = be.stats()["kernel_launches"]
+    be.save_layers(layers, 0, [e.cuda_event for e in events])
+    events[-1].synchronize()
+    assert be.stats()["kernel_launches"] == before + 1
+    hv = host_view(slab, n_layers * 2 * len(ids) * seg)
+    for li in range(n_layers):
+        for r in range(2):
+            for i, b in enumerate(ids):
+                o = li * 2 * 3 * seg + r * 3 * seg + i * seg
+                src = r * num_blocks * seg + b * seg
+                assert np.array_equal(hv[o:o + seg], inits[li][src:src + seg])
+    for dev in devs:
+        mem.zero(dev)
+    be.load_layers(layers, 0, None)
+    mem.sync()
+    assert be.stats()["kernel_launches"] == before + 2
+    for li in range(n_layers):
+        want = np.zeros(2 * num_blocks * seg, dtype=np.uint8)
+        for r in range(2):
+            for b in ids:
+                o = r * num_blocks * seg + b * seg
+                want[o:o + seg] = inits[li][o:o + seg]
+        assert np.array_equal(mem.read(devs[li]), want)
+    assert be.stats()["device_status"] == 0
+    be.close()
+    pool.release(handle)
