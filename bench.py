@@ -41,6 +41,8 @@ def workloads():
     # segment); 1 = one segment per block with page-first host pages (one page per block holding every layer).
     return {
         "llama3.1-8b": dict(layers=32, seg_bytes=16 * 8 * 128 * 2, gpu_blocks=8192, requests=8, blocks=640, segments=2),
+        # Qwen3-0.6B round trip: 256 GPU blocks, 64 saved and loaded back into 64 other ids
+        "qwen3-0.6b": dict(layers=28, seg_bytes=16 * 8 * 128 * 2, gpu_blocks=256, requests=1, blocks=64, segments=2),
         "small": dict(layers=4, seg_bytes=16 * 8 * 128 * 2, gpu_blocks=2048, requests=2, blocks=256, segments=2),
         # one rank of Llama-3.1-70B TP=8: 1 KV head per rank -> 4 KiB segments, 4 prompts of 32768 tokens
         "llama70b-tp8-rank": dict(layers=80, seg_bytes=16 * 1 * 128 * 2, gpu_blocks=16384, requests=4, blocks=2048,

@@ -36,7 +36,8 @@ constexpr uint32_t kPackChunk = 16384;   // bytes one CTA iteration of the ld/st
 constexpr int kStages = 4;               // ring depth of the TMA kernels
 constexpr uint32_t kStageBytes = 32768;  // bytes per ring stage
 constexpr unsigned kStatusWaitExpired = 0x57A17u;
-constexpr size_t kSmallTaskBytes = 2u << 20;  // multi-layer tasks up to this size take one launch
+constexpr size_t kSmallTaskBytes = 2u << 20;
+constexpr size_t kMinEventGroupBytes = 8u << 20;  // a layer with fewer staged bytes shares the DMA of the next ones  // multi-layer tasks up to this size take one launch
 
 __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t t;
@@ -634,54 +635,88 @@ void TransferBackend::join_copy_streams(cudaStream_t target, std::vector<char> &
   }
 }
 
-// Moves run.n_blocks items (`item_bytes` each) between the device side and a host run through
-// the staging ring.  `dev_side.ids` / `.table` already point at the run's first item.
+// Adds run.n_blocks items (`item_bytes` each) to the staged route.  `dev_side.ids` / `.table`
+// already point at the run's first item.  A run is cut into equal chunks that fit a staging
+// slot; chunks whose host bytes follow each other without a gap share a slot and one DMA (the
+// group), so many small (layer, K-or-V) runs in neighbouring pool allocations still reach the
+// copy engine as one large transfer.  Nothing is enqueued until the group is flushed.
 void TransferBackend::staged_run(const Side &dev_side, const pf_host_run &run, size_t item_bytes, bool host_is_src,
                                  cudaStream_t stream) {
-  ensure_staging();
   const size_t cap = cfg_.staging_slot_bytes / item_bytes;
-  // Equal chunks: a run that needs k slots is cut into k pieces of (almost) the same size.
   const size_t n_chunks = (run.n_blocks + cap - 1) / cap;
   const size_t per_chunk = (run.n_blocks + n_chunks - 1) / n_chunks;
   char *host = static_cast<char *>(run.host);
-  const bool dense = run.stride_bytes == item_bytes;
+  const bool dense = run.stride_bytes == item_bytes || run.n_blocks == 1;
   for (size_t b0 = 0; b0 < run.n_blocks; b0 += per_chunk) {
     const size_t nb = std::min(per_chunk, run.n_blocks - b0);
-    Side d = dev_side;
-    if (d.table) d.table += b0;
-    if (d.ids) d.ids += b0;
-    if (!d.table && !d.ids) d.base += (uint64_t)b0 * d.stride;
-    Slot &slot = next_slot();
-    const Side st{(uint64_t)(uintptr_t)slot.ptr, item_bytes, nullptr, nullptr};
-    char *h = host + b0 * run.stride_bytes;
-    cudaStream_t copy = aux_[next_aux()];
-    if (!host_is_src) {
-      if (slot.used) PF_CUDA(cudaStreamWaitEvent(stream, slot.drained, 0));
-      launch_pack(d, st, nb, item_bytes, stream, true);
-      PF_CUDA(cudaEventRecord(slot.filled, stream));
-      PF_CUDA(cudaStreamWaitEvent(copy, slot.filled, 0));
-      if (dense)
-        PF_CUDA(cudaMemcpyAsync(h, slot.ptr, nb * item_bytes, cudaMemcpyDeviceToHost, copy));
-      else
-        PF_CUDA(cudaMemcpy2DAsync(h, run.stride_bytes, slot.ptr, item_bytes, item_bytes, nb, cudaMemcpyDeviceToHost,
-                                  copy));
-      PF_CUDA(cudaEventRecord(slot.drained, copy));
-    } else {
-      if (slot.used) PF_CUDA(cudaStreamWaitEvent(copy, slot.drained, 0));
-      if (dense)
-        PF_CUDA(cudaMemcpyAsync(slot.ptr, h, nb * item_bytes, cudaMemcpyHostToDevice, copy));
-      else
-        PF_CUDA(cudaMemcpy2DAsync(slot.ptr, item_bytes, h, run.stride_bytes, item_bytes, nb, cudaMemcpyHostToDevice,
-                                  copy));
-      PF_CUDA(cudaEventRecord(slot.filled, copy));
-      PF_CUDA(cudaStreamWaitEvent(stream, slot.filled, 0));
-      launch_pack(st, d, nb, item_bytes, stream, false);
-      PF_CUDA(cudaEventRecord(slot.drained, stream));
+    StagedUnit u;
+    u.dev = dev_side;
+    if (u.dev.table) u.dev.table += b0;
+    if (u.dev.ids) u.dev.ids += b0;
+    if (!u.dev.table && !u.dev.ids) u.dev.base += (uint64_t)b0 * u.dev.stride;
+    u.n_items = nb;
+    u.item_bytes = item_bytes;
+    u.host = host + b0 * run.stride_bytes;
+    u.host_stride = run.stride_bytes;
+    const size_t bytes = nb * item_bytes;
+    const bool joins = !group_.empty() && group_dense_ && dense && group_host_is_src_ == host_is_src &&
+                       group_stream_ == stream && group_host_end_ == u.host &&
+                       group_bytes_ + bytes <= cfg_.staging_slot_bytes && (group_bytes_ & 15u) == 0;
+    if (!joins) {
+      flush_group();
+      group_dense_ = dense;
+      group_host_is_src_ = host_is_src;
+      group_stream_ = stream;
+      group_host_begin_ = u.host;
+      group_bytes_ = 0;
     }
-    slot.used = true;
-    ++stats_.dma_copies;
-    stats_.bytes_staged += nb * item_bytes;
+    u.slot_offset = group_bytes_;
+    group_bytes_ += bytes;
+    group_host_end_ = u.host + bytes;
+    group_.push_back(u);
   }
+}
+
+// Enqueues the open group: gather kernels then one DMA out (save), or one DMA in then scatter
+// kernels (load).
+void TransferBackend::flush_group() {
+  if (group_.empty()) return;
+  ensure_staging();
+  cudaStream_t stream = group_stream_;
+  Slot &slot = next_slot();
+  cudaStream_t copy = aux_[next_aux()];
+  const StagedUnit &first = group_.front();
+  auto slot_side = [&](const StagedUnit &u) {
+    return Side{(uint64_t)(uintptr_t)(slot.ptr + u.slot_offset), u.item_bytes, nullptr, nullptr};
+  };
+  if (!group_host_is_src_) {
+    if (slot.used) PF_CUDA(cudaStreamWaitEvent(stream, slot.drained, 0));
+    for (const StagedUnit &u : group_) launch_pack(u.dev, slot_side(u), u.n_items, u.item_bytes, stream, true);
+    PF_CUDA(cudaEventRecord(slot.filled, stream));
+    PF_CUDA(cudaStreamWaitEvent(copy, slot.filled, 0));
+    if (group_dense_)
+      PF_CUDA(cudaMemcpyAsync(group_host_begin_, slot.ptr, group_bytes_, cudaMemcpyDeviceToHost, copy));
+    else
+      PF_CUDA(cudaMemcpy2DAsync(first.host, first.host_stride, slot.ptr, first.item_bytes, first.item_bytes,
+                                first.n_items, cudaMemcpyDeviceToHost, copy));
+    PF_CUDA(cudaEventRecord(slot.drained, copy));
+  } else {
+    if (slot.used) PF_CUDA(cudaStreamWaitEvent(copy, slot.drained, 0));
+    if (group_dense_)
+      PF_CUDA(cudaMemcpyAsync(slot.ptr, group_host_begin_, group_bytes_, cudaMemcpyHostToDevice, copy));
+    else
+      PF_CUDA(cudaMemcpy2DAsync(slot.ptr, first.item_bytes, first.host, first.host_stride, first.item_bytes,
+                                first.n_items, cudaMemcpyHostToDevice, copy));
+    PF_CUDA(cudaEventRecord(slot.filled, copy));
+    PF_CUDA(cudaStreamWaitEvent(stream, slot.filled, 0));
+    for (const StagedUnit &u : group_) launch_pack(slot_side(u), u.dev, u.n_items, u.item_bytes, stream, false);
+    PF_CUDA(cudaEventRecord(slot.drained, stream));
+  }
+  slot.used = true;
+  ++stats_.dma_copies;
+  stats_.bytes_staged += group_bytes_;
+  group_.clear();
+  group_bytes_ = 0;
 }
 
 void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, bool host_is_src,
@@ -812,10 +847,15 @@ void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, 
 
   // ---- enqueue, layer by layer.
   std::fill(aux_task_dirty_.begin(), aux_task_dirty_.end(), 0);
+  // Events of layers whose bytes are still in an open (small) group wait here until it is flushed.
+  std::vector<cudaEvent_t> deferred;
+  bool layer_stream = false;
   for (size_t li = 0; li < n_layers; ++li) {
     const pf_layer_xfer &L = layers[li];
-    bool layer_stream = false;
-    std::fill(aux_layer_dirty_.begin(), aux_layer_dirty_.end(), 0);
+    if (deferred.empty()) {
+      layer_stream = false;
+      std::fill(aux_layer_dirty_.begin(), aux_layer_dirty_.end(), 0);
+    }
     if (L.n_blocks) {
       const uint32_t *ids_dev = reinterpret_cast<const uint32_t *>(meta_dev_ + base + ids_off[li]);
       for (uint32_t r = 0; r < L.n_ranges; ++r) {
@@ -856,20 +896,28 @@ void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, 
       }
     }
     cudaEvent_t done = layer_done ? (cudaEvent_t)layer_done[li] : nullptr;
-    if (done) {
-      // A saved layer is complete when its DMAs (copy streams) and its zero-copy kernels
-      // (caller's stream) are; a loaded layer always ends with a scatter on the caller's stream.
+    if (done) deferred.push_back(done);
+    // A layer's event should not wait for later layers - unless its bytes are so few that a DMA
+    // of its own would waste the link: then it shares the group, and the event, of its successors.
+    const bool keep_open = !group_.empty() && group_bytes_ < kMinEventGroupBytes && li + 1 < n_layers;
+    if (!deferred.empty() && !keep_open) {
+      flush_group();
+      // Saved layers are complete when their DMAs (copy streams) and zero-copy kernels (caller's
+      // stream) are; loaded layers always end with a scatter on the caller's stream.
       const bool layer_aux = std::find(aux_layer_dirty_.begin(), aux_layer_dirty_.end(), 1) != aux_layer_dirty_.end();
+      cudaStream_t where = stream;
       if (!host_is_src && layer_aux && !layer_stream) {
-        // Signal from the copy stream that took the layer's last DMA, after the others.
+        // Signal from the copy stream that took the last DMA, after the others.
         join_copy_streams(aux_[aux_last_], aux_layer_dirty_, aux_last_);
-        PF_CUDA(cudaEventRecord(done, aux_[aux_last_]));
-      } else {
-        if (!host_is_src && layer_aux) join_copy_streams(stream, aux_layer_dirty_, -1);
-        PF_CUDA(cudaEventRecord(done, stream));
+        where = aux_[aux_last_];
+      } else if (!host_is_src && layer_aux) {
+        join_copy_streams(stream, aux_layer_dirty_, -1);
       }
+      for (cudaEvent_t ev : deferred) PF_CUDA(cudaEventRecord(ev, where));
+      deferred.clear();
     }
   }
+  flush_group();
   if (!host_is_src) join_copy_streams(stream, aux_task_dirty_, -1);
   // The meta region is free once everything enqueued above has run.
   cudaEvent_t ev = take_event();
@@ -943,6 +991,7 @@ void TransferBackend::copy_descs(const pf_copy_desc *copies, size_t n, bool host
     staged_run(dev, run, c0.size, host_is_src, stream);
     table_cursor += r.count;
   }
+  flush_group();
   launch_descs(reinterpret_cast<const uint64_t *>(meta_dev_ + base + table_bytes), n_direct, aligned, stream);
   if (!host_is_src) join_copy_streams(stream, aux_task_dirty_, -1);
   cudaEvent_t ev = take_event();

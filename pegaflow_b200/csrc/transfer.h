@@ -87,12 +87,26 @@ class TransferBackend {
   // One run of one range of one layer through the staged route.
   void staged_run(const Side &dev_side, const pf_host_run &run, size_t item_bytes, bool host_is_src,
                   cudaStream_t stream);
+  void flush_group();
   int next_aux();
   void join_copy_streams(cudaStream_t target, std::vector<char> &dirty, int skip);
 
   int device_;
   pf_backend_config cfg_;
   int sm_count_ = 0;
+  // The open group of the staged route: units that will share one staging slot and one DMA.
+  struct StagedUnit {
+    Side dev;
+    size_t n_items, item_bytes, slot_offset;
+    char *host;
+    size_t host_stride;
+  };
+  std::vector<StagedUnit> group_;
+  size_t group_bytes_ = 0;
+  char *group_host_begin_ = nullptr, *group_host_end_ = nullptr;
+  bool group_dense_ = true, group_host_is_src_ = false;
+  cudaStream_t group_stream_ = nullptr;
+
   std::vector<cudaStream_t> aux_;      // copy-engine streams of the staged route
   std::vector<cudaEvent_t> aux_join_;  // one per copy stream, for joining it into another stream
   std::vector<char> aux_layer_dirty_, aux_task_dirty_;  // copy streams used by the current layer / call
