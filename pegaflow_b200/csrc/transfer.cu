@@ -37,6 +37,7 @@ constexpr int kStages = 4;               // ring depth of the TMA kernels
 constexpr uint32_t kStageBytes = 32768;  // bytes per ring stage
 constexpr unsigned kStatusWaitExpired = 0x57A17u;
 constexpr size_t kSmallTaskBytes = 2u << 20;
+constexpr size_t kFirstGroupBytes = 4u << 20;     // size limit of a call's first staging group, doubled per group
 constexpr size_t kMinEventGroupBytes = 8u << 20;  // a layer with fewer staged bytes shares the DMA of the next ones  // multi-layer tasks up to this size take one launch
 
 __device__ __forceinline__ uint64_t global_timer_ns() {
@@ -187,6 +188,55 @@ copy_items_ldst(Side src, Side dst, uint32_t n_items, uint32_t item_bytes, uint3
   }
   uint32_t len;
   while (gen.next(s, d, len)) copy_span<kHints>(d, s, len, pol_src, pol_dst);
+  if (stamp) {
+    __syncthreads();
+    if (threadIdx.x == 0) atomicMax(&stamp[1], (unsigned long long)global_timer_ns());
+  }
+}
+
+// One launch for a whole staging group: up to kMaxGroupUnits runs of equally sized items, each
+// with its own KV-side addressing, laid back to back in the staging slot.  `to_staging` selects
+// the direction.  The unit table travels in the kernel parameters (no upload).
+constexpr int kMaxGroupUnits = 40;
+struct GroupUnit {
+  Side kv;               // the scattered side (KV cache blocks)
+  uint64_t slot_addr;    // where the unit starts in the staging slot
+  uint32_t item_bytes;
+  uint32_t chunks_per_item;
+  uint64_t chunk_end;    // exclusive prefix sum of chunks over the units
+};
+struct GroupParams {
+  uint32_t n_units;
+  uint32_t chunk_bytes;
+  GroupUnit unit[kMaxGroupUnits];
+};
+
+template <int kHints>
+__global__ void __launch_bounds__(kLdstThreads)
+copy_group_ldst(const __grid_constant__ GroupParams p, int to_staging, unsigned long long *stamp) {
+  if (stamp && threadIdx.x == 0) atomicMin(&stamp[0], (unsigned long long)global_timer_ns());
+  uint64_t pol_src = 0, pol_dst = 0;
+  if (kHints == 1) {
+    pol_src = l2_policy_evict_first();
+    pol_dst = l2_policy_evict_last();
+  } else if (kHints == 2) {
+    pol_src = l2_policy_evict_first();
+    pol_dst = l2_policy_evict_first();
+  }
+  const uint64_t total = p.unit[p.n_units - 1].chunk_end;
+  uint32_t k = 0;
+  for (uint64_t c = blockIdx.x; c < total; c += gridDim.x) {
+    while (c >= p.unit[k].chunk_end) ++k;  // chunks are visited in ascending order
+    const GroupUnit &u = p.unit[k];
+    const uint64_t local = c - (k ? p.unit[k - 1].chunk_end : 0);
+    const uint32_t item = (uint32_t)(local / u.chunks_per_item);
+    const uint32_t off = (uint32_t)(local % u.chunks_per_item) * p.chunk_bytes;
+    const uint32_t len = min(p.chunk_bytes, u.item_bytes - off);
+    const uint64_t kv = side_addr(u.kv, item) + off;
+    const uint64_t st = u.slot_addr + (uint64_t)item * u.item_bytes + off;
+    if (to_staging) copy_span<kHints>(st, kv, len, pol_src, pol_dst);
+    else copy_span<kHints>(kv, st, len, pol_src, pol_dst);
+  }
   if (stamp) {
     __syncthreads();
     if (threadIdx.x == 0) atomicMax(&stamp[1], (unsigned long long)global_timer_ns());
@@ -548,10 +598,23 @@ TransferBackend::Slot &TransferBackend::next_slot() {
   return s;
 }
 
-void TransferBackend::launch_pack(const Side &src, const Side &dst, size_t n_items, size_t item_bytes,
-                                  cudaStream_t s, bool into_staging) {
-  if (n_items == 0) return;
-  const uint64_t chunks = (uint64_t)n_items * ((item_bytes + kPackChunk - 1) / kPackChunk);
+// Gathers (to_staging) or scatters the units [first, first + count) of the open group in one launch.
+void TransferBackend::launch_group(char *slot_ptr, size_t first, size_t count, bool to_staging, cudaStream_t s) {
+  GroupParams p;
+  p.n_units = (uint32_t)count;
+  p.chunk_bytes = kPackChunk;
+  uint64_t chunks = 0, payload = 0;
+  for (size_t i = 0; i < count; ++i) {
+    const StagedUnit &u = group_[first + i];
+    GroupUnit &g = p.unit[i];
+    g.kv = u.dev;
+    g.slot_addr = (uint64_t)(uintptr_t)(slot_ptr + u.slot_offset);
+    g.item_bytes = (uint32_t)u.item_bytes;
+    g.chunks_per_item = (uint32_t)((u.item_bytes + kPackChunk - 1) / kPackChunk);
+    chunks += (uint64_t)u.n_items * g.chunks_per_item;
+    g.chunk_end = chunks;
+    payload += (uint64_t)u.n_items * u.item_bytes;
+  }
   const int grid = (int)std::min<uint64_t>(chunks, (uint64_t)cfg_.pack_ctas);
   cudaEvent_t t0;
   time_begin(s, &t0);
@@ -561,15 +624,15 @@ void TransferBackend::launch_pack(const Side &src, const Side &dst, size_t n_ite
     stamp_idx = (int)stamps_used_++;
     stamp = stamps_dev_ + 2 * (size_t)stamp_idx;
   }
-  const uint32_t n = (uint32_t)n_items, ib = (uint32_t)item_bytes;
+  const int dir = to_staging ? 1 : 0;
   if (!pack_hints_)
-    copy_items_ldst<0><<<grid, kLdstThreads, 0, s>>>(src, dst, n, ib, kPackChunk, stamp);
-  else if (into_staging)
-    copy_items_ldst<1><<<grid, kLdstThreads, 0, s>>>(src, dst, n, ib, kPackChunk, stamp);
+    copy_group_ldst<0><<<grid, kLdstThreads, 0, s>>>(p, dir, stamp);
+  else if (to_staging)
+    copy_group_ldst<1><<<grid, kLdstThreads, 0, s>>>(p, dir, stamp);
   else
-    copy_items_ldst<2><<<grid, kLdstThreads, 0, s>>>(src, dst, n, ib, kPackChunk, stamp);
+    copy_group_ldst<2><<<grid, kLdstThreads, 0, s>>>(p, dir, stamp);
   PF_CUDA(cudaGetLastError());
-  time_end(s, t0, 2ull * n_items * item_bytes, false, stamp_idx);
+  time_end(s, t0, 2 * payload, false, stamp_idx);
   ++stats_.kernel_launches;
 }
 
@@ -661,7 +724,8 @@ void TransferBackend::staged_run(const Side &dev_side, const pf_host_run &run, s
     const size_t bytes = nb * item_bytes;
     const bool joins = !group_.empty() && group_dense_ && dense && group_host_is_src_ == host_is_src &&
                        group_stream_ == stream && group_host_end_ == u.host &&
-                       group_bytes_ + bytes <= cfg_.staging_slot_bytes && (group_bytes_ & 15u) == 0;
+                       group_bytes_ + bytes <= std::min(cfg_.staging_slot_bytes, group_limit_) &&
+                       (group_bytes_ & 15u) == 0;
     if (!joins) {
       flush_group();
       group_dense_ = dense;
@@ -686,12 +750,10 @@ void TransferBackend::flush_group() {
   Slot &slot = next_slot();
   cudaStream_t copy = aux_[next_aux()];
   const StagedUnit &first = group_.front();
-  auto slot_side = [&](const StagedUnit &u) {
-    return Side{(uint64_t)(uintptr_t)(slot.ptr + u.slot_offset), u.item_bytes, nullptr, nullptr};
-  };
   if (!group_host_is_src_) {
     if (slot.used) PF_CUDA(cudaStreamWaitEvent(stream, slot.drained, 0));
-    for (const StagedUnit &u : group_) launch_pack(u.dev, slot_side(u), u.n_items, u.item_bytes, stream, true);
+    for (size_t i = 0; i < group_.size(); i += kMaxGroupUnits)
+      launch_group(slot.ptr, i, std::min<size_t>(kMaxGroupUnits, group_.size() - i), true, stream);
     PF_CUDA(cudaEventRecord(slot.filled, stream));
     PF_CUDA(cudaStreamWaitEvent(copy, slot.filled, 0));
     if (group_dense_)
@@ -709,7 +771,8 @@ void TransferBackend::flush_group() {
                                 first.n_items, cudaMemcpyHostToDevice, copy));
     PF_CUDA(cudaEventRecord(slot.filled, copy));
     PF_CUDA(cudaStreamWaitEvent(stream, slot.filled, 0));
-    for (const StagedUnit &u : group_) launch_pack(slot_side(u), u.dev, u.n_items, u.item_bytes, stream, false);
+    for (size_t i = 0; i < group_.size(); i += kMaxGroupUnits)
+      launch_group(slot.ptr, i, std::min<size_t>(kMaxGroupUnits, group_.size() - i), false, stream);
     PF_CUDA(cudaEventRecord(slot.drained, stream));
   }
   slot.used = true;
@@ -717,6 +780,7 @@ void TransferBackend::flush_group() {
   stats_.bytes_staged += group_bytes_;
   group_.clear();
   group_bytes_ = 0;
+  group_limit_ = std::min(group_limit_ * 2, cfg_.staging_slot_bytes);  // ramp up: the first DMAs start early
 }
 
 void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, bool host_is_src,
@@ -846,6 +910,7 @@ void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, 
   meta_upload(base, meta_bytes, stream);
 
   // ---- enqueue, layer by layer.
+  group_limit_ = kFirstGroupBytes;
   std::fill(aux_task_dirty_.begin(), aux_task_dirty_.end(), 0);
   // Events of layers whose bytes are still in an open (small) group wait here until it is flushed.
   std::vector<cudaEvent_t> deferred;

@@ -78,8 +78,7 @@ class TransferBackend {
   void ensure_staging();
 
   // Kernel launchers (transfer.cu).
-  void launch_pack(const Side &src, const Side &dst, size_t n_items, size_t item_bytes, cudaStream_t s,
-                   bool into_staging);
+  void launch_group(char *slot_ptr, size_t first, size_t count, bool to_staging, cudaStream_t s);
   void launch_link(const Side &src, const Side &dst, size_t n_items, size_t item_bytes, cudaStream_t s,
                    bool peer);
   void launch_descs(const uint64_t *triples_dev, size_t n, bool aligned, cudaStream_t s);
@@ -103,6 +102,7 @@ class TransferBackend {
   };
   std::vector<StagedUnit> group_;
   size_t group_bytes_ = 0;
+  size_t group_limit_ = ~(size_t)0;  // current size limit of a group (ramps up within a call)
   char *group_host_begin_ = nullptr, *group_host_end_ = nullptr;
   bool group_dense_ = true, group_host_is_src_ = false;
   cudaStream_t group_stream_ = nullptr;
