@@ -394,6 +394,8 @@ TransferBackend::TransferBackend(int device, const pf_backend_config *config) : 
   aux_join_.resize(cfg_.copy_streams, nullptr);
   aux_layer_dirty_.assign(cfg_.copy_streams, 0);
   aux_task_dirty_.assign(cfg_.copy_streams, 0);
+  aux_forked_.assign(cfg_.copy_streams, 0);
+  PF_CUDA(cudaEventCreateWithFlags(&fork_, cudaEventDisableTiming));
   for (int i = 0; i < cfg_.copy_streams; ++i) {
     if (cudaStreamCreateWithFlags(&aux_[i], cudaStreamNonBlocking) != cudaSuccess)
       throw Error::cuda_init("failed to create a copy stream");
@@ -435,6 +437,7 @@ TransferBackend::~TransferBackend() {
   if (meta_dev_) cudaFree(meta_dev_);
   if (meta_host_) cudaFreeHost(meta_host_);
   if (status_host_) cudaFreeHost(status_host_);
+  if (fork_) cudaEventDestroy(fork_);
   for (auto ev : aux_join_)
     if (ev) cudaEventDestroy(ev);
   for (auto st : aux_)
@@ -748,7 +751,8 @@ void TransferBackend::flush_group() {
   ensure_staging();
   cudaStream_t stream = group_stream_;
   Slot &slot = next_slot();
-  cudaStream_t copy = aux_[next_aux()];
+  const int copy_index = next_aux();
+  cudaStream_t copy = aux_[copy_index];
   const StagedUnit &first = group_.front();
   if (!group_host_is_src_) {
     if (slot.used) PF_CUDA(cudaStreamWaitEvent(stream, slot.drained, 0));
@@ -763,6 +767,12 @@ void TransferBackend::flush_group() {
                                 first.n_items, cudaMemcpyDeviceToHost, copy));
     PF_CUDA(cudaEventRecord(slot.drained, copy));
   } else {
+    // The DMA reads host memory that earlier work on the caller's stream may still be writing
+    // (a save enqueued just before): each copy stream joins the caller's stream once per call.
+    if (!aux_forked_[copy_index]) {
+      PF_CUDA(cudaStreamWaitEvent(copy, fork_, 0));
+      aux_forked_[copy_index] = 1;
+    }
     if (slot.used) PF_CUDA(cudaStreamWaitEvent(copy, slot.drained, 0));
     if (group_dense_)
       PF_CUDA(cudaMemcpyAsync(slot.ptr, group_host_begin_, group_bytes_, cudaMemcpyHostToDevice, copy));
@@ -912,6 +922,8 @@ void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, 
   // ---- enqueue, layer by layer.
   group_limit_ = kFirstGroupBytes;
   std::fill(aux_task_dirty_.begin(), aux_task_dirty_.end(), 0);
+  std::fill(aux_forked_.begin(), aux_forked_.end(), 0);
+  if (host_is_src) PF_CUDA(cudaEventRecord(fork_, stream));
   // Events of layers whose bytes are still in an open (small) group wait here until it is flushed.
   std::vector<cudaEvent_t> deferred;
   bool layer_stream = false;
@@ -1048,6 +1060,9 @@ void TransferBackend::copy_descs(const pf_copy_desc *copies, size_t n, bool host
   }
   meta_upload(base, meta_bytes, stream);
   std::fill(aux_task_dirty_.begin(), aux_task_dirty_.end(), 0);
+  std::fill(aux_forked_.begin(), aux_forked_.end(), 0);
+  group_limit_ = kFirstGroupBytes;
+  if (host_is_src) PF_CUDA(cudaEventRecord(fork_, stream));
   size_t table_cursor = 0;
   for (auto &r : staged) {
     const pf_copy_desc &c0 = copies[r.first];

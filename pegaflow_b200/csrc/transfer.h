@@ -109,6 +109,8 @@ class TransferBackend {
 
   std::vector<cudaStream_t> aux_;      // copy-engine streams of the staged route
   std::vector<cudaEvent_t> aux_join_;  // one per copy stream, for joining it into another stream
+  cudaEvent_t fork_ = nullptr;         // caller's stream position at the start of a load call
+  std::vector<char> aux_forked_;       // copy streams that already wait for fork_ in this call
   std::vector<char> aux_layer_dirty_, aux_task_dirty_;  // copy streams used by the current layer / call
   size_t aux_cursor_ = 0;
   int aux_last_ = 0;

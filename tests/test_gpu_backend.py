@@ -337,3 +337,31 @@ def test_small_multi_layer_task_takes_one_launch(env):
     assert be.stats()["device_status"] == 0
     be.close()
     pool.release(handle)
+
+
+@pytest.mark.parametrize("route", ["staged", "zerocopy"])
+def test_save_then_load_on_one_stream_needs_no_sync_in_between(env, route):
+    """Stream order is the contract (transfer/mod.rs:15-16): a load enqueued right after a save on
+    the same stream must see the bytes that save wrote, although the copies run on internal streams."""
+    pf, mem, pool, torch = env
+    rng = np.random.default_rng(99)
+    num_blocks, seg, n = 1024, 65536, 384
+    dev = mem.alloc(num_blocks * seg)
+    host, host_dev, handle = pool.alloc(n * seg)
+    be = pf.TransferBackend(0, route=ROUTES[route], staging_slot_bytes=4 << 20)
+    stream = torch.cuda.Stream()
+    src = rng.permutation(num_blocks // 2)[:n]
+    dst = rng.permutation(num_blocks // 2)[:n] + num_blocks // 2
+    runs = [[pf.HostRun(0, n, host, host_dev, seg)]]
+    xs = pf.TransferBackend.make_layers([pf.LayerXfer(dev.data_ptr(), seg, 0, seg, 1, src, runs)])
+    xl = pf.TransferBackend.make_layers([pf.LayerXfer(dev.data_ptr(), seg, 0, seg, 1, dst, runs)])
+    for it in range(3):
+        data = rng.integers(0, 256, size=num_blocks * seg, dtype=np.uint8)
+        mem.write(dev, data)
+        be.save_layers(xs, stream.cuda_stream)
+        be.load_layers(xl, stream.cuda_stream)
+        stream.synchronize()
+        got = mem.read(dev).reshape(num_blocks, seg)
+        assert np.array_equal(got[dst], data.reshape(num_blocks, seg)[src]), f"iteration {it}: stale host bytes loaded"
+    be.close()
+    pool.release(handle)
