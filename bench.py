@@ -528,7 +528,7 @@ def run_b200(args, rank, world, local):
     hbm_peak = peaks.get("hbm_gbs", 6650.0)
     if pack_launches and pack_ms > 0:
         ach = pack_bytes / 1e6 / pack_ms
-        roofline = {"kernel": "copy_items_ldst (HBM gather/scatter of the staged route)", "bound": "hbm",
+        roofline = {"kernel": "copy_group_ldst (HBM gather/scatter of the staged route)", "bound": "hbm",
                     "achieved": round(ach, 1), "peak": hbm_peak, "unit": "GB/s", "frac": round(ach / hbm_peak, 4),
                     "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback",
                     "launches": pack_launches, "avg_launch_us": round(pack_ms / pack_launches * 1e3, 2),
