@@ -533,10 +533,10 @@ def run_b200(args, rank, world, local):
                     "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback",
                     "launches": pack_launches, "avg_launch_us": round(pack_ms / pack_launches * 1e3, 2),
                     "algorithmic_bytes_per_launch": pack_bytes // pack_launches,
-                    # DRAM bytes per launch: the ncu capture of a smaller case (8.40 MB read, 0 written per
-                    # 8.39 MB of payload: profiles/copy_items_ldst_small_full_set.md) scaled by payload
+                    # DRAM bytes per launch: the ncu capture of a smaller case (8.398 MB read, 0 written per
+                    # 8.389 MB of payload: profiles/copy_group_ldst_small_full_set.md) scaled by payload
                     "traffic": args.traffic_per_launch if args.traffic_per_launch is not None
-                    else round(pack_bytes / pack_launches / 2 * (8.396544 / 8.388608)),
+                    else round(pack_bytes / pack_launches / 2 * (8.398336 / 8.388608)),
                     "how": "one CUDA event pair around every launch, on the launching stream, inside the timed region"}
         dev_n = st1["pack_kernel_device_launches"] - st0["pack_kernel_device_launches"]
         dev_ms = st1["pack_kernel_device_ms"] - st0["pack_kernel_device_ms"]
