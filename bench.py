@@ -444,7 +444,8 @@ def run_b200(args, rank, world, local):
     route = {"auto": 0, "staged": 1, "zerocopy": 2}[args.route]
 
     # ---------------- transfer-only arm: backend + pool, KV resident in HBM -------------------
-    pool = pf.PinnedPool(wl.payload + (64 << 20), numa_node=-1)
+    # each rank's pool on its GPU's own NUMA node (what the engine's per-node pools do)
+    pool = pf.PinnedPool(wl.payload + (64 << 20), numa_node=pf.numa_node_of_device(local))
     allocs = alloc_host_images(pool, wl)
     be = pf.TransferBackend(local, route=route, time_kernels=not args.no_kernel_timing, link_ctas=args.link_ctas,
                             staging_slot_bytes=args.slot_mib << 20, staging_slots=args.slots,
@@ -604,8 +605,8 @@ def run_e2e(args, pf, wl, rank, world, local, route):
     spec = wl.spec
     L, seg, per, n_req = spec["layers"], spec["seg_bytes"], spec["blocks"], spec["requests"]
     steps_total = args.steps + max(1, args.warmup)
-    # room for two steps' blocks: older steps are evicted (LRU) while a new one is being saved
-    eng = pf.PegaEngine(2 * wl.payload + (256 << 20), route=route, link_ctas=args.link_ctas,
+    # room for one and a half steps' blocks: older steps are evicted (LRU) while a new one is saved
+    eng = pf.PegaEngine(wl.payload + wl.payload // 2 + (256 << 20), route=route, link_ctas=args.link_ctas,
                         staging_slot_bytes=args.slot_mib << 20, staging_slots=args.slots,
                         copy_streams=args.copy_streams)
     names = [f"model.layers.{l}.self_attn.attn" for l in range(L)]

@@ -5,7 +5,7 @@ TEST / BENCHMARK INFRASTRUCTURE ONLY.
 Two flavours:
 
 * ``oracle/_ref/libpf_refpath.so`` — when the reference checkout is present
-  (``PEGAFLOW_REFERENCE`` or ``/root/reference``): the reference's only CUDA kernel, which it
+  (``PEGAFLOW_REFERENCE``, default: a ``reference`` directory beside this repository): the reference's only CUDA kernel, which it
   keeps as a source string inside ``pegaflow-core/src/transfer/kernel.rs`` and compiles with
   NVRTC at run time, is extracted from where it lies, compiled unchanged into the library, and
   the extracted text is deleted again.  Only the binary stays (``oracle/_ref/`` is git-ignored).
@@ -23,7 +23,7 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("PEGAFLOW_REFERENCE", "/root/reference")
+REF = os.environ.get("PEGAFLOW_REFERENCE", os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
 KERNEL_RS = os.path.join(REF, "pegaflow-core", "src", "transfer", "kernel.rs")
 REF_DIR = os.path.join(HERE, "_ref")
 LIB_WITH_KERNEL = os.path.join(REF_DIR, "libpf_refpath.so")

@@ -6,5 +6,5 @@ CPU fallback.
 """
 from ._native import PegaFlowError, PegaflowInternal, PegaflowInvalidArgument  # noqa: F401
 from .backend import (HostRun, LayerXfer, PinnedPool, TransferBackend, enable_peer_access,  # noqa: F401
-                      save_blocks_noalloc)
+                      numa_node_of_device, save_blocks_noalloc)
 from .engine import Block, Completion, PegaEngine, PyLoadState  # noqa: F401

@@ -159,6 +159,11 @@ class TransferBackend:
         return {f: getattr(st, f) for f, _ in N.BackendStats._fields_}
 
 
+def numa_node_of_device(device_id: int) -> int:
+    """NUMA node of a CUDA device from sysfs, -1 when unknown (pegaflow-common/src/numa.rs:344-411)."""
+    return int(N.lib.pf_numa_node_of_device(device_id))
+
+
 def enable_peer_access(device_id: int, peer_device: int):
     N.check(N.lib.pf_enable_peer_access(device_id, peer_device))
 

@@ -41,8 +41,19 @@ void parallel_pre_touch(char *ptr, size_t bytes, size_t page, int node) {
 PinnedMemory::PinnedMemory(size_t bytes, Strategy strategy, int numa_node) : size_(bytes), strategy_(strategy) {
   if (bytes == 0) throw Error::storage("pinned memory size must be greater than zero");
   if (strategy == Strategy::CudaHostAlloc) {
+    // The driver places the pages by the calling thread's memory policy, so a known node is
+    // honoured by allocating from a thread pinned to it (pinned_mem.rs:149-185 does the same
+    // through its per-node allocation threads).  The helper thread keeps the caller's device.
     void *p = nullptr;
-    cudaError_t e = cudaHostAlloc(&p, bytes, cudaHostAllocMapped | cudaHostAllocPortable);
+    cudaError_t e = cudaSuccess;
+    int device = 0;
+    cudaGetDevice(&device);
+    auto alloc = [&] {
+      cudaSetDevice(device);
+      e = cudaHostAlloc(&p, bytes, cudaHostAllocMapped | cudaHostAllocPortable);
+    };
+    if (numa_node >= 0) numa::run_on_node(numa_node, alloc);
+    else alloc();
     if (e != cudaSuccess) throw Error::storage(cuda_msg("cudaHostAlloc", e));
     host_ = static_cast<char *>(p);
   } else {

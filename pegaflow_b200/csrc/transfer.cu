@@ -102,26 +102,10 @@ struct DescGen {
   }
 };
 
-// L2 policies for the staged route: the KV side is streamed (evict first), the staging side is
-// kept (evict last) so that the copy engine finds a gathered slot in L2 and a scattered slot is
-// read back from L2, not HBM.
-__device__ __forceinline__ uint64_t l2_policy_evict_first() {
-  uint64_t p;
-  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
-  return p;
-}
-__device__ __forceinline__ uint64_t l2_policy_evict_last() {
-  uint64_t p;
-  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
-  return p;
-}
-
 // CTA-wide copy of one span.  16-byte vectors when source and destination share their
-// misalignment (head bytes are peeled), plain bytes otherwise.  kHints: 0 none, 1 source is
-// streamed / destination kept in L2 (gather into staging), 2 the reverse (scatter from staging).
-template <int kHints>
-__device__ __forceinline__ void copy_span(uint64_t dst, uint64_t src, uint32_t len, uint64_t pol_src,
-                                          uint64_t pol_dst) {
+// misalignment (head bytes are peeled), plain bytes otherwise.  (L2 eviction-priority hints on
+// either side were measured and changed nothing: the staging slot stays in L2 without them.)
+__device__ __forceinline__ void copy_span(uint64_t dst, uint64_t src, uint32_t len) {
   const uint32_t tid = threadIdx.x, nthr = blockDim.x;
   if (((dst ^ src) & 15ull) != 0) {
     char *d = reinterpret_cast<char *>(dst);
@@ -142,27 +126,15 @@ __device__ __forceinline__ void copy_span(uint64_t dst, uint64_t src, uint32_t l
     for (int u = 0; u < kLdstUnroll; ++u) {
       uint32_t jj = j + u * nthr;
       if (jj < n16) {
-        if (kHints)
-          asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.s32 {%0,%1,%2,%3}, [%4], %5;"
-                       : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
-                       : "l"(s16 + jj), "l"(pol_src));
-        else
-          asm volatile("ld.global.nc.L1::no_allocate.v4.s32 {%0,%1,%2,%3}, [%4];"
-                       : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
-                       : "l"(s16 + jj));
+        asm volatile("ld.global.nc.L1::no_allocate.v4.s32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
+                     : "l"(s16 + jj));
       }
     }
 #pragma unroll
     for (int u = 0; u < kLdstUnroll; ++u) {
       uint32_t jj = j + u * nthr;
-      if (jj < n16) {
-        if (kHints)
-          asm volatile("st.global.L2::cache_hint.v4.s32 [%0], {%1,%2,%3,%4}, %5;" ::"l"(d16 + jj), "r"(v[u].x),
-                       "r"(v[u].y), "r"(v[u].z), "r"(v[u].w), "l"(pol_dst)
-                       : "memory");
-        else
-          d16[jj] = v[u];
-      }
+      if (jj < n16) d16[jj] = v[u];
     }
   }
   const uint32_t tail_at = head + (n16 << 4);
@@ -172,22 +144,14 @@ __device__ __forceinline__ void copy_span(uint64_t dst, uint64_t src, uint32_t l
 
 // `stamp` (optional) points at {first start, last end} in %globaltimer nanoseconds, pre-set to
 // {UINT64_MAX, 0}: a device-side measure of the launch that needs no event around it.
-template <int kHints>
 __global__ void __launch_bounds__(kLdstThreads)
 copy_items_ldst(Side src, Side dst, uint32_t n_items, uint32_t item_bytes, uint32_t chunk_bytes,
                 unsigned long long *stamp) {
   if (stamp && threadIdx.x == 0) atomicMin(&stamp[0], (unsigned long long)global_timer_ns());
   ItemGen gen(src, dst, n_items, item_bytes, chunk_bytes);
-  uint64_t s, d, pol_src = 0, pol_dst = 0;
-  if (kHints == 1) {
-    pol_src = l2_policy_evict_first();
-    pol_dst = l2_policy_evict_last();
-  } else if (kHints == 2) {
-    pol_src = l2_policy_evict_first();  // a staging slot is dead once it has been scattered
-    pol_dst = l2_policy_evict_first();
-  }
+  uint64_t s, d;
   uint32_t len;
-  while (gen.next(s, d, len)) copy_span<kHints>(d, s, len, pol_src, pol_dst);
+  while (gen.next(s, d, len)) copy_span(d, s, len);
   if (stamp) {
     __syncthreads();
     if (threadIdx.x == 0) atomicMax(&stamp[1], (unsigned long long)global_timer_ns());
@@ -211,18 +175,9 @@ struct GroupParams {
   GroupUnit unit[kMaxGroupUnits];
 };
 
-template <int kHints>
 __global__ void __launch_bounds__(kLdstThreads)
 copy_group_ldst(const __grid_constant__ GroupParams p, int to_staging, unsigned long long *stamp) {
   if (stamp && threadIdx.x == 0) atomicMin(&stamp[0], (unsigned long long)global_timer_ns());
-  uint64_t pol_src = 0, pol_dst = 0;
-  if (kHints == 1) {
-    pol_src = l2_policy_evict_first();
-    pol_dst = l2_policy_evict_last();
-  } else if (kHints == 2) {
-    pol_src = l2_policy_evict_first();
-    pol_dst = l2_policy_evict_first();
-  }
   const uint64_t total = p.unit[p.n_units - 1].chunk_end;
   uint32_t k = 0;
   for (uint64_t c = blockIdx.x; c < total; c += gridDim.x) {
@@ -234,8 +189,8 @@ copy_group_ldst(const __grid_constant__ GroupParams p, int to_staging, unsigned 
     const uint32_t len = min(p.chunk_bytes, u.item_bytes - off);
     const uint64_t kv = side_addr(u.kv, item) + off;
     const uint64_t st = u.slot_addr + (uint64_t)item * u.item_bytes + off;
-    if (to_staging) copy_span<kHints>(st, kv, len, pol_src, pol_dst);
-    else copy_span<kHints>(kv, st, len, pol_src, pol_dst);
+    if (to_staging) copy_span(st, kv, len);
+    else copy_span(kv, st, len);
   }
   if (stamp) {
     __syncthreads();
@@ -248,7 +203,7 @@ copy_descs_ldst(const uint64_t *__restrict__ triples, uint32_t n, uint32_t chunk
   DescGen gen(triples, n, chunk_bytes);
   uint64_t s, d;
   uint32_t len;
-  while (gen.next(s, d, len)) copy_span<0>(d, s, len, 0, 0);
+  while (gen.next(s, d, len)) copy_span(d, s, len);
 }
 
 // ---- bulk async copy (TMA) primitives ------------------------------------------------------
@@ -388,8 +343,6 @@ TransferBackend::TransferBackend(int device, const pf_backend_config *config) : 
                                 prop.minor));
   sm_count_ = prop.multiProcessorCount;
   if (cfg_.pack_ctas <= 0) cfg_.pack_ctas = sm_count_ * 8;
-  if (const char *e = getenv("PF_EXP_PACK_HINTS")) pack_hints_ = atoi(e) != 0;
-  if (const char *e = getenv("PF_EXP_PEER_LDST")) peer_ldst_ = atoi(e) != 0;
   aux_.resize(cfg_.copy_streams, nullptr);
   aux_join_.resize(cfg_.copy_streams, nullptr);
   aux_layer_dirty_.assign(cfg_.copy_streams, 0);
@@ -627,13 +580,7 @@ void TransferBackend::launch_group(char *slot_ptr, size_t first, size_t count, b
     stamp_idx = (int)stamps_used_++;
     stamp = stamps_dev_ + 2 * (size_t)stamp_idx;
   }
-  const int dir = to_staging ? 1 : 0;
-  if (!pack_hints_)
-    copy_group_ldst<0><<<grid, kLdstThreads, 0, s>>>(p, dir, stamp);
-  else if (to_staging)
-    copy_group_ldst<1><<<grid, kLdstThreads, 0, s>>>(p, dir, stamp);
-  else
-    copy_group_ldst<2><<<grid, kLdstThreads, 0, s>>>(p, dir, stamp);
+  copy_group_ldst<<<grid, kLdstThreads, 0, s>>>(p, to_staging ? 1 : 0, stamp);
   PF_CUDA(cudaGetLastError());
   time_end(s, t0, 2 * payload, false, stamp_idx);
   ++stats_.kernel_launches;
@@ -646,7 +593,6 @@ void TransferBackend::launch_link(const Side &src, const Side &dst, size_t n_ite
   // whoever fills an address table clears tables_aligned_ when an entry is not aligned.
   auto aligned16 = [](const Side &x) { return x.table != nullptr || ((x.base | x.stride) & 15ull) == 0; };
   bool tma_ok = aligned16(src) && aligned16(dst) && (item_bytes & 15u) == 0 && tables_aligned_;
-  if (peer && peer_ldst_) tma_ok = false;
   int ctas = cfg_.link_ctas > 0 ? cfg_.link_ctas : (peer ? 2 * sm_count_ : 16);
   cudaEvent_t t0;
   time_begin(s, &t0);
@@ -659,7 +605,7 @@ void TransferBackend::launch_link(const Side &src, const Side &dst, size_t n_ite
   } else {
     const uint64_t chunks = (uint64_t)n_items * ((item_bytes + kPackChunk - 1) / kPackChunk);
     const int grid = (int)std::min<uint64_t>(chunks, (uint64_t)(peer ? std::max(ctas, cfg_.pack_ctas) : std::max(ctas, sm_count_)));
-    copy_items_ldst<0><<<grid, kLdstThreads, 0, s>>>(src, dst, (uint32_t)n_items, (uint32_t)item_bytes, kPackChunk,
+    copy_items_ldst<<<grid, kLdstThreads, 0, s>>>(src, dst, (uint32_t)n_items, (uint32_t)item_bytes, kPackChunk,
                                                      nullptr);
   }
   PF_CUDA(cudaGetLastError());
@@ -1202,7 +1148,7 @@ extern "C" int pf_save_blocks_noalloc(int device_id, const pf_device_layout *lay
       const Side dst{(uint64_t)(uintptr_t)(dev.scratch + r * per_range), layout->range_bytes, nullptr, nullptr};
       const uint64_t chunks = (uint64_t)n_blocks * ((layout->range_bytes + kPackChunk - 1) / kPackChunk);
       const int grid = (int)std::min<uint64_t>(chunks, (uint64_t)dev.sm_count * 8);
-      copy_items_ldst<0><<<grid, kLdstThreads, 0, s>>>(src, dst, (uint32_t)n_blocks, (uint32_t)layout->range_bytes,
+      copy_items_ldst<<<grid, kLdstThreads, 0, s>>>(src, dst, (uint32_t)n_blocks, (uint32_t)layout->range_bytes,
                                                        kPackChunk, nullptr);
       PF_CUDA(cudaGetLastError());
     }

@@ -139,8 +139,6 @@ class TransferBackend {
   std::vector<unsigned long long> stamps_host_;
   size_t stamps_used_ = 0;
 
-  bool peer_ldst_ = false;
-  bool pack_hints_ = false;              // L2 eviction hints in the gather/scatter kernel
   bool tables_aligned_ = true;           // set while an address table is filled
   pf_backend_stats stats_{};
 };

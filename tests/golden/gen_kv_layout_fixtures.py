@@ -1,7 +1,7 @@
 """Generate ``kv_layout_inference.json`` by running the reference's own layout inference.
 
-Run in a container that has the reference checkout (``PEGAFLOW_REFERENCE`` or
-``/root/reference``).  The reference's pure-Python ``_infer_kv_cache_registration``
+Run where the reference checkout is available (``PEGAFLOW_REFERENCE``, default: a ``reference``
+directory beside this repository).  The reference's pure-Python ``_infer_kv_cache_registration``
 (python/pegaflow/connector/worker.py:65-151) is imported with the native extension stubbed
 out by the reference's own ``unit_stubs`` helper, and evaluated on a grid of tensor
 shapes/strides.  The output is committed so the tests never need the reference at run time.
@@ -11,7 +11,8 @@ import json
 import os
 import sys
 
-REF = os.environ.get("PEGAFLOW_REFERENCE", "/root/reference")
+_REPO = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+REF = os.environ.get("PEGAFLOW_REFERENCE", os.path.join(os.path.dirname(_REPO), "reference"))
 sys.path.insert(0, os.path.join(REF, "python"))
 from tests.unit_stubs import install_connector_unit_stubs  # noqa: E402
 
