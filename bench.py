@@ -45,7 +45,8 @@ def workloads():
         "qwen3-0.6b": dict(layers=28, seg_bytes=16 * 8 * 128 * 2, gpu_blocks=256, requests=1, blocks=64, segments=2),
         "small": dict(layers=4, seg_bytes=16 * 8 * 128 * 2, gpu_blocks=2048, requests=2, blocks=256, segments=2),
         # one rank of Llama-3.1-70B TP=8: 1 KV head per rank -> 4 KiB segments, 4 prompts of 32768 tokens
-        "llama70b-tp8-rank": dict(layers=80, seg_bytes=16 * 1 * 128 * 2, gpu_blocks=16384, requests=4, blocks=2048,
+        # (gpu_blocks leaves room for disjoint save and load ids when both directions run at once)
+        "llama70b-tp8-rank": dict(layers=80, seg_bytes=16 * 1 * 128 * 2, gpu_blocks=16640, requests=4, blocks=2048,
                                   segments=2),
         # DeepSeek-V3-style latent cache [num_blocks, 64, 576], bf16 and fp8 byte widths
         "mla-bf16": dict(layers=61, seg_bytes=64 * 576 * 2, gpu_blocks=1024, requests=1, blocks=256, segments=1),
@@ -213,16 +214,29 @@ def make_layer_xfers(pf, wl, pool_allocs, ids_per_request):
     return out
 
 
-def measure_pcie_ceiling(device, nbytes=1 << 30, iters=5):
-    """One large pinned<->device cudaMemcpyAsync per direction, best of `iters` (GB/s)."""
+def measure_pcie_ceiling(device, nbytes=1 << 30, iters=5, sustained=False, world=1):
+    """One large pinned<->device cudaMemcpyAsync per direction (GB/s): best of `iters`, or with
+    `sustained` the mean over `iters` back-to-back copies (for ranks that run it at the same time)."""
     import torch
 
     host = torch.empty(nbytes, dtype=torch.uint8, pin_memory=True)
     dev = torch.empty(nbytes, dtype=torch.uint8, device=device)
     res = {}
     for name, (dst, src) in {"d2h": (host, dev), "h2d": (dev, host)}.items():
+        dst.copy_(src, non_blocking=True)
+        torch.cuda.synchronize()
+        if sustained:
+            barrier(world)   # all ranks start a direction together
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(iters):
+                dst.copy_(src, non_blocking=True)
+            b.record()
+            b.synchronize()
+            res[name] = iters * nbytes / 1e6 / a.elapsed_time(b)
+            continue
         best = 0.0
-        for _ in range(iters + 1):
+        for _ in range(iters):
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
             dst.copy_(src, non_blocking=True)
@@ -232,6 +246,27 @@ def measure_pcie_ceiling(device, nbytes=1 << 30, iters=5):
         res[name] = best
     del host, dev
     return res
+
+
+def concurrent_pcie_ceiling(device, world):
+    """What the host platform gives when every rank copies at once: per-rank sustained GB/s per
+    direction, gathered on all ranks.  Several GPUs can share a root port, a socket link or the
+    host's memory write bandwidth, so this, not `world` x the solo figure, bounds the N-GPU value."""
+    import torch
+    import torch.distributed as dist
+
+    mine = measure_pcie_ceiling(device, sustained=True, world=world)
+    t = torch.tensor([mine["d2h"], mine["h2d"]], dtype=torch.float64, device=device)
+    every = [torch.zeros_like(t) for _ in range(world)]
+    dist.all_gather(every, t)
+    d2h = [round(float(x[0]), 2) for x in every]
+    h2d = [round(float(x[1]), 2) for x in every]
+    # the bench's value is bytes of all ranks over the slowest rank's time for a save pass plus a load pass
+    slowest = max(1.0 / a + 1.0 / b for a, b in zip(d2h, h2d))
+    return {"d2h_per_rank": d2h, "h2d_per_rank": h2d, "d2h_sum": round(sum(d2h), 2), "h2d_sum": round(sum(h2d), 2),
+            "value_bound": round(2 * world / slowest, 2),
+            "how": "every rank copies 5 x 1 GiB per direction at the same time; value_bound = 2 * ranks / "
+                   "max over ranks of (1/d2h + 1/h2d), the same max-over-ranks rule as `value`"}
 
 
 def cpu_baseline(wl, seconds_budget=8.0):
@@ -430,6 +465,49 @@ def run_reference(args, rank, world, local, launched_world=1):
     print(json.dumps(line))
 
 
+def build_roofline(stat_pairs, args):
+    """The `roofline` object from backend counters taken before and after the timed region
+    (summed over `stat_pairs`, one pair per backend that ran in it)."""
+    def delta(key):
+        return sum(b[key] - a[key] for a, b in stat_pairs)
+
+    pack_launches, pack_ms, pack_bytes = delta("pack_kernel_launches"), delta("pack_kernel_ms"), delta("pack_kernel_bytes")
+    link_launches, link_ms, link_bytes = delta("link_kernel_launches"), delta("link_kernel_ms"), delta("link_kernel_bytes")
+    dev_n, dev_ms = delta("pack_kernel_device_launches"), delta("pack_kernel_device_ms")
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except OSError:
+        pass
+    hbm_peak = peaks.get("hbm_gbs", 6650.0)
+    if pack_launches and pack_ms > 0:
+        ach = pack_bytes / 1e6 / pack_ms
+        roofline = {"kernel": "copy_group_ldst (HBM gather/scatter of the staged route)", "bound": "hbm",
+                    "achieved": round(ach, 1), "peak": hbm_peak, "unit": "GB/s", "frac": round(ach / hbm_peak, 4),
+                    "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback",
+                    "launches": pack_launches, "avg_launch_us": round(pack_ms / pack_launches * 1e3, 2),
+                    "algorithmic_bytes_per_launch": pack_bytes // pack_launches,
+                    # DRAM bytes per launch: the ncu capture of a smaller case (8.398 MB read, 0 written per
+                    # 8.389 MB of payload: profiles/copy_group_ldst_small_full_set.md) scaled by payload
+                    "traffic": args.traffic_per_launch if args.traffic_per_launch is not None
+                    else round(pack_bytes / pack_launches / 2 * (8.398336 / 8.388608)),
+                    "how": "one CUDA event pair around every launch, on the launching stream, inside the timed region"}
+        if dev_n and dev_ms > 0:
+            dev_ach = (pack_bytes / pack_launches) * dev_n / 1e6 / dev_ms
+            roofline["device_clock"] = {
+                "avg_launch_us": round(dev_ms / dev_n * 1e3, 2), "achieved": round(dev_ach, 1),
+                "frac": round(dev_ach / hbm_peak, 4), "launches": dev_n,
+                "how": "the kernel's own %globaltimer stamps (first CTA start to last CTA end) for the same launches; "
+                       "an event pair around a ~10 us kernel measures mostly the pair"}
+    else:
+        ach = link_bytes / 1e6 / link_ms if link_ms > 0 else 0.0
+        roofline = {"kernel": "copy_items_tma (zero-copy over PCIe)", "bound": "hbm", "achieved": round(ach, 1),
+                    "peak": hbm_peak, "unit": "GB/s", "frac": round(ach / hbm_peak, 4),
+                    "note": "this kernel is bound by the PCIe link, not HBM: see the `link` object",
+                    "launches": link_launches, "traffic": args.traffic_per_launch}
+    return roofline
+
+
 def run_b200(args, rank, world, local):
     import torch
     import pegaflow_b200 as pf
@@ -515,51 +593,15 @@ def run_b200(args, rank, world, local):
     pool.close()
 
     value = 2 * wl.payload * args.steps * world / (total_ms / 1e3) / 1e9
-    pack_launches = st1["pack_kernel_launches"] - st0["pack_kernel_launches"]
-    pack_ms = st1["pack_kernel_ms"] - st0["pack_kernel_ms"]
-    pack_bytes = st1["pack_kernel_bytes"] - st0["pack_kernel_bytes"]
-    link_launches = st1["link_kernel_launches"] - st0["link_kernel_launches"]
-    link_ms = st1["link_kernel_ms"] - st0["link_kernel_ms"]
-    link_bytes = st1["link_kernel_bytes"] - st0["link_kernel_bytes"]
-    peaks = {}
-    try:
-        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-    except OSError:
-        pass
-    hbm_peak = peaks.get("hbm_gbs", 6650.0)
-    if pack_launches and pack_ms > 0:
-        ach = pack_bytes / 1e6 / pack_ms
-        roofline = {"kernel": "copy_group_ldst (HBM gather/scatter of the staged route)", "bound": "hbm",
-                    "achieved": round(ach, 1), "peak": hbm_peak, "unit": "GB/s", "frac": round(ach / hbm_peak, 4),
-                    "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback",
-                    "launches": pack_launches, "avg_launch_us": round(pack_ms / pack_launches * 1e3, 2),
-                    "algorithmic_bytes_per_launch": pack_bytes // pack_launches,
-                    # DRAM bytes per launch: the ncu capture of a smaller case (8.398 MB read, 0 written per
-                    # 8.389 MB of payload: profiles/copy_group_ldst_small_full_set.md) scaled by payload
-                    "traffic": args.traffic_per_launch if args.traffic_per_launch is not None
-                    else round(pack_bytes / pack_launches / 2 * (8.398336 / 8.388608)),
-                    "how": "one CUDA event pair around every launch, on the launching stream, inside the timed region"}
-        dev_n = st1["pack_kernel_device_launches"] - st0["pack_kernel_device_launches"]
-        dev_ms = st1["pack_kernel_device_ms"] - st0["pack_kernel_device_ms"]
-        if dev_n and dev_ms > 0:
-            dev_ach = (pack_bytes / pack_launches) * dev_n / 1e6 / dev_ms
-            roofline["device_clock"] = {
-                "avg_launch_us": round(dev_ms / dev_n * 1e3, 2), "achieved": round(dev_ach, 1),
-                "frac": round(dev_ach / hbm_peak, 4), "launches": dev_n,
-                "how": "the kernel's own %globaltimer stamps (first CTA start to last CTA end) for the same launches; "
-                       "an event pair around a ~10 us kernel measures mostly the pair"}
-    else:
-        ach = link_bytes / 1e6 / link_ms if link_ms > 0 else 0.0
-        roofline = {"kernel": "copy_items_tma (zero-copy over PCIe)", "bound": "hbm", "achieved": round(ach, 1),
-                    "peak": hbm_peak, "unit": "GB/s", "frac": round(ach / hbm_peak, 4),
-                    "note": "this kernel is bound by the PCIe link, not HBM: see the `link` object",
-                    "launches": link_launches, "traffic": args.traffic_per_launch}
+    roofline = build_roofline([(st0, st1)], args)
 
     # ---------------- end-to-end arm: the engine's public API ----------------------------------
     e2e = None
     if not args.skip_e2e:
         e2e = run_e2e(args, pf, wl, rank, world, local, route)
 
+    concurrent = concurrent_pcie_ceiling(device, world) if world > 1 else None
+    barrier(world)
     ceiling = measure_pcie_ceiling(device) if rank == 0 else None
     cpu = None
     if rank == 0 and world == 1 and not args.skip_cpu_baseline:
@@ -582,7 +624,9 @@ def run_b200(args, rank, world, local):
                  "measured_ceiling_d2h": round(ceiling["d2h"], 2), "measured_ceiling_h2d": round(ceiling["h2d"], 2),
                  "save_frac_of_ceiling": round(save_gbs / ceiling["d2h"], 4),
                  "load_frac_of_ceiling": round(load_gbs / ceiling["h2d"], 4),
-                 "ceiling_how": "one 1 GiB pinned<->device cudaMemcpyAsync per direction, best of 5"},
+                 "ceiling_how": "one 1 GiB pinned<->device cudaMemcpyAsync per direction, best of 5, rank 0 alone",
+                 "all_ranks_at_once": concurrent,
+                 "value_frac_of_all_ranks_bound": round(value / concurrent["value_bound"], 4) if concurrent else None},
         "per_layer_save": {"first_layer_ms": round(first_layer_ms, 3), "all_layers_ms": round(all_layers_ms, 3),
                            "mean_layer_ms": round(all_layers_ms / L, 3), "layers": L,
                            "gbs": round(L * layer_bytes / 1e6 / all_layers_ms, 2),
@@ -596,7 +640,147 @@ def run_b200(args, rank, world, local):
     print(json.dumps(line))
 
 
-def run_e2e(args, pf, wl, rank, world, local, route):
+def run_duplex(args, rank, world, local):
+    """Save and load at the same time, as a serving rank does when one request's prefill is being
+    offloaded while another's prefix is being fetched: the save backend and the load backend of one
+    GPU run on their own streams, each driven by its own host thread (the engine's two workers per
+    GPU, gpu_worker.rs:161-262).  PCIe is full duplex, so the two directions add up.
+
+    Two sets of host images alternate: step k saves into set k % 2 while it loads from the other
+    set, which the step before filled.  Block ids saved from and loaded into are disjoint."""
+    import torch
+    import pegaflow_b200 as pf
+
+    device = torch.device("cuda", local)
+    spec = workloads()[args.workload]
+    wl = Workload(spec, device, 42 + 2 + rank)
+    L, seg, per, n_req = spec["layers"], spec["seg_bytes"], spec["blocks"], spec["requests"]
+    if 2 * n_req * per > spec["gpu_blocks"] - 1:
+        raise SystemExit("--duplex needs gpu_blocks > 2 * requests * blocks")
+    ids = np.random.default_rng(1000 + rank).permutation(spec["gpu_blocks"] - 1)[: 2 * n_req * per] + 1
+    wl.save_ids = [ids[r * per:(r + 1) * per].astype(np.uint32) for r in range(n_req)]
+    wl.load_ids = [ids[(n_req + r) * per:(n_req + r + 1) * per].astype(np.uint32) for r in range(n_req)]
+    route = {"auto": 0, "staged": 1, "zerocopy": 2}[args.route]
+    kw = dict(route=route, time_kernels=not args.no_kernel_timing, link_ctas=args.link_ctas,
+              staging_slot_bytes=args.slot_mib << 20, staging_slots=args.slots, copy_streams=args.copy_streams,
+              pack_ctas=args.pack_ctas)
+
+    pool = pf.PinnedPool(2 * wl.payload + (64 << 20), numa_node=pf.numa_node_of_device(local))
+    sets = [alloc_host_images(pool, wl) for _ in range(2)]
+    be_save, be_load = pf.TransferBackend(local, **kw), pf.TransferBackend(local, **kw)
+    save_x = [make_layer_xfers(pf, wl, a, wl.save_ids) for a in sets]
+    load_x = [make_layer_xfers(pf, wl, a, wl.load_ids) for a in sets]
+    s_save, s_load, main = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+
+    from concurrent.futures import ThreadPoolExecutor
+
+    threads = ThreadPoolExecutor(max_workers=2)
+
+    def issue_saves(k):
+        torch.cuda.set_device(local)
+        for x in save_x[k % 2]:
+            be_save.save_layers(x, s_save.cuda_stream)
+
+    def issue_loads(k):
+        torch.cuda.set_device(local)
+        for x in load_x[(k + 1) % 2]:
+            be_load.load_layers(x, s_load.cuda_stream)
+
+    def step(k, events=None):
+        # both directions start after everything of the step before (either stream) is done
+        s_save.wait_stream(main)
+        s_load.wait_stream(main)
+        if events:
+            events[0].record(s_save)
+            events[1].record(s_load)
+        jobs = [threads.submit(issue_saves, k), threads.submit(issue_loads, k)]
+        for j in jobs:
+            j.result()
+        if events:
+            events[2].record(s_save)
+            events[3].record(s_load)
+        main.wait_stream(s_save)
+        main.wait_stream(s_load)
+        if events:
+            events[4].record(main)
+
+    # prime set 1 so that step 0 has something to load; clear the destination blocks
+    for x in save_x[1]:
+        be_save.save_layers(x, s_save.cuda_stream)
+    s_save.synchronize()
+    every_dst = torch.from_numpy(np.concatenate(wl.load_ids).astype(np.int64)).to(device)
+    every_src = torch.from_numpy(np.concatenate(wl.save_ids).astype(np.int64)).to(device)
+    for l in range(L):
+        wl.kv[l][:, every_dst] = 0
+    torch.cuda.synchronize()
+
+    warm = max(3, args.warmup) if not args.allow_short_warmup else args.warmup
+    for k in range(warm):
+        step(k)
+    torch.cuda.synchronize()
+    st0 = [be_save.stats(), be_load.stats()]
+    barrier(world)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(args.steps)]
+    first = torch.cuda.Event(enable_timing=True)
+    first.record(main)
+    for k in range(args.steps):
+        step(warm + k, evs[k])
+    torch.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = barrier_and_max(first.elapsed_time(evs[-1][4]), world, device)
+    save_ms = sum(e[0].elapsed_time(e[2]) for e in evs)
+    load_ms = sum(e[1].elapsed_time(e[3]) for e in evs)
+    st1 = [be_save.stats(), be_load.stats()]
+    # bit-exactness of the timed path: what was loaded is what had been saved, for every layer
+    verified = all(torch.equal(wl.kv[l][:, every_dst], wl.kv[l][:, every_src]) for l in range(L))
+    status = be_save.stats()["device_status"] | be_load.stats()["device_status"]
+    del save_x, load_x
+    be_save.close()
+    be_load.close()
+    pool.close()
+    threads.shutdown()
+
+    value = 2 * wl.payload * args.steps * world / (total_ms / 1e3) / 1e9
+    roofline = build_roofline(list(zip(st0, st1)), args)
+    e2e = None
+    if not args.skip_e2e:
+        e2e = run_e2e(args, pf, wl, rank, world, local, route, duplex=True)
+    concurrent = concurrent_pcie_ceiling(device, world) if world > 1 else None
+    barrier(world)
+    ceiling = measure_pcie_ceiling(device) if rank == 0 else None
+    if rank != 0:
+        return
+    save_gbs = wl.payload * args.steps / (save_ms / 1e3) / 1e9
+    load_gbs = wl.payload * args.steps / (load_ms / 1e3) / 1e9
+    line = {
+        "metric": "kv_save_load_GBps", "value": round(value, 3), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(total_ms / args.steps, 3), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+        "config": {"workload": args.workload, **spec, "route": args.route,
+                   "mode": "duplex: every step saves one set of blocks and loads another at the same time",
+                   "between_iterations": "inputs (payload per direction per step far exceeds the 126 MB L2) are not "
+                                         "re-read from cache; no flush needed",
+                   "values": "bf16 N(0,1) from a seeded generator; disjoint save and load block ids by seeded permutation"},
+        "save_gbs": round(save_gbs, 3), "load_gbs": round(load_gbs, 3), "bit_exact": bool(verified),
+        "link": {"bound": "pcie_gen5_x16 full duplex", "peak_theoretical": round(2 * PCIE_GEN5_X16_GBS, 2),
+                 "measured_ceiling_d2h": round(ceiling["d2h"], 2), "measured_ceiling_h2d": round(ceiling["h2d"], 2),
+                 "value_frac_of_sum_of_ceilings": round(value / world / (ceiling["d2h"] + ceiling["h2d"]), 4),
+                 "ceiling_how": "one 1 GiB pinned<->device cudaMemcpyAsync per direction, best of 5, one direction "
+                                "at a time, rank 0 alone",
+                 "all_ranks_at_once": concurrent},
+        "roofline": roofline, "cpu_baseline": None, "e2e": e2e,
+        "gpu_launches": sum(b["kernel_launches"] - a["kernel_launches"] for a, b in zip(st0, st1)),
+        "dma_copies": sum(b["dma_copies"] - a["dma_copies"] for a, b in zip(st0, st1)), "device_status": status,
+        "clocks": clocks,
+    }
+    print(json.dumps(line))
+
+
+def run_e2e(args, pf, wl, rank, world, local, route, duplex=False):
     """Same workload through the engine API: register, batch_save per request (hashes, dedupe, pinned
     allocation, GPU batch, cache insert), prefix query + lease, batch_load into other block ids."""
     import torch
@@ -606,7 +790,8 @@ def run_e2e(args, pf, wl, rank, world, local, route):
     L, seg, per, n_req = spec["layers"], spec["seg_bytes"], spec["blocks"], spec["requests"]
     steps_total = args.steps + max(1, args.warmup)
     # room for one and a half steps' blocks: older steps are evicted (LRU) while a new one is saved
-    eng = pf.PegaEngine(wl.payload + wl.payload // 2 + (256 << 20), route=route, link_ctas=args.link_ctas,
+    # (duplex: two steps' blocks are live at once, the one being saved and the one being loaded)
+    eng = pf.PegaEngine((5 if duplex else 3) * wl.payload // 2 + (256 << 20), route=route, link_ctas=args.link_ctas,
                         staging_slot_bytes=args.slot_mib << 20, staging_slots=args.slots,
                         copy_streams=args.copy_streams)
     names = [f"model.layers.{l}.self_attn.attn" for l in range(L)]
@@ -631,10 +816,16 @@ def run_e2e(args, pf, wl, rank, world, local, route):
     callers = ThreadPoolExecutor(max_workers=2)
 
     def step(k):
-        list(callers.map(lambda req: eng.batch_save("bench", 0, 0, local, req[0]), prepared[k]))
-        eng.flush_saves()
+        if duplex:
+            # this step's saves run while the blocks of the step before are loaded
+            saving = [callers.submit(eng.batch_save, "bench", 0, 0, local, req[0]) for req in prepared[k]]
+            load_from = k - 1
+        else:
+            list(callers.map(lambda req: eng.batch_save("bench", 0, 0, local, req[0]), prepared[k]))
+            eng.flush_saves()
+            load_from = k
         pending = []
-        for r, (_, hashes) in enumerate(prepared[k]):
+        for r, (_, hashes) in enumerate(prepared[load_from] if load_from >= 0 else []):
             blocks, missing = eng.query_prefix("bench", hashes)
             if missing:
                 raise RuntimeError(f"prefix query missed {missing} blocks")
@@ -643,6 +834,10 @@ def run_e2e(args, pf, wl, rank, world, local, route):
         for p in pending:
             if p.wait(120) != 1:
                 raise RuntimeError("load failed: " + p.error())
+        if duplex:
+            for f in saving:
+                f.result()
+            eng.flush_saves()
 
     for k in range(max(1, args.warmup)):
         step(k)
@@ -660,7 +855,8 @@ def run_e2e(args, pf, wl, rank, world, local, route):
             "h2d_bytes_per_step": wl.payload, "d2h_bytes_per_step": wl.payload,
             "ms_per_step": round(elapsed / args.steps * 1e3, 3), "clock": "host wall clock around a synchronised region",
             "api": "pf_engine_batch_save / flush_saves / query_prefix / create_query_lease / batch_load_inproc, "
-                   "arguments marshalled once outside the timed region; saves issued from two caller threads",
+                   "arguments marshalled once outside the timed region; saves issued from two caller threads"
+                   + ("; each step's saves overlap the loads of the step before" if duplex else ""),
             "evicted_blocks": m["evicted_blocks"], "load_failures": m["load_failures"]}
 
 
@@ -771,6 +967,8 @@ def main():
     ap.add_argument("--allow-short-warmup", action="store_true", help="profiling runs only")
     ap.add_argument("--traffic-per-launch", type=float, default=None,
                     help="DRAM bytes per launch of the dominant kernel from an ncu capture (recorded in the line)")
+    ap.add_argument("--duplex", action="store_true",
+                    help="save and load at the same time (the TP=8 configuration's wording) instead of one after the other")
     ap.add_argument("--peer", action="store_true", help="measure the NVLink peer-copy path (one process, two GPUs)")
     args = ap.parse_args()
     if args.peer:
@@ -793,7 +991,7 @@ def main():
         return
     rank, world, local = dist_setup(args.gpus)
     try:
-        run_b200(args, rank, world, local)
+        (run_duplex if args.duplex else run_b200)(args, rank, world, local)
     except BaseException:
         # Leave at once: a clean process-group shutdown would wait for the other ranks, and the
         # launcher only stops them when it sees this rank die.

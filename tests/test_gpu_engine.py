@@ -358,3 +358,68 @@ def test_layerwise_async_save_and_per_layer_load_events(pf):
             assert np.array_equal(out.cpu().numpy(), want), "consumer ran before the layer's bytes had landed"
     finally:
         eng.close()
+
+
+@pytest.mark.parametrize("route", list(ROUTES))
+def test_saves_and_loads_running_at_once_stay_bit_exact(pf, route):
+    """The save worker and the load worker of one GPU run at the same time (gpu_worker.rs:161-262 gives
+    each its own thread and stream): a request's blocks are saved from one thread while another
+    request's stored blocks are loaded into different block ids; both results are checked byte for byte."""
+    import threading
+
+    eng = pf.PegaEngine(256 << 20, route=ROUTES[route], min_dma_bytes=64 << 10)
+    mem = CudaMem(0)
+    try:
+        n_layers, num_blocks, seg = 4, 512, 16384
+        layers = [sc.Layer(f"l{i}", num_blocks, seg, segments=2, kv_stride=num_blocks * seg) for i in range(n_layers)]
+        sc.register(eng, mem, "dx", "ns", layers)
+        fills = [sc.seeded_bytes(L.region_bytes, 300 + i) for i, L in enumerate(layers)]
+        for L, f in zip(layers, fills):
+            mem.write(L.buf, f)
+        rng = np.random.default_rng(77)
+        perm = (rng.permutation(num_blocks - 1) + 1).tolist()
+        first, dst = perm[:96], perm[96:192]
+        rounds = [perm[192 + 96 * k: 192 + 96 * (k + 1)] for k in range(3)]
+        h_first = sc.make_block_hashes(96, 40)
+        eng.batch_save("dx", 0, 0, 0, [(L.name, first, h_first) for L in layers])
+        eng.flush_saves()
+        blocks, missing = eng.query_prefix("dx", h_first)
+        assert missing == 0
+        names = [L.name for L in layers]
+        for k, ids in enumerate(rounds):
+            hk = sc.make_block_hashes(96, 41 + k)
+            errors = []
+
+            def saver():
+                try:
+                    eng.batch_save("dx", 0, 0, 0, [(L.name, ids, hk) for L in layers])
+                except Exception as e:   # surfaced below, on the test's thread
+                    errors.append(e)
+
+            t = threading.Thread(target=saver)
+            done = eng.batch_load_async("dx", 0, 0, [names], [(eng.create_query_lease("dx", blocks), [dst])])
+            t.start()
+            assert done.wait(20) == 1
+            t.join()
+            assert not errors, errors
+            eng.flush_saves()
+            mem.sync()
+            for li, (L, f) in enumerate(zip(layers, fills)):
+                got = mem.read(L.buf)
+                want = f.copy()
+                loaded = sc.expected_after_roundtrip(L, f, first, dst)
+                for d in dst:
+                    for off in (0, L.kv_stride):
+                        want[off + d * seg: off + (d + 1) * seg] = loaded[off + d * seg: off + (d + 1) * seg]
+                assert np.array_equal(got, want), f"round {k}: {L.name} differs after a load that overlapped a save"
+                for j in (0, 47, 95):
+                    img = eng.block_slot_image("dx", hk[j], li)
+                    assert img is not None
+                    b = ids[j]
+                    assert [bytes(x) for x in img] == [bytes(f[off + b * seg: off + (b + 1) * seg])
+                                                       for off in (0, L.kv_stride)]
+            for L, f in zip(layers, fills):   # the destinations get their own bytes back for the next round
+                mem.write(L.buf, f)
+        assert eng.metrics()["load_failures"] == 0
+    finally:
+        eng.close()
