@@ -32,6 +32,10 @@ namespace {
 
 constexpr int kLdstThreads = 256;
 constexpr int kLdstUnroll = 4;
+// Full occupancy (2048 threads per SM, so at most 32 registers per thread): with 4 KiB items a
+// thread has a single 16-byte load in flight per iteration, and the number of resident threads is
+// what keeps HBM busy (measured on 4 KiB items: 4 CTAs per SM 4.3 TB/s, 8 CTAs per SM 5.7 TB/s).
+constexpr int kLdstCtasPerSm = 8;
 constexpr uint32_t kPackChunk = 16384;   // bytes one CTA iteration of the ld/st kernel moves
 constexpr int kStages = 4;               // ring depth of the TMA kernels
 constexpr uint32_t kStageBytes = 32768;  // bytes per ring stage
@@ -102,10 +106,10 @@ struct DescGen {
   }
 };
 
-// CTA-wide copy of one span.  16-byte vectors when source and destination share their
-// misalignment (head bytes are peeled), plain bytes otherwise.  (L2 eviction-priority hints on
-// either side were measured and changed nothing: the staging slot stays in L2 without them.)
-__device__ __forceinline__ void copy_span(uint64_t dst, uint64_t src, uint32_t len) {
+// CTA-wide copy of one span, any alignment: 16-byte vectors when source and destination share
+// their misalignment (head bytes are peeled), plain bytes otherwise.  Kept out of line so that its
+// registers do not count against the aligned fast path below.
+__device__ __noinline__ void copy_span_any(uint64_t dst, uint64_t src, uint32_t len) {
   const uint32_t tid = threadIdx.x, nthr = blockDim.x;
   if (((dst ^ src) & 15ull) != 0) {
     char *d = reinterpret_cast<char *>(dst);
@@ -118,33 +122,46 @@ __device__ __forceinline__ void copy_span(uint64_t dst, uint64_t src, uint32_t l
   if (tid < head) reinterpret_cast<char *>(dst)[tid] = reinterpret_cast<const char *>(src)[tid];
   const int4 *s16 = reinterpret_cast<const int4 *>(src + head);
   int4 *d16 = reinterpret_cast<int4 *>(dst + head);
-  const uint32_t body = len - head;
-  const uint32_t n16 = body >> 4;
-  for (uint32_t j = tid; j < n16; j += nthr * kLdstUnroll) {
+  const uint32_t n16 = (len - head) >> 4;
+  for (uint32_t j = tid; j < n16; j += nthr) d16[j] = s16[j];
+  for (uint32_t j = head + (n16 << 4) + tid; j < len; j += nthr)
+    reinterpret_cast<char *>(dst)[j] = reinterpret_cast<const char *>(src)[j];
+}
+
+// CTA-wide copy of one span.  Fast path: both addresses and the length are multiples of 16, every
+// thread keeps kLdstUnroll independent 16-byte loads in flight (streamed past L1).  (L2
+// eviction-priority hints on either side were measured and changed nothing: the staging slot
+// stays in L2 without them.)
+template <bool kAligned = false>
+__device__ __forceinline__ void copy_span(uint64_t dst, uint64_t src, uint32_t len) {
+  if (!kAligned && ((dst | src | len) & 15ull) != 0) {
+    copy_span_any(dst, src, len);
+    return;
+  }
+  const int4 *s16 = reinterpret_cast<const int4 *>(src);
+  int4 *d16 = reinterpret_cast<int4 *>(dst);
+  const uint32_t n16 = len >> 4;
+  for (uint32_t j = threadIdx.x; j < n16; j += kLdstThreads * kLdstUnroll) {
     int4 v[kLdstUnroll];
 #pragma unroll
     for (int u = 0; u < kLdstUnroll; ++u) {
-      uint32_t jj = j + u * nthr;
-      if (jj < n16) {
+      const uint32_t jj = j + u * kLdstThreads;
+      if (jj < n16)
         asm volatile("ld.global.nc.L1::no_allocate.v4.s32 {%0,%1,%2,%3}, [%4];"
                      : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
                      : "l"(s16 + jj));
-      }
     }
 #pragma unroll
     for (int u = 0; u < kLdstUnroll; ++u) {
-      uint32_t jj = j + u * nthr;
+      const uint32_t jj = j + u * kLdstThreads;
       if (jj < n16) d16[jj] = v[u];
     }
   }
-  const uint32_t tail_at = head + (n16 << 4);
-  for (uint32_t j = tail_at + tid; j < len; j += nthr)
-    reinterpret_cast<char *>(dst)[j] = reinterpret_cast<const char *>(src)[j];
 }
 
 // `stamp` (optional) points at {first start, last end} in %globaltimer nanoseconds, pre-set to
 // {UINT64_MAX, 0}: a device-side measure of the launch that needs no event around it.
-__global__ void __launch_bounds__(kLdstThreads)
+__global__ void __launch_bounds__(kLdstThreads, kLdstCtasPerSm)
 copy_items_ldst(Side src, Side dst, uint32_t n_items, uint32_t item_bytes, uint32_t chunk_bytes,
                 unsigned long long *stamp) {
   if (stamp && threadIdx.x == 0) atomicMin(&stamp[0], (unsigned long long)global_timer_ns());
@@ -175,22 +192,31 @@ struct GroupParams {
   GroupUnit unit[kMaxGroupUnits];
 };
 
-__global__ void __launch_bounds__(kLdstThreads)
+// kAligned: the host has checked that every address and size in the group is a multiple of 16
+// (the usual case), so the kernel carries no byte path and fits 32 registers without spilling.
+template <bool kAligned>
+__global__ void __launch_bounds__(kLdstThreads, kLdstCtasPerSm)
 copy_group_ldst(const __grid_constant__ GroupParams p, int to_staging, unsigned long long *stamp) {
   if (stamp && threadIdx.x == 0) atomicMin(&stamp[0], (unsigned long long)global_timer_ns());
-  const uint64_t total = p.unit[p.n_units - 1].chunk_end;
-  uint32_t k = 0;
-  for (uint64_t c = blockIdx.x; c < total; c += gridDim.x) {
-    while (c >= p.unit[k].chunk_end) ++k;  // chunks are visited in ascending order
-    const GroupUnit &u = p.unit[k];
-    const uint64_t local = c - (k ? p.unit[k - 1].chunk_end : 0);
-    const uint32_t item = (uint32_t)(local / u.chunks_per_item);
-    const uint32_t off = (uint32_t)(local % u.chunks_per_item) * p.chunk_bytes;
-    const uint32_t len = min(p.chunk_bytes, u.item_bytes - off);
-    const uint64_t kv = side_addr(u.kv, item) + off;
-    const uint64_t st = u.slot_addr + (uint64_t)item * u.item_bytes + off;
-    if (to_staging) copy_span(st, kv, len);
-    else copy_span(kv, st, len);
+  // 32-bit chunk arithmetic: a group holds at most one staging slot of bytes
+  const uint32_t total = (uint32_t)p.unit[p.n_units - 1].chunk_end;
+  uint32_t k = 0, unit_begin = 0, unit_end = (uint32_t)p.unit[0].chunk_end;
+  for (uint32_t c = blockIdx.x; c < total; c += gridDim.x) {
+    while (c >= unit_end) {  // chunks are visited in ascending order
+      ++k;
+      unit_begin = unit_end;
+      unit_end = (uint32_t)p.unit[k].chunk_end;
+    }
+    const uint32_t local = c - unit_begin;
+    const uint32_t cpi = p.unit[k].chunks_per_item, item_bytes = p.unit[k].item_bytes;
+    const uint32_t item = local / cpi;
+    const uint32_t off = (local - item * cpi) * p.chunk_bytes;
+    const uint32_t len = min(p.chunk_bytes, item_bytes - off);
+    const uint32_t *ids = p.unit[k].kv.ids;
+    const uint64_t *table = p.unit[k].kv.table;
+    const uint64_t kv = (table ? table[item] : p.unit[k].kv.base + (uint64_t)(ids ? ids[item] : item) * p.unit[k].kv.stride) + off;
+    const uint64_t st = p.unit[k].slot_addr + (uint64_t)item * item_bytes + off;
+    copy_span<kAligned>(to_staging ? st : kv, to_staging ? kv : st, len);
   }
   if (stamp) {
     __syncthreads();
@@ -560,6 +586,7 @@ void TransferBackend::launch_group(char *slot_ptr, size_t first, size_t count, b
   p.n_units = (uint32_t)count;
   p.chunk_bytes = kPackChunk;
   uint64_t chunks = 0, payload = 0;
+  bool aligned = true;
   for (size_t i = 0; i < count; ++i) {
     const StagedUnit &u = group_[first + i];
     GroupUnit &g = p.unit[i];
@@ -567,6 +594,7 @@ void TransferBackend::launch_group(char *slot_ptr, size_t first, size_t count, b
     g.slot_addr = (uint64_t)(uintptr_t)(slot_ptr + u.slot_offset);
     g.item_bytes = (uint32_t)u.item_bytes;
     g.chunks_per_item = (uint32_t)((u.item_bytes + kPackChunk - 1) / kPackChunk);
+    aligned = aligned && !u.dev.table && (u.dev.base | u.dev.stride | g.slot_addr | u.item_bytes) % 16 == 0;
     chunks += (uint64_t)u.n_items * g.chunks_per_item;
     g.chunk_end = chunks;
     payload += (uint64_t)u.n_items * u.item_bytes;
@@ -580,7 +608,8 @@ void TransferBackend::launch_group(char *slot_ptr, size_t first, size_t count, b
     stamp_idx = (int)stamps_used_++;
     stamp = stamps_dev_ + 2 * (size_t)stamp_idx;
   }
-  copy_group_ldst<<<grid, kLdstThreads, 0, s>>>(p, to_staging ? 1 : 0, stamp);
+  if (aligned) copy_group_ldst<true><<<grid, kLdstThreads, 0, s>>>(p, to_staging ? 1 : 0, stamp);
+  else copy_group_ldst<false><<<grid, kLdstThreads, 0, s>>>(p, to_staging ? 1 : 0, stamp);
   PF_CUDA(cudaGetLastError());
   time_end(s, t0, 2 * payload, false, stamp_idx);
   ++stats_.kernel_launches;

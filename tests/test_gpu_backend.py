@@ -135,6 +135,10 @@ LAYER_CASES = [
     _layer_case("odd_bytes", 10, 1001, 1, 0, 0, 7, 0, 8),
     # a single block
     _layer_case("single", 4, 65536, 1, 0, 0, 1, 0, 9),
+    # small items that share a kernel chunk: 33 vectors per item, ragged last chunk
+    _layer_case("small_528", 700, 528, 2, 700 * 528, 0, 611, 0, 10),
+    # small items with a device stride that is not 16-byte aligned: one item per chunk, byte path
+    _layer_case("small_unaligned_stride", 300, 2048, 1, 0, 2052, 257, 0, 11),
 ]
 
 
