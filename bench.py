@@ -878,15 +878,20 @@ def run_peer(args):
     sids = (rng.permutation(nb - 1)[:n] + 1).astype(np.uint32)
     dids = (rng.permutation(nb - 1)[:n] + 1).astype(np.uint32)
     payload = L * n * 2 * seg
-    pf.enable_peer_access(1, 0)
-    be = pf.TransferBackend(1, link_ctas=args.link_ctas)
-    torch.cuda.set_device(1)
-    stream = torch.cuda.Stream(device=d1)
+    # The kernel runs on the destination GPU and reads across NVLink (pull), or with --peer-push on the
+    # source GPU and writes across it (push).
+    run_on = 0 if args.peer_push else 1
+    pf.enable_peer_access(run_on, 1 - run_on)
+    be = pf.TransferBackend(run_on, link_ctas=args.link_ctas)
+    torch.cuda.set_device(run_on)
+    stream = torch.cuda.Stream(device=torch.device("cuda", run_on))
+
+    src_layouts = [(src[l].data_ptr(), seg, nb * seg, seg, 2) for l in range(L)]
+    dst_layouts = [(dst[l].data_ptr(), seg, nb * seg, seg, 2) for l in range(L)]
 
     def peer_step():
-        for l in range(L):
-            be.peer_copy((src[l].data_ptr(), seg, nb * seg, seg, 2), sids, (dst[l].data_ptr(), seg, nb * seg, seg, 2), dids,
-                         stream.cuda_stream)
+        # what the engine's peer_load does: every layer of the hit in one call
+        be.peer_copy_layers(src_layouts, sids, dst_layouts, dids, stream.cuda_stream)
 
     for _ in range(max(3, args.warmup)):
         peer_step()
@@ -914,8 +919,8 @@ def run_peer(args):
     del big0, big1
     # the reference's way today: GPU 0 -> pinned host pool -> GPU 1
     pool = pf.PinnedPool(payload + (64 << 20))
-    be0 = pf.TransferBackend(0)
-    st0 = torch.cuda.Stream(device=d0)
+    be0, be1 = pf.TransferBackend(0), pf.TransferBackend(1)
+    st0, st1 = torch.cuda.Stream(device=d0), torch.cuda.Stream(device=d1)
     layers_save, layers_load = [], []
     for l in range(L):
         k, v = pool.alloc(n * seg), pool.alloc(n * seg)
@@ -930,15 +935,16 @@ def run_peer(args):
         t0 = time.perf_counter()
         be0.save_layers(xs, st0.cuda_stream)
         st0.synchronize()
-        be.load_layers(xl, stream.cuda_stream)
-        stream.synchronize()
+        be1.load_layers(xl, st1.cuda_stream)
+        st1.synchronize()
         t_host.append(time.perf_counter() - t0)
     host_gbs = payload / min(t_host) / 1e9
     stats = be.stats()
     print(json.dumps({
         "metric": "kv_peer_copy_GBps", "value": round(peer_gbs, 2), "unit": "GB/s", "n_gpus": 2, "steps": args.steps,
         "higher_is_better": True, "dtype": "u8", "data": "synthetic", "bit_exact": bool(ok),
-        "config": {"workload": "qwen3-32b-tp4-rank prefix hit", "layers": L, "seg_bytes": seg, "gpu_blocks": nb,
+        "config": {"workload": "qwen3-32b-tp4-rank prefix hit", "kernel_runs_on": "source GPU (push)" if args.peer_push
+                   else "destination GPU (pull)", "layers": L, "seg_bytes": seg, "gpu_blocks": nb,
                    "blocks": n, "segments": 2},
         "link": {"bound": "nvlink5", "peak_nominal": 900.0, "measured_ceiling": round(best, 1),
                  "frac_of_nominal": round(peer_gbs / 900.0, 4), "frac_of_ceiling": round(peer_gbs / best, 4),
@@ -969,6 +975,7 @@ def main():
                     help="DRAM bytes per launch of the dominant kernel from an ncu capture (recorded in the line)")
     ap.add_argument("--duplex", action="store_true",
                     help="save and load at the same time (the TP=8 configuration's wording) instead of one after the other")
+    ap.add_argument("--peer-push", action="store_true", help="with --peer: run the copy kernel on the source GPU")
     ap.add_argument("--peer", action="store_true", help="measure the NVLink peer-copy path (one process, two GPUs)")
     args = ap.parse_args()
     if args.peer:

@@ -110,7 +110,7 @@ typedef struct pf_backend_config {
   size_t staging_slot_bytes; /* bytes per HBM staging slot (0 = 32 MiB) */
   int staging_slots;         /* ring depth (0 = 4) */
   int pack_ctas;             /* CTAs of the HBM gather/scatter kernel (0 = 8 per SM) */
-  int link_ctas;             /* CTAs of the zero-copy / peer kernel (0 = 16 for PCIe, 2 per SM for NVLink) */
+  int link_ctas;             /* CTAs of the zero-copy / peer kernel (0 = 16 for PCIe, 8 per SM for NVLink) */
   size_t min_dma_bytes;      /* smallest host-contiguous run sent through the copy engine (0 = 256 KiB) */
   int route;                 /* enum pf_route */
   int time_kernels;          /* 1: bracket every kernel launch with CUDA events (see pf_backend_stats) */
@@ -178,6 +178,11 @@ typedef struct pf_device_layout {
 int pf_backend_peer_copy(pf_backend *backend, const pf_device_layout *src, const uint32_t *src_ids,
                          const pf_device_layout *dst, const uint32_t *dst_ids, size_t n_blocks,
                          void *stream);
+/* The same for `n_layers` layers that share the block ids (a whole model's prefix hit): the ids
+ * are uploaded once and up to 96 (layer, range) units of equal block size go into one launch. */
+int pf_backend_peer_copy_layers(pf_backend *backend, const pf_device_layout *src, const pf_device_layout *dst,
+                                size_t n_layers, const uint32_t *src_ids, const uint32_t *dst_ids,
+                                size_t n_blocks, void *stream);
 /* Make `peer_device`'s memory addressable from `device_id` (cudaDeviceEnablePeerAccess). */
 int pf_enable_peer_access(int device_id, int peer_device);
 

@@ -153,6 +153,24 @@ class TransferBackend:
         N.check(N.lib.pf_backend_peer_copy(self._h, C.byref(s), sa.ctypes.data_as(U), C.byref(d), da.ctypes.data_as(U), n,
                                            C.c_void_p(stream or None)))
 
+    def peer_copy_layers(self, src_layouts, src_ids, dst_layouts, dst_ids, stream: int = 0):
+        """One call for every layer of a prefix hit: the layers share the block ids."""
+        import numpy as np
+
+        n = len(src_ids)
+        if len(dst_ids) != n:
+            raise N.PegaflowInvalidArgument(3, "invalid argument: peer copy needs one destination per source block")
+        if len(src_layouts) != len(dst_layouts):
+            raise N.PegaflowInvalidArgument(3, "invalid argument: peer copy needs one destination layout per source layout")
+        sa = np.ascontiguousarray(src_ids, dtype=np.uint32)
+        da = np.ascontiguousarray(dst_ids, dtype=np.uint32)
+        L = len(src_layouts)
+        s = (N.DeviceLayout * L)(*[N.DeviceLayout(*x) for x in src_layouts])
+        d = (N.DeviceLayout * L)(*[N.DeviceLayout(*x) for x in dst_layouts])
+        U = C.POINTER(C.c_uint32)
+        N.check(N.lib.pf_backend_peer_copy_layers(self._h, s, d, L, sa.ctypes.data_as(U), da.ctypes.data_as(U), n,
+                                                  C.c_void_p(stream or None)))
+
     def stats(self) -> dict:
         st = N.BackendStats()
         N.check(N.lib.pf_backend_get_stats(self._h, C.byref(st)))

@@ -128,6 +128,17 @@ int pf_backend_peer_copy(pf_backend *backend, const pf_device_layout *src, const
   });
 }
 
+int pf_backend_peer_copy_layers(pf_backend *backend, const pf_device_layout *src, const pf_device_layout *dst,
+                                size_t n_layers, const uint32_t *src_ids, const uint32_t *dst_ids, size_t n_blocks,
+                                void *stream) {
+  return guarded([&] {
+    if (!backend) throw Error::invalid("peer copy: null backend");
+    if (n_layers && (!src || !dst)) throw Error::invalid("peer copy: null layout array");
+    if (n_blocks && (!src_ids || !dst_ids)) throw Error::invalid("peer copy: null block id array");
+    backend->impl.peer_copy_layers(src, dst, n_layers, src_ids, dst_ids, n_blocks, (cudaStream_t)stream);
+  });
+}
+
 int pf_enable_peer_access(int device_id, int peer_device) {
   return guarded([&] { enable_peer_access(device_id, peer_device); });
 }

@@ -1232,7 +1232,12 @@ void Engine::peer_load(const std::string &src_instance, int src_device, const st
   auto finished = done->get_future();
   dst->load_worker->submit([=](TransferBackend &backend, cudaStream_t stream) {
     try {
-      for (auto &p : *pairs) backend.peer_copy(p.s, sids->data(), p.d, dids->data(), sids->size(), stream);
+      std::vector<pf_device_layout> from, to;
+      for (auto &p : *pairs) {
+        from.push_back(p.s);
+        to.push_back(p.d);
+      }
+      backend.peer_copy_layers(from.data(), to.data(), from.size(), sids->data(), dids->data(), sids->size(), stream);
       cuda_or_storage(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
       done->set_value();
     } catch (...) {

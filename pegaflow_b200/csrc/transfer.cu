@@ -175,6 +175,57 @@ copy_items_ldst(Side src, Side dst, uint32_t n_items, uint32_t item_bytes, uint3
   }
 }
 
+// The NVLink peer path.  Warp-granular copy of equally sized, 16-byte aligned blocks between two
+// scattered sides: every warp moves pieces of kWarpPiece bytes on its own (no CTA-wide step), 4
+// independent 16-byte loads per lane.  The reads cross the link (the kernel runs on the
+// destination GPU), and with 2048 resident threads per SM there are enough of them in flight to
+// cover its latency whatever the block size.  Measured on scattered 4 / 8 / 32 KiB blocks between
+// two B200s: 676 / 670 / 677 GB/s, against 525 / 637 / 653 for a bulk-copy (TMA) ring and 775 for
+// one large cudaMemcpy; running on the source GPU (stores across the link) gave 625.
+// One launch covers up to kMaxPeerUnits (layer, range) units that share block ids and size, so a
+// whole model's layers take a handful of launches and one upload of the ids.
+constexpr uint32_t kWarpPiece = 32 * 16 * kLdstUnroll;
+constexpr int kMaxPeerUnits = 96;
+struct PeerUnit {
+  uint64_t src_base, src_stride, dst_base, dst_stride;
+};
+struct PeerParams {
+  const uint32_t *src_ids, *dst_ids;
+  uint32_t n_units, n_items, item_bytes, pieces_per_item;
+  PeerUnit unit[kMaxPeerUnits];
+};
+__global__ void __launch_bounds__(kLdstThreads, kLdstCtasPerSm)
+copy_peer_warp(const __grid_constant__ PeerParams p) {
+  const uint32_t lane = threadIdx.x & 31;
+  const uint32_t per_unit = p.n_items * p.pieces_per_item;  // the host keeps this below 2^32
+  const uint64_t total = (uint64_t)p.n_units * per_unit;
+  const uint64_t n_warps = (uint64_t)gridDim.x * (kLdstThreads / 32);
+  for (uint64_t c = (uint64_t)blockIdx.x * (kLdstThreads / 32) + (threadIdx.x >> 5); c < total; c += n_warps) {
+    const uint32_t k = (uint32_t)(c / per_unit);
+    const uint32_t r = (uint32_t)(c - (uint64_t)k * per_unit);
+    const uint32_t item = r / p.pieces_per_item;
+    const uint32_t off = (r - item * p.pieces_per_item) * kWarpPiece;
+    const uint32_t n16 = min(kWarpPiece, p.item_bytes - off) >> 4;
+    const int4 *s16 =
+        reinterpret_cast<const int4 *>(p.unit[k].src_base + (uint64_t)p.src_ids[item] * p.unit[k].src_stride + off);
+    int4 *d16 = reinterpret_cast<int4 *>(p.unit[k].dst_base + (uint64_t)p.dst_ids[item] * p.unit[k].dst_stride + off);
+    int4 v[kLdstUnroll];
+#pragma unroll
+    for (int u = 0; u < kLdstUnroll; ++u) {
+      const uint32_t jj = lane + u * 32;
+      if (jj < n16)
+        asm volatile("ld.global.nc.L1::no_allocate.v4.s32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
+                     : "l"(s16 + jj));
+    }
+#pragma unroll
+    for (int u = 0; u < kLdstUnroll; ++u) {
+      const uint32_t jj = lane + u * 32;
+      if (jj < n16) d16[jj] = v[u];
+    }
+  }
+}
+
 // One launch for a whole staging group: up to kMaxGroupUnits runs of equally sized items, each
 // with its own KV-side addressing, laid back to back in the staging slot.  `to_staging` selects
 // the direction.  The unit table travels in the kernel parameters (no upload).
@@ -618,20 +669,21 @@ void TransferBackend::launch_group(char *slot_ptr, size_t first, size_t count, b
 void TransferBackend::launch_link(const Side &src, const Side &dst, size_t n_items, size_t item_bytes,
                                   cudaStream_t s, bool peer) {
   if (n_items == 0) return;
-  // Bulk async copies need 16-byte aligned addresses and sizes.  Affine sides are checked here;
+  // Bulk async copies and the vector kernels need 16-byte aligned addresses and sizes.  Affine sides are checked here;
   // whoever fills an address table clears tables_aligned_ when an entry is not aligned.
   auto aligned16 = [](const Side &x) { return x.table != nullptr || ((x.base | x.stride) & 15ull) == 0; };
-  bool tma_ok = aligned16(src) && aligned16(dst) && (item_bytes & 15u) == 0 && tables_aligned_;
-  int ctas = cfg_.link_ctas > 0 ? cfg_.link_ctas : (peer ? 2 * sm_count_ : 16);
+  const bool all16 = aligned16(src) && aligned16(dst) && (item_bytes & 15u) == 0 && tables_aligned_;
+  int ctas = cfg_.link_ctas > 0 ? cfg_.link_ctas : 16;
   cudaEvent_t t0;
   time_begin(s, &t0);
-  if (tma_ok) {
+  if (all16 && !peer) {
     const uint32_t stage = (uint32_t)std::min<size_t>(kStageBytes, item_bytes);
     const uint64_t chunks = (uint64_t)n_items * ((item_bytes + stage - 1) / stage);
     const int grid = (int)std::min<uint64_t>(chunks, (uint64_t)ctas);
     copy_items_tma<<<grid, 32, (size_t)kStages * stage, s>>>(src, dst, (uint32_t)n_items, (uint32_t)item_bytes, stage,
                                                              status_dev_);
   } else {
+    // unaligned geometry (and, over NVLink, the rare unit that copy_peer_warp cannot take)
     const uint64_t chunks = (uint64_t)n_items * ((item_bytes + kPackChunk - 1) / kPackChunk);
     const int grid = (int)std::min<uint64_t>(chunks, (uint64_t)(peer ? std::max(ctas, cfg_.pack_ctas) : std::max(ctas, sm_count_)));
     copy_items_ldst<<<grid, kLdstThreads, 0, s>>>(src, dst, (uint32_t)n_items, (uint32_t)item_bytes, kPackChunk,
@@ -1056,27 +1108,72 @@ void TransferBackend::copy_descs(const pf_copy_desc *copies, size_t n, bool host
 
 void TransferBackend::peer_copy(const pf_device_layout &src, const uint32_t *src_ids, const pf_device_layout &dst,
                                 const uint32_t *dst_ids, size_t n_blocks, cudaStream_t stream) {
-  if (n_blocks == 0) return;
+  peer_copy_layers(&src, &dst, 1, src_ids, dst_ids, n_blocks, stream);
+}
+
+void TransferBackend::peer_copy_layers(const pf_device_layout *src, const pf_device_layout *dst, size_t n_layers,
+                                       const uint32_t *src_ids, const uint32_t *dst_ids, size_t n_blocks,
+                                       cudaStream_t stream) {
+  if (n_blocks == 0 || n_layers == 0) return;
   DeviceGuard on_device(device_);
-  if (src.n_ranges != dst.n_ranges || src.range_bytes != dst.range_bytes)
-    throw Error::invalid("peer copy needs the same block geometry on both sides");
-  if (src.n_ranges < 1 || src.n_ranges > 2 || src.range_bytes == 0 || src.range_bytes > 0xFFFFFFFFull)
-    throw Error::invalid("peer copy: unsupported block geometry");
+  for (size_t l = 0; l < n_layers; ++l) {
+    if (src[l].n_ranges != dst[l].n_ranges || src[l].range_bytes != dst[l].range_bytes)
+      throw Error::invalid("peer copy needs the same block geometry on both sides");
+    if (src[l].n_ranges < 1 || src[l].n_ranges > 2 || src[l].range_bytes == 0 || src[l].range_bytes > 0xFFFFFFFFull)
+      throw Error::invalid("peer copy: unsupported block geometry");
+  }
   if (n_blocks > 0xFFFFFFFFull) throw Error::invalid("peer copy: too many blocks");
+  // one upload of the ids serves every layer
   const size_t ids_bytes = align_up(n_blocks * sizeof(uint32_t), 256);
   const size_t base = meta_alloc(2 * ids_bytes);
   std::memcpy(meta_host_ + base, src_ids, n_blocks * sizeof(uint32_t));
   std::memcpy(meta_host_ + base + ids_bytes, dst_ids, n_blocks * sizeof(uint32_t));
   meta_upload(base, 2 * ids_bytes, stream);
+  const uint32_t *sids_dev = reinterpret_cast<const uint32_t *>(meta_dev_ + base);
+  const uint32_t *dids_dev = reinterpret_cast<const uint32_t *>(meta_dev_ + base + ids_bytes);
   tables_aligned_ = true;
-  for (uint32_t r = 0; r < src.n_ranges; ++r) {
-    const Side s{src.data_ptr + (uint64_t)r * src.kv_stride_bytes, src.block_stride_bytes,
-                 reinterpret_cast<const uint32_t *>(meta_dev_ + base), nullptr};
-    const Side d{dst.data_ptr + (uint64_t)r * dst.kv_stride_bytes, dst.block_stride_bytes,
-                 reinterpret_cast<const uint32_t *>(meta_dev_ + base + ids_bytes), nullptr};
-    launch_link(s, d, n_blocks, src.range_bytes, stream, true);
-    stats_.bytes_peer += n_blocks * src.range_bytes;
+
+  PeerParams p;
+  p.src_ids = sids_dev;
+  p.dst_ids = dids_dev;
+  p.n_items = (uint32_t)n_blocks;
+  p.n_units = 0;
+  p.item_bytes = 0;
+  auto flush = [&]() {
+    if (p.n_units == 0) return;
+    const uint64_t pieces = (uint64_t)p.n_units * p.n_items * p.pieces_per_item;
+    const uint64_t want = (pieces + kLdstThreads / 32 - 1) / (kLdstThreads / 32);
+    const int ctas = cfg_.link_ctas > 0 ? cfg_.link_ctas : cfg_.pack_ctas;
+    cudaEvent_t t0;
+    time_begin(stream, &t0);
+    copy_peer_warp<<<(int)std::min<uint64_t>(want, (uint64_t)ctas), kLdstThreads, 0, stream>>>(p);
+    PF_CUDA(cudaGetLastError());
+    time_end(stream, t0, (uint64_t)p.n_units * p.n_items * p.item_bytes, true, -1);
+    ++stats_.kernel_launches;
+    p.n_units = 0;
+  };
+  for (size_t l = 0; l < n_layers; ++l) {
+    const size_t bytes = src[l].range_bytes;
+    const uint64_t pieces_per_item = (bytes + kWarpPiece - 1) / kWarpPiece;
+    for (uint32_t r = 0; r < src[l].n_ranges; ++r) {
+      const uint64_t sb = src[l].data_ptr + (uint64_t)r * src[l].kv_stride_bytes;
+      const uint64_t db = dst[l].data_ptr + (uint64_t)r * dst[l].kv_stride_bytes;
+      const bool fits = ((sb | db | src[l].block_stride_bytes | dst[l].block_stride_bytes | bytes) & 15ull) == 0 &&
+                        n_blocks * pieces_per_item <= 0xFFFFFFFFull;
+      if (!fits) {
+        flush();
+        launch_link(Side{sb, src[l].block_stride_bytes, sids_dev, nullptr},
+                    Side{db, dst[l].block_stride_bytes, dids_dev, nullptr}, n_blocks, bytes, stream, true);
+      } else {
+        if (p.n_units == kMaxPeerUnits || (p.n_units && p.item_bytes != bytes)) flush();
+        p.item_bytes = (uint32_t)bytes;
+        p.pieces_per_item = (uint32_t)pieces_per_item;
+        p.unit[p.n_units++] = PeerUnit{sb, src[l].block_stride_bytes, db, dst[l].block_stride_bytes};
+      }
+      stats_.bytes_peer += n_blocks * bytes;
+    }
   }
+  flush();
   cudaEvent_t ev = take_event();
   PF_CUDA(cudaEventRecord(ev, stream));
   meta_inflight_.push_back({base, base + 2 * ids_bytes, ev});

@@ -48,6 +48,9 @@ class TransferBackend {
                    void *const *layer_done);
   void peer_copy(const pf_device_layout &src, const uint32_t *src_ids, const pf_device_layout &dst,
                  const uint32_t *dst_ids, size_t n_blocks, cudaStream_t stream);
+  // The same for several layers that share the block ids: one upload of the ids, a few launches.
+  void peer_copy_layers(const pf_device_layout *src, const pf_device_layout *dst, size_t n_layers,
+                        const uint32_t *src_ids, const uint32_t *dst_ids, size_t n_blocks, cudaStream_t stream);
   void stats(pf_backend_stats *out);
 
  private:

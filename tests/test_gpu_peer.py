@@ -81,3 +81,42 @@ def test_backend_peer_copy_unaligned_geometry(env):
         want[d_ * bb:(d_ + 1) * bb] = data[s_ * bb:(s_ + 1) * bb]
     assert np.array_equal(mem.read(dst), want)
     be.close()
+
+
+def test_backend_peer_copy_layers_mixed_geometry(env):
+    """Layers with different block sizes, one of them not a multiple of 16 bytes, in one call: the
+    aligned ones share launches of the warp kernel, the odd one takes the byte path; more (layer,
+    range) units than one launch holds."""
+    pf, torch = env
+    mem = CudaMem(0)
+    rng = np.random.default_rng(23)
+    nb, n = 96, 50
+    shapes = [(8192, 2)] * 60 + [(1001, 1), (4096, 2), (2064, 1)] + [(8192, 2)] * 3   # 60*2 units > 96 per launch
+    sids = (rng.permutation(nb)[:n]).astype(np.uint32)
+    dids = (rng.permutation(nb)[:n]).astype(np.uint32)
+    srcs, dsts, fills, s_lay, d_lay = [], [], [], [], []
+    for i, (bb, ranges) in enumerate(shapes):
+        region = ranges * nb * bb
+        a, b = mem.alloc(region), mem.alloc(region)
+        f = sc.seeded_bytes(region, 900 + i)
+        mem.write(a, f)
+        mem.zero(b)
+        srcs.append(a), dsts.append(b), fills.append(f)
+        s_lay.append((a.data_ptr(), bb, nb * bb, bb, ranges))
+        d_lay.append((b.data_ptr(), bb, nb * bb, bb, ranges))
+    be = pf.TransferBackend(0)
+    before = be.stats()["kernel_launches"]
+    be.peer_copy_layers(s_lay, sids, d_lay, dids, 0)
+    mem.sync()
+    for (bb, ranges), f, b in zip(shapes, fills, dsts):
+        want = np.zeros(ranges * nb * bb, dtype=np.uint8)
+        for r in range(ranges):
+            for s_, d_ in zip(sids.tolist(), dids.tolist()):
+                want[(r * nb + d_) * bb:(r * nb + d_ + 1) * bb] = f[(r * nb + s_) * bb:(r * nb + s_ + 1) * bb]
+        assert np.array_equal(mem.read(b), want), f"block size {bb} x {ranges} ranges differs"
+    st = be.stats()
+    assert st["device_status"] == 0
+    assert st["bytes_peer"] == sum(bb * ranges for bb, ranges in shapes) * n
+    # 120 units of 8 KiB -> 2 launches, the byte-path layer 1, 4 KiB 1, 2064 B 1, the last three 8 KiB layers 1
+    assert st["kernel_launches"] - before == 6
+    be.close()
