@@ -860,6 +860,66 @@ def run_e2e(args, pf, wl, rank, world, local, route, duplex=False):
             "evicted_blocks": m["evicted_blocks"], "load_failures": m["load_failures"]}
 
 
+def peer_pairs_phase(pf, torch, n_pairs, args, L, seg, nb, n):
+    """`n_pairs` prefix hits at once: instance B's rank i (GPU n_pairs + i) pulls the blocks of instance A's
+    rank i (GPU i), rank-aligned shards of two instances with the same TP degree.  No collective."""
+    payload = L * n * 2 * seg
+    pairs = []
+    for i in range(n_pairs):
+        s_dev, d_dev = i, n_pairs + i
+        rng = np.random.default_rng(4200 + i)
+        ds, dd = torch.device("cuda", s_dev), torch.device("cuda", d_dev)
+        src = [torch.randint(0, 256, (2, nb, seg), dtype=torch.uint8, device=ds) for _ in range(L)]
+        dst = [torch.zeros((2, nb, seg), dtype=torch.uint8, device=dd) for _ in range(L)]
+        sids = (rng.permutation(nb - 1)[:n] + 1).astype(np.uint32)
+        dids = (rng.permutation(nb - 1)[:n] + 1).astype(np.uint32)
+        pf.enable_peer_access(d_dev, s_dev)
+        be = pf.TransferBackend(d_dev, link_ctas=args.link_ctas)
+        torch.cuda.set_device(d_dev)
+        pairs.append(dict(src=src, dst=dst, sids=sids, dids=dids, be=be, stream=torch.cuda.Stream(device=dd),
+                          sl=[(t.data_ptr(), seg, nb * seg, seg, 2) for t in src],
+                          dl=[(t.data_ptr(), seg, nb * seg, seg, 2) for t in dst], dev=d_dev, ds=ds, dd=dd))
+
+    def enqueue(steps, events=False):
+        for p in pairs:
+            torch.cuda.set_device(p["dev"])
+            if events:
+                p["a"] = torch.cuda.Event(enable_timing=True)
+                p["b"] = torch.cuda.Event(enable_timing=True)
+                p["a"].record(p["stream"])
+            for _ in range(steps):
+                p["be"].peer_copy_layers(p["sl"], p["sids"], p["dl"], p["dids"], p["stream"].cuda_stream)
+            if events:
+                p["b"].record(p["stream"])
+
+    def sync_all():
+        for p in pairs:
+            p["stream"].synchronize()
+
+    enqueue(max(3, args.warmup))
+    sync_all()
+    ok = True
+    for p in pairs:
+        si = torch.from_numpy(p["sids"].astype(np.int64))
+        di = torch.from_numpy(p["dids"].astype(np.int64))
+        ok = ok and all(torch.equal(p["dst"][l][:, di.to(p["dd"])].cpu(), p["src"][l][:, si.to(p["ds"])].cpu())
+                        for l in (0, L - 1))
+    t0 = time.perf_counter()
+    enqueue(args.steps, events=True)
+    sync_all()
+    wall = time.perf_counter() - t0
+    per_pair = [round(payload * args.steps / 1e6 / p["a"].elapsed_time(p["b"]), 2) for p in pairs]
+    status = 0
+    for p in pairs:
+        status |= p["be"].stats()["device_status"]
+        p["be"].close()
+    return {"pairs": [[i, n_pairs + i] for i in range(n_pairs)], "per_pair_GBps": per_pair,
+            "aggregate_GBps": round(n_pairs * payload * args.steps / wall / 1e9, 2), "bit_exact": bool(ok),
+            "device_status": status,
+            "how": "per pair: CUDA events on the pair's stream; aggregate: all pairs' bytes over the host wall clock "
+                   "from the first enqueue to the last stream's completion"}
+
+
 def run_peer(args):
     """Same-box prefix hit: blocks of instance A (GPU 0) land in other block ids of instance B (GPU 1),
     over NVLink with the peer-copy kernel and, for comparison, through the pinned host pool.
@@ -940,6 +1000,15 @@ def run_peer(args):
         t_host.append(time.perf_counter() - t0)
     host_gbs = payload / min(t_host) / 1e9
     stats = be.stats()
+    concurrent = None
+    if args.peer_pairs > 1:
+        if torch.cuda.device_count() < 2 * args.peer_pairs:
+            concurrent = {"unavailable": f"{args.peer_pairs} pairs need {2 * args.peer_pairs} GPUs"}
+        else:
+            del src, dst
+            be.close(), be0.close(), be1.close(), pool.close()
+            torch.cuda.empty_cache()
+            concurrent = peer_pairs_phase(pf, torch, args.peer_pairs, args, L, seg, nb, n)
     print(json.dumps({
         "metric": "kv_peer_copy_GBps", "value": round(peer_gbs, 2), "unit": "GB/s", "n_gpus": 2, "steps": args.steps,
         "higher_is_better": True, "dtype": "u8", "data": "synthetic", "bit_exact": bool(ok),
@@ -950,6 +1019,7 @@ def run_peer(args):
                  "frac_of_nominal": round(peer_gbs / 900.0, 4), "frac_of_ceiling": round(peer_gbs / best, 4),
                  "ceiling_how": "one 1 GiB device-to-device copy GPU0 -> GPU1, best of 6"},
         "via_host_pool_GBps": round(host_gbs, 2), "speedup_vs_host_pool": round(peer_gbs / host_gbs, 2),
+        "concurrent_pairs": concurrent,
         "gpu_launches": stats["kernel_launches"], "device_status": stats["device_status"]}))
 
 
@@ -975,6 +1045,8 @@ def main():
                     help="DRAM bytes per launch of the dominant kernel from an ncu capture (recorded in the line)")
     ap.add_argument("--duplex", action="store_true",
                     help="save and load at the same time (the TP=8 configuration's wording) instead of one after the other")
+    ap.add_argument("--peer-pairs", type=int, default=1,
+                    help="with --peer: also run this many GPU i -> GPU pairs+i copies at once (needs 2 x pairs GPUs)")
     ap.add_argument("--peer-push", action="store_true", help="with --peer: run the copy kernel on the source GPU")
     ap.add_argument("--peer", action="store_true", help="measure the NVLink peer-copy path (one process, two GPUs)")
     args = ap.parse_args()
