@@ -64,11 +64,18 @@ size_t ReadCache::evict_lru(size_t n) {
   std::vector<BlockRef> dropped;  // destroyed outside the lock (frees pool memory)
   {
     std::lock_guard<std::mutex> g(mu_);
-    while (n-- && !lru_.empty()) {
+    // Every resident block is looked at once at most.  A block that someone else still holds (a
+    // lease, a load in flight, a handle given to the caller) frees nothing when dropped and must
+    // stay findable: it is skipped and its recency refreshed (storage/read_cache.rs:362-389).
+    for (size_t candidates = lru_.size(); candidates > 0 && dropped.size() < n; --candidates) {
       auto it = map_.find(lru_.back());
-      dropped.push_back(std::move(it->second.block));
-      map_.erase(it);
-      lru_.pop_back();
+      if (it->second.block.use_count() == 1) {
+        dropped.push_back(std::move(it->second.block));
+        map_.erase(it);
+        lru_.pop_back();
+      } else {
+        lru_.splice(lru_.begin(), lru_, it->second.pos);
+      }
     }
   }
   return dropped.size();

@@ -276,6 +276,83 @@ def test_pool_exhaustion_evicts_lru_then_fails(pf):
         eng.close()
 
 
+def _eviction_env(pf, instance, **kw):
+    """tests/eviction.rs:12-25: one layer of 4 blocks x 4096 bytes, a pool that holds two batches."""
+    eng = pf.PegaEngine(4 * 4096 * 2, enable_numa_affinity=False, **kw)
+    mem = CudaMem(0)
+    L = sc.Layer("layer_0", 4, 4096)
+    sc.register(eng, mem, instance, "ns-evict", [L])
+    return eng, mem, L
+
+
+def _load_and_read(eng, mem, L, instance, lease, n):
+    mem.zero(L.buf)
+    eng.batch_load(instance, 0, 0, [["layer_0"]], [(lease, [list(range(n))])])
+    mem.sync()
+    return mem.read(L.buf)
+
+
+@pytest.mark.parametrize("shards", [1, 2])
+def test_eviction_reclaims_old_blocks_for_new(pf, shards):
+    """tests/eviction.rs:27-49 and :84-107 (the same with pool_shards = 2): blocks saved after the GPU
+    data was overwritten load the overwritten data, whatever had to be evicted for them."""
+    eng, mem, L = _eviction_env(pf, "inst-evict", pool_shards=shards)
+    try:
+        mem.write(L.buf, sc.fill_pattern(4, 4096))
+        eng.batch_save("inst-evict", 0, 0, 0, [("layer_0", [0, 1, 2, 3], sc.make_block_hashes(4, 1))])
+        eng.flush_saves()
+        fresh = sc.fill_pattern(4, 4096, delta=42)
+        mem.write(L.buf, fresh)
+        new = sc.make_block_hashes(4, 2)
+        eng.batch_save("inst-evict", 0, 0, 0, [("layer_0", [0, 1, 2, 3], new)])
+        eng.flush_saves()
+        third = sc.make_block_hashes(4, 3)
+        eng.batch_save("inst-evict", 0, 0, 0, [("layer_0", [0, 1, 2, 3], third)])   # cannot fit without eviction
+        eng.flush_saves()
+        assert eng.metrics()["evicted_blocks"] >= 1
+        for hashes in (new, third):
+            blocks, missing = eng.query_prefix("inst-evict", hashes)
+            if missing:
+                continue   # this batch was the one reclaimed
+            got = _load_and_read(eng, mem, L, "inst-evict", eng.create_query_lease("inst-evict", blocks), 4)
+            assert np.array_equal(got, fresh)
+        assert eng.query_prefix("inst-evict", third)[1] == 0
+    finally:
+        eng.close()
+
+
+def test_leased_blocks_survive_eviction_pressure(pf):
+    """tests/eviction.rs:51-81: a query lease pins its blocks' memory and their cache entries; pressure
+    reclaims the unleased batch instead."""
+    eng, mem, L = _eviction_env(pf, "inst-lease")
+    try:
+        fill = sc.fill_pattern(4, 4096)
+        mem.write(L.buf, fill)
+        hashes = sc.make_block_hashes(4, 10)
+        eng.batch_save("inst-lease", 0, 0, 0, [("layer_0", [0, 1, 2, 3], hashes)])
+        eng.flush_saves()
+        blocks, missing = eng.query_prefix("inst-lease", hashes)
+        assert missing == 0
+        lease = eng.create_query_lease("inst-lease", blocks)
+        del blocks    # the lease alone pins them from here on
+        reclaimed = sc.make_block_hashes(4, 20)
+        eng.batch_save("inst-lease", 0, 0, 0, [("layer_0", [0, 1, 2, 3], reclaimed)])
+        eng.flush_saves()
+        pressure = sc.make_block_hashes(4, 21)
+        eng.batch_save("inst-lease", 0, 0, 0, [("layer_0", [0, 1, 2, 3], pressure)])
+        eng.flush_saves()
+        assert len(eng.query_prefix("inst-lease", reclaimed)[0]) == 0
+        again, missing = eng.query_prefix("inst-lease", hashes)
+        assert missing == 0 and len(again) == 4
+        second = eng.create_query_lease("inst-lease", again)
+        del again
+        assert eng.release_query_lease(second) is True
+        got = _load_and_read(eng, mem, L, "inst-lease", lease, 4)
+        assert np.array_equal(got, fill)
+    finally:
+        eng.close()
+
+
 def test_load_state_shm_completion_and_failure(pf):
     """lib.rs:654-680 + sync_state.rs: a cross-process style load completes through the
     shared-memory word; a pre-submit error flips it to ERROR."""
