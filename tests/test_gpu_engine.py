@@ -500,3 +500,93 @@ def test_saves_and_loads_running_at_once_stay_bit_exact(pf, route):
         assert eng.metrics()["load_failures"] == 0
     finally:
         eng.close()
+
+
+def test_recurrent_group_seals_final_block_save(pf):
+    """tests/hybrid_groups.rs:16-178 and :180-217, replayed on the CUDA engine and on the oracle model:
+    an attention group saves every block, the recurrent group only a tail checkpoint; membership is per
+    group; one load with two leases restores the attention prefix and the checkpoint into another slot."""
+    eng, gmem, ora, nmem = _pair(pf)
+    try:
+        results = []
+        for e, m in ((eng, gmem), (ora, nmem)):
+            layers = [sc.Layer("attn_0", 8, 1024, group=0), sc.Layer("attn_1", 8, 1024, group=0),
+                      sc.Layer("recurrent_state", 8, 2048, group=1)]
+            sc.register(e, m, "hybrid-hma", "hybrid-hma-ns", layers, use_groups=True)
+            fills = [sc.seeded_bytes(L.region_bytes, 60 + i) for i, L in enumerate(layers)]
+            for L, f in zip(layers, fills):
+                m.write(L.buf, f)
+            hashes = sc.make_block_hashes(8, 10)
+            prefix = hashes[:3]
+            e.batch_save("hybrid-hma", 0, 0, 0, [("attn_0", [0, 1, 2], prefix), ("attn_1", [0, 1, 2], prefix)])
+            e.batch_save("hybrid-hma", 0, 0, 0, [("recurrent_state", [5], [hashes[2]])])
+            e.flush_saves()
+            attn_hits = e.query_group_membership("hybrid-hma", 0, prefix)
+            assert [b is not None for b in attn_hits] == [True, True, True]
+            recur_hits = e.query_group_membership("hybrid-hma", 1, prefix)
+            assert [b is not None for b in recur_hits] == [False, False, True]
+            blocks, missing = e.query_prefix("hybrid-hma", prefix)
+            assert len(blocks) == 3 and missing == 0
+            attn_lease = e.create_query_lease("hybrid-hma", blocks)
+            recur_lease = e.create_query_lease("hybrid-hma", [recur_hits[2]])
+            for L in layers:
+                m.zero(L.buf)
+            e.batch_load("hybrid-hma", 0, 0, [["attn_0", "attn_1"], ["recurrent_state"]],
+                         [(attn_lease, [[0, 1, 2], [None, None, None]]), (recur_lease, [[None], [7]])])
+            m.sync()
+            got = [m.read(L.buf) for L in layers]
+            for g, f in zip(got[:2], fills[:2]):
+                want = np.zeros_like(f)
+                want[:3 * 1024] = f[:3 * 1024]
+                assert np.array_equal(g, want)
+            want = np.zeros_like(fills[2])
+            want[7 * 2048:8 * 2048] = fills[2][5 * 2048:6 * 2048]
+            assert np.array_equal(got[2], want)
+            results.append(got)
+        for a, b in zip(*results):
+            assert np.array_equal(a, b)
+
+        # single-group instances: group 0 behaves as before, any other group is an error, not a miss
+        for e, m in ((eng, gmem), (ora, nmem)):
+            layers = [sc.Layer("layer_0", 4, 1024), sc.Layer("layer_1", 4, 1024)]
+            sc.register(e, m, "hybrid-compat", "hybrid-compat-ns", layers)
+            for L in layers:
+                m.write(L.buf, sc.fill_pattern(4, 1024))
+            h = sc.make_block_hashes(4, 7)
+            e.batch_save("hybrid-compat", 0, 0, 0, [(L.name, [0, 1], h[:2]) for L in layers])
+            e.flush_saves()
+            hits = e.query_group_membership("hybrid-compat", 0, h)
+            assert [b is not None for b in hits] == [True, True, False, False]
+        with pytest.raises(pf.PegaFlowError) as e1:
+            eng.query_group_membership("hybrid-compat", 7, h[:1])
+        with pytest.raises(EngineError) as e2:
+            ora.query_group_membership("hybrid-compat", 7, h[:1])
+        assert e1.value.kind == e2.value.kind
+    finally:
+        eng.close()
+
+
+def test_query_lease_protocol_and_stateless_queries(pf):
+    """tests/prefetch_lease.rs:11-27 (a released lease cannot be loaded) and prefix_semantics.rs:86-126
+    (a miss does not hide blocks saved later under the same request id; an empty query is zero / zero)."""
+    eng, gmem, ora, nmem = _pair(pf)
+    try:
+        for e, m in ((eng, gmem), (ora, nmem)):
+            L = sc.Layer("layer_0", 4, 1024)
+            sc.register(e, m, "lease-proto", "test-ns", [L])
+            m.write(L.buf, sc.fill_pattern(4, 1024))
+            h = sc.make_block_hashes(4, 40)
+            blocks, missing = e.query_prefix("lease-proto", h)
+            assert len(blocks) == 0 and missing == 4
+            e.batch_save("lease-proto", 0, 0, 0, [("layer_0", [0, 1, 2, 3], h)])
+            e.flush_saves()
+            blocks, missing = e.query_prefix("lease-proto", h)
+            assert len(blocks) == 4 and missing == 0
+            blocks0, missing0 = e.query_prefix("lease-proto", [])
+            assert len(blocks0) == 0 and missing0 == 0
+            lease = e.create_query_lease("lease-proto", blocks)
+            assert e.release_query_lease(lease) is True
+            with pytest.raises((pf.PegaFlowError, EngineError), match="query lease is unknown or expired"):
+                e.batch_load("lease-proto", 0, 0, [["layer_0"]], [(lease, [[0, 1, 2, 3]])])
+    finally:
+        eng.close()
