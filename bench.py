@@ -1023,6 +1023,170 @@ def run_peer(args):
         "gpu_launches": stats["kernel_launches"], "device_status": stats["device_status"]}))
 
 
+def run_ttft(args):
+    """The reference's KV-cache benchmark shape (README.md:89-94: Llama-3.1-8B, 8 prompts of 10 K tokens,
+    1-token decode) replayed on one GPU through the worker-connector hooks, with synthetic layers standing
+    in for the model (torch matmuls and attention of the model's sizes, random weights shared by all layers).
+
+    cold = prefill of the whole prompt + save of its KV blocks; warm = prefix load + one decode token.
+    "blocking" follows the reference's worker: a device-wide synchronise, then all layers saved in one batch
+    before the step returns (worker.py:767-929), and a load that must finish before the request is scheduled
+    (worker.py:549-710, its wait_for_layer_load is empty, :712-713).  "layerwise" uses the per-layer hooks
+    this library fills in: every layer's save is queued behind an event recorded after that layer's
+    compute, and the decode step waits per layer on the layer's load event."""
+    import torch
+    import torch.nn.functional as F
+    import pegaflow_b200 as pf
+    from pegaflow_b200 import connector
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    L, H, NQ, NKV, D, FFN, BS = 32, 4096, 32, 8, 128, 14336, 16
+    T, n_req, nb = 10240, args.ttft_requests, 8192
+    per = T // BS
+    g = torch.Generator(device=dev)
+    g.manual_seed(7)
+
+    def rnd(*shape, scale=0.02):
+        return (torch.randn(*shape, generator=g, device=dev, dtype=torch.float32) * scale).to(torch.bfloat16)
+
+    w_qkv, w_o, w_gu, w_d = rnd(H, (NQ + 2 * NKV) * D), rnd(NQ * D, H), rnd(H, 2 * FFN), rnd(FFN, H)
+    names = [f"model.layers.{l}.self_attn.attn" for l in range(L)]
+    caches = {n: torch.zeros((2, nb, BS, NKV, D), dtype=torch.bfloat16, device=dev) for n in names}
+    eng = pf.PegaEngine((2 * n_req + 2) * (L * per * 2 * BS * NKV * D * 2) + (256 << 20))
+    conn = connector.PegaWorkerConnector(connector.InProcEngineClient(eng), eng, instance_id="ttft", namespace="ttft-ns",
+                                         device_id=0, block_size=BS)
+    conn.register_kv_caches(caches)
+    rng = np.random.default_rng(11)
+    compute = torch.cuda.Stream()
+
+    def layer_prefill(x, cache, ids):
+        x = F.rms_norm(x, (H,))
+        qkv = x @ w_qkv
+        q, k, v = qkv.split([NQ * D, NKV * D, NKV * D], dim=-1)
+        cache[0][ids] = k.view(per, BS, NKV, D)          # the layer's attention writes its KV pages
+        cache[1][ids] = v.view(per, BS, NKV, D)
+        a = F.scaled_dot_product_attention(q.view(1, T, NQ, D).transpose(1, 2), k.view(1, T, NKV, D).transpose(1, 2),
+                                           v.view(1, T, NKV, D).transpose(1, 2), is_causal=True, enable_gqa=True)
+        x = x + a.transpose(1, 2).reshape(T, NQ * D) @ w_o
+        gate, up = (x @ w_gu).chunk(2, dim=-1)
+        return x + (F.silu(gate) * up) @ w_d
+
+    def layer_decode(x, cache, ids):
+        x = F.rms_norm(x, (H,))
+        qkv = x @ w_qkv
+        q, _k, _v = qkv.split([NQ * D, NKV * D, NKV * D], dim=-1)
+        k = cache[0][ids].view(1, T, NKV, D).transpose(1, 2)   # reads the pages the load brought in
+        v = cache[1][ids].view(1, T, NKV, D).transpose(1, 2)
+        a = F.scaled_dot_product_attention(q.view(1, 1, NQ, D).transpose(1, 2), k, v, enable_gqa=True)
+        x = x + a.transpose(1, 2).reshape(1, NQ * D) @ w_o
+        gate, up = (x @ w_gu).chunk(2, dim=-1)
+        return x + (F.silu(gate) * up) @ w_d
+
+    def cold(mode, r):
+        ids_np = (rng.permutation(nb - 1)[:per] + 1)
+        ids = torch.from_numpy(ids_np.astype(np.int64)).to(dev)
+        hashes = [b"%s-c%02d-" % (mode.encode(), r) + int(i).to_bytes(4, "little") for i in range(per)]
+        ids_list = ids_np.tolist()
+        x = rnd(T, H, scale=1.0)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        events = []
+        with torch.cuda.stream(compute):
+            for name in names:
+                x = layer_prefill(x, caches[name], ids)
+                if mode == "layerwise":
+                    ev = torch.cuda.Event()
+                    ev.record(compute)
+                    events.append(ev)        # must outlive the save that waits on it
+                    conn.save_kv_layer(name, ids_list, hashes, ev.cuda_event)
+        if mode == "blocking":
+            torch.cuda.synchronize()
+            conn.wait_for_save([(name, ids_list, hashes) for name in names])
+        else:
+            compute.synchronize()
+            conn.wait_for_save()
+        return (time.perf_counter() - t0) * 1e3, hashes, ids_np
+
+    def warm(mode, r, hashes):
+        dst_np = (rng.permutation(nb - 1)[:per] + 1)
+        dst = torch.from_numpy(dst_np.astype(np.int64)).to(dev)
+        for c in caches.values():
+            c[:, dst] = 0
+        x = rnd(1, H, scale=1.0)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        q = conn.client.query_prefetch("ttft", hashes, f"{mode}-w{r}")
+        if q.num_hit_blocks != per:
+            raise RuntimeError(f"prefix query hit {q.num_hit_blocks} of {per} blocks")
+        conn.start_load_kv([(f"{mode}-w{r}", q.lease, dst_np.tolist())])
+        if mode == "blocking":
+            done = []
+            while not done:
+                done, failed = conn.get_finished()
+                if failed:
+                    raise RuntimeError("load failed")
+        with torch.cuda.stream(compute):
+            for name in names:
+                if mode == "layerwise":
+                    conn.wait_for_layer_load(name, compute.cuda_stream)
+                x = layer_decode(x, caches[name], dst)
+        compute.synchronize()
+        ms = (time.perf_counter() - t0) * 1e3
+        if mode == "layerwise":
+            done = []
+            while not done:
+                done, failed = conn.get_finished()
+                if failed:
+                    raise RuntimeError("load failed")
+        return ms, x.float().cpu()
+
+    # warm-up of kernels, allocator and pool (not reported)
+    _, h0, _ = cold("blocking", 99)
+    warm("blocking", 99, h0)
+    res = {"cold": {"blocking": [], "layerwise": []}, "warm": {"blocking": [], "layerwise": []}}
+    saved, same = {}, True
+    for r in range(n_req):
+        for mode in ("blocking", "layerwise"):
+            ms, hashes, _ = cold(mode, r)
+            res["cold"][mode].append(ms)
+            saved[(mode, r)] = hashes
+    for r in range(n_req):
+        # both warm modes load the same stored prompt into the same kind of destination and feed the same
+        # token: the outputs must be identical bit for bit, or a layer was consumed before it had landed
+        outs = {}
+        state, gstate = rng.bit_generator.state, g.get_state()
+        for mode in ("blocking", "layerwise"):
+            rng.bit_generator.state = state
+            g.set_state(gstate)
+            ms, out = warm(mode, r, saved[("layerwise", r)])
+            res["warm"][mode].append(ms)
+            outs[mode] = out
+        # bit patterns, not values: equal NaNs must count as equal
+        same = same and torch.equal(outs["blocking"].view(torch.int32), outs["layerwise"].view(torch.int32)) \
+            and bool(torch.isfinite(outs["blocking"]).all())
+    m = eng.metrics()
+    conn.unregister()
+    eng.close()
+
+    def summary(v):
+        return {"mean_ms": round(float(np.mean(v)), 2), "max_ms": round(float(np.max(v)), 2)}
+
+    kv_gib = L * per * 2 * BS * NKV * D * 2 / 2**30
+    print(json.dumps({
+        "metric": "ttft_shape_ms", "unit": "ms", "higher_is_better": False, "n_gpus": 1, "data": "synthetic",
+        "config": {"workload": "llama3.1-8b, prompts of 10240 tokens, 1-token decode", "requests": n_req,
+                   "kv_gib_per_request": round(kv_gib, 3), "layers": L,
+                   "model": "synthetic layers of the model's sizes (torch matmul + SDPA, random weights)"},
+        "cold": {k: summary(v) for k, v in res["cold"].items()},
+        "warm": {k: summary(v) for k, v in res["warm"].items()},
+        "cold_saved_ms": round(float(np.mean(res["cold"]["blocking"]) - np.mean(res["cold"]["layerwise"])), 2),
+        "warm_saved_ms": round(float(np.mean(res["warm"]["blocking"]) - np.mean(res["warm"]["layerwise"])), 2),
+        "warm_outputs_identical": bool(same), "load_failures": m["load_failures"],
+        "published_reference": {"cold_mean_ms": 572.5, "warm_mean_ms": 61.5,
+                                "note": "README.md:89-94: H800, real vLLM serving at 4 req/s; context only"}}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1048,10 +1212,16 @@ def main():
     ap.add_argument("--peer-pairs", type=int, default=1,
                     help="with --peer: also run this many GPU i -> GPU pairs+i copies at once (needs 2 x pairs GPUs)")
     ap.add_argument("--peer-push", action="store_true", help="with --peer: run the copy kernel on the source GPU")
+    ap.add_argument("--ttft", action="store_true",
+                    help="cold / warm time-to-first-token shape through the connector hooks, blocking vs layer-wise")
+    ap.add_argument("--ttft-requests", type=int, default=8)
     ap.add_argument("--peer", action="store_true", help="measure the NVLink peer-copy path (one process, two GPUs)")
     args = ap.parse_args()
     if args.peer:
         run_peer(args)
+        return
+    if args.ttft:
+        run_ttft(args)
         return
     world_env = int(os.environ.get("WORLD_SIZE", "1"))
     if args.gpus != world_env and world_env == 1 and args.gpus > 1:

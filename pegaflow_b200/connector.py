@@ -284,10 +284,18 @@ class PegaWorkerConnector:
         """Blocking batch save of `saves` (all layers, one GPU batch), then a flush that also
         covers layer saves queued by save_kv_layer."""
         if saves:
-            cleaned = []
+            cleaned, memo = [], {}
             for name, ids, hashes in saves:
-                keep = [(b, h) for b, h in zip(ids, hashes) if b != 0]
-                cleaned.append((name, [b for b, _ in keep], [h for _, h in keep]))
+                # layers usually share one (ids, hashes) pair: filter it once and hand the engine the
+                # same list objects for every layer, so that it marshals them once as well
+                key = (id(ids), id(hashes))
+                if key not in memo:
+                    if 0 in ids:
+                        keep = [(b, h) for b, h in zip(ids, hashes) if b != 0]
+                        memo[key] = ([b for b, _ in keep], [h for _, h in keep])
+                    else:
+                        memo[key] = (ids, hashes)
+                cleaned.append((name,) + memo[key])
             ok, msg = self.client.save(self.instance_id, self.tp_rank, self.pp_rank, self.device_id, cleaned)
             if not ok:
                 raise RuntimeError(f"save failed: {msg}")
