@@ -304,6 +304,25 @@ class PegaWorkerConnector:
         if not ok:
             raise RuntimeError(f"save failed: {msg}")
 
+    # worker.py:549-560 / :767-800: the scheduler's per-step metadata drives both directions
+    def start_load_kv_from_metadata(self, metadata, shard_index: int = 0):
+        """Start every load the scheduler planned for this step (one lease per TP shard: this
+        worker's shard consumes `leases[shard_index]`)."""
+        self.start_load_kv([(req_id, intent.leases[shard_index], list(intent.block_ids_by_group[0]))
+                            for req_id, intent in metadata.load_intents.items()])
+
+    def wait_for_save_from_metadata(self, metadata):
+        """Save what the scheduler marked as newly full this step: every registered layer stores the
+        same block ids under the same hashes.  Returns the request ids whose saves are now in the pool
+        (what the worker reports back as `finished_sending`)."""
+        intents = list(metadata.ready_save_intents.items()) + list(metadata.save_intents.items())
+        saves = []
+        for _req_id, intent in intents:
+            ids, hashes = list(intent.block_ids_by_group[0]), list(intent.block_hashes)
+            saves.extend((name, ids, hashes) for name in self.registered_layers)
+        self.wait_for_save(saves)
+        return {req_id for req_id, _ in intents}
+
     # worker.py:422-547
     def get_finished(self) -> Tuple[List[str], List[str]]:
         """(request ids whose load finished, request ids whose load failed)."""

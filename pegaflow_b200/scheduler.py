@@ -1,0 +1,353 @@
+"""Scheduler-side half of the connector: decides, per scheduling step, which blocks a worker
+loads from the host pool and which it saves to it.
+
+Mirrors the reference's ``SchedulerConnector`` (python/pegaflow/connector/scheduler.py) and
+``TpShardQueryClient`` (python/pegaflow/connector/tp_shards.py) for attention-only models with one
+KV-cache group: prefix lookup with query leases, the identity check that protects a lookup
+against a request that moved on while a slower tier was loading, load intents after block
+allocation, incremental save intents as blocks fill up, and the hold on a finished request's
+blocks until its saves have been sent.  Not mirrored: hybrid (recurrent-state) cache groups and
+the prefill/decode tail-block extension.
+
+Everything here is host bookkeeping over block ids, hashes and leases; no KV bytes are touched.
+The objects it reads are vLLM's (``Request.request_id/.block_hashes/.num_tokens``,
+``KVCacheBlocks.get_block_ids()/.blocks``, ``SchedulerOutput.scheduled_new_reqs/
+.scheduled_cached_reqs/.num_scheduled_tokens/.preempted_req_ids``) and are duck-typed.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+from .connector import QueryLoading, QueryReady
+
+
+@dataclass(frozen=True)
+class LoadIntent:
+    """common.py:220-231."""
+    block_ids_by_group: Tuple[Tuple[Optional[int], ...], ...]
+    leases: Tuple[bytes, ...]
+    num_tokens: int
+
+
+@dataclass(frozen=True)
+class SaveIntent:
+    """common.py:288-293."""
+    block_ids_by_group: Tuple[Tuple[int, ...], ...]
+    block_hashes: Tuple[bytes, ...]
+
+
+class PegaConnectorMetadata:
+    """What the scheduler hands the workers for one step (common.py:440-461)."""
+
+    def __init__(self, load_intents=None, save_intents=None, ready_save_intents=None, preempted_req_ids=None):
+        self.load_intents: Dict[str, LoadIntent] = load_intents or {}
+        self.save_intents: Dict[str, SaveIntent] = save_intents or {}
+        self.ready_save_intents: Dict[str, SaveIntent] = ready_save_intents or {}
+        self.preempted_req_ids: set = preempted_req_ids or set()
+
+    def __repr__(self):
+        return (f"PegaConnectorMetadata(loads={len(self.load_intents)}, saves={len(self.save_intents)}, "
+                f"ready_saves={len(self.ready_save_intents)})")
+
+
+@dataclass
+class _Probe:
+    """One prefix lookup: what was asked (the request's position and remaining hashes at that
+    moment) and, once the backend answered Ready, how many blocks it holds under which leases."""
+    computed_blocks: int
+    hashes: Tuple[bytes, ...]
+    hit_blocks: Optional[int] = None      # None: the backend is still loading
+    leases: Tuple[bytes, ...] = ()
+
+    def same_query(self, computed_blocks: int, hashes: Tuple[bytes, ...]) -> bool:
+        return self.computed_blocks == computed_blocks and self.hashes == hashes
+
+
+@dataclass
+class _Tracked:
+    """Save-side state of a request from its first allocation to its cleanup."""
+    request: object
+    hashes: Tuple[bytes, ...]
+    first_local_block: int                 # blocks before this index came from the host pool
+    next_to_store: int
+    block_ids: List[int] = field(default_factory=list)
+    scheduled_tokens: int = 0
+
+
+class ShardQuery:
+    """Prefix query across node-local TP shards (tp_shards.py:23-97): the usable hit is the prefix
+    every shard holds; shards that answered with more are re-leased for exactly that prefix."""
+
+    def __init__(self, clients: Sequence[object]):
+        if not clients:
+            raise ValueError("at least one engine client is needed")
+        self.clients = tuple(clients)
+
+    def query(self, instance_id: str, hashes: List[bytes], req_id: str, wait_for_full_prefix: bool):
+        """(hit blocks, one lease per shard), or None while some shard is still loading."""
+        answers: List[QueryReady] = []
+        try:
+            for index, client in enumerate(self.clients):
+                got = client.query_prefetch(instance_id, hashes, req_id=req_id, wait_for_full_prefix=wait_for_full_prefix)
+                if _is_loading(got):
+                    self.release([a.lease for a in answers], req_id)
+                    return None
+                self._check(got, len(hashes), index)
+                answers.append(got)
+        except Exception:
+            self.release([a.lease for a in answers], req_id)
+            raise
+        common = min(a.num_hit_blocks for a in answers)
+        leases = [a.lease for a in answers]
+        if common == 0:
+            self.release(leases, req_id)
+            return 0, tuple(b"" for _ in answers)
+        try:
+            for index, (client, answer) in enumerate(zip(self.clients, answers)):
+                if answer.num_hit_blocks == common:
+                    continue
+                exact = client.query_prefetch(instance_id, hashes[:common], req_id=f"{req_id}:tp-common-{common}",
+                                              wait_for_full_prefix=False)
+                if _is_loading(exact):
+                    raise RuntimeError(f"TP shard {index} could not lease the common {common}-block prefix")
+                try:
+                    self._check(exact, common, index)
+                    if exact.num_hit_blocks != common:
+                        raise RuntimeError(f"TP shard {index} could not lease the common {common}-block prefix")
+                except Exception:
+                    self._release_one(client, exact.lease)
+                    raise
+                longer, leases[index] = leases[index], exact.lease
+                self._release_one(client, longer)
+        except Exception:
+            self.release(leases, req_id)
+            raise
+        return common, tuple(leases)
+
+    def release(self, leases: Sequence[bytes], req_id: str = "") -> bool:
+        ok = True
+        for client, lease in zip(self.clients, leases):
+            ok = self._release_one(client, lease) and ok
+        return ok
+
+    @staticmethod
+    def _release_one(client, lease: bytes) -> bool:
+        if not lease:
+            return True
+        try:
+            client.release(lease)
+        except Exception:
+            return False
+        return True
+
+    @staticmethod
+    def _check(answer, asked: int, index: int):
+        if answer.num_hit_blocks > asked:
+            raise RuntimeError(f"TP shard {index} reported {answer.num_hit_blocks} hits for a {asked}-block query")
+        if answer.num_hit_blocks and not answer.lease:
+            raise RuntimeError(f"TP shard {index} returned {answer.num_hit_blocks} hits without a lease")
+
+
+def _is_loading(answer) -> bool:
+    # A client may answer with its own Loading type (the reference's native client does): anything
+    # that carries no hit count is "still loading".
+    return isinstance(answer, QueryLoading) or not hasattr(answer, "num_hit_blocks")
+
+
+class SchedulerConnector:
+    def __init__(self, clients: Sequence[object], *, instance_id: str, block_size: int, read_enabled: bool = True,
+                 wait_for_full_prefix: bool = False):
+        self.instance_id, self.block_size = instance_id, block_size
+        self.read_enabled, self.wait_for_full_prefix = read_enabled, wait_for_full_prefix
+        self._shards = ShardQuery(clients)
+        self._probes: Dict[str, _Probe] = {}
+        self._matched_blocks: Dict[str, int] = {}      # local prefix + blocks to be loaded, per request
+        self._tracked: Dict[str, _Tracked] = {}
+        self._loads: Dict[str, LoadIntent] = {}
+        self._deferred_saves: Dict[str, SaveIntent] = {}
+        self._unsent: set = set()                      # requests with saves the workers have not reported sent
+        self._held: set = set()                        # finished requests whose blocks wait for those saves
+
+    # ------------------------------------------------------------------ lookup (scheduler.py:210-407)
+    def get_num_new_matched_tokens(self, request, num_computed_tokens: int) -> Tuple[Optional[int], bool]:
+        """(tokens the host pool can supply beyond the local prefix, load asynchronously?) or
+        (None, False) while a slower tier is still fetching and the scheduler should ask again."""
+        req_id = request.request_id
+        if not self.read_enabled:
+            return 0, False
+        computed = num_computed_tokens // self.block_size
+        hashes = tuple(request.block_hashes[computed:])
+        if not hashes:
+            self._drop_probe(req_id)
+            self._matched_blocks[req_id] = computed
+            return 0, False
+
+        probe = self._probes.get(req_id)
+        if probe is not None and probe.hit_blocks is not None:
+            if probe.same_query(computed, hashes):
+                return self._answer(req_id, request.num_tokens, probe)
+            self._drop_probe(req_id)      # a Ready for a query the request has left behind: give the lease back
+            probe = None
+
+        # A lookup that is loading is known to the backend by request id: keep polling with the
+        # hashes it was started with, and judge the answer against today's position afterwards.
+        moved_on = probe is not None and not probe.same_query(computed, hashes)
+        answer = self._shards.query(self.instance_id, list(probe.hashes if moved_on else hashes), req_id,
+                                    self.wait_for_full_prefix)
+        if answer is None:
+            if probe is None:
+                self._probes[req_id] = _Probe(computed, hashes)
+            return None, False
+        hit_blocks, leases = answer
+        if moved_on:
+            self._shards.release(leases, req_id)
+            self._probes.pop(req_id, None)
+            return None, False
+        if probe is None:
+            probe = self._probes[req_id] = _Probe(computed, hashes)
+        if hit_blocks > len(probe.hashes):
+            raise RuntimeError(f"invariant violated: server returned {hit_blocks} hits for {len(probe.hashes)} hashes")
+        probe.hit_blocks, probe.leases = hit_blocks, leases
+        return self._answer(req_id, request.num_tokens, probe)
+
+    def _answer(self, req_id: str, num_tokens: int, probe: _Probe) -> Tuple[int, bool]:
+        bs = self.block_size
+        hit_tokens = probe.hit_blocks * bs
+        # one token is always left for the forward pass that produces the first logits
+        hit_tokens = min(hit_tokens, max(0, num_tokens - probe.computed_blocks * bs - 1))
+        self._matched_blocks[req_id] = probe.computed_blocks + (hit_tokens + bs - 1) // bs
+        if hit_tokens <= 0:
+            self._drop_probe(req_id)
+            return 0, False
+        return hit_tokens, True
+
+    # ------------------------------------------------------------------ allocation (scheduler.py:409-497)
+    def update_state_after_alloc(self, request, blocks, num_external_tokens: int) -> None:
+        req_id = request.request_id
+        t = self._tracked.get(req_id)
+        if t is None:
+            first = self._matched_blocks.get(req_id, 0)
+            t = self._tracked[req_id] = _Tracked(request, tuple(request.block_hashes), first, first)
+        else:
+            t.request, t.hashes = request, tuple(request.block_hashes)
+        if num_external_tokens <= 0:
+            return
+        ids = self._one_group(blocks.get_block_ids()) if blocks else ()
+        already_computed = sum(b.block_hash is not None for b in blocks.blocks[0]) if blocks else 0
+        n_load = (num_external_tokens + self.block_size - 1) // self.block_size
+        if len(ids) < already_computed + n_load:
+            self._drop_probe(req_id)
+            raise RuntimeError(f"load block mismatch: start={already_computed} count={n_load} available={len(ids)}")
+        probe = self._probes.get(req_id)
+        intent = LoadIntent((tuple(ids[already_computed:already_computed + n_load]),),
+                            probe.leases if probe is not None else (), num_external_tokens)
+        if probe is not None:
+            if not probe.same_query(already_computed, tuple(request.block_hashes[already_computed:])):
+                self._drop_probe(req_id)
+                raise RuntimeError(f"req {req_id} query identity changed before external load")
+            if probe.hit_blocks is None:
+                raise RuntimeError("query probe is still loading")
+            if probe.hit_blocks != n_load:
+                self._drop_probe(req_id)
+                raise RuntimeError(f"req {req_id} leased block mismatch: leased={probe.hit_blocks} load={n_load}")
+        if not intent.leases or any(not lease for lease in intent.leases):
+            raise RuntimeError(f"req {req_id} missing query lease for external load")
+        self._loads[req_id] = intent
+        self._probes.pop(req_id, None)     # the lease now travels with the load intent; the worker consumes it
+
+    # ------------------------------------------------------------------ per step (scheduler.py:499-596)
+    def build_connector_meta(self, scheduler_output) -> PegaConnectorMetadata:
+        ready_saves, self._deferred_saves = self._deferred_saves, {}
+        loads, self._loads = self._loads, {}
+        saves: Dict[str, SaveIntent] = {}
+        scheduled = scheduler_output.num_scheduled_tokens
+
+        for new in scheduler_output.scheduled_new_reqs:
+            t = self._tracked.get(new.req_id)
+            assert t is not None, f"req {new.req_id} not initialized in update_state_after_alloc"
+            if new.block_ids:
+                t.block_ids = list(self._one_group(new.block_ids))
+            self._count_tokens(t, new.num_computed_tokens, scheduled.get(new.req_id, 0))
+            intent = self._next_save(t)
+            if intent:
+                saves[new.req_id] = intent
+
+        running = scheduler_output.scheduled_cached_reqs
+        for i, req_id in enumerate(running.req_ids):
+            t = self._tracked.get(req_id)
+            if t is None:
+                continue
+            t.hashes = tuple(t.request.block_hashes)      # decode completes new blocks: pick up their hashes
+            fresh = running.new_block_ids[i]
+            if req_id in running.resumed_req_ids:
+                t.block_ids = list(self._one_group(fresh)) if fresh else []
+            elif fresh:
+                t.block_ids.extend(self._one_group(fresh))
+            self._count_tokens(t, running.num_computed_tokens[i], scheduled.get(req_id, 0))
+            intent = self._next_save(t)
+            if intent:
+                saves[req_id] = intent
+
+        self._unsent.update(saves)
+        return PegaConnectorMetadata(loads, saves, ready_saves, set(scheduler_output.preempted_req_ids or ()))
+
+    def _count_tokens(self, t: _Tracked, computed_before: int, now: int):
+        if self.read_enabled:
+            t.scheduled_tokens += now
+        else:
+            t.scheduled_tokens = max(t.scheduled_tokens, computed_before + now)
+
+    def _next_save(self, t: _Tracked) -> Optional[SaveIntent]:
+        """Blocks that became full since the last step (scheduler.py:700-770): block ids and hashes
+        are both in request order, and the prefix that was loaded from the pool is never re-saved."""
+        full_local = min(len(t.block_ids), t.scheduled_tokens // self.block_size)
+        end = min(len(t.hashes), t.first_local_block + full_local)
+        if end <= t.next_to_store:
+            return None
+        start, t.next_to_store = t.next_to_store, end
+        return SaveIntent((tuple(t.block_ids[start:end]),), t.hashes[start:end])
+
+    # ------------------------------------------------------------------ completion (scheduler.py:874-925)
+    def update_connector_output(self, connector_output) -> None:
+        for req_id in connector_output.finished_sending or []:
+            self._unsent.discard(req_id)
+            if req_id in self._held and req_id not in self._deferred_saves:
+                self._forget(req_id)
+                self._held.discard(req_id)
+
+    def request_finished(self, request, block_ids) -> Tuple[bool, Optional[dict]]:
+        """True: the caller must keep the request's blocks until its saves are reported sent."""
+        req_id = request.request_id
+        if req_id in self._unsent:
+            self._held.add(req_id)
+            return True, None
+        self._forget(req_id)
+        return False, None
+
+    def shutdown(self) -> None:
+        for req_id in list(self._probes):
+            self._drop_probe(req_id)
+
+    # ------------------------------------------------------------------ helpers
+    def _forget(self, req_id: str):
+        self._drop_probe(req_id)
+        self._tracked.pop(req_id, None)
+        self._matched_blocks.pop(req_id, None)
+        self._deferred_saves.pop(req_id, None)
+        self._unsent.discard(req_id)
+
+    def _drop_probe(self, req_id: str) -> bool:
+        probe = self._probes.pop(req_id, None)
+        if probe is None or not any(probe.leases):
+            return True
+        return self._shards.release(probe.leases, req_id)
+
+    @staticmethod
+    def _one_group(block_ids) -> Tuple[int, ...]:
+        groups = tuple(tuple(g) for g in block_ids)
+        if len(groups) != 1:
+            raise RuntimeError(f"KV cache group count mismatch: expected=1 actual={len(groups)}")
+        if any(b < 0 for b in groups[0]):
+            raise RuntimeError("KV cache block IDs must be non-negative")
+        return groups[0]

@@ -1,0 +1,299 @@
+"""Scripted request lifecycles for the scheduler-side connector.
+
+One interpreter, two users: ``tests/golden/gen_scheduler_traces.py`` runs the scripts on the
+reference's ``SchedulerConnector`` (python/pegaflow/connector/scheduler.py) and commits what it
+answered; ``tests/test_scheduler_connector.py`` runs them on this repository's mirror and compares.
+The fake engine client, request and scheduler-output objects carry only what the connector reads
+from vLLM's (`Request.block_hashes`, `KVCacheBlocks.get_block_ids()`, `SchedulerOutput` fields).
+"""
+from types import SimpleNamespace
+
+BLOCK = 16
+
+
+def H(i):
+    return b"hash-%04d" % i
+
+
+class FakeClient:
+    """Stands in for one TP shard's engine client: a set of stored hashes, prefix queries that hand
+    out numbered leases, and a log of everything the connector asked for."""
+
+    def __init__(self, name, ready_cls, loading_cls):
+        self.name, self.ready_cls, self.loading_cls = name, ready_cls, loading_cls
+        self.store, self.loading, self.live, self.log, self.issued = set(), {}, {}, [], 0
+
+    def query_prefetch(self, instance_id, block_hashes, req_id, wait_for_full_prefix=False, group_id=0):
+        if self.loading.get(req_id, 0) > 0:
+            self.loading[req_id] -= 1
+            self.log.append(["loading", self.name, req_id, len(block_hashes)])
+            return self.loading_cls()
+        n = 0
+        for h in block_hashes:
+            if bytes(h) not in self.store:
+                break
+            n += 1
+        if n == 0:
+            self.log.append(["miss", self.name, req_id, len(block_hashes)])
+            return self.ready_cls(0, b"")
+        self.issued += 1
+        lease = b"%s-lease-%03d" % (self.name.encode(), self.issued)
+        self.live[lease] = n
+        self.log.append(["lease", self.name, req_id, len(block_hashes), n, lease.decode(), bool(wait_for_full_prefix)])
+        return self.ready_cls(n, lease)
+
+    def release(self, lease):
+        self.log.append(["release", self.name, bytes(lease).decode()])
+        self.live.pop(bytes(lease), None)
+
+
+class FakeRequest:
+    def __init__(self, request_id, hashes, num_tokens):
+        self.request_id = request_id
+        self.block_hashes = [H(i) for i in hashes]
+        self.num_tokens = num_tokens
+        self.num_prompt_tokens = num_tokens
+        self.num_computed_tokens = 0
+        self.prompt_token_ids = list(range(num_tokens))
+        self.lora_request = None
+        self.cache_salt = None
+        self.mm_features = None
+
+
+class FakeBlocks:
+    """`KVCacheBlocks` as the connector sees it: ids per group, and which blocks already carry a
+    hash (the locally computed prefix)."""
+
+    def __init__(self, block_ids, n_cached):
+        self._ids = [list(block_ids)]
+        self.blocks = [[SimpleNamespace(block_hash=(b"x" if i < n_cached else None)) for i in range(len(block_ids))]]
+
+    def get_block_ids(self):
+        return tuple(self._ids)
+
+
+def _intent(x):
+    out = {"block_ids": [list(g) for g in x.block_ids_by_group]}
+    if hasattr(x, "leases"):
+        out["leases"] = [bytes(l).decode() for l in x.leases]
+        out["num_tokens"] = x.num_tokens
+    else:
+        out["hashes"] = [bytes(h).decode() for h in x.block_hashes]
+    return out
+
+
+def run_script(script, make_connector, ready_cls, loading_cls):
+    cfg = dict(block_size=BLOCK, read_enabled=True, wait_for_full_prefix=False, shards=1)
+    cfg.update(script.get("config", {}))
+    clients = [FakeClient("shard%d" % i, ready_cls, loading_cls) for i in range(cfg["shards"])]
+    conn = make_connector(clients, block_size=cfg["block_size"], read_enabled=cfg["read_enabled"],
+                          wait_for_full_prefix=cfg["wait_for_full_prefix"], group_count=1)
+    requests, trace = {}, []
+    for op in script["ops"]:
+        kind, args = op[0], op[1:]
+        result = None
+        try:
+            if kind == "store":
+                clients[args[0]].store.update(H(i) for i in args[1])
+            elif kind == "evict":
+                clients[args[0]].store.difference_update(H(i) for i in args[1])
+            elif kind == "loading":
+                clients[args[0]].loading[args[1]] = args[2]
+            elif kind == "request":
+                requests[args[0]] = FakeRequest(args[0], args[1], args[2])
+            elif kind == "grow":
+                requests[args[0]].block_hashes.extend(H(i) for i in args[1])
+                requests[args[0]].num_tokens = args[2]
+            elif kind == "match":
+                tokens, load_async = conn.get_num_new_matched_tokens(requests[args[0]], args[1])
+                result = [tokens, bool(load_async)]
+            elif kind == "alloc":
+                req_id, block_ids, n_cached, n_external = args
+                blocks = FakeBlocks(block_ids, n_cached) if block_ids is not None else None
+                conn.update_state_after_alloc(requests[req_id], blocks, n_external)
+                result = "ok"
+            elif kind == "step":
+                spec = args[0]
+                new = [SimpleNamespace(req_id=r, block_ids=(tuple([list(ids)]) if ids is not None else None),
+                                       num_computed_tokens=nc) for r, ids, nc, _n in spec.get("new", [])]
+                cached = spec.get("cached", [])
+                out = SimpleNamespace(
+                    scheduled_new_reqs=new,
+                    scheduled_cached_reqs=SimpleNamespace(
+                        req_ids=[c[0] for c in cached],
+                        new_block_ids=[(tuple([list(c[1])]) if c[1] is not None else None) for c in cached],
+                        num_computed_tokens=[c[2] for c in cached],
+                        resumed_req_ids={c[0] for c in cached if len(c) > 4 and c[4]}),
+                    num_scheduled_tokens={**{r: n for r, _i, _c, n in spec.get("new", [])},
+                                          **{c[0]: c[3] for c in cached}},
+                    preempted_req_ids=set(spec.get("preempted", [])))
+                meta = conn.build_connector_meta(out)
+                result = {"loads": {k: _intent(v) for k, v in sorted(meta.load_intents.items())},
+                          "saves": {k: _intent(v) for k, v in sorted(meta.save_intents.items())},
+                          "ready_saves": {k: _intent(v) for k, v in sorted(meta.ready_save_intents.items())},
+                          "preempted": sorted(meta.preempted_req_ids)}
+            elif kind == "finished":
+                held, extra = conn.request_finished(requests[args[0]], tuple([list(args[1])]))
+                result = [bool(held), extra]
+            elif kind == "sent":
+                conn.update_connector_output(SimpleNamespace(finished_sending=set(args[0]), finished_recving=None))
+            elif kind == "shutdown":
+                conn.shutdown()
+            else:
+                raise ValueError("unknown op " + kind)
+        except (RuntimeError, AssertionError) as e:
+            result = "error:" + type(e).__name__
+        log = []
+        for c in clients:
+            log.extend(c.log)
+            c.log = []
+        trace.append({"op": [kind] + [a if not isinstance(a, (set, tuple)) else list(a) for a in args],
+                      "result": result, "client_log": log, "live_leases": sorted(l.decode() for c in clients for l in c.live)})
+    return trace
+
+
+def _r(a, b):
+    return list(range(a, b))
+
+
+SCRIPTS = {
+    # 56-token prompt (3 full blocks + 8), no cached prefix anywhere: chunked prefill, blocks are saved as
+    # they fill, decode completes the fourth block, the request finishes while its last save is pending.
+    "cold_prefill_then_decode": {"ops": [
+        ("request", "a", _r(0, 3), 56),
+        ("match", "a", 0),
+        ("alloc", "a", [10, 11, 12, 13], 0, 0),
+        ("step", {"new": [["a", [10, 11, 12, 13], 0, 40]]}),
+        ("step", {"cached": [["a", None, 40, 16]]}),
+        ("grow", "a", [3], 65),
+        ("step", {"cached": [["a", [14], 56, 1]]}),
+        ("step", {"cached": [["a", None, 57, 1]]}),
+        ("step", {"cached": [["a", None, 58, 1]]}),
+        ("step", {"cached": [["a", None, 59, 1]]}),
+        ("step", {"cached": [["a", None, 60, 1]]}),
+        ("step", {"cached": [["a", None, 61, 1]]}),
+        ("step", {"cached": [["a", None, 62, 1]]}),
+        ("step", {"cached": [["a", None, 63, 1]]}),
+        ("step", {"cached": [["a", None, 64, 1]]}),
+        ("finished", "a", [10, 11, 12, 13, 14]),
+        ("sent", ["a"]),
+        ("finished", "a", [10, 11, 12, 13, 14]),
+    ]},
+    # every block of a 64-token prompt is stored: the hit is clamped so that one token is left to compute
+    "warm_full_hit": {"ops": [
+        ("store", 0, _r(0, 4)),
+        ("request", "w", _r(0, 4), 64),
+        ("match", "w", 0),
+        ("alloc", "w", [5, 6, 7, 8], 0, 63),
+        ("step", {"new": [["w", [5, 6, 7, 8], 63, 1]]}),
+        ("grow", "w", [], 65),
+        ("step", {"cached": [["w", [9], 64, 1]]}),
+        ("finished", "w", [5, 6, 7, 8, 9]),
+    ]},
+    # two blocks are in the local prefix cache, the store holds the next three of five
+    "partial_hit_after_local_prefix": {"ops": [
+        ("store", 0, _r(0, 5)),
+        ("evict", 0, [0]),
+        ("request", "p", _r(0, 6), 100),
+        ("match", "p", 0),
+        ("store", 0, [0]),
+        ("evict", 0, [5]),
+        ("match", "p", 32),
+        ("alloc", "p", [20, 21, 22, 23, 24, 25, 26], 2, 48),
+        ("step", {"new": [["p", [20, 21, 22, 23, 24, 25, 26], 80, 20]]}),
+        ("step", {"cached": [["p", None, 100, 1]]}),
+        ("finished", "p", [20, 21, 22, 23, 24, 25, 26]),
+        ("sent", ["p"]),
+    ]},
+    # the backend answers Loading twice (a slower tier is fetching), then Ready
+    "loading_then_ready": {"config": {"wait_for_full_prefix": True}, "ops": [
+        ("store", 0, _r(0, 3)),
+        ("request", "l", _r(0, 3), 50),
+        ("loading", 0, "l", 2),
+        ("match", "l", 0),
+        ("match", "l", 0),
+        ("match", "l", 0),
+        ("match", "l", 0),
+        ("alloc", "l", [1, 2, 3, 4], 0, 48),
+        ("step", {"new": [["l", [1, 2, 3, 4], 48, 2]]}),
+    ]},
+    # the request makes local progress while the backend is loading: the Ready that finally arrives
+    # belongs to the old query and is released, the next poll starts over
+    "identity_drift_while_loading": {"ops": [
+        ("store", 0, _r(0, 4)),
+        ("request", "d", _r(0, 4), 70),
+        ("loading", 0, "d", 1),
+        ("match", "d", 0),
+        ("match", "d", 16),
+        ("match", "d", 16),
+        ("alloc", "d", [1, 2, 3, 4, 5], 1, 48),
+        ("step", {"new": [["d", [1, 2, 3, 4, 5], 64, 6]]}),
+    ]},
+    # a cached Ready is reused while the query stays the same, released when it no longer matches,
+    # and released at shutdown when nothing consumed it
+    "ready_reuse_and_stale_release": {"ops": [
+        ("store", 0, _r(0, 4)),
+        ("request", "s", _r(0, 4), 80),
+        ("match", "s", 0),
+        ("match", "s", 0),
+        ("match", "s", 32),
+        ("request", "t", _r(0, 2), 40),
+        ("match", "t", 0),
+        ("shutdown",),
+    ]},
+    # nothing left to query; a miss; a hit whose allocation does not match the lease
+    "edge_cases_and_errors": {"ops": [
+        ("store", 0, _r(0, 2)),
+        ("request", "e1", _r(0, 2), 33),
+        ("match", "e1", 32),
+        ("request", "e2", _r(7, 9), 40),
+        ("match", "e2", 0),
+        ("request", "e3", _r(0, 2), 40),
+        ("match", "e3", 0),
+        ("alloc", "e3", [1, 2, 3], 0, 16),
+        ("request", "e4", _r(0, 2), 40),
+        ("alloc", "e4", [1, 2, 3], 0, 32),
+        ("request", "e5", _r(0, 2), 40),
+        ("match", "e5", 0),
+        ("alloc", "e5", [1], 0, 32),
+        ("request", "e6", _r(0, 2), 40),
+        ("step", {"new": [["e6", [4, 5, 6], 0, 40]]}),
+    ]},
+    # two node-local TP shards: the hit is the prefix both hold, the longer shard is re-leased exactly
+    "two_shards_common_prefix": {"config": {"shards": 2}, "ops": [
+        ("store", 0, _r(0, 4)),
+        ("store", 1, _r(0, 2)),
+        ("request", "x", _r(0, 4), 70),
+        ("match", "x", 0),
+        ("alloc", "x", [1, 2, 3, 4, 5], 0, 32),
+        ("step", {"new": [["x", [1, 2, 3, 4, 5], 32, 38]]}),
+        ("request", "y", _r(0, 4), 70),
+        ("loading", 1, "y", 1),
+        ("match", "y", 0),
+        ("evict", 1, _r(0, 2)),
+        ("match", "y", 0),
+    ]},
+    # save-only mode: no lookups, saves follow the scheduler's computed-token counts
+    "save_only_mode": {"config": {"read_enabled": False}, "ops": [
+        ("store", 0, _r(0, 3)),
+        ("request", "o", _r(0, 3), 50),
+        ("match", "o", 0),
+        ("alloc", "o", [1, 2, 3, 4], 0, 0),
+        ("step", {"new": [["o", [1, 2, 3, 4], 0, 20]]}),
+        ("step", {"cached": [["o", None, 20, 30]]}),
+        ("finished", "o", [1, 2, 3, 4]),
+        ("sent", ["o"]),
+        ("finished", "o", [1, 2, 3, 4]),
+    ]},
+    # preempted after two blocks were saved, resumed with a fresh block table
+    "preempt_and_resume": {"ops": [
+        ("request", "r", _r(0, 4), 64),
+        ("match", "r", 0),
+        ("alloc", "r", [1, 2, 3, 4], 0, 0),
+        ("step", {"new": [["r", [1, 2, 3, 4], 0, 32]]}),
+        ("step", {"preempted": ["r"]}),
+        ("step", {"cached": [["r", [7, 8, 9, 10], 0, 48, True]]}),
+        ("step", {"cached": [["r", None, 48, 16]]}),
+        ("finished", "r", [7, 8, 9, 10]),
+    ]},
+}

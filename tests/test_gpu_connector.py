@@ -155,3 +155,70 @@ def test_layerwise_saves_and_failed_load_reporting(env):
         assert eng.metrics()["load_failures"] == 0
     finally:
         eng.close()
+
+
+def test_scheduler_and_worker_connectors_end_to_end(env):
+    """A cold request and a warm one through both halves of the connector and the engine: the
+    scheduler plans saves as blocks fill, the worker stores them; the second request's lookup hits,
+    its load intent carries the lease, and the worker's load puts the first request's bytes into the
+    second request's blocks."""
+    pf, connector, torch = env
+    from types import SimpleNamespace as NS
+
+    from pegaflow_b200.scheduler import SchedulerConnector
+
+    dev = torch.device("cuda", 0)
+    eng = pf.PegaEngine(256 << 20, min_dma_bytes=64 << 10)
+    try:
+        client = connector.InProcEngineClient(eng)
+        worker = connector.PegaWorkerConnector(client, eng, instance_id="both", namespace="ns", device_id=0, block_size=16)
+        sched = SchedulerConnector([client], instance_id="both", block_size=16)
+        caches = {f"l{i}": torch.empty((2, 64, 16, 2, 128), dtype=torch.bfloat16, device=dev) for i in range(3)}
+        for i, t in enumerate(caches.values()):
+            t.view(torch.uint8).random_(0, 256, generator=torch.Generator(device=dev).manual_seed(40 + i))
+        worker.register_kv_caches(caches)
+        hashes = sc.make_block_hashes(5, 12)
+
+        def request(name, n_tokens):
+            return NS(request_id=name, block_hashes=list(hashes[:n_tokens // 16]), num_tokens=n_tokens)
+
+        def step(new=(), running=()):
+            return NS(scheduled_new_reqs=[NS(req_id=r, block_ids=([*ids],), num_computed_tokens=c) for r, ids, c, _ in new],
+                      scheduled_cached_reqs=NS(req_ids=[r for r, *_ in running], new_block_ids=[None for _ in running],
+                                               num_computed_tokens=[c for _, c, _ in running], resumed_req_ids=set()),
+                      num_scheduled_tokens={**{r: n for r, _, _, n in new}, **{r: n for r, _, n in running}},
+                      preempted_req_ids=set())
+
+        # cold: 80-token prompt in blocks 10..14, prefilled in two chunks
+        cold = request("cold", 80)
+        assert sched.get_num_new_matched_tokens(cold, 0) == (0, False)
+        sched.update_state_after_alloc(cold, NS(get_block_ids=lambda: ([10, 11, 12, 13, 14],), blocks=[[]]), 0)
+        meta = sched.build_connector_meta(step(new=[("cold", [10, 11, 12, 13, 14], 0, 48)]))
+        assert list(meta.save_intents["cold"].block_ids_by_group[0]) == [10, 11, 12]
+        sent = worker.wait_for_save_from_metadata(meta)
+        meta = sched.build_connector_meta(step(running=[("cold", 48, 32)]))
+        assert list(meta.save_intents["cold"].block_ids_by_group[0]) == [13, 14]
+        sent |= worker.wait_for_save_from_metadata(meta)
+        assert sched.request_finished(cold, ([10, 11, 12, 13, 14],)) == (True, None)
+        sched.update_connector_output(NS(finished_sending=sent, finished_recving=None))
+        assert sched.request_finished(cold, ([10, 11, 12, 13, 14],)) == (False, None)
+
+        # warm: the same prompt; one token is left to compute, the other 79 come from the pool
+        warm = request("warm", 80)
+        tokens, load_async = sched.get_num_new_matched_tokens(warm, 0)
+        assert (tokens, load_async) == (79, True)
+        dst = [30, 31, 32, 33, 34]
+        blocks = NS(get_block_ids=lambda: (dst,), blocks=[[NS(block_hash=None) for _ in dst]])
+        sched.update_state_after_alloc(warm, blocks, tokens)
+        meta = sched.build_connector_meta(step(new=[("warm", dst, 79, 1)]))
+        assert list(meta.load_intents["warm"].block_ids_by_group[0]) == dst and not meta.save_intents
+        before = {k: t.clone() for k, t in caches.items()}
+        worker.start_load_kv_from_metadata(meta)
+        done, failed = _wait_loads(worker, 1)
+        assert done == ["warm"] and not failed
+        torch.cuda.synchronize()
+        for k, t in caches.items():
+            assert torch.equal(t[:, dst].view(torch.uint8), before[k][:, [10, 11, 12, 13, 14]].view(torch.uint8))
+        assert eng.metrics()["load_failures"] == 0
+    finally:
+        eng.close()
