@@ -191,7 +191,7 @@ class SchedulerConnector:
             probe = None
 
         # A lookup that is loading is known to the backend by request id: keep polling with the
-        # hashes it was started with, and judge the answer against today's position afterwards.
+        # hashes it was started with, and compare the answer with today's position afterwards.
         moved_on = probe is not None and not probe.same_query(computed, hashes)
         answer = self._shards.query(self.instance_id, list(probe.hashes if moved_on else hashes), req_id,
                                     self.wait_for_full_prefix)
