@@ -199,3 +199,13 @@ def check(status: int):
     if status in (4, 5, 6):
         raise PegaflowInternal(status, msg)
     raise PegaFlowError(status, msg)
+
+
+def release(fn_name: str, handle) -> None:
+    """Call a `*_free` / `*_release` entry point from `close()` or `__del__`.  During interpreter
+    shutdown module globals may already be gone when a finalizer runs; the handle is then left to
+    the process exit."""
+    library = globals().get("lib")
+    if library is None:
+        return
+    getattr(library, fn_name)(handle)

@@ -13,6 +13,11 @@ from typing import List, Optional, Sequence
 from . import _native as N
 
 
+def _release(fn_name, handle, _native=N):
+    # bound at definition time: a finalizer may run after this module's globals were cleared
+    _native.release(fn_name, handle)
+
+
 @dataclass
 class HostRun:
     first_block: int
@@ -45,7 +50,7 @@ class PinnedPool:
 
     def close(self):
         if getattr(self, "_h", None):
-            N.lib.pf_pool_free(self._h)
+            _release("pf_pool_free", self._h)
             self._h = None
 
     __del__ = close
@@ -77,7 +82,7 @@ class TransferBackend:
 
     def close(self):
         if getattr(self, "_h", None):
-            N.lib.pf_backend_free(self._h)
+            _release("pf_backend_free", self._h)
             self._h = None
 
     __del__ = close

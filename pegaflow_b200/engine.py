@@ -15,6 +15,11 @@ import numpy as np
 from . import _native as N
 from ._native import PegaFlowError, PegaflowInternal, PegaflowInvalidArgument  # noqa: F401  (re-exported)
 
+def _release(fn_name, handle, _native=N):
+    # bound at definition time: a finalizer may run after this module's globals were cleared
+    _native.release(fn_name, handle)
+
+
 TRANSFER_MODES = {"direct": 0, "kernel": 1}  # transfer/mod.rs:66-76; both run on the one B200 backend
 
 LOAD_STATE_PENDING, LOAD_STATE_SUCCESS, LOAD_STATE_ERROR = 0, 1, -1
@@ -40,7 +45,7 @@ class Block:
 
     def __del__(self):
         if getattr(self, "_h", None):
-            N.lib.pf_block_release(self._h)
+            _release("pf_block_release", self._h)
             self._h = None
 
     @property
@@ -68,7 +73,7 @@ class Completion:
 
     def __del__(self):
         if getattr(self, "_h", None):
-            N.lib.pf_completion_free(self._h)
+            _release("pf_completion_free", self._h)
             self._h = None
 
     def poll(self) -> int:
@@ -98,7 +103,7 @@ class PyLoadState:
 
     def __del__(self):
         if getattr(self, "_h", None):
-            N.lib.pf_load_state_free(self._h)
+            _release("pf_load_state_free", self._h)
             self._h = None
 
     def shm_name(self) -> str:
@@ -144,7 +149,7 @@ class PegaEngine:
 
     def close(self):
         if getattr(self, "_h", None):
-            N.lib.pf_engine_free(self._h)
+            _release("pf_engine_free", self._h)
             self._h = None
 
     __del__ = close
