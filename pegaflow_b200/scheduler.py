@@ -222,6 +222,11 @@ class SchedulerConnector:
             return 0, False
         return hit_tokens, True
 
+    def pending_lookup_position(self, req_id: str) -> Optional[int]:
+        """Locally computed blocks at the time of the request's pending Ready lookup, if any."""
+        probe = self._probes.get(req_id)
+        return probe.computed_blocks if probe is not None and probe.hit_blocks is not None else None
+
     # ------------------------------------------------------------------ allocation (scheduler.py:409-497)
     def update_state_after_alloc(self, request, blocks, num_external_tokens: int) -> None:
         req_id = request.request_id

@@ -1,0 +1,193 @@
+"""vLLM v1 KV-connector plug-in on top of this library: ``PegaKVConnector``.
+
+Takes the place of the reference's ``pegaflow.connector.PegaKVConnector``
+(python/pegaflow/connector/__init__.py) for the case this library covers: one node, the engine
+in the vLLM process (no sidecar), attention-only models with one KV-cache group.  Configure it as
+
+    KVTransferConfig(kv_connector="PegaKVConnector",
+                     kv_connector_module_path="pegaflow_b200.vllm_connector",
+                     kv_role="kv_both",
+                     kv_connector_extra_config={"pegaflow.pool_bytes": 8 << 30})
+
+Extra-config keys: ``pegaflow.pool_bytes`` (pinned pool size), ``pegaflow.mode`` ("read_write" or
+"save_only", as in the reference), ``pegaflow.layerwise`` (default true: loads are synchronous
+from the scheduler's point of view and every attention layer waits on the stream for its own
+layer's bytes, saves are queued per layer behind the layer's compute; false: the reference's
+behaviour — asynchronous request-level loads, one batch save after the forward pass).
+
+The scheduler role and the worker role of one vLLM process share one engine (looked up by
+instance id), so this works with the in-process engine core and the uniprocess executor
+(``VLLM_ENABLE_V1_MULTIPROCESSING=0``, tensor_parallel_size 1); tensor-parallel workers in other
+processes would need the reference's sidecar, which this library does not provide.
+"""
+from __future__ import annotations
+
+import threading
+from typing import Any, Dict, Optional
+
+import torch
+from vllm.distributed.kv_transfer.kv_connector.v1.base import KVConnectorBase_V1, KVConnectorMetadata, KVConnectorRole
+
+from . import connector as _connector
+from .engine import PegaEngine
+from .scheduler import PegaConnectorMetadata, SchedulerConnector
+
+_ENGINES: Dict[str, PegaEngine] = {}
+_ENGINES_LOCK = threading.Lock()
+
+
+def shared_engine(instance_id: str, pool_bytes: int) -> PegaEngine:
+    """The engine both roles of one process use."""
+    with _ENGINES_LOCK:
+        eng = _ENGINES.get(instance_id)
+        if eng is None:
+            eng = _ENGINES[instance_id] = PegaEngine(pool_bytes)
+        return eng
+
+
+def close_shared_engines() -> None:
+    with _ENGINES_LOCK:
+        for eng in _ENGINES.values():
+            eng.close()
+        _ENGINES.clear()
+
+
+class _Metadata(PegaConnectorMetadata, KVConnectorMetadata):
+    """The scheduler connector's metadata, typed for vLLM."""
+
+
+class _LocalPrefixView:
+    """`KVCacheBlocks` as the scheduler connector reads it, with the locally computed prefix given
+    explicitly instead of inferred from block hashes."""
+
+    def __init__(self, blocks, local_blocks: int):
+        self._blocks = blocks
+        ids = blocks.get_block_ids()[0]
+        self.blocks = [[_Hashed(i < local_blocks) for i in range(len(ids))]]
+
+    def get_block_ids(self):
+        return self._blocks.get_block_ids()
+
+
+class _Hashed:
+    __slots__ = ("block_hash",)
+
+    def __init__(self, hashed: bool):
+        self.block_hash = b"local" if hashed else None
+
+
+class PegaKVConnector(KVConnectorBase_V1):
+    def __init__(self, vllm_config, role: KVConnectorRole, kv_cache_config=None):
+        super().__init__(vllm_config, role, kv_cache_config)
+        cfg = vllm_config.kv_transfer_config
+        extra = cfg.get_from_extra_config
+        self._instance_id = str(getattr(vllm_config, "instance_id", "") or cfg.engine_id or "vllm")
+        self._block_size = vllm_config.cache_config.block_size
+        self._layerwise = bool(extra("pegaflow.layerwise", True))
+        self._read_enabled = str(extra("pegaflow.mode", "read_write")).strip().lower() == "read_write"
+        model = vllm_config.model_config
+        self._namespace = f"{model.model}:{model.dtype}:bs{self._block_size}"
+        self._is_mla = bool(getattr(model, "use_mla", False))
+        self._engine = shared_engine(self._instance_id, int(extra("pegaflow.pool_bytes", 4 << 30)))
+        self._client = _connector.InProcEngineClient(self._engine)
+        self._scheduler: Optional[SchedulerConnector] = None
+        self._worker: Optional[_connector.PegaWorkerConnector] = None
+        if role == KVConnectorRole.SCHEDULER:
+            self._scheduler = SchedulerConnector([self._client], instance_id=self._instance_id, block_size=self._block_size,
+                                                 read_enabled=self._read_enabled)
+        else:
+            device = torch.cuda.current_device()
+            self._worker = _connector.PegaWorkerConnector(
+                self._client, self._engine, instance_id=self._instance_id, namespace=self._namespace, device_id=device,
+                block_size=self._block_size, is_mla=self._is_mla)
+            self._saved_requests: set = set()      # requests with saves in the pool, not yet reported sent
+            self._events = []                      # per-layer "KV written" events of the current step
+            self._loading_this_step = False
+
+    # ================================================================== scheduler role
+    def get_num_new_matched_tokens(self, request, num_computed_tokens):
+        tokens, load_async = self._scheduler.get_num_new_matched_tokens(request, num_computed_tokens)
+        if tokens and self._layerwise:
+            # The request is scheduled in this very step; its attention layers wait for their own
+            # layer's bytes (wait_for_layer_load), so nothing has to be parked in the scheduler.
+            load_async = False
+        return tokens, load_async
+
+    def update_state_after_alloc(self, request, blocks, num_external_tokens):
+        if self._layerwise and num_external_tokens > 0:
+            # With a synchronous load vLLM has already given every full block its hash, the ones
+            # about to be loaded included, so "blocks that carry a hash" no longer means "computed
+            # locally": the local prefix is where the lookup started.
+            local = self._scheduler.pending_lookup_position(request.request_id)
+            if local is not None:
+                blocks = _LocalPrefixView(blocks, local)
+        self._scheduler.update_state_after_alloc(request, blocks, num_external_tokens)
+
+    def build_connector_meta(self, scheduler_output) -> KVConnectorMetadata:
+        meta = self._scheduler.build_connector_meta(scheduler_output)
+        return _Metadata(meta.load_intents, meta.save_intents, meta.ready_save_intents, meta.preempted_req_ids)
+
+    def update_connector_output(self, connector_output):
+        self._scheduler.update_connector_output(connector_output)
+
+    def request_finished(self, request, block_ids):
+        return self._scheduler.request_finished(request, (block_ids,))
+
+    # ================================================================== worker role
+    def register_kv_caches(self, kv_caches: Dict[str, torch.Tensor]):
+        self._worker.register_kv_caches(kv_caches)
+
+    def start_load_kv(self, forward_context, **kwargs: Any) -> None:
+        meta = self._get_connector_metadata()
+        self._loading_this_step = bool(meta.load_intents)
+        if meta.load_intents:
+            # layer-wise: this step's forward pass consumes the blocks, layer by layer, on the compute
+            # stream (wait_for_layer_load); otherwise the scheduler parks the requests until
+            # get_finished reports them received
+            self._worker.start_load_kv_from_metadata(meta)
+
+    def wait_for_layer_load(self, layer_name: str) -> None:
+        if self._layerwise and self._loading_this_step:
+            self._worker.wait_for_layer_load(layer_name, torch.cuda.current_stream().cuda_stream)
+
+    def save_kv_layer(self, layer_name: str, kv_layer, attn_metadata, **kwargs: Any) -> None:
+        if not self._layerwise:
+            return
+        meta = self._get_connector_metadata()
+        if not meta.save_intents and not meta.ready_save_intents:
+            return
+        ready = torch.cuda.Event()
+        ready.record(torch.cuda.current_stream())
+        self._events.append(ready)      # kept until wait_for_save: the engine waits on it from another thread
+        for intent in list(meta.ready_save_intents.values()) + list(meta.save_intents.values()):
+            self._worker.save_kv_layer(layer_name, list(intent.block_ids_by_group[0]), list(intent.block_hashes),
+                                       ready.cuda_event)
+
+    def wait_for_save(self):
+        meta = self._get_connector_metadata()
+        if self._layerwise:
+            self._worker.wait_for_save()        # the layers were queued one by one: this only flushes
+            self._saved_requests.update(meta.save_intents)
+            self._saved_requests.update(meta.ready_save_intents)
+            self._events.clear()
+        else:
+            torch.cuda.current_stream().synchronize()
+            self._saved_requests.update(self._worker.wait_for_save_from_metadata(meta))
+        self._loading_this_step = False
+
+    def get_finished(self, finished_req_ids):
+        sending = {r for r in finished_req_ids if r in self._saved_requests}
+        self._saved_requests -= sending
+        done, failed = self._worker.get_finished()
+        # Only request-level (asynchronous) loads are parked in the scheduler and need reporting.
+        receiving = None if self._layerwise else (set(done) | set(failed))
+        return (sending or None), (receiving or None)
+
+    def get_block_ids_with_load_errors(self):
+        return self._worker.get_block_ids_with_load_errors()
+
+    def shutdown(self):
+        if self._scheduler is not None:
+            self._scheduler.shutdown()
+        if self._worker is not None:
+            self._worker.unregister()

@@ -1,0 +1,34 @@
+"""This library as the KV connector of a real vLLM engine (the reference's
+python/tests/test_vllm_e2e_correctness.py idea, with a randomly initialised model): prompts served
+warm from the host pool must produce exactly what the same prompts produce warm from vLLM's own GPU
+prefix cache."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+@pytest.mark.parametrize("mode", ["layerwise", "after-forward"])
+def test_vllm_serves_prompts_from_the_host_pool(mode):
+    pytest.importorskip("vllm")
+    if os.environ.get("PEGAFLOW_TEST_VLLM", "0") != "1":
+        pytest.skip("set PEGAFLOW_TEST_VLLM=1 to start a vLLM engine (takes a few minutes)")
+    import torch
+
+    if not torch.cuda.is_available():
+        pytest.fail("this test needs a CUDA device")
+    cmd = [sys.executable, os.path.join(HERE, "vllm_scenario.py")] + (["--after-forward"] if mode == "after-forward" else [])
+    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=900)
+    lines = [ln for ln in proc.stdout.splitlines() if ln.startswith("{")]
+    assert proc.returncode == 0 and lines, proc.stderr[-3000:]
+    out = json.loads(lines[-1])
+    assert out["saved_bytes_cold"] > 0, "the cold run saved nothing"
+    assert out["loaded_bytes_gpu_cache_run"] == 0, "the GPU-cache run should not touch the host pool"
+    assert out["loaded_bytes_host_pool_run"] > 0, "the third run did not load from the host pool"
+    assert out["load_failures"] == 0
+    assert out["warm_runs_identical"], "tokens or log-probabilities differ between GPU-cache and host-pool warm runs"

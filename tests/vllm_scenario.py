@@ -1,0 +1,69 @@
+"""One vLLM process with this library as its KV connector (run by tests/test_gpu_vllm.py in a
+subprocess; prints one JSON line).
+
+A small randomly initialised Llama runs three times over the same prompts: cold (computes the
+prompt, the connector saves its KV blocks), warm from vLLM's own GPU prefix cache, and — after that
+cache has been reset — warm from the host pool through the connector.  The two warm runs take the
+same compute path for the remaining token, so their sampled tokens and log-probabilities must be
+identical if the loaded KV bytes are the saved ones and no layer was read before it had landed.
+"""
+import json
+import os
+import sys
+import tempfile
+
+os.environ.setdefault("VLLM_ENABLE_V1_MULTIPROCESSING", "0")
+os.environ.setdefault("VLLM_LOGGING_LEVEL", "WARNING")
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def main():
+    layerwise = "--after-forward" not in sys.argv
+    import numpy as np
+    from transformers import LlamaConfig
+    from vllm import LLM, SamplingParams
+    from vllm.config import KVTransferConfig
+
+    from pegaflow_b200 import vllm_connector
+
+    model_dir = tempfile.mkdtemp(prefix="tiny-llama-")
+    LlamaConfig(vocab_size=2048, hidden_size=512, intermediate_size=1024, num_hidden_layers=4, num_attention_heads=8,
+                num_key_value_heads=2, head_dim=64, max_position_embeddings=4096, torch_dtype="bfloat16",
+                architectures=["LlamaForCausalLM"]).save_pretrained(model_dir)
+    llm = LLM(model=model_dir, load_format="dummy", skip_tokenizer_init=True, enforce_eager=True, max_model_len=2048,
+              gpu_memory_utilization=0.10, dtype="bfloat16", seed=0, enable_prefix_caching=True, block_size=16,
+              kv_transfer_config=KVTransferConfig(
+                  kv_connector="PegaKVConnector", kv_connector_module_path="pegaflow_b200.vllm_connector", kv_role="kv_both",
+                  kv_connector_extra_config={"pegaflow.pool_bytes": 1 << 30, "pegaflow.layerwise": layerwise}))
+    rng = np.random.default_rng(3)
+    prompts = [{"prompt_token_ids": rng.integers(1, 2000, size=n).tolist()} for n in (200, 333, 64, 1000)]
+    params = SamplingParams(temperature=0.0, max_tokens=6, detokenize=False, logprobs=1)
+
+    def run():
+        outs = llm.generate(prompts, params, use_tqdm=False)
+        return [[(int(t), float(next(iter(lp.values())).logprob)) for t, lp in zip(o.outputs[0].token_ids, o.outputs[0].logprobs)]
+                for o in outs]
+
+    engine = next(iter(vllm_connector._ENGINES.values()))
+    cold = run()
+    after_cold = engine.metrics()
+    gpu_cache = run()
+    after_gpu_cache = engine.metrics()
+    llm.reset_prefix_cache()
+    host_pool = run()
+    after_host = engine.metrics()
+    print(json.dumps({
+        "layerwise": layerwise,
+        "warm_runs_identical": gpu_cache == host_pool, "cold_equals_warm_tokens": [[t for t, _ in a] for a in cold] ==
+        [[t for t, _ in a] for a in host_pool],
+        "saved_bytes_cold": after_cold["save_bytes"], "loaded_bytes_gpu_cache_run": after_gpu_cache["load_bytes"],
+        "loaded_bytes_host_pool_run": after_host["load_bytes"] - after_gpu_cache["load_bytes"],
+        "load_failures": after_host["load_failures"], "cache_blocks": after_host["cache_blocks"],
+        "tokens": [[t for t, _ in a] for a in host_pool]}))
+    sys.stdout.flush()
+    vllm_connector.close_shared_engines()
+    os._exit(0)      # vLLM's own teardown is not what this scenario tests
+
+
+if __name__ == "__main__":
+    main()
