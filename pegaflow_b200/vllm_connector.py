@@ -22,6 +22,8 @@ processes would need the reference's sidecar, which this library does not provid
 """
 from __future__ import annotations
 
+import os
+import sys
 import threading
 from typing import Any, Dict, Optional
 
@@ -32,6 +34,7 @@ from . import connector as _connector
 from .engine import PegaEngine
 from .scheduler import PegaConnectorMetadata, SchedulerConnector
 
+_DEBUG = os.environ.get("PEGAFLOW_B200_TRACE", "0") == "1"
 _ENGINES: Dict[str, PegaEngine] = {}
 _ENGINES_LOCK = threading.Lock()
 
@@ -107,6 +110,9 @@ class PegaKVConnector(KVConnectorBase_V1):
     # ================================================================== scheduler role
     def get_num_new_matched_tokens(self, request, num_computed_tokens):
         tokens, load_async = self._scheduler.get_num_new_matched_tokens(request, num_computed_tokens)
+        if _DEBUG:
+            print(f"[pegaflow_b200] lookup {request.request_id}: local={num_computed_tokens} "
+                  f"hashes={len(request.block_hashes)} tokens={request.num_tokens} -> {tokens}", file=sys.stderr)
         if tokens and self._layerwise:
             # The request is scheduled in this very step; its attention layers wait for their own
             # layer's bytes (wait_for_layer_load), so nothing has to be parked in the scheduler.

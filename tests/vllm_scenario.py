@@ -49,11 +49,15 @@ def main():
     after_cold = engine.metrics()
     gpu_cache = run()
     after_gpu_cache = engine.metrics()
-    llm.reset_prefix_cache()
+    # A request whose last save happened in its final steps keeps its blocks until the worker has
+    # reported the save as sent, which takes one more engine step; then nothing is in use any more.
+    llm.generate([{"prompt_token_ids": [5, 6, 7]}], SamplingParams(temperature=0.0, max_tokens=1, detokenize=False),
+                 use_tqdm=False)
+    reset_ok = llm.reset_prefix_cache()
     host_pool = run()
     after_host = engine.metrics()
     print(json.dumps({
-        "layerwise": layerwise,
+        "layerwise": layerwise, "prefix_cache_reset": bool(reset_ok),
         "warm_runs_identical": gpu_cache == host_pool, "cold_equals_warm_tokens": [[t for t, _ in a] for a in cold] ==
         [[t for t, _ in a] for a in host_pool],
         "saved_bytes_cold": after_cold["save_bytes"], "loaded_bytes_gpu_cache_run": after_gpu_cache["load_bytes"],
