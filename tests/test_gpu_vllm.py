@@ -16,8 +16,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 @pytest.mark.parametrize("mode", ["layerwise", "after-forward"])
 def test_vllm_serves_prompts_from_the_host_pool(mode):
     pytest.importorskip("vllm")
-    if os.environ.get("PEGAFLOW_TEST_VLLM", "0") != "1":
-        pytest.skip("set PEGAFLOW_TEST_VLLM=1 to start a vLLM engine (takes a few minutes)")
+    if os.environ.get("PEGAFLOW_TEST_VLLM", "1") == "0":
+        pytest.skip("PEGAFLOW_TEST_VLLM=0: not starting a vLLM engine (it takes about a minute per mode)")
     import torch
 
     if not torch.cuda.is_available():
@@ -27,6 +27,9 @@ def test_vllm_serves_prompts_from_the_host_pool(mode):
     lines = [ln for ln in proc.stdout.splitlines() if ln.startswith("{")]
     assert proc.returncode == 0 and lines, proc.stderr[-3000:]
     out = json.loads(lines[-1])
+    if out.get("engine_start_failed"):
+        assert not out["ours"], out["traceback"]
+        pytest.skip("the vLLM engine could not start here: " + out["traceback"].strip().splitlines()[-1])
     assert out["saved_bytes_cold"] > 0, "the cold run saved nothing"
     assert out["prefix_cache_reset"], "vLLM could not reset its prefix cache: some request still holds blocks"
     # the GPU-cache run only asks the pool for what vLLM's own cache left over (at most a block per prompt)

