@@ -1196,6 +1196,78 @@ def run_ttft(args):
                                 "note": "README.md:89-94: H800, real vLLM serving at 4 req/s; context only"}}))
 
 
+def run_vllm_ttft(args):
+    """The reference's KV-cache benchmark (README.md:89-94: Llama-3.1-8B, 8 prompts of 10 K tokens, 1-token
+    decode) under a real vLLM engine with this library as its KV connector.  The model has the published
+    architecture sizes and random weights (there are no checkpoints here); prompts are random token ids.
+    cold = first time a prompt is seen (prefill + save), warm = the same prompt after vLLM's own prefix cache
+    was reset, so its KV comes from the host pool.  One process per hook mode (--after-forward selects the
+    reference's behaviour)."""
+    os.environ.setdefault("VLLM_ENABLE_V1_MULTIPROCESSING", "0")
+    os.environ.setdefault("VLLM_LOGGING_LEVEL", "WARNING")
+    import tempfile
+
+    from transformers import LlamaConfig
+    from vllm import LLM, SamplingParams
+    from vllm.config import KVTransferConfig
+
+    from pegaflow_b200 import vllm_connector
+
+    layerwise = not args.after_forward
+    model_dir = tempfile.mkdtemp(prefix="llama31-8b-shape-")
+    LlamaConfig(vocab_size=128256, hidden_size=4096, intermediate_size=14336, num_hidden_layers=32, num_attention_heads=32,
+                num_key_value_heads=8, head_dim=128, max_position_embeddings=131072, rope_theta=500000.0,
+                torch_dtype="bfloat16", architectures=["LlamaForCausalLM"]).save_pretrained(model_dir)
+    n_req, prompt_len = args.ttft_requests, 10240
+    llm = LLM(model=model_dir, load_format="dummy", skip_tokenizer_init=True, enforce_eager=True, max_model_len=12288,
+              max_num_batched_tokens=16384, gpu_memory_utilization=0.5, dtype="bfloat16", seed=0,
+              enable_prefix_caching=True, block_size=16,
+              kv_transfer_config=KVTransferConfig(
+                  kv_connector="PegaKVConnector", kv_connector_module_path="pegaflow_b200.vllm_connector", kv_role="kv_both",
+                  kv_connector_extra_config={"pegaflow.pool_bytes": (n_req + 3) * (5 << 28),
+                                             "pegaflow.layerwise": layerwise}))
+    rng = np.random.default_rng(17)
+    prompts = [{"prompt_token_ids": rng.integers(1, 120000, size=prompt_len).tolist()} for _ in range(n_req)]
+    one = SamplingParams(temperature=0.0, max_tokens=1, detokenize=False)
+    engine = next(iter(vllm_connector._ENGINES.values()))
+
+    def timed(p):
+        t0 = time.perf_counter()
+        out = llm.generate([p], one, use_tqdm=False)
+        return (time.perf_counter() - t0) * 1e3, out[0].outputs[0].token_ids[0]
+
+    warmup = {"prompt_token_ids": rng.integers(1, 120000, size=prompt_len).tolist()}
+    timed(warmup)
+    timed(warmup)
+    cold = [timed(p) for p in prompts]
+    saved = engine.metrics()["save_bytes"]
+    timed({"prompt_token_ids": [5, 6, 7]})             # one more step: finished requests' blocks are released
+    reset_ok = llm.reset_prefix_cache()
+    loaded0 = engine.metrics()["load_bytes"]
+    warm = [timed(p) for p in prompts]
+    m = engine.metrics()
+
+    def summary(v):
+        ms = [x for x, _ in v]
+        return {"mean_ms": round(float(np.mean(ms)), 2), "max_ms": round(float(np.max(ms)), 2)}
+
+    print(json.dumps({
+        "metric": "vllm_ttft_ms", "unit": "ms", "higher_is_better": False, "n_gpus": 1, "data": "synthetic",
+        "config": {"workload": "vLLM, Llama-3.1-8B sizes with random weights, prompts of 10240 random tokens, 1-token decode, "
+                               "one request at a time, eager mode", "requests": n_req,
+                   "hooks": "layerwise" if layerwise else "after_forward"},
+        "cold": summary(cold), "warm_from_host_pool": summary(warm),
+        "warm_speedup": round(float(np.mean([x for x, _ in cold]) / np.mean([x for x, _ in warm])), 2),
+        "same_first_token": [t for _, t in cold] == [t for _, t in warm], "prefix_cache_reset": bool(reset_ok),
+        "saved_gib": round(saved / 2**30, 3), "loaded_gib": round((m["load_bytes"] - loaded0) / 2**30, 3),
+        "load_failures": m["load_failures"],
+        "published_reference": {"cold_mean_ms": 572.5, "warm_mean_ms": 61.5,
+                                "note": "README.md:89-94: H800, real checkpoint, serving at 4 req/s; context only"}}))
+    sys.stdout.flush()
+    vllm_connector.close_shared_engines()
+    os._exit(0)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1224,6 +1296,10 @@ def main():
     ap.add_argument("--ttft", action="store_true",
                     help="cold / warm time-to-first-token shape through the connector hooks, blocking vs layer-wise")
     ap.add_argument("--ttft-requests", type=int, default=8)
+    ap.add_argument("--vllm-ttft", action="store_true",
+                    help="cold / warm time-to-first-token under a real vLLM engine with this library as its KV connector")
+    ap.add_argument("--after-forward", action="store_true",
+                    help="with --vllm-ttft: the reference's hook behaviour instead of the layer-wise hooks")
     ap.add_argument("--peer", action="store_true", help="measure the NVLink peer-copy path (one process, two GPUs)")
     args = ap.parse_args()
     if args.peer:
@@ -1231,6 +1307,9 @@ def main():
         return
     if args.ttft:
         run_ttft(args)
+        return
+    if args.vllm_ttft:
+        run_vllm_ttft(args)
         return
     world_env = int(os.environ.get("WORLD_SIZE", "1"))
     if args.gpus != world_env and world_env == 1 and args.gpus > 1:

@@ -107,6 +107,11 @@ class PegaKVConnector(KVConnectorBase_V1):
             self._events = []                      # per-layer "KV written" events of the current step
             self._loading_this_step = False
 
+    @classmethod
+    def requires_piecewise_for_cudagraph(cls, extra_config) -> bool:
+        # the per-layer hooks are Python between attention layers: a full CUDA graph would skip them
+        return bool((extra_config or {}).get("pegaflow.layerwise", True))
+
     # ================================================================== scheduler role
     def get_num_new_matched_tokens(self, request, num_computed_tokens):
         tokens, load_async = self._scheduler.get_num_new_matched_tokens(request, num_computed_tokens)
