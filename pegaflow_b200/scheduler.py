@@ -93,8 +93,8 @@ class ShardQuery:
                 if _is_loading(got):
                     self.release([a.lease for a in answers], req_id)
                     return None
+                answers.append(got)      # before the check: a malformed answer's lease is given back too
                 self._check(got, len(hashes), index)
-                answers.append(got)
         except Exception:
             self.release([a.lease for a in answers], req_id)
             raise

@@ -68,3 +68,78 @@ def test_scheduler_feeds_the_worker_connector_format():
     assert loads == [("q", b"shard0-lease-001", [3, 4, 5])]
     saves = [("layer", list(i.block_ids_by_group[0]), list(i.block_hashes)) for i in meta.save_intents.values()]
     assert saves == [("layer", [6], [scripts.H(3)])]
+
+
+# ---- known answers from the reference's own unit tests (python/tests/test_tp_shards.py:196-306) -----------
+def _mock_pair():
+    from unittest.mock import MagicMock
+
+    return MagicMock(), MagicMock()
+
+
+def test_kat_common_prefix_and_exact_per_shard_leases():
+    from unittest.mock import call
+
+    from pegaflow_b200.connector import QueryReady
+    from pegaflow_b200.scheduler import ShardQuery
+
+    first, second = _mock_pair()
+    first.query_prefetch.side_effect = [QueryReady(3, b"first-long"), QueryReady(2, b"first-exact")]
+    second.query_prefetch.return_value = QueryReady(2, b"second-exact")
+    hashes = [b"h0", b"h1", b"h2"]
+    assert ShardQuery((first, second)).query("instance", hashes, "request", False) == (2, (b"first-exact", b"second-exact"))
+    assert first.query_prefetch.call_args_list == [
+        call("instance", hashes, req_id="request", wait_for_full_prefix=False),
+        call("instance", hashes[:2], req_id="request:tp-common-2", wait_for_full_prefix=False)]
+    first.release.assert_called_once_with(b"first-long")
+    second.release.assert_not_called()
+
+
+def test_kat_ready_shards_are_released_when_another_is_loading():
+    from pegaflow_b200.connector import QueryLoading, QueryReady
+    from pegaflow_b200.scheduler import ShardQuery
+
+    first, second = _mock_pair()
+    first.query_prefetch.return_value = QueryReady(2, b"first")
+    second.query_prefetch.return_value = QueryLoading()
+    assert ShardQuery((first, second)).query("instance", [b"h0", b"h1"], "request", False) is None
+    first.release.assert_called_once_with(b"first")
+
+
+def test_kat_drifted_prefetch_is_discarded_before_new_hashes_are_queried():
+    from types import SimpleNamespace
+    from unittest.mock import call
+
+    from pegaflow_b200.connector import QueryLoading, QueryReady
+    from pegaflow_b200.scheduler import SchedulerConnector
+
+    first, second = _mock_pair()
+    first.query_prefetch.side_effect = [QueryLoading(), QueryReady(4, b"first-old"), QueryLoading()]
+    second.query_prefetch.return_value = QueryReady(4, b"second-old")
+    sched = SchedulerConnector((first, second), instance_id="instance", block_size=16)
+    request = SimpleNamespace(request_id="request", block_hashes=[b"h0", b"h1", b"h2", b"h3"], num_tokens=64)
+    assert sched.get_num_new_matched_tokens(request, 0) == (None, False)
+    assert sched.get_num_new_matched_tokens(request, 32) == (None, False)
+    assert sched.get_num_new_matched_tokens(request, 32) == (None, False)
+    old, new = request.block_hashes, request.block_hashes[2:]
+    assert first.query_prefetch.call_args_list == [
+        call("instance", old, req_id="request", wait_for_full_prefix=False),
+        call("instance", old, req_id="request", wait_for_full_prefix=False),
+        call("instance", new, req_id="request", wait_for_full_prefix=False)]
+    first.release.assert_called_once_with(b"first-old")
+    second.release.assert_called_once_with(b"second-old")
+
+
+@pytest.mark.parametrize("hits,lease", [(3, b"too-many"), (1, b"")])
+def test_kat_invalid_shard_answers_do_not_leak_leases(hits, lease):
+    from pegaflow_b200.connector import QueryReady
+    from pegaflow_b200.scheduler import ShardQuery
+
+    first, second = _mock_pair()
+    first.query_prefetch.return_value = QueryReady(2, b"first")
+    second.query_prefetch.return_value = QueryReady(hits, lease)
+    with pytest.raises(RuntimeError, match="TP shard 1"):
+        ShardQuery((first, second)).query("instance", [b"h0", b"h1"], "request", False)
+    first.release.assert_called_once_with(b"first")
+    if lease:
+        second.release.assert_called_once_with(lease)
