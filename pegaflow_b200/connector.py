@@ -207,6 +207,7 @@ class PegaWorkerConnector:
         self.registrations: Dict[str, KVCacheRegistrationInfo] = {}
         self._pending_loads: List[_PendingLoad] = []
         self._load_errors: set = set()
+        self._rejected_loads: List[str] = []      # requests whose load could not even be submitted
         self._saves_in_flight = 0
 
     # worker.py:261-412
@@ -250,12 +251,18 @@ class PegaWorkerConnector:
         try:
             ok, msg = self.client.load(self.instance_id, self.tp_rank, self.device_id, state.shm_name(),
                                        [list(self.registered_layers)], [(lease, [list(ids)]) for _, lease, ids in loads])
-        except ValueError as e:
+        except Exception as e:      # a load that cannot be submitted never raises into the model step
             ok, msg = False, str(e)
         if not ok:
+            # worker.py:650-684: the leases go back, the blocks are reported invalid so that they
+            # are recomputed, and the requests are reported as received so that they are not left parked
             for _, lease, _ in loads:
-                self.client.release(lease)          # worker.py:650-684
+                try:
+                    self.client.release(lease)
+                except Exception:
+                    pass
             self._load_errors.update(pending.block_ids)
+            self._rejected_loads.extend(pending.request_ids)
             return
         self._pending_loads.append(pending)
 
@@ -326,7 +333,8 @@ class PegaWorkerConnector:
     # worker.py:422-547
     def get_finished(self) -> Tuple[List[str], List[str]]:
         """(request ids whose load finished, request ids whose load failed)."""
-        done, failed, still = [], [], []
+        done, still = [], []
+        failed, self._rejected_loads = self._rejected_loads, []
         for p in self._pending_loads:
             st = p.state.get_state()
             if st == 0:

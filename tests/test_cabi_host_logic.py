@@ -195,3 +195,35 @@ def test_connector_layout_inference_matches_reference_fixture():
     assert resolve_transfer_backend(True, "direct") == "direct"
     with pytest.raises(ValueError, match="Unsupported pegaflow.transfer_backend"):
         resolve_transfer_backend(False, "nvlink")
+
+
+# ---- worker connector: a load that cannot be submitted (python/tests/test_connector_fault_tolerance.py:170-333) ----
+class _RejectingClient:
+    def __init__(self, mode):
+        self.mode, self.load_calls, self.released = mode, 0, []
+
+    def load(self, *args):
+        self.load_calls += 1
+        if self.mode == "exception":
+            raise ConnectionError("server gone")
+        return False, "load refused"
+
+    def release(self, lease):
+        self.released.append(bytes(lease))
+
+
+@pytest.mark.parametrize("mode", ["ok_false", "exception"])
+def test_worker_reports_a_rejected_load_instead_of_raising(mode):
+    from pegaflow_b200.connector import PegaWorkerConnector
+
+    client = _RejectingClient(mode)
+    worker = PegaWorkerConnector(client, None, instance_id="i", namespace="n", device_id=0, block_size=16)
+    worker.registered_layers = ["layer"]
+    worker.start_load_kv([("r1", b"lease-r1", [1])])           # must not raise
+    worker.start_load_kv([("r2", b"lease-r2", [2, None, 3])])
+    assert client.load_calls == 2 and client.released == [b"lease-r1", b"lease-r2"]
+    assert worker.get_block_ids_with_load_errors() == {1, 2, 3}
+    assert worker.get_block_ids_with_load_errors() == set()      # drained by the first call
+    done, failed = worker.get_finished()
+    assert done == [] and failed == ["r1", "r2"]                 # reported, so that nothing stays parked
+    assert worker.get_finished() == ([], [])
