@@ -1268,6 +1268,105 @@ def run_vllm_ttft(args):
     os._exit(0)
 
 
+def run_transfer_grid(args):
+    """The reference's descriptor-level micro-benchmark (pegaflow-core/benches/transfer_h2d.rs:23-33, 301-339)
+    on three backends: 4096-byte fragments x {1 Ki, 4 Ki, 16 Ki, 64 Ki} x {contiguous, every other device
+    block, shuffled descriptor order} x {D2H, H2D}, 3 warm-up + 20 timed submissions, each followed by a stream
+    synchronise, host clock.  Backends: this library through `pf_backend_d2h/h2d` on the same `CopyDesc` array
+    (the narrowest drop-in), the reference's direct backend and its kernel backend (oracle/ref_path.cu)."""
+    import torch
+    import pegaflow_b200 as pf
+    from pegaflow_b200 import _native as N
+    from oracle import build_ref
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    seg, counts, warm, iters = 4096, [1024, 4096, 16384, 65536], 3, 20
+    ref = C.CDLL(build_ref.build())
+    ref.pfr_submit_direct.argtypes = [C.c_void_p, C.c_size_t, C.c_int, C.c_void_p, C.POINTER(C.c_size_t)]
+    ref.pfr_submit_kernel.argtypes = [C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]
+    ref.pfr_sync.argtypes = [C.c_void_p]
+    has_kernel = bool(ref.pfr_has_reference_kernel())
+    pool = pf.PinnedPool(max(counts) * seg + (1 << 20))
+    host, host_dev, _ = pool.alloc(max(counts) * seg)
+    device = torch.empty(((max(counts) - 1) * 2 + 1) * seg, dtype=torch.uint8, device=dev)
+    hview = np.ctypeslib.as_array(C.cast(host, C.POINTER(C.c_uint8)), shape=(max(counts) * seg,))
+    hview[:] = (np.arange(hview.size, dtype=np.uint64) * 31 + 7).astype(np.uint8)
+    be = pf.TransferBackend(0)
+    stream = torch.cuda.Stream()
+    sp = C.c_void_p(stream.cuda_stream)
+
+    def shuffled(n):
+        state, perm = 0x9E3779B97F4A7C15, list(range(n))     # the reference's seeded xorshift64 Fisher-Yates
+        for i in range(n - 1, 0, -1):
+            state ^= (state << 13) & 0xFFFFFFFFFFFFFFFF
+            state ^= state >> 7
+            state ^= (state << 17) & 0xFFFFFFFFFFFFFFFF
+            j = state % (i + 1)
+            perm[i], perm[j] = perm[j], perm[i]
+        return np.asarray(perm, dtype=np.uint64)
+
+    def descs(layout, n):
+        slots = np.arange(n, dtype=np.uint64)
+        if layout == "contiguous":
+            d_off, h_off = slots * seg, slots * seg
+        elif layout == "strided_device":
+            d_off, h_off = slots * 2 * seg, slots * seg
+        else:
+            p = shuffled(n)
+            d_off, h_off = p * seg, p * seg
+        a = np.zeros((n, 6), dtype=np.uint64)      # device, host, host_device, size, device_allocation, host_allocation
+        a[:, 0], a[:, 1], a[:, 2], a[:, 3] = device.data_ptr() + d_off, host + h_off, host_dev + h_off, seg
+        return a, d_off // seg, h_off // seg
+
+    def submitters(a, n):
+        ptr = a.ctypes.data_as(C.c_void_p)
+        calls = C.c_size_t()
+        out = {"b200": lambda h2d: N.check((N.lib.pf_backend_h2d if h2d else N.lib.pf_backend_d2h)(
+            be._h, C.cast(ptr, C.POINTER(N.CopyDesc)), n, sp))}
+        out["reference_direct"] = lambda h2d: ref.pfr_submit_direct(ptr, n, int(h2d), sp, C.byref(calls))
+        if has_kernel:
+            out["reference_kernel"] = lambda h2d: ref.pfr_submit_kernel(ptr, n, int(h2d), sp)
+        return out
+
+    rows, exact = [], True
+    for layout in ("contiguous", "strided_device", "shuffled"):
+        for n in counts:
+            a, d_slots, h_slots = descs(layout, n)
+            subs = submitters(a, n)
+            # this library's copy is checked once per cell: device fragments == host fragments after H2D
+            device.zero_()
+            torch.cuda.synchronize()
+            subs["b200"](True)
+            stream.synchronize()
+            got = device.view(-1, seg)[torch.from_numpy(d_slots.astype(np.int64)).to(dev)].cpu().numpy()
+            exact = exact and bool(np.array_equal(got, hview.reshape(-1, seg)[h_slots.astype(np.int64)]))
+            for direction in ("D2H", "H2D"):
+                for name, submit in subs.items():
+                    if name == "reference_direct" and layout != "contiguous" and n > 16384:
+                        iters_here = 5          # 64 Ki single-fragment copies per submission: keep the run short
+                    else:
+                        iters_here = iters
+                    for _ in range(warm):
+                        submit(direction == "H2D")
+                        stream.synchronize()
+                    t0 = time.perf_counter()
+                    for _ in range(iters_here):
+                        submit(direction == "H2D")
+                        stream.synchronize()
+                    secs = time.perf_counter() - t0
+                    rows.append({"layout": layout, "blocks": n, "direction": direction, "backend": name,
+                                 "avg_ms": round(secs * 1e3 / iters_here, 4),
+                                 "GiBps": round(n * seg * iters_here / secs / 2**30, 2)})
+    st = be.stats()
+    be.close()
+    pool.close()
+    print(json.dumps({"metric": "transfer_grid_GiBps", "unit": "GiB/s", "higher_is_better": True, "n_gpus": 1,
+                      "data": "synthetic", "config": {"workload": "transfer_h2d grid", "fragment_bytes": seg,
+                                                      "warmup": warm, "iterations": iters},
+                      "bit_exact": exact, "device_status": st["device_status"], "rows": rows}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1296,6 +1395,8 @@ def main():
     ap.add_argument("--ttft", action="store_true",
                     help="cold / warm time-to-first-token shape through the connector hooks, blocking vs layer-wise")
     ap.add_argument("--ttft-requests", type=int, default=8)
+    ap.add_argument("--transfer-grid", action="store_true",
+                    help="the reference's descriptor-level transfer_h2d grid on this library and both reference backends")
     ap.add_argument("--vllm-ttft", action="store_true",
                     help="cold / warm time-to-first-token under a real vLLM engine with this library as its KV connector")
     ap.add_argument("--after-forward", action="store_true",
@@ -1310,6 +1411,9 @@ def main():
         return
     if args.vllm_ttft:
         run_vllm_ttft(args)
+        return
+    if args.transfer_grid:
+        run_transfer_grid(args)
         return
     world_env = int(os.environ.get("WORLD_SIZE", "1"))
     if args.gpus != world_env and world_env == 1 and args.gpus > 1:

@@ -1036,33 +1036,76 @@ void TransferBackend::copy_descs(const pf_copy_desc *copies, size_t n, bool host
   // Split the batch: maximal runs of equally sized descriptors whose host side is contiguous
   // go through the staging ring (the device side may be scattered); the rest become
   // [dst, src, size] triples for the zero-copy kernel.
+  // Descriptors that arrive in arbitrary order but whose host sides tile one dense range (equal
+  // sizes, every slot of the range hit exactly once) are put into slot order first - a counting
+  // sort, O(n) - so that the range becomes a single staged run instead of n zero-copy fragments.
+  // The outcome of a batch does not depend on descriptor order (destinations do not overlap).
+  std::vector<pf_copy_desc> in_slot_order;
+  if (n >= 2 && cfg_.route != PF_ROUTE_ZEROCOPY && copies[0].size > 0) {
+    const size_t sz = copies[0].size;
+    uintptr_t lo = (uintptr_t)copies[0].host;
+    bool uniform = true, ascending = true;
+    for (size_t i = 0; i < n && uniform; ++i) {
+      const uintptr_t h = (uintptr_t)copies[i].host;
+      uniform = copies[i].size == sz && copies[i].host_allocation == copies[0].host_allocation &&
+                copies[i].host_device - copies[0].host_device == (uint64_t)(h - (uintptr_t)copies[0].host);
+      if (i && h < (uintptr_t)copies[i - 1].host) ascending = false;
+      lo = std::min(lo, h);
+    }
+    if (uniform && !ascending) {
+      std::vector<char> seen(n, 0);
+      bool tiles = true;
+      for (size_t i = 0; i < n && tiles; ++i) {
+        const uintptr_t d = (uintptr_t)copies[i].host - lo;
+        const size_t slot = d / sz;
+        tiles = d % sz == 0 && slot < n && !seen[slot];
+        if (tiles) seen[slot] = 1;
+      }
+      if (tiles) {
+        in_slot_order.resize(n);
+        for (size_t i = 0; i < n; ++i) in_slot_order[((uintptr_t)copies[i].host - lo) / sz] = copies[i];
+        copies = in_slot_order.data();
+      }
+    }
+  }
+
+  // A run whose device side is contiguous as well needs no gather at all: it is one plain DMA,
+  // which is what the reference's merge rule produces for it (memcpy.rs:25-55).
   struct Run {
     size_t first, count;
+    bool dense;
   };
   std::vector<Run> staged;
-  std::vector<char> is_staged(n, 0);
+  std::vector<char> is_staged(n, 0);   // 0: zero-copy descriptor, 1: staged through the ring, 2: part of a dense run
+  size_t n_staged = 0, n_dense = 0;
   if (cfg_.route != PF_ROUTE_ZEROCOPY) {
     size_t i = 0;
     while (i < n) {
       size_t j = i + 1;
       const size_t sz = copies[i].size;
+      bool dense = true;
       while (j < n && copies[j].size == sz &&
              (char *)copies[j].host == (char *)copies[j - 1].host + sz &&
              copies[j].host_device == copies[j - 1].host_device + sz &&
-             copies[j].host_allocation == copies[i].host_allocation)
+             copies[j].host_allocation == copies[i].host_allocation) {
+        dense = dense && copies[j].device == copies[j - 1].device + sz;
         ++j;
+      }
       const size_t bytes = (j - i) * sz;
       const bool want = cfg_.route == PF_ROUTE_STAGED || bytes >= cfg_.min_dma_bytes;
-      if (want && sz > 0 && sz <= cfg_.staging_slot_bytes && sz <= 0xFFFFFFFFull) {
-        staged.push_back({i, j - i});
+      if (want && sz > 0 && dense && copies[i].device && copies[i].host) {
+        staged.push_back({i, j - i, true});
+        for (size_t k = i; k < j; ++k) is_staged[k] = 2;
+        n_dense += j - i;
+      } else if (want && sz > 0 && sz <= cfg_.staging_slot_bytes && sz <= 0xFFFFFFFFull) {
+        staged.push_back({i, j - i, false});
         for (size_t k = i; k < j; ++k) is_staged[k] = 1;
+        n_staged += j - i;
       }
       i = j;
     }
   }
-  size_t n_staged = 0;
-  for (auto &r : staged) n_staged += r.count;
-  const size_t n_direct = n - n_staged;
+  const size_t n_direct = n - n_staged - n_dense;
   const size_t table_bytes = align_up(n_staged * sizeof(uint64_t), 256);
   const size_t triple_bytes = align_up(n_direct * 3 * sizeof(uint64_t), 256);
   const size_t meta_bytes = table_bytes + triple_bytes;
@@ -1073,7 +1116,8 @@ void TransferBackend::copy_descs(const pf_copy_desc *copies, size_t n, bool host
   size_t t = 0, q = 0;
   for (size_t i = 0; i < n; ++i) {
     const pf_copy_desc &c = copies[i];
-    if (is_staged[i]) {
+    if (is_staged[i] == 2) continue;
+    if (is_staged[i] == 1) {
       table[t++] = c.device;
     } else {
       if (c.size && (!c.device || !c.host_device)) throw Error::invalid(strf("copy descriptor %zu has a null address", i));
@@ -1085,7 +1129,7 @@ void TransferBackend::copy_descs(const pf_copy_desc *copies, size_t n, bool host
       ++q;
     }
   }
-  meta_upload(base, meta_bytes, stream);
+  if (meta_bytes) meta_upload(base, meta_bytes, stream);
   std::fill(aux_task_dirty_.begin(), aux_task_dirty_.end(), 0);
   std::fill(aux_forked_.begin(), aux_forked_.end(), 0);
   group_limit_ = kFirstGroupBytes;
@@ -1093,6 +1137,16 @@ void TransferBackend::copy_descs(const pf_copy_desc *copies, size_t n, bool host
   size_t table_cursor = 0;
   for (auto &r : staged) {
     const pf_copy_desc &c0 = copies[r.first];
+    if (r.dense) {
+      const size_t bytes = r.count * c0.size;
+      if (host_is_src)
+        PF_CUDA(cudaMemcpyAsync((void *)(uintptr_t)c0.device, c0.host, bytes, cudaMemcpyHostToDevice, stream));
+      else
+        PF_CUDA(cudaMemcpyAsync(c0.host, (const void *)(uintptr_t)c0.device, bytes, cudaMemcpyDeviceToHost, stream));
+      ++stats_.dma_copies;
+      stats_.bytes_staged += bytes;
+      continue;
+    }
     const Side dev{0, 0, nullptr, reinterpret_cast<const uint64_t *>(meta_dev_ + base) + table_cursor};
     const pf_host_run run{0, r.count, c0.host, c0.host_device, c0.size};
     staged_run(dev, run, c0.size, host_is_src, stream);
