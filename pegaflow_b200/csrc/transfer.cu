@@ -1036,36 +1036,79 @@ void TransferBackend::copy_descs(const pf_copy_desc *copies, size_t n, bool host
   // Split the batch: maximal runs of equally sized descriptors whose host side is contiguous
   // go through the staging ring (the device side may be scattered); the rest become
   // [dst, src, size] triples for the zero-copy kernel.
-  // Descriptors that arrive in arbitrary order but whose host sides tile one dense range (equal
-  // sizes, every slot of the range hit exactly once) are put into slot order first - a counting
-  // sort, O(n) - so that the range becomes a single staged run instead of n zero-copy fragments.
-  // The outcome of a batch does not depend on descriptor order (destinations do not overlap).
-  std::vector<pf_copy_desc> in_slot_order;
-  if (n >= 2 && cfg_.route != PF_ROUTE_ZEROCOPY && copies[0].size > 0) {
+  //
+  // Fast path first: equally sized descriptors whose host sides tile one dense range - every slot
+  // of the range hit exactly once, in whatever order they arrive - need no run detection at all.
+  // The device addresses go straight into the table in slot order (a counting sort, O(n)) and the
+  // whole batch is a single staged run, or one plain DMA when the device side is dense as well.
+  // (The outcome of a batch does not depend on descriptor order: destinations do not overlap.)
+  if (n >= 2 && cfg_.route != PF_ROUTE_ZEROCOPY && copies[0].size > 0 && copies[0].size <= cfg_.staging_slot_bytes &&
+      copies[0].size <= 0xFFFFFFFFull && (cfg_.route == PF_ROUTE_STAGED || n * copies[0].size >= cfg_.min_dma_bytes)) {
     const size_t sz = copies[0].size;
     uintptr_t lo = (uintptr_t)copies[0].host;
-    bool uniform = true, ascending = true;
+    bool uniform = true, in_order = true;   // in_order: already ascending and dense on both sides
     for (size_t i = 0; i < n && uniform; ++i) {
       const uintptr_t h = (uintptr_t)copies[i].host;
-      uniform = copies[i].size == sz && copies[i].host_allocation == copies[0].host_allocation &&
+      uniform = copies[i].size == sz && copies[i].device != 0 && h != 0 &&
                 copies[i].host_device - copies[0].host_device == (uint64_t)(h - (uintptr_t)copies[0].host);
-      if (i && h < (uintptr_t)copies[i - 1].host) ascending = false;
+      if (i) in_order = in_order && h == (uintptr_t)copies[i - 1].host + sz && copies[i].device == copies[i - 1].device + sz;
       lo = std::min(lo, h);
     }
-    if (uniform && !ascending) {
-      std::vector<char> seen(n, 0);
+    if (uniform && in_order) {
+      const size_t bytes = n * sz;
+      if (host_is_src)
+        PF_CUDA(cudaMemcpyAsync((void *)(uintptr_t)copies[0].device, copies[0].host, bytes, cudaMemcpyHostToDevice, stream));
+      else
+        PF_CUDA(cudaMemcpyAsync(copies[0].host, (const void *)(uintptr_t)copies[0].device, bytes, cudaMemcpyDeviceToHost, stream));
+      ++stats_.dma_copies;
+      stats_.bytes_staged += bytes;
+      return;
+    }
+    if (uniform) {
+      const size_t table_bytes = align_up(n * sizeof(uint64_t), 256);
+      const size_t base = meta_alloc(table_bytes);
+      uint64_t *table = reinterpret_cast<uint64_t *>(meta_host_ + base);
+      std::memset(table, 0, n * sizeof(uint64_t));
       bool tiles = true;
       for (size_t i = 0; i < n && tiles; ++i) {
         const uintptr_t d = (uintptr_t)copies[i].host - lo;
         const size_t slot = d / sz;
-        tiles = d % sz == 0 && slot < n && !seen[slot];
-        if (tiles) seen[slot] = 1;
+        tiles = d % sz == 0 && slot < n && table[slot] == 0;
+        if (tiles) table[slot] = copies[i].device;
       }
       if (tiles) {
-        in_slot_order.resize(n);
-        for (size_t i = 0; i < n; ++i) in_slot_order[((uintptr_t)copies[i].host - lo) / sz] = copies[i];
-        copies = in_slot_order.data();
+        bool dense = true;
+        for (size_t k = 1; k < n && dense; ++k) dense = table[k] == table[k - 1] + sz;
+        char *host_lo = reinterpret_cast<char *>(lo);
+        const uint64_t host_dev_lo = copies[0].host_device - (uint64_t)((uintptr_t)copies[0].host - lo);
+        if (dense) {
+          const size_t bytes = n * sz;
+          if (host_is_src)
+            PF_CUDA(cudaMemcpyAsync((void *)(uintptr_t)table[0], host_lo, bytes, cudaMemcpyHostToDevice, stream));
+          else
+            PF_CUDA(cudaMemcpyAsync(host_lo, (const void *)(uintptr_t)table[0], bytes, cudaMemcpyDeviceToHost, stream));
+          ++stats_.dma_copies;
+          stats_.bytes_staged += bytes;
+          meta_head_ = base;  // nothing was uploaded: the region is handed out again
+          return;
+        }
+        meta_upload(base, table_bytes, stream);
+        std::fill(aux_task_dirty_.begin(), aux_task_dirty_.end(), 0);
+        std::fill(aux_forked_.begin(), aux_forked_.end(), 0);
+        group_limit_ = kFirstGroupBytes;
+        if (host_is_src) PF_CUDA(cudaEventRecord(fork_, stream));
+        const Side dev{0, 0, nullptr, reinterpret_cast<const uint64_t *>(meta_dev_ + base)};
+        staged_run(dev, pf_host_run{0, n, host_lo, host_dev_lo, sz}, sz, host_is_src, stream);
+        flush_group();
+        if (!host_is_src) join_copy_streams(stream, aux_task_dirty_, -1);
+        cudaEvent_t ev = take_event();
+        PF_CUDA(cudaEventRecord(ev, stream));
+        meta_inflight_.push_back({base, base + table_bytes, ev});
+        return;
       }
+      // not a tiling (gaps, duplicates, mixed strides): the general path below; the table region is
+      // simply handed out again, nothing in flight refers to it
+      meta_head_ = base;
     }
   }
 
