@@ -201,11 +201,12 @@ def check(status: int):
     raise PegaFlowError(status, msg)
 
 
-def release(fn_name: str, handle) -> None:
+def release(fn_name: str, handle, _module_dict=globals()) -> None:
     """Call a `*_free` / `*_release` entry point from `close()` or `__del__`.  During interpreter
-    shutdown module globals may already be gone when a finalizer runs; the handle is then left to
-    the process exit."""
-    library = globals().get("lib")
+    shutdown module globals are set to None one by one while finalizers still run; the module
+    dictionary is bound at definition time, and a library that is already gone means the handle is
+    left to the process exit."""
+    library = _module_dict.get("lib")
     if library is None:
         return
     getattr(library, fn_name)(handle)

@@ -13,9 +13,9 @@ from typing import List, Optional, Sequence
 from . import _native as N
 
 
-def _release(fn_name, handle, _native=N):
-    # bound at definition time: a finalizer may run after this module's globals were cleared
-    _native.release(fn_name, handle)
+def _release(fn_name, handle, _release_native=N.release):
+    # bound at definition time: a finalizer may run after module globals were cleared
+    _release_native(fn_name, handle)
 
 
 @dataclass

@@ -15,9 +15,9 @@ import numpy as np
 from . import _native as N
 from ._native import PegaFlowError, PegaflowInternal, PegaflowInvalidArgument  # noqa: F401  (re-exported)
 
-def _release(fn_name, handle, _native=N):
-    # bound at definition time: a finalizer may run after this module's globals were cleared
-    _native.release(fn_name, handle)
+def _release(fn_name, handle, _release_native=N.release):
+    # bound at definition time: a finalizer may run after module globals were cleared
+    _release_native(fn_name, handle)
 
 
 TRANSFER_MODES = {"direct": 0, "kernel": 1}  # transfer/mod.rs:66-76; both run on the one B200 backend
