@@ -494,6 +494,9 @@ def build_roofline(stat_pairs, args):
                     "how": "one CUDA event pair around every launch, on the launching stream, inside the timed region"}
         if dev_n and dev_ms > 0:
             dev_ach = (pack_bytes / pack_launches) * dev_n / 1e6 / dev_ms
+            roofline["note"] = ("an event pair around a ~8 us kernel also brackets its launch latency and the two event "
+                                "records; `device_clock` is the same launches timed by the kernel's own clock: "
+                                f"{round(dev_ach / hbm_peak, 4)} of peak")
             roofline["device_clock"] = {
                 "avg_launch_us": round(dev_ms / dev_n * 1e3, 2), "achieved": round(dev_ach, 1),
                 "frac": round(dev_ach / hbm_peak, 4), "launches": dev_n,
