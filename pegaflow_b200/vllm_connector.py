@@ -105,6 +105,7 @@ class PegaKVConnector(KVConnectorBase_V1):
                 block_size=self._block_size, is_mla=self._is_mla)
             self._saved_requests: set = set()      # requests with saves in the pool, not yet reported sent
             self._events = []                      # per-layer "KV written" events of the current step
+            self._layers_queued: set = set()       # layers whose save_kv_layer hook ran in the current step
             self._loading_this_step = False
 
     @classmethod
@@ -170,18 +171,28 @@ class PegaKVConnector(KVConnectorBase_V1):
         ready = torch.cuda.Event()
         ready.record(torch.cuda.current_stream())
         self._events.append(ready)      # kept until wait_for_save: the engine waits on it from another thread
+        self._layers_queued.add(layer_name)
         for intent in list(meta.ready_save_intents.values()) + list(meta.save_intents.values()):
             self._worker.save_kv_layer(layer_name, list(intent.block_ids_by_group[0]), list(intent.block_hashes),
                                        ready.cuda_event)
 
     def wait_for_save(self):
         meta = self._get_connector_metadata()
-        if self._layerwise:
+        wanted = bool(meta.save_intents or meta.ready_save_intents)
+        if self._layerwise and not (wanted and len(self._layers_queued) < len(self._worker.registered_layers)):
             self._worker.wait_for_save()        # the layers were queued one by one: this only flushes
             self._saved_requests.update(meta.save_intents)
             self._saved_requests.update(meta.ready_save_intents)
             self._events.clear()
+            self._layers_queued.clear()
         else:
+            # Request-level mode - or a step whose per-layer hooks did not run for every layer (a
+            # forward pass replayed from a full CUDA graph skips the Python between layers): save
+            # everything after the forward pass (a layer that was queued already is copied again; the
+            # first copy of a slot wins in the engine).
+            self._worker.wait_for_save()
+            self._events.clear()
+            self._layers_queued.clear()
             torch.cuda.current_stream().synchronize()
             self._saved_requests.update(self._worker.wait_for_save_from_metadata(meta))
         self._loading_this_step = False
