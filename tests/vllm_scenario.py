@@ -45,7 +45,8 @@ def main():
 
 
 def _start(LLM, KVTransferConfig, model_dir, layerwise):
-    return LLM(model=model_dir, load_format="dummy", skip_tokenizer_init=True, enforce_eager=True, max_model_len=2048,
+    return LLM(model=model_dir, load_format="dummy", skip_tokenizer_init=True,
+               enforce_eager="--cuda-graphs" not in sys.argv, max_model_len=2048,
               gpu_memory_utilization=0.10, dtype="bfloat16", seed=0, enable_prefix_caching=True, block_size=16,
               kv_transfer_config=KVTransferConfig(
                   kv_connector="PegaKVConnector", kv_connector_module_path="pegaflow_b200.vllm_connector", kv_role="kv_both",
@@ -75,7 +76,7 @@ def _scenario(llm, SamplingParams, vllm_connector, layerwise, np):
     host_pool = run()
     after_host = engine.metrics()
     print(json.dumps({
-        "layerwise": layerwise, "prefix_cache_reset": bool(reset_ok),
+        "layerwise": layerwise, "cuda_graphs": "--cuda-graphs" in sys.argv, "prefix_cache_reset": bool(reset_ok),
         "warm_runs_identical": gpu_cache == host_pool, "cold_equals_warm_tokens": [[t for t, _ in a] for a in cold] ==
         [[t for t, _ in a] for a in host_pool],
         "saved_bytes_cold": after_cold["save_bytes"], "loaded_bytes_gpu_cache_run": after_gpu_cache["load_bytes"],
