@@ -1370,6 +1370,49 @@ def run_transfer_grid(args):
                       "bit_exact": exact, "device_status": st["device_status"], "rows": rows}))
 
 
+def run_pool_coldstart(args):
+    """Time to first usable byte of the pinned pool, per allocation strategy (the reference times the same
+    thing in pegaflow-core/examples/pinned_alloc_*: `cudaHostAlloc`, `mmap` + parallel pre-touch +
+    `cudaHostRegister`, and the same on huge pages, pinned_mem.rs:149-270)."""
+    import torch
+    import pegaflow_b200 as pf
+
+    torch.cuda.set_device(0)
+    torch.cuda.synchronize()
+    gib = args.pool_gib
+    rows = []
+    for name, kw in (("cudaHostAlloc", {}), ("mmap+pretouch+register", {"use_mmap": True}),
+                     ("hugepages+register", {"use_mmap": True, "use_hugepages": True})):
+        t0 = time.perf_counter()
+        try:
+            pool = pf.PinnedPool(gib << 30, numa_node=pf.numa_node_of_device(0), **kw)
+        except pf.PegaFlowError as e:
+            rows.append({"strategy": name, "unavailable": str(e)[:120]})
+            continue
+        secs = time.perf_counter() - t0
+        # the memory must be usable by the copy engine at once: one 1 GiB copy each way
+        host, host_dev, handle = pool.alloc(1 << 30)
+        d = torch.empty(1 << 30, dtype=torch.uint8, device="cuda")
+        be = pf.TransferBackend(0)
+        descs, nd = be.make_descs([(d.data_ptr(), host, host_dev, 1 << 30)])
+        stream = torch.cuda.Stream()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        be.h2d(descs, nd, stream.cuda_stream)
+        b.record(stream)
+        b.synchronize()
+        rows.append({"strategy": name, "gib": gib, "seconds": round(secs, 3), "GiB_per_s": round(gib / secs, 2),
+                     "first_h2d_GBps": round((1 << 30) / 1e6 / a.elapsed_time(b), 1)})
+        be.close()
+        del d
+        pool.release(handle)
+        t1 = time.perf_counter()
+        pool.close()
+        rows[-1]["free_seconds"] = round(time.perf_counter() - t1, 3)
+    print(json.dumps({"metric": "pinned_pool_coldstart", "unit": "s", "higher_is_better": False, "n_gpus": 1,
+                      "host_cores": os.cpu_count(), "rows": rows}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1398,6 +1441,8 @@ def main():
     ap.add_argument("--ttft", action="store_true",
                     help="cold / warm time-to-first-token shape through the connector hooks, blocking vs layer-wise")
     ap.add_argument("--ttft-requests", type=int, default=8)
+    ap.add_argument("--pool-coldstart", action="store_true", help="time the pinned-pool allocation strategies")
+    ap.add_argument("--pool-gib", type=int, default=16)
     ap.add_argument("--transfer-grid", action="store_true",
                     help="the reference's descriptor-level transfer_h2d grid on this library and both reference backends")
     ap.add_argument("--vllm-ttft", action="store_true",
@@ -1417,6 +1462,9 @@ def main():
         return
     if args.transfer_grid:
         run_transfer_grid(args)
+        return
+    if args.pool_coldstart:
+        run_pool_coldstart(args)
         return
     world_env = int(os.environ.get("WORLD_SIZE", "1"))
     if args.gpus != world_env and world_env == 1 and args.gpus > 1:
