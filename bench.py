@@ -923,6 +923,57 @@ def peer_pairs_phase(pf, torch, n_pairs, args, L, seg, nb, n):
                    "from the first enqueue to the last stream's completion"}
 
 
+def run_peer_local(args):
+    """The peer-copy kernel with source and destination on one GPU (two instances sharing a device, or a
+    profiling run on a single-GPU box): every byte is read from and written to HBM, so the kernel is timed
+    against the HBM roofline instead of NVLink."""
+    import torch
+    import pegaflow_b200 as pf
+
+    L, seg, nb, n = args.peer_layers, 16 * 2 * 128 * 2, 8192, 4096
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    rng = np.random.default_rng(42 + 5)
+    src = [torch.randint(0, 256, (2, nb, seg), dtype=torch.uint8, device=dev) for _ in range(L)]
+    dst = [torch.zeros((2, nb, seg), dtype=torch.uint8, device=dev) for _ in range(L)]
+    sids = (rng.permutation(nb - 1)[:n] + 1).astype(np.uint32)
+    dids = (rng.permutation(nb - 1)[:n] + 1).astype(np.uint32)
+    payload = L * n * 2 * seg
+    be = pf.TransferBackend(0, link_ctas=args.link_ctas)
+    stream = torch.cuda.Stream()
+    sl = [(t.data_ptr(), seg, nb * seg, seg, 2) for t in src]
+    dl = [(t.data_ptr(), seg, nb * seg, seg, 2) for t in dst]
+    for _ in range(max(1, args.warmup)):
+        be.peer_copy_layers(sl, sids, dl, dids, stream.cuda_stream)
+    stream.synchronize()
+    si, di = torch.from_numpy(sids.astype(np.int64)).to(dev), torch.from_numpy(dids.astype(np.int64)).to(dev)
+    ok = all(torch.equal(dst[l][:, di], src[l][:, si]) for l in (0, L - 1))
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(stream)
+    for _ in range(args.steps):
+        be.peer_copy_layers(sl, sids, dl, dids, stream.cuda_stream)
+    b.record(stream)
+    b.synchronize()
+    ms = a.elapsed_time(b) / args.steps
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except OSError:
+        pass
+    hbm = peaks.get("hbm_gbs", 6650.0)
+    st = be.stats()
+    print(json.dumps({
+        "metric": "kv_peer_copy_local_GBps", "value": round(payload / 1e6 / ms, 1), "unit": "GB/s", "n_gpus": 1,
+        "steps": args.steps, "higher_is_better": True, "dtype": "u8", "data": "synthetic", "bit_exact": bool(ok),
+        "config": {"workload": "qwen3-32b-tp4-rank prefix hit, both instances on one GPU", "layers": L, "seg_bytes": seg,
+                   "blocks": n},
+        "roofline": {"kernel": "copy_peer_warp", "bound": "hbm", "achieved": round(2 * payload / 1e6 / ms, 1), "peak": hbm,
+                     "unit": "GB/s", "frac": round(2 * payload / 1e6 / ms / hbm, 4),
+                     "algorithmic_bytes_per_step": 2 * payload, "launches_per_step": st["kernel_launches"] // (args.steps + max(1, args.warmup)),
+                     "how": "one CUDA event pair around all launches of the timed steps"},
+        "gpu_launches": st["kernel_launches"], "device_status": st["device_status"]}))
+
+
 def run_peer(args):
     """Same-box prefix hit: blocks of instance A (GPU 0) land in other block ids of instance B (GPU 1),
     over NVLink with the peer-copy kernel and, for comparison, through the pinned host pool.
@@ -930,6 +981,8 @@ def run_peer(args):
     import torch
     import pegaflow_b200 as pf
 
+    if args.peer_local:
+        return run_peer_local(args)
     if torch.cuda.device_count() < 2:
         print(json.dumps({"metric": "kv_peer_copy_GBps", "unavailable": "needs two GPUs on one box"}))
         return
@@ -1435,6 +1488,8 @@ def main():
                     help="DRAM bytes per launch of the dominant kernel from an ncu capture (recorded in the line)")
     ap.add_argument("--duplex", action="store_true",
                     help="save and load at the same time (the TP=8 configuration's wording) instead of one after the other")
+    ap.add_argument("--peer-local", action="store_true", help="with --peer: source and destination on one GPU")
+    ap.add_argument("--peer-layers", type=int, default=64)
     ap.add_argument("--peer-pairs", type=int, default=1,
                     help="with --peer: also run this many GPU i -> GPU pairs+i copies at once (needs 2 x pairs GPUs)")
     ap.add_argument("--peer-push", action="store_true", help="with --peer: run the copy kernel on the source GPU")
