@@ -183,6 +183,22 @@ int pf_backend_peer_copy(pf_backend *backend, const pf_device_layout *src, const
 int pf_backend_peer_copy_layers(pf_backend *backend, const pf_device_layout *src, const pf_device_layout *dst,
                                 size_t n_layers, const uint32_t *src_ids, const uint32_t *dst_ids,
                                 size_t n_blocks, void *stream);
+/* Cross-process registration (python/pegaflow/ipc_wrapper.py:101-163 + pegaflow-server/src/registry.rs:172-203):
+ * the process that owns a KV-cache tensor exports the region, the process that runs the engine
+ * opens it and registers the returned pointer.  The region travels as these 104 plain bytes.
+ * Devices are matched by UUID, so the two processes may number their GPUs differently.  A region
+ * cannot be opened by the process that exported it (a CUDA IPC rule).  Mappings are shared: regions
+ * of one allocation open it once; pf_ipc_close drops one use. */
+typedef struct pf_ipc_region {
+  uint8_t handle[64];      /* cudaIpcMemHandle_t of the allocation that contains the region */
+  uint64_t offset;         /* of the region inside that allocation */
+  uint64_t nbytes;
+  uint8_t device_uuid[16];
+} pf_ipc_region;
+int pf_ipc_export(uint64_t device_ptr, size_t nbytes, pf_ipc_region *out);
+int pf_ipc_open(const pf_ipc_region *region, uint64_t *device_ptr, int *device_id);
+int pf_ipc_close(const pf_ipc_region *region);
+
 /* Make `peer_device`'s memory addressable from `device_id` (cudaDeviceEnablePeerAccess). */
 int pf_enable_peer_access(int device_id, int peer_device);
 

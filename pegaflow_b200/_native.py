@@ -126,6 +126,13 @@ _sig("pf_backend_save_layers", C.c_int, vp, P(LayerXfer), sz, vp, P(vp))
 _sig("pf_backend_load_layers", C.c_int, vp, P(LayerXfer), sz, vp, P(vp))
 _sig("pf_backend_peer_copy", C.c_int, vp, P(DeviceLayout), P(u32), P(DeviceLayout), P(u32), sz, vp)
 _sig("pf_backend_peer_copy_layers", C.c_int, vp, P(DeviceLayout), P(DeviceLayout), sz, P(u32), P(u32), sz, vp)
+class IpcRegion(C.Structure):
+    _fields_ = [("handle", C.c_uint8 * 64), ("offset", u64), ("nbytes", u64), ("device_uuid", C.c_uint8 * 16)]
+
+
+_sig("pf_ipc_export", C.c_int, u64, sz, P(IpcRegion))
+_sig("pf_ipc_open", C.c_int, P(IpcRegion), P(u64), P(C.c_int))
+_sig("pf_ipc_close", C.c_int, P(IpcRegion))
 _sig("pf_enable_peer_access", C.c_int, C.c_int, C.c_int)
 _sig("pf_save_blocks_noalloc", C.c_int, C.c_int, P(DeviceLayout), P(u32), sz, vp, sz, vp)
 _sig("pf_backend_get_stats", C.c_int, vp, P(BackendStats))

@@ -102,6 +102,14 @@ def _region_of(obj) -> Tuple[int, int]:
     storage, like the reference's IPC wrapper, ipc_wrapper.py:101-163) or an explicit pair."""
     if isinstance(obj, tuple):
         return int(obj[0]), int(obj[1])
+    if isinstance(obj, (bytes, bytearray)):
+        # the reference's `wrapper_bytes_list`: a pickled IPC wrapper from a worker in another process
+        from .ipc import CudaIPCWrapper
+
+        obj = CudaIPCWrapper.from_bytes(bytes(obj))
+    if hasattr(obj, "region") and hasattr(obj, "open"):
+        ptr, nbytes, _device = obj.open()
+        return ptr, nbytes
     if obj.storage_offset() != 0:
         raise ValueError("KV cache tensor must have zero storage offset")
     return obj.data_ptr(), obj.untyped_storage().nbytes()
