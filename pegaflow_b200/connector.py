@@ -13,10 +13,10 @@
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence, Tuple, Union
+from typing import Dict, List, Optional, Sequence, Tuple
 
 from . import _native as N
-from .engine import Completion, PegaEngine, PyLoadState
+from .engine import PegaEngine, PyLoadState
 
 CROSS_LAYER_KEY = "ALL_LAYERS"  # worker.py:32
 

@@ -1,5 +1,4 @@
 """Pin the CPU oracle to the reference's own known-answer tests (no GPU needed)."""
-import ctypes as C
 import json
 import os
 
