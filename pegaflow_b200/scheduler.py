@@ -75,6 +75,34 @@ class _Tracked:
     scheduled_tokens: int = 0
 
 
+def require_single_attention_group(kv_cache_config) -> None:
+    """Accept what this scheduler connector can serve and refuse the rest loudly: one KV-cache
+    group of full-attention or MLA layers (or a uniformly typed group of MLA layers), the
+    single-group cases of the reference's `CacheGroupLayout.from_config` (common.py:305-356).
+    Hybrid configurations (attention + recurrent-state groups) need the reference's reconcile
+    logic, which is not mirrored.  Specs are matched by class name so that vLLM need not be
+    importable where this runs."""
+    groups = tuple(getattr(kv_cache_config, "kv_cache_groups", ()) or ())
+    if not groups:
+        return
+    if len(groups) > 1:
+        raise RuntimeError(f"this connector supports a single KV cache group, the model has {len(groups)} "
+                           "(hybrid attention + recurrent-state caches are not supported)")
+    def kinds(obj):
+        return {c.__name__ for c in type(obj).__mro__}
+
+    spec = groups[0].kv_cache_spec
+    kind = type(spec).__name__
+    if kinds(spec) & {"FullAttentionSpec", "MLAAttentionSpec"}:
+        return
+    if kind == "UniformTypeKVCacheSpecs":
+        inner = list((getattr(spec, "kv_cache_specs", None) or {}).values())
+        if inner and all("MLAAttentionSpec" in kinds(x) for x in inner):
+            return
+    raise RuntimeError("this connector supports a single cache group only for FullAttention, MLA, or uniformly "
+                       f"grouped MLA layers (got {kind})")
+
+
 class ShardQuery:
     """Prefix query across node-local TP shards (tp_shards.py:23-97): the usable hit is the prefix
     every shard holds; shards that answered with more are re-leased for exactly that prefix."""

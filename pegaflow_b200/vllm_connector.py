@@ -32,7 +32,7 @@ from vllm.distributed.kv_transfer.kv_connector.v1.base import KVConnectorBase_V1
 
 from . import connector as _connector
 from .engine import PegaEngine
-from .scheduler import PegaConnectorMetadata, SchedulerConnector
+from .scheduler import PegaConnectorMetadata, SchedulerConnector, require_single_attention_group
 
 _DEBUG = os.environ.get("PEGAFLOW_B200_TRACE", "0") == "1"
 _ENGINES: Dict[str, PegaEngine] = {}
@@ -82,6 +82,7 @@ class _Hashed:
 class PegaKVConnector(KVConnectorBase_V1):
     def __init__(self, vllm_config, role: KVConnectorRole, kv_cache_config=None):
         super().__init__(vllm_config, role, kv_cache_config)
+        require_single_attention_group(kv_cache_config)
         cfg = vllm_config.kv_transfer_config
         extra = cfg.get_from_extra_config
         self._instance_id = str(getattr(vllm_config, "instance_id", "") or cfg.engine_id or "vllm")

@@ -143,3 +143,38 @@ def test_kat_invalid_shard_answers_do_not_leak_leases(hits, lease):
     first.release.assert_called_once_with(b"first")
     if lease:
         second.release.assert_called_once_with(lease)
+
+
+# ---- which KV-cache group layouts are served (python/tests/test_cache_group_layout.py:72-135) ---------------
+def _spec(name, **attrs):
+    return type(name, (), {})() if not attrs else type(name, (), attrs)()
+
+
+def _cfg(*specs):
+    from types import SimpleNamespace
+
+    return SimpleNamespace(kv_cache_groups=[SimpleNamespace(layer_names=("l",), kv_cache_spec=s) for s in specs])
+
+
+def test_single_attention_or_mla_groups_are_accepted():
+    from pegaflow_b200.scheduler import require_single_attention_group as check
+
+    check(None)
+    check(_cfg())
+    check(_cfg(_spec("FullAttentionSpec")))
+    check(_cfg(_spec("MLAAttentionSpec")))
+    check(_cfg(_spec("UniformTypeKVCacheSpecs", kv_cache_specs={"a": _spec("MLAAttentionSpec"), "b": _spec("MLAAttentionSpec")})))
+
+
+@pytest.mark.parametrize("specs", [
+    (_spec("MambaSpec"),), (_spec("SlidingWindowSpec"),),
+    (_spec("UniformTypeKVCacheSpecs", kv_cache_specs={}),),
+    (_spec("UniformTypeKVCacheSpecs", kv_cache_specs={"a": _spec("MLAAttentionSpec"), "b": _spec("FullAttentionSpec")}),),
+    (_spec("FullAttentionSpec"), _spec("MambaSpec")),
+    (_spec("FullAttentionSpec"), _spec("FullAttentionSpec")),
+])
+def test_other_group_layouts_are_refused(specs):
+    from pegaflow_b200.scheduler import require_single_attention_group as check
+
+    with pytest.raises(RuntimeError, match="single"):
+        check(_cfg(*specs))
