@@ -14,6 +14,17 @@ data-path collective).
 Prints ONE JSON line:  value = payload GB/s (10^9 B/s) with the KV cache resident in HBM,
 timed with CUDA events; e2e = the same metric through the engine's public API (save with
 hashes, prefix query, lease, load), host wall clock around a synchronised region.
+
+Other modes (each prints one JSON line of its own):
+    --workload W         the other baseline shapes (qwen3-0.6b, llama70b-tp8-rank, mla-bf16, mla-fp8, small)
+    --duplex             every step saves one set of blocks and loads another at the same time
+    --peer [--peer-pairs K | --peer-local]
+                         NVLink block copy between instances (GPU pairs, or both on one GPU)
+    --transfer-grid      the reference's descriptor-level transfer_h2d grid on three backends
+    --ttft               cold / warm time-to-first-token shape through the connector hooks
+    --vllm-ttft [--after-forward]
+                         the same shape under a real vLLM engine with this library as KV connector
+    --pool-coldstart     pinned-pool allocation strategies
 """
 from __future__ import annotations
 
