@@ -285,6 +285,65 @@ SCRIPTS = {
         ("sent", ["o"]),
         ("finished", "o", [1, 2, 3, 4]),
     ]},
+    # two requests in flight: one warm (loads), one cold (saves), scheduled in the same steps
+    "two_requests_interleaved": {"ops": [
+        ("store", 0, _r(0, 3)),
+        ("request", "u", _r(0, 3), 60),
+        ("request", "v", _r(10, 14), 70),
+        ("match", "u", 0),
+        ("alloc", "u", [1, 2, 3, 4], 0, 48),
+        ("match", "v", 0),
+        ("alloc", "v", [5, 6, 7, 8, 9], 0, 0),
+        ("step", {"new": [["u", [1, 2, 3, 4], 48, 12], ["v", [5, 6, 7, 8, 9], 0, 40]]}),
+        ("step", {"cached": [["u", None, 60, 1], ["v", None, 40, 30]]}),
+        ("grow", "u", [3], 70),
+        ("step", {"cached": [["u", None, 61, 1], ["v", None, 70, 1]]}),
+        ("finished", "v", [5, 6, 7, 8, 9]),
+        ("step", {"cached": [["u", None, 62, 2]]}),
+        ("sent", ["v"]),
+        ("finished", "u", [1, 2, 3, 4]),
+    ]},
+    # a request is dropped while it still holds a Ready lookup (never allocated): the lease goes back
+    "finished_before_allocation": {"ops": [
+        ("store", 0, _r(0, 2)),
+        ("request", "z", _r(0, 2), 40),
+        ("match", "z", 0),
+        ("finished", "z", []),
+        ("request", "z2", _r(0, 2), 40),
+        ("loading", 0, "z2", 5),
+        ("match", "z2", 0),
+        ("finished", "z2", []),
+    ]},
+    # a long decode: hashes appear one block at a time and are saved as soon as their block is full
+    "decode_fills_blocks": {"ops": [
+        ("request", "g", _r(0, 1), 20),
+        ("match", "g", 0),
+        ("alloc", "g", [1, 2], 0, 0),
+        ("step", {"new": [["g", [1, 2], 0, 20]]}),
+        ("step", {"cached": [["g", None, 20, 6]]}),
+        ("step", {"cached": [["g", None, 26, 6]]}),
+        ("grow", "g", [1], 33),
+        ("step", {"cached": [["g", [3], 32, 6]]}),
+        ("step", {"cached": [["g", None, 38, 10]]}),
+        ("grow", "g", [2], 49),
+        ("step", {"cached": [["g", [4], 48, 1]]}),
+        ("finished", "g", [1, 2, 3, 4]),
+        ("sent", ["g"]),
+        ("finished", "g", [1, 2, 3, 4]),
+    ]},
+    # a warm request is preempted after its load and resumed later: the loaded prefix is not saved again
+    "hit_then_preempt_and_resume": {"ops": [
+        ("store", 0, _r(0, 2)),
+        ("request", "h", _r(0, 4), 64),
+        ("match", "h", 0),
+        ("alloc", "h", [1, 2, 3, 4], 0, 32),
+        ("step", {"new": [["h", [1, 2, 3, 4], 32, 16]]}),
+        ("step", {"preempted": ["h"]}),
+        ("match", "h", 0),
+        ("alloc", "h", [7, 8, 9, 10], 0, 32),
+        ("step", {"cached": [["h", [7, 8, 9, 10], 32, 32, True]]}),
+        ("finished", "h", [7, 8, 9, 10]),
+    ]},
     # preempted after two blocks were saved, resumed with a fresh block table
     "preempt_and_resume": {"ops": [
         ("request", "r", _r(0, 4), 64),
