@@ -12,6 +12,12 @@ GOLDEN = os.path.join(ROOT, "tests", "golden")
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200)")
+    # A fresh checkout has no built libraries (they are not tracked): build them once, as
+    # `__graft_entry__.build()` does, so that the suite can be run directly.
+    if not os.path.exists(os.path.join(ROOT, "pegaflow_b200", "libpegaflow_b200.so")):
+        import __graft_entry__
+
+        __graft_entry__.build()
 
 
 @pytest.fixture(scope="session")
