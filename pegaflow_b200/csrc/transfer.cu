@@ -982,6 +982,30 @@ void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, 
             stats_.bytes_zero_copy += run.n_blocks * L.range_bytes;
             layer_stream = true;
           } else {
+            // Consecutive block ids (a fresh prompt usually gets them from an ordered free list) are
+            // one strided region on the device as well: a single pitched DMA, nothing to gather.  It
+            // runs on the caller's stream like the zero-copy launches, which keeps the layer's event
+            // and the ordering rules unchanged.
+            const uint32_t *ids = L.block_ids + run.first_block;
+            const bool linear = L.block_stride_bytes == L.range_bytes && run.stride_bytes == L.range_bytes;
+            // (pitched rows are only worth a DMA of their own when they are long: the staged route
+            // already turns short padded rows into large linear copies)
+            bool consecutive = run.n_blocks >= 2 && L.block_stride_bytes >= L.range_bytes &&
+                               run.stride_bytes >= L.range_bytes && (linear || L.range_bytes >= (32u << 10));
+            for (size_t k = 1; k < run.n_blocks && consecutive; ++k) consecutive = ids[k] == ids[k - 1] + 1;
+            if (consecutive) {
+              char *device_first = reinterpret_cast<char *>(dev_base + (uint64_t)ids[0] * L.block_stride_bytes);
+              if (host_is_src)
+                PF_CUDA(cudaMemcpy2DAsync(device_first, L.block_stride_bytes, run.host, run.stride_bytes, L.range_bytes,
+                                          run.n_blocks, cudaMemcpyHostToDevice, stream));
+              else
+                PF_CUDA(cudaMemcpy2DAsync(run.host, run.stride_bytes, device_first, L.block_stride_bytes, L.range_bytes,
+                                          run.n_blocks, cudaMemcpyDeviceToHost, stream));
+              ++stats_.dma_copies;
+              stats_.bytes_staged += run.n_blocks * L.range_bytes;
+              layer_stream = true;
+              continue;
+            }
             const Side dev{dev_base, L.block_stride_bytes, ids_dev + run.first_block, nullptr};
             staged_run(dev, run, L.range_bytes, host_is_src, stream);
           }

@@ -167,9 +167,10 @@ def test_unaligned_and_ragged_descriptors(env, route):
     pool.release(handle)
 
 
-def _layer_case(name, num_blocks, seg, segments, kv_stride, block_stride, n_move, host_stride_pad, seed):
+def _layer_case(name, num_blocks, seg, segments, kv_stride, block_stride, n_move, host_stride_pad, seed,
+                consecutive=False):
     return dict(name=name, num_blocks=num_blocks, seg=seg, segments=segments, kv_stride=kv_stride,
-                block_stride=block_stride, n_move=n_move, pad=host_stride_pad, seed=seed)
+                block_stride=block_stride, n_move=n_move, pad=host_stride_pad, seed=seed, consecutive=consecutive)
 
 
 LAYER_CASES = [
@@ -195,6 +196,12 @@ LAYER_CASES = [
     _layer_case("small_528", 700, 528, 2, 700 * 528, 0, 611, 0, 10),
     # small items with a device stride that is not 16-byte aligned: one item per chunk, byte path
     _layer_case("small_unaligned_stride", 300, 2048, 1, 0, 2052, 257, 0, 11),
+    # consecutive block ids (a fresh prompt on an ordered free list): one DMA per range, no gather
+    _layer_case("consecutive_ids_32k", 64, 32768, 2, 64 * 32768, 0, 20, 0, 12, consecutive=True),
+    # consecutive ids, block stride larger than the block and a padded host stride: pitched DMA
+    _layer_case("consecutive_ids_pitched", 40, 73728, 1, 0, 2 * 73728, 12, 512, 13, consecutive=True),
+    # consecutive ids but short padded rows: stays on the gather route
+    _layer_case("consecutive_ids_short_rows", 300, 4096, 2, 300 * 4096, 0, 200, 512, 14, consecutive=True),
 ]
 
 
@@ -217,6 +224,9 @@ def test_layer_save_load_matches_oracle(env, case, route):
     n = case["n_move"]
     save_ids = rng.permutation(case["num_blocks"])[:n]
     load_ids = rng.permutation(case["num_blocks"])[:n]
+    if case["consecutive"]:
+        save_ids = int(rng.integers(0, case["num_blocks"] - n + 1)) + np.arange(n)
+        load_ids = int(rng.integers(0, case["num_blocks"] - n + 1)) + np.arange(n)
     hstride = range_bytes + case["pad"]
     allocs = [pool.alloc(hstride * n) for _ in range(n_ranges)]
     for a in allocs:
@@ -254,7 +264,12 @@ def test_layer_save_load_matches_oracle(env, case, route):
     d, nd, _ = po.build_copy_descs([(olay, blocks(load_ids))])
     po.execute(d, nd, host_is_src=True)
     assert np.array_equal(mem.read(dev), shadow)
-    assert be.stats()["device_status"] == 0
+    st = be.stats()
+    assert st["device_status"] == 0
+    if case["name"] in ("consecutive_ids_32k", "consecutive_ids_pitched") and route != "zerocopy":
+        assert st["kernel_launches"] == 0 and st["dma_copies"] == 2 * n_ranges, "expected one DMA per range and direction"
+    if case["name"] == "consecutive_ids_short_rows" and route != "zerocopy":
+        assert st["kernel_launches"] > 0
     be.close()
     for a in allocs:
         pool.release(a[2])
