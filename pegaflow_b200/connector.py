@@ -301,6 +301,14 @@ class PegaWorkerConnector:
         if saves:
             cleaned, memo = [], {}
             for name, ids, hashes in saves:
+                if self.page_first and self.tp_size > 1:
+                    # worker.py:982-1005: a page needs every layer, so page-first spreads the save work
+                    # by block, not by layer: rank r writes the pages of blocks with id % tp_size == r
+                    key = ("stripe", id(ids), id(hashes))
+                    if key not in memo:
+                        keep = [(b, h) for b, h in zip(ids, hashes) if b % self.tp_size == self.tp_rank]
+                        memo[key] = ([b for b, _ in keep], [h for _, h in keep])
+                    ids, hashes = memo[key]
                 # layers usually share one (ids, hashes) pair: filter it once and hand the engine the
                 # same list objects for every layer, so that it marshals them once as well
                 key = (id(ids), id(hashes))

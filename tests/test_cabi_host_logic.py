@@ -227,3 +227,43 @@ def test_worker_reports_a_rejected_load_instead_of_raising(mode):
     done, failed = worker.get_finished()
     assert done == [] and failed == ["r1", "r2"]                 # reported, so that nothing stays parked
     assert worker.get_finished() == ([], [])
+
+
+class _RecordingClient:
+    def __init__(self):
+        self.saves = []
+
+    def save(self, instance_id, tp_rank, pp_rank, device_id, saves):
+        self.saves.append([(n, list(i), list(h)) for n, i, h in saves])
+        return True, ""
+
+    def flush_saves(self):
+        return True, ""
+
+
+def test_page_first_saves_are_striped_over_tp_ranks():
+    """worker.py:982-1005: under page-first every rank holds all layers of a block, so rank r saves the
+    blocks with id % tp_size == r (all their layers); the stripes are disjoint and complete."""
+    from pegaflow_b200.connector import PegaWorkerConnector
+
+    ids = [0, 4, 5, 6, 7, 9, 12, 13]
+    hashes = [b"h%d" % i for i in ids]
+    seen = []
+    for rank in range(4):
+        client = _RecordingClient()
+        w = PegaWorkerConnector(client, None, instance_id="i", namespace="n", device_id=rank, block_size=64, tp_rank=rank,
+                                tp_size=4, world_size=4, is_mla=True)
+        assert w.page_first
+        w.wait_for_save([("layer_a", ids, hashes), ("layer_b", ids, hashes)])
+        (batch,) = client.saves
+        assert batch[0][1:] == batch[1][1:]                       # every layer of the stripe
+        assert all(b % 4 == rank and b != 0 for b in batch[0][1])    # block 0 is vLLM's null block
+        assert batch[0][2] == [b"h%d" % b for b in batch[0][1]]
+        seen += batch[0][1]
+    assert sorted(seen) == [b for b in ids if b != 0]
+    # layer-first (non-MLA) workers save everything themselves
+    client = _RecordingClient()
+    w = PegaWorkerConnector(client, None, instance_id="i", namespace="n", device_id=1, block_size=16, tp_rank=1, tp_size=4,
+                            world_size=4)
+    w.wait_for_save([("layer_a", ids, hashes)])
+    assert client.saves[0][0][1] == [b for b in ids if b != 0]
