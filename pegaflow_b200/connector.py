@@ -346,6 +346,16 @@ class PegaWorkerConnector:
         self.wait_for_save(saves)
         return {req_id for req_id, _ in intents}
 
+    # worker.py:1007-1037
+    def handle_preemptions(self, preempted_req_ids) -> None:
+        """Called before the blocks of preempted requests are handed to someone else: any layer save
+        still queued (save_kv_layer is asynchronous) must have read them by then."""
+        if preempted_req_ids and self._saves_in_flight:
+            ok, msg = self.client.flush_saves()
+            self._saves_in_flight = 0
+            if not ok:
+                raise RuntimeError(f"save failed: {msg}")
+
     # worker.py:422-547
     def get_finished(self) -> Tuple[List[str], List[str]]:
         """(request ids whose load finished, request ids whose load failed)."""

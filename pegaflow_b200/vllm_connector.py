@@ -150,6 +150,9 @@ class PegaKVConnector(KVConnectorBase_V1):
     def register_kv_caches(self, kv_caches: Dict[str, torch.Tensor]):
         self._worker.register_kv_caches(kv_caches)
 
+    def handle_preemptions(self, kv_connector_metadata) -> None:
+        self._worker.handle_preemptions(getattr(kv_connector_metadata, "preempted_req_ids", None))
+
     def start_load_kv(self, forward_context, **kwargs: Any) -> None:
         meta = self._get_connector_metadata()
         self._loading_this_step = bool(meta.load_intents)

@@ -267,3 +267,28 @@ def test_page_first_saves_are_striped_over_tp_ranks():
                             world_size=4)
     w.wait_for_save([("layer_a", ids, hashes)])
     assert client.saves[0][0][1] == [b for b in ids if b != 0]
+
+
+def test_preemption_flushes_queued_layer_saves():
+    from pegaflow_b200.connector import PegaWorkerConnector
+
+    class Client(_RecordingClient):
+        flushed = 0
+
+        def save_async(self, *a):
+            return True, ""
+
+        def flush_saves(self):
+            Client.flushed += 1
+            return True, ""
+
+    w = PegaWorkerConnector(Client(), None, instance_id="i", namespace="n", device_id=0, block_size=16)
+    w.handle_preemptions({"r"})
+    assert Client.flushed == 0                       # nothing queued: nothing to wait for
+    w.save_kv_layer("layer", [3, 4], [b"a", b"b"], 0)
+    w.handle_preemptions(set())
+    assert Client.flushed == 0                       # nobody was preempted
+    w.handle_preemptions({"r"})
+    assert Client.flushed == 1
+    w.handle_preemptions({"r"})
+    assert Client.flushed == 1
