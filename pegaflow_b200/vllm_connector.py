@@ -151,7 +151,8 @@ class PegaKVConnector(KVConnectorBase_V1):
         self._worker.register_kv_caches(kv_caches)
 
     def handle_preemptions(self, kv_connector_metadata) -> None:
-        self._worker.handle_preemptions(getattr(kv_connector_metadata, "preempted_req_ids", None))
+        if self._worker is not None:
+            self._worker.handle_preemptions(getattr(kv_connector_metadata, "preempted_req_ids", None))
 
     def start_load_kv(self, forward_context, **kwargs: Any) -> None:
         meta = self._get_connector_metadata()
