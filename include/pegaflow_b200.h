@@ -185,7 +185,7 @@ int pf_backend_peer_copy_layers(pf_backend *backend, const pf_device_layout *src
                                 size_t n_blocks, void *stream);
 /* Cross-process registration (python/pegaflow/ipc_wrapper.py:101-163 + pegaflow-server/src/registry.rs:172-203):
  * the process that owns a KV-cache tensor exports the region, the process that runs the engine
- * opens it and registers the returned pointer.  The region travels as these 104 plain bytes.
+ * opens it and registers the returned pointer.  The region travels as these 96 plain bytes.
  * Devices are matched by UUID, so the two processes may number their GPUs differently.  A region
  * cannot be opened by the process that exported it (a CUDA IPC rule).  Mappings are shared: regions
  * of one allocation open it once; pf_ipc_close drops one use. */

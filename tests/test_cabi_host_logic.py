@@ -292,3 +292,18 @@ def test_preemption_flushes_queued_layer_saves():
     assert Client.flushed == 1
     w.handle_preemptions({"r"})
     assert Client.flushed == 1
+
+
+def test_ipc_entry_points_reject_bad_arguments_without_a_gpu():
+    import ctypes as C
+
+    from pegaflow_b200 import _native as N
+
+    region = N.IpcRegion()
+    assert N.lib.pf_ipc_export(0, 4096, C.byref(region)) == 3            # invalid argument
+    assert b"null pointer or empty region" in N.lib.pf_last_error()
+    assert N.lib.pf_ipc_export(0x1000, 0, C.byref(region)) == 3
+    assert N.lib.pf_ipc_close(C.byref(region)) == 3
+    assert b"not open" in N.lib.pf_last_error()
+    assert N.lib.pf_ipc_open(None, None, None) == 3
+    assert C.sizeof(N.IpcRegion) == 96
