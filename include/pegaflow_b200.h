@@ -163,6 +163,14 @@ int pf_backend_save_layers(pf_backend *backend, const pf_layer_xfer *layers, siz
                            void *stream, void *const *layer_done);
 int pf_backend_load_layers(pf_backend *backend, const pf_layer_xfer *layers, size_t n_layers,
                            void *stream, void *const *layer_done);
+/* Measurement aid without a counterpart in the reference: the device half of a staged save on
+ * its own.  The gather kernels pack the blocks into the backend's HBM staging ring exactly as
+ * pf_backend_save_layers would, but no DMA leaves the ring and nothing reaches the host, so the
+ * kernel can be timed back to back (bench.py's roofline figure).  Every run must be one the
+ * staged route gathers (scattered block ids, at least `min_dma_bytes`, a block no larger than a
+ * staging slot); anything else is PF_INVALID_ARGUMENT.  Synchronise `stream` before the next
+ * real transfer on this backend. */
+int pf_backend_gather_layers(pf_backend *backend, const pf_layer_xfer *layers, size_t n_layers, void *stream);
 
 /* GPU -> GPU block copy over NVLink for same-box prefix hits: block src_ids[i] of the source
  * layout (memory of a peer GPU, reachable from this backend's device) lands in block

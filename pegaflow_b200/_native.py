@@ -124,6 +124,7 @@ _sig("pf_backend_h2d", C.c_int, vp, P(CopyDesc), sz, vp)
 _sig("pf_backend_d2h", C.c_int, vp, P(CopyDesc), sz, vp)
 _sig("pf_backend_save_layers", C.c_int, vp, P(LayerXfer), sz, vp, P(vp))
 _sig("pf_backend_load_layers", C.c_int, vp, P(LayerXfer), sz, vp, P(vp))
+_sig("pf_backend_gather_layers", C.c_int, vp, P(LayerXfer), sz, vp)
 _sig("pf_backend_peer_copy", C.c_int, vp, P(DeviceLayout), P(u32), P(DeviceLayout), P(u32), sz, vp)
 _sig("pf_backend_peer_copy_layers", C.c_int, vp, P(DeviceLayout), P(DeviceLayout), sz, P(u32), P(u32), sz, vp)
 class IpcRegion(C.Structure):

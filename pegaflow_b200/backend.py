@@ -144,6 +144,12 @@ class TransferBackend:
         arr, n, keep = layers if isinstance(layers, tuple) else self.make_layers(layers)
         N.check(N.lib.pf_backend_load_layers(self._h, arr, n, C.c_void_p(stream or None), self._events(layer_done, n)))
 
+    def gather_layers(self, layers, stream: int = 0):
+        """The gather kernels of a staged save without the DMA (nothing reaches the host): for timing
+        the kernel alone.  Synchronise the stream before the next real transfer on this backend."""
+        arr, n, keep = layers if isinstance(layers, tuple) else self.make_layers(layers)
+        N.check(N.lib.pf_backend_gather_layers(self._h, arr, n, C.c_void_p(stream or None)))
+
     def peer_copy(self, src_layout, src_ids, dst_layout, dst_ids, stream: int = 0):
         """layouts: (data_ptr, block_stride_bytes, kv_stride_bytes, range_bytes, n_ranges)."""
         import numpy as np

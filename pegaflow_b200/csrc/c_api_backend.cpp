@@ -120,6 +120,14 @@ int pf_backend_load_layers(pf_backend *backend, const pf_layer_xfer *layers, siz
   });
 }
 
+int pf_backend_gather_layers(pf_backend *backend, const pf_layer_xfer *layers, size_t n_layers, void *stream) {
+  return guarded([&] {
+    if (!backend) throw Error::invalid("backend is null");
+    if (!layers && n_layers) throw Error::invalid("layers is null");
+    backend->impl.gather_layers(layers, n_layers, (cudaStream_t)stream);
+  });
+}
+
 int pf_backend_peer_copy(pf_backend *backend, const pf_device_layout *src, const uint32_t *src_ids,
                          const pf_device_layout *dst, const uint32_t *dst_ids, size_t n_blocks, void *stream) {
   return guarded([&] {

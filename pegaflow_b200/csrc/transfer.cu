@@ -781,6 +781,16 @@ void TransferBackend::flush_group() {
   const int copy_index = next_aux();
   cudaStream_t copy = aux_[copy_index];
   const StagedUnit &first = group_.front();
+  if (gather_only_) {
+    // gather_layers: the kernels alone, back to back; the slot's previous content was never
+    // handed to a copy stream by this mode, and the caller synchronises before a real transfer
+    for (size_t i = 0; i < group_.size(); i += kMaxGroupUnits)
+      launch_group(slot.ptr, i, std::min<size_t>(kMaxGroupUnits, group_.size() - i), true, stream);
+    group_.clear();
+    group_bytes_ = 0;
+    group_limit_ = std::min(group_limit_ * 2, cfg_.staging_slot_bytes);
+    return;
+  }
   if (!group_host_is_src_) {
     if (slot.used) PF_CUDA(cudaStreamWaitEvent(stream, slot.drained, 0));
     for (size_t i = 0; i < group_.size(); i += kMaxGroupUnits)
@@ -818,6 +828,41 @@ void TransferBackend::flush_group() {
   group_.clear();
   group_bytes_ = 0;
   group_limit_ = std::min(group_limit_ * 2, cfg_.staging_slot_bytes);  // ramp up: the first DMAs start early
+}
+
+void TransferBackend::gather_layers(const pf_layer_xfer *layers, size_t n_layers, cudaStream_t stream) {
+  // Every run must be one the staged route gathers: anything else would move bytes to the host.
+  for (size_t li = 0; li < n_layers; ++li) {
+    const pf_layer_xfer &L = layers[li];
+    if (L.n_blocks == 0) continue;
+    if (!L.block_ids || L.n_ranges < 1 || L.n_ranges > 2 || L.range_bytes == 0 ||
+        L.range_bytes > cfg_.staging_slot_bytes)
+      throw Error::invalid(strf("layer %zu: not a staged transfer", li));
+    for (uint32_t r = 0; r < L.n_ranges; ++r)
+      for (size_t j = 0; j < L.n_runs[r]; ++j) {
+        const pf_host_run &run = L.runs[r][j];
+        if (run.n_blocks == 0) continue;
+        if (run.first_block + run.n_blocks > L.n_blocks)
+          throw Error::invalid(strf("layer %zu range %u: host run outside the block list", li, r));
+        const bool staged = cfg_.route == PF_ROUTE_STAGED ||
+                            (cfg_.route == PF_ROUTE_AUTO && run.n_blocks * L.range_bytes >= cfg_.min_dma_bytes);
+        bool consecutive = run.n_blocks >= 2;
+        for (size_t k = 1; k < run.n_blocks && consecutive; ++k)
+          consecutive = L.block_ids[run.first_block + k] == L.block_ids[run.first_block + k - 1] + 1;
+        if (!staged || consecutive)
+          throw Error::invalid(strf("layer %zu range %u run %zu: takes a route without a gather kernel", li, r, j));
+      }
+  }
+  size_t total_bytes = 0;
+  for (size_t li = 0; li < n_layers; ++li) total_bytes += layers[li].n_blocks * layers[li].range_bytes * layers[li].n_ranges;
+  if (cfg_.route != PF_ROUTE_STAGED && n_layers > 1 && total_bytes <= kSmallTaskBytes)
+    throw Error::invalid("task small enough for the single zero-copy launch: no gather kernel");
+  struct Reset {
+    bool &flag;
+    ~Reset() { flag = false; }
+  } reset{gather_only_};
+  gather_only_ = true;
+  move_layers(layers, n_layers, false, stream, nullptr);
 }
 
 void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, bool host_is_src,

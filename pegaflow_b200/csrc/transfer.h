@@ -46,6 +46,10 @@ class TransferBackend {
   void copy_descs(const pf_copy_desc *copies, size_t n, bool host_is_src, cudaStream_t stream);
   void move_layers(const pf_layer_xfer *layers, size_t n_layers, bool host_is_src, cudaStream_t stream,
                    void *const *layer_done);
+  // The HBM half of a staged save on its own: the gather kernels fill the staging ring exactly
+  // as move_layers(.., host_is_src = false, ..) would, and no DMA leaves the ring.  For timing the
+  // kernel alone; runs that do not take the staged route are rejected.
+  void gather_layers(const pf_layer_xfer *layers, size_t n_layers, cudaStream_t stream);
   void peer_copy(const pf_device_layout &src, const uint32_t *src_ids, const pf_device_layout &dst,
                  const uint32_t *dst_ids, size_t n_blocks, cudaStream_t stream);
   // The same for several layers that share the block ids: one upload of the ids, a few launches.
@@ -108,6 +112,7 @@ class TransferBackend {
   size_t group_limit_ = ~(size_t)0;  // current size limit of a group (ramps up within a call)
   char *group_host_begin_ = nullptr, *group_host_end_ = nullptr;
   bool group_dense_ = true, group_host_is_src_ = false;
+  bool gather_only_ = false;             // set for the duration of gather_layers
   cudaStream_t group_stream_ = nullptr;
 
   std::vector<cudaStream_t> aux_;      // copy-engine streams of the staged route

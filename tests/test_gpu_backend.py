@@ -440,3 +440,51 @@ def test_save_then_load_on_one_stream_needs_no_sync_in_between(env, route):
         assert np.array_equal(got[dst], data.reshape(num_blocks, seg)[src]), f"iteration {it}: stale host bytes loaded"
     be.close()
     pool.release(handle)
+
+
+def test_gather_layers_runs_the_kernel_and_moves_nothing_to_the_host(env):
+    """pf_backend_gather_layers (the timing aid behind bench.py's roofline figure): kernel launches,
+    no DMA, the host image untouched; a real save on the same backend afterwards is still bit-exact;
+    runs that would not be gathered are refused."""
+    pf, mem, pool, torch = env
+    rng = np.random.default_rng(21)
+    num_blocks, seg, n = 200, 32768, 96
+    region = 2 * num_blocks * seg
+    dev = mem.alloc(region)
+    init = rng.integers(0, 256, size=region, dtype=np.uint8)
+    mem.write(dev, init)
+    ids = rng.permutation(num_blocks)[:n]
+    allocs = [pool.alloc(seg * n) for _ in range(2)]
+    for a in allocs:
+        host_view(a[0], seg * n)[:] = 0x5A
+    runs = [[pf.HostRun(0, n, a[0], a[1], seg)] for a in allocs]
+    be = pf.TransferBackend(0, min_dma_bytes=64 << 10, staging_slot_bytes=1 << 20)
+    stream = torch.cuda.Stream()
+    X = pf.LayerXfer(dev.data_ptr(), seg, num_blocks * seg, seg, 2, list(ids), runs)
+    for _ in range(3):
+        be.gather_layers([X], stream.cuda_stream)
+    stream.synchronize()
+    st = be.stats()
+    assert st["kernel_launches"] >= 6 and st["dma_copies"] == 0 and st["bytes_zero_copy"] == 0
+    assert st["device_status"] == 0
+    for a in allocs:
+        assert (host_view(a[0], seg * n) == 0x5A).all(), "gather_layers must not write host memory"
+    assert np.array_equal(mem.read(dev), init), "gather_layers must not write the KV cache"
+    # the same backend still saves correctly afterwards
+    be.save_layers([X], stream.cuda_stream)
+    stream.synchronize()
+    for r, a in enumerate(allocs):
+        got = host_view(a[0], seg * n).reshape(n, seg)
+        want = init[r * num_blocks * seg:(r + 1) * num_blocks * seg].reshape(num_blocks, seg)[ids]
+        assert np.array_equal(got, want)
+    # refused: consecutive ids (a DMA, no kernel) and runs below the DMA threshold (zero-copy route)
+    Xc = pf.LayerXfer(dev.data_ptr(), seg, num_blocks * seg, seg, 2, list(range(5, 5 + n)), runs)
+    with pytest.raises(ValueError):
+        be.gather_layers([Xc], stream.cuda_stream)
+    short = [[pf.HostRun(0, 1, a[0], a[1], seg)] for a in allocs]
+    Xs = pf.LayerXfer(dev.data_ptr(), seg, num_blocks * seg, seg, 2, [int(ids[0])], short)
+    with pytest.raises(ValueError):
+        be.gather_layers([Xs], stream.cuda_stream)
+    be.close()
+    for a in allocs:
+        pool.release(a[2])
