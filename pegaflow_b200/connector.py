@@ -190,6 +190,13 @@ class InProcEngineClient:
     def shutdown(self):
         return True, ""
 
+    def start_session_watcher(self, instance_id, namespace, tp_size, world_size) -> None:
+        """The reference opens a liveness stream here so that a server outliving the worker releases
+        its CUDA IPC mappings (python/src/lib.rs:591-617).  The engine lives and dies with this process:
+        there is nothing to watch."""
+        if not instance_id:
+            raise ValueError("instance_id must be non-empty")
+
 
 @dataclass
 class _PendingLoad:

@@ -307,3 +307,32 @@ def test_ipc_entry_points_reject_bad_arguments_without_a_gpu():
     assert b"not open" in N.lib.pf_last_error()
     assert N.lib.pf_ipc_open(None, None, None) == 3
     assert C.sizeof(N.IpcRegion) == 96
+
+
+def test_python_client_surface_matches_the_reference_stub():
+    """A caller written against the reference's native module (python/pegaflow/pegaflow.pyi) finds
+    the same methods with the same parameter order here.  The fixture is that stub's surface, read
+    with `ast` by tests/golden/gen_client_surface.py.  Two differences are intended: the client is
+    built around an engine instead of an endpoint, and register_context_batch takes the tensors (or
+    pickled IPC wrappers) in the position of `wrapper_bytes_list`."""
+    import inspect
+    import json
+
+    golden = json.load(open(os.path.join(ROOT, "tests", "golden", "engine_client_surface.json")))["classes"]
+    mine = {"EngineRpcClient": pf.InProcEngineClient, "PyLoadState": pf.PyLoadState, "QueryReady": pf.QueryReady,
+            "QueryLoading": pf.QueryLoading}
+    renamed = {("EngineRpcClient", "register_context_batch", "wrapper_bytes_list"): "tensors"}
+    for cls_name, spec in golden.items():
+        cls = mine[cls_name]
+        for method, params in spec["methods"].items():
+            if method == "__init__" and cls_name in ("EngineRpcClient", "PyLoadState"):
+                continue   # constructed from an engine / optionally attached to an existing segment
+            assert hasattr(cls, method), f"{cls_name}.{method} is missing"
+            sig = inspect.signature(getattr(cls, method))
+            got = [(p.name, p.default is not inspect.Parameter.empty) for p in sig.parameters.values()
+                   if p.name != "self" and p.kind not in (p.VAR_POSITIONAL, p.VAR_KEYWORD)]
+            want = [(renamed.get((cls_name, method, name), name), has_default) for name, has_default in params]
+            assert got[:len(want)] == want, f"{cls_name}.{method}: {got} != {want}"
+            assert all(d for _, d in got[len(want):]), f"{cls_name}.{method}: extra parameters must be optional"
+        for field in spec["fields"]:
+            assert field in getattr(cls, "__dataclass_fields__", {}) or hasattr(cls, field), f"{cls_name}.{field}"
