@@ -31,6 +31,7 @@ import torch
 from vllm.distributed.kv_transfer.kv_connector.v1.base import KVConnectorBase_V1, KVConnectorMetadata, KVConnectorRole
 
 from . import connector as _connector
+from .config import PegaConnectorMode, derive_namespace, resolve_instance_id
 from .engine import PegaEngine
 from .scheduler import PegaConnectorMetadata, SchedulerConnector, require_single_attention_group
 
@@ -85,12 +86,16 @@ class PegaKVConnector(KVConnectorBase_V1):
         require_single_attention_group(kv_cache_config)
         cfg = vllm_config.kv_transfer_config
         extra = cfg.get_from_extra_config
-        self._instance_id = str(getattr(vllm_config, "instance_id", "") or cfg.engine_id or "vllm")
+        # the reference's rule (common.py:488-516); without any configured id both roles of this process
+        # must still agree, so the generated-uuid fallback is replaced by a fixed name
+        configured = cfg.engine_id or getattr(vllm_config, "instance_id", "") or os.environ.get("PEGAFLOW_INSTANCE_ID")
+        self._instance_id = resolve_instance_id(vllm_config) if configured else "vllm"
         self._block_size = vllm_config.cache_config.block_size
         self._layerwise = bool(extra("pegaflow.layerwise", True))
-        self._read_enabled = str(extra("pegaflow.mode", "read_write")).strip().lower() == "read_write"
+        self._read_enabled = PegaConnectorMode.from_config(extra("pegaflow.mode", "read_write")) is PegaConnectorMode.READ_WRITE
         model = vllm_config.model_config
-        self._namespace = f"{model.model}:{model.dtype}:bs{self._block_size}"
+        # every factor that changes a stored block's layout, hashed as the reference does (common.py:519-565)
+        self._namespace = derive_namespace(vllm_config, vllm_config.parallel_config.tensor_parallel_size)
         self._is_mla = bool(getattr(model, "use_mla", False))
         self._engine = shared_engine(self._instance_id, int(extra("pegaflow.pool_bytes", 4 << 30)))
         self._client = _connector.InProcEngineClient(self._engine)
