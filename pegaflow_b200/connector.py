@@ -12,6 +12,8 @@
 """
 from __future__ import annotations
 
+import os
+import time
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -198,15 +200,29 @@ class InProcEngineClient:
             raise ValueError("instance_id must be non-empty")
 
 
+def _load_timeout_seconds() -> int:
+    """worker.py:34-43: PEGA_LOAD_TIMEOUT_SECONDS, default 120, never below 30; an unparsable value
+    falls back to the default (common.py:464-485)."""
+    raw = os.environ.get("PEGA_LOAD_TIMEOUT_SECONDS")
+    try:
+        seconds = 120 if raw is None else int(raw)
+    except ValueError:
+        seconds = 120
+    return max(seconds, 30)
+
+
 @dataclass
 class _PendingLoad:
     state: PyLoadState
     request_ids: List[str]
     block_ids: List[int]
+    started: float = 0.0
 
 
 class PegaWorkerConnector:
     """Worker-side hooks on the transfer path for one GPU of one instance."""
+
+    LOAD_TIMEOUT_SECONDS: int = _load_timeout_seconds()   # read once at import, like worker.py:185-187
 
     def __init__(self, client: InProcEngineClient, engine: PegaEngine, *, instance_id: str, namespace: str,
                  device_id: int, block_size: int, tp_rank: int = 0, pp_rank: int = 0, tp_size: int = 1,
@@ -223,6 +239,8 @@ class PegaWorkerConnector:
         self._pending_loads: List[_PendingLoad] = []
         self._load_errors: set = set()
         self._rejected_loads: List[str] = []      # requests whose load could not even be submitted
+        self.load_history: List[Tuple[float, int, bool]] = []   # (seconds, blocks, ok) per finished load task
+        self.available = True                      # cleared by a load timeout (worker.py:509-510)
         self._saves_in_flight = 0
 
     # worker.py:261-412
@@ -262,7 +280,8 @@ class PegaWorkerConnector:
         if not loads:
             return
         state = PyLoadState()
-        pending = _PendingLoad(state, [r for r, _, _ in loads], [b for _, _, ids in loads for b in ids if b is not None])
+        pending = _PendingLoad(state, [r for r, _, _ in loads], [b for _, _, ids in loads for b in ids if b is not None],
+                               time.perf_counter())
         try:
             ok, msg = self.client.load(self.instance_id, self.tp_rank, self.device_id, state.shm_name(),
                                        [list(self.registered_layers)], [(lease, [list(ids)]) for _, lease, ids in loads])
@@ -368,16 +387,25 @@ class PegaWorkerConnector:
         """(request ids whose load finished, request ids whose load failed)."""
         done, still = [], []
         failed, self._rejected_loads = self._rejected_loads, []
+        now = time.perf_counter()
         for p in self._pending_loads:
             st = p.state.get_state()
-            if st == 0:
+            if st == 0 and now - p.started <= self.LOAD_TIMEOUT_SECONDS:
                 still.append(p)
-            elif st == 1:
+                continue
+            if st == 1:
                 done.extend(p.request_ids)
             else:
+                # failed, or (worker.py:454-507) pending for longer than the timeout: the requests are
+                # handed back as received and their blocks are reported invalid, so that vLLM recomputes
+                # them instead of waiting for ever
                 failed.extend(p.request_ids)
                 self._load_errors.update(p.block_ids)
+                if st == 0:
+                    self.available = False
+            self.load_history.append((now - p.started, len(p.block_ids), st == 1))
         self._pending_loads = still
+        del self.load_history[:-1024]
         return done, failed
 
     def get_block_ids_with_load_errors(self) -> set:

@@ -336,3 +336,34 @@ def test_python_client_surface_matches_the_reference_stub():
             assert all(d for _, d in got[len(want):]), f"{cls_name}.{method}: extra parameters must be optional"
         for field in spec["fields"]:
             assert field in getattr(cls, "__dataclass_fields__", {}) or hasattr(cls, field), f"{cls_name}.{field}"
+
+
+def test_a_load_that_never_completes_times_out_and_its_blocks_are_reported(monkeypatch):
+    """worker.py:454-507: a load still pending after LOAD_TIMEOUT_SECONDS is handed back as failed and
+    its destination blocks are reported invalid; PEGA_LOAD_TIMEOUT_SECONDS is clamped to 30 s."""
+    from pegaflow_b200 import connector
+    from pegaflow_b200.connector import PegaWorkerConnector
+
+    class Client(_RecordingClient):
+        def load(self, *a):
+            return True, ""          # accepted, and then nothing ever sets the state
+
+    w = PegaWorkerConnector(Client(), None, instance_id="i", namespace="n", device_id=0, block_size=16)
+    w.registered_layers = ["layer"]
+    w.start_load_kv([("req-a", b"L" * 16, [4, None, 9])])
+    assert w.get_finished() == ([], []) and w.available
+    w._pending_loads[0].started -= w.LOAD_TIMEOUT_SECONDS + 1
+    assert w.get_finished() == ([], ["req-a"])
+    assert w.get_block_ids_with_load_errors() == {4, 9}
+    assert not w.available and w.load_history[-1][1:] == (2, False)
+    assert w.get_finished() == ([], [])
+    # a load that completes in time is unaffected
+    w.start_load_kv([("req-b", b"M" * 16, [5])])
+    w._pending_loads[0].state.set_completed()
+    assert w.get_finished() == (["req-b"], []) and w.load_history[-1][1:] == (1, True)
+    for raw, want in [(None, 120), ("45", 45), ("5", 30), ("abc", 120), ("-1", 30)]:
+        if raw is None:
+            monkeypatch.delenv("PEGA_LOAD_TIMEOUT_SECONDS", raising=False)
+        else:
+            monkeypatch.setenv("PEGA_LOAD_TIMEOUT_SECONDS", raw)
+        assert connector._load_timeout_seconds() == want
