@@ -13,6 +13,7 @@
 from __future__ import annotations
 
 import os
+import threading
 import time
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
@@ -200,6 +201,55 @@ class InProcEngineClient:
             raise ValueError("instance_id must be non-empty")
 
 
+class ServiceStateManager:
+    """Whether the engine behind ``client`` is believed to be usable (state_manager.py:21-99).  The
+    worker marks it unavailable when a load cannot be submitted or times out; from then on a daemon
+    thread asks ``client.health()`` every ``health_check_interval`` seconds and the first healthy
+    answer makes the service available again.  Load and save calls do not consult the flag — as in
+    the reference it is there for whoever decides whether to look the cache up at all."""
+
+    def __init__(self, engine_client, health_check_interval: float = 10.0):
+        self._client = engine_client
+        self._interval = health_check_interval
+        self._lock = threading.Lock()
+        self._available = True
+        self._stop = threading.Event()
+        self._probe: Optional[threading.Thread] = None
+        self.last_reason = ""
+
+    def is_available(self) -> bool:
+        with self._lock:
+            return self._available
+
+    def mark_unavailable(self, reason: str) -> None:
+        with self._lock:
+            if not self._available:
+                return
+            self._available = False
+            self.last_reason = reason
+            if self._probe is None or not self._probe.is_alive():
+                self._stop.clear()
+                self._probe = threading.Thread(target=self._probe_until_healthy, daemon=True, name="PegaHealthCheck")
+                self._probe.start()
+
+    def _probe_until_healthy(self) -> None:
+        while not self._stop.wait(self._interval):
+            try:
+                ok, _ = self._client.health()
+            except Exception:
+                continue
+            if ok:
+                with self._lock:
+                    self._available = True
+                return
+
+    def shutdown(self) -> None:
+        self._stop.set()
+        probe = self._probe
+        if probe is not None and probe.is_alive():
+            probe.join(timeout=1.0)
+
+
 def _load_timeout_seconds() -> int:
     """worker.py:34-43: PEGA_LOAD_TIMEOUT_SECONDS, default 120, never below 30; an unparsable value
     falls back to the default (common.py:464-485)."""
@@ -227,8 +277,9 @@ class PegaWorkerConnector:
     def __init__(self, client: InProcEngineClient, engine: PegaEngine, *, instance_id: str, namespace: str,
                  device_id: int, block_size: int, tp_rank: int = 0, pp_rank: int = 0, tp_size: int = 1,
                  world_size: int = 1, is_mla: bool = False, transfer_backend: Optional[str] = None,
-                 page_first: Optional[bool] = None):
+                 page_first: Optional[bool] = None, state_manager: Optional[ServiceStateManager] = None):
         self.client, self.engine = client, engine
+        self.state_manager = state_manager if state_manager is not None else ServiceStateManager(client)
         self.instance_id, self.namespace, self.device_id = instance_id, namespace, device_id
         self.block_size, self.is_mla = block_size, is_mla
         self.tp_rank, self.pp_rank, self.tp_size, self.world_size = tp_rank, pp_rank, tp_size, world_size
@@ -240,7 +291,6 @@ class PegaWorkerConnector:
         self._load_errors: set = set()
         self._rejected_loads: List[str] = []      # requests whose load could not even be submitted
         self.load_history: List[Tuple[float, int, bool]] = []   # (seconds, blocks, ok) per finished load task
-        self.available = True                      # cleared by a load timeout (worker.py:509-510)
         self._saves_in_flight = 0
 
     # worker.py:261-412
@@ -269,7 +319,12 @@ class PegaWorkerConnector:
         key = f"{CROSS_LAYER_KEY}_pp{self.pp_rank}" if self.world_size > self.tp_size else CROSS_LAYER_KEY
         self.register_kv_caches({key: kv_cache})
 
+    @property
+    def available(self) -> bool:
+        return self.state_manager.is_available()
+
     def unregister(self):
+        self.state_manager.shutdown()
         if self.registered_layers:
             self.client.unregister_context(self.instance_id)
             self.registered_layers = []
@@ -297,6 +352,7 @@ class PegaWorkerConnector:
                     pass
             self._load_errors.update(pending.block_ids)
             self._rejected_loads.extend(pending.request_ids)
+            self.state_manager.mark_unavailable(f"load rpc failed: {msg}")   # worker.py:659,677
             return
         self._pending_loads.append(pending)
 
@@ -402,7 +458,7 @@ class PegaWorkerConnector:
                 failed.extend(p.request_ids)
                 self._load_errors.update(p.block_ids)
                 if st == 0:
-                    self.available = False
+                    self.state_manager.mark_unavailable("load timeout")   # worker.py:522-523
             self.load_history.append((now - p.started, len(p.block_ids), st == 1))
         self._pending_loads = still
         del self.load_history[:-1024]

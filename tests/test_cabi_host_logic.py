@@ -367,3 +367,45 @@ def test_a_load_that_never_completes_times_out_and_its_blocks_are_reported(monke
         else:
             monkeypatch.setenv("PEGA_LOAD_TIMEOUT_SECONDS", raw)
         assert connector._load_timeout_seconds() == want
+
+
+def test_service_state_recovers_once_the_health_probe_succeeds():
+    """state_manager.py:47-92: unavailable after a failure, a background probe asks health() and the first
+    healthy answer (exceptions and unhealthy answers are skipped) makes the service available again."""
+    import time
+
+    from pegaflow_b200.connector import PegaWorkerConnector, ServiceStateManager
+
+    class Client(_RecordingClient):
+        answers = [RuntimeError("connection refused"), (False, "starting"), (True, "ok")]
+        asked = 0
+
+        def health(self):
+            Client.asked += 1
+            a = Client.answers.pop(0)
+            if isinstance(a, Exception):
+                raise a
+            return a
+
+        def load(self, *a):
+            return False, "engine restarting"
+
+        def release(self, lease):
+            pass
+
+    client = Client()
+    sm = ServiceStateManager(client, health_check_interval=0.02)
+    w = PegaWorkerConnector(client, None, instance_id="i", namespace="n", device_id=0, block_size=16, state_manager=sm)
+    w.registered_layers = ["layer"]
+    assert w.available
+    w.start_load_kv([("req", b"L" * 16, [7])])          # rejected: leases back, blocks invalid, service marked
+    assert sm.last_reason == "load rpc failed: engine restarting"
+    assert w.get_finished() == ([], ["req"]) and w.get_block_ids_with_load_errors() == {7}
+    sm.mark_unavailable("second reason is ignored while unavailable")
+    assert sm.last_reason.startswith("load rpc failed")
+    deadline = time.time() + 5
+    while not sm.is_available() and time.time() < deadline:
+        time.sleep(0.01)
+    assert sm.is_available() and Client.asked == 3
+    w.registered_layers = []
+    w.unregister()          # also stops the probe thread
