@@ -10,7 +10,8 @@ in the vLLM process (no sidecar), attention-only models with one KV-cache group.
                      kv_connector_extra_config={"pegaflow.pool_bytes": 8 << 30})
 
 Extra-config keys: ``pegaflow.pool_bytes`` (pinned pool size), ``pegaflow.mode`` ("read_write" or
-"save_only", as in the reference), ``pegaflow.layerwise`` (default true: loads are synchronous
+"save_only", as in the reference), ``pegaflow.transfer_backend`` ("direct" or "kernel": accepted and
+validated as in the reference, both served by the one transfer path here), ``pegaflow.layerwise`` (default true: loads are synchronous
 from the scheduler's point of view and every attention layer waits on the stream for its own
 layer's bytes, saves are queued per layer behind the layer's compute; false: the reference's
 behaviour — asynchronous request-level loads, one batch save after the forward pass).
@@ -108,7 +109,10 @@ class PegaKVConnector(KVConnectorBase_V1):
             device = torch.cuda.current_device()
             self._worker = _connector.PegaWorkerConnector(
                 self._client, self._engine, instance_id=self._instance_id, namespace=self._namespace, device_id=device,
-                block_size=self._block_size, is_mla=self._is_mla)
+                block_size=self._block_size, is_mla=self._is_mla,
+                # "direct" / "kernel", validated like the reference (common.py:577-594); both name this library's
+                # one transfer path
+                transfer_backend=extra("pegaflow.transfer_backend", None))
             self._saved_requests: set = set()      # requests with saves in the pool, not yet reported sent
             self._events = []                      # per-layer "KV written" events of the current step
             self._layers_queued: set = set()       # layers whose save_kv_layer hook ran in the current step
