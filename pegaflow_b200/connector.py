@@ -19,6 +19,7 @@ from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
 from . import _native as N
+from .config import resolve_transfer_backend  # noqa: F401  (re-exported)
 from .engine import PegaEngine, PyLoadState
 
 CROSS_LAYER_KEY = "ALL_LAYERS"  # worker.py:32
@@ -75,18 +76,6 @@ def infer_kv_cache_registration(kv_cache, logical_block_size: int, *, is_mla: bo
     if bytes_per_block == 0:
         raise ValueError(f"Invalid bytes_per_block: shape={shape} stride={stride}")
     return KVCacheRegistrationInfo("blocks-first", rows // ratio, bytes_per_block, 0, 1, ratio)
-
-
-def resolve_transfer_backend(is_mla: bool, override: Optional[str]) -> str:
-    """python/pegaflow/connector/common.py:577-594: "kernel" for MLA, "direct" otherwise, unless
-    overridden.  Both names select the one backend this library has."""
-    allowed = ("direct", "kernel")
-    if override is not None:
-        if override not in allowed:
-            raise ValueError(f"Unsupported pegaflow.transfer_backend {override!r}; expected one of: "
-                             + ", ".join(allowed))
-        return override
-    return "kernel" if is_mla else "direct"
 
 
 class QueryLoading:

@@ -58,6 +58,11 @@ def run_all(mod, rng):
     out = {"mode": [], "topology": [], "config": [], "hybrid": []}
     for value in ["read_write", " Save_Only ", "READ_WRITE", "write", "", None, 3, "save-only"]:
         out["mode"].append({"in": value, "out": _record(lambda: mod.PegaConnectorMode.from_config(value).value)})
+    out["backend"] = []
+    for is_mla in (True, False):
+        for override in (None, "direct", "kernel", " Kernel ", "DIRECT", "bogus", "", "kernel2"):
+            out["backend"].append({"in": [is_mla, override],
+                                   "out": _record(lambda: mod.resolve_transfer_backend(is_mla, override))})
     for default, configured, tp, world in TOPOLOGIES:
         def build():
             t = mod.TpShardTopology.from_config(default, configured, tp, world)
