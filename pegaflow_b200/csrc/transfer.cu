@@ -782,8 +782,9 @@ void TransferBackend::flush_group() {
   cudaStream_t copy = aux_[copy_index];
   const StagedUnit &first = group_.front();
   if (gather_only_) {
-    // gather_layers: the kernels alone, back to back; the slot's previous content was never
-    // handed to a copy stream by this mode, and the caller synchronises before a real transfer
+    // gather_layers: the kernels alone, back to back.  A slot that an earlier real save still
+    // drains is waited for as usual; slots this mode filled are never handed to a copy stream.
+    if (slot.used) PF_CUDA(cudaStreamWaitEvent(stream, slot.drained, 0));
     for (size_t i = 0; i < group_.size(); i += kMaxGroupUnits)
       launch_group(slot.ptr, i, std::min<size_t>(kMaxGroupUnits, group_.size() - i), true, stream);
     group_.clear();
