@@ -54,6 +54,78 @@ TOPOLOGIES = [
 ]
 
 
+def cache_group_configs():
+    """(name, kv_cache_config) pairs built from vLLM's own spec classes."""
+    import torch
+    from vllm.v1.kv_cache_interface import (ChunkedLocalAttentionSpec, FullAttentionSpec, KVCacheGroupSpec, MambaSpec,
+                                            MLAAttentionSpec, SlidingWindowSpec, UniformTypeKVCacheSpecs)
+
+    def full(bs=16):
+        return FullAttentionSpec(block_size=bs, num_kv_heads=8, head_size=128, dtype=torch.bfloat16)
+
+    def mla(bs=64):
+        return MLAAttentionSpec(block_size=bs, num_kv_heads=1, head_size=576, dtype=torch.bfloat16)
+
+    def mamba(bs=16, mode="align"):
+        return MambaSpec(block_size=bs, shapes=((4, 8),), dtypes=(torch.float32,), mamba_cache_mode=mode)
+
+    def sliding(bs=16):
+        return SlidingWindowSpec(block_size=bs, num_kv_heads=8, head_size=128, dtype=torch.bfloat16, sliding_window=128)
+
+    def chunked(bs=16):
+        return ChunkedLocalAttentionSpec(block_size=bs, num_kv_heads=8, head_size=128, dtype=torch.bfloat16,
+                                         attention_chunk_size=256)
+
+    def uniform(specs, bs=64):
+        return UniformTypeKVCacheSpecs(block_size=bs, kv_cache_specs=specs)
+
+    def cfg(*groups):
+        return SimpleNamespace(kv_cache_groups=[KVCacheGroupSpec(layer_names=list(n), kv_cache_spec=s) for n, s in groups])
+
+    return [
+        ("none", None), ("empty", SimpleNamespace(kv_cache_groups=[])),
+        ("full", cfg((["l0", "l1"], full()))), ("mla", cfg((["l0"], mla()))),
+        ("sliding_alone", cfg((["l0"], sliding()))), ("chunked_alone", cfg((["l0"], chunked()))),
+        ("mamba_alone", cfg((["m0"], mamba()))),
+        ("uniform_mla", cfg((["l0", "l1"], uniform({"l0": mla(), "l1": mla()})))),
+        ("uniform_mixed", cfg((["l0", "l1"], uniform({"l0": mla(), "l1": full(64)})))),
+        ("uniform_empty", cfg((["l0"], uniform({})))),
+        ("full_mamba", cfg((["a0", "a1"], full()), (["m0", "m1"], mamba()))),
+        ("mamba_full_mamba", cfg((["m0"], mamba()), (["a0"], full()), (["m1", "m2"], mamba()))),
+        ("mla_mamba", cfg((["a0"], mla(16)), (["m0"], mamba()))),
+        ("full_full", cfg((["a0"], full()), (["a1"], full()))),
+        ("mamba_mamba", cfg((["m0"], mamba()), (["m1"], mamba()))),
+        ("full_sliding", cfg((["a0"], full()), (["s0"], sliding()))),
+        ("full_mamba_none", cfg((["a0"], full()), (["m0"], mamba(mode="none")))),
+        ("full_mamba_block_sizes", cfg((["a0"], full(16)), (["m0"], mamba(32)))),
+        ("duplicate_layer", cfg((["a0", "x"], full()), (["x"], mamba()))),
+        ("full_two_mamba_full", cfg((["a0"], full()), (["m0"], mamba()), (["m1"], mamba()), (["a1"], full()))),
+    ]
+
+
+def _record_runtime(fn):
+    try:
+        return {"ok": fn()}
+    except RuntimeError as e:
+        return {"error": str(e)}
+
+
+def run_cache_groups(mod):
+    out = []
+    for name, config in cache_group_configs():
+        def build():
+            lay = mod.CacheGroupLayout.from_config(config)
+            return {"layer_names": [list(n) for n in lay.layer_names], "hash_group_index": lay.hash_group_index,
+                    "has_recurrent_state": lay.has_recurrent_state,
+                    "recurrent_group_indices": sorted(lay.recurrent_group_indices),
+                    "recurrent_layer_names": sorted(lay.recurrent_layer_names),
+                    "storage_group_ids": list(lay.storage_group_ids), "group_count": lay.group_count,
+                    "storage_group_of": [lay.storage_group_of(i) for i in range(lay.group_count)],
+                    "layer_to_group": _record_runtime(lay.layer_to_group)}
+        out.append({"in": name, "out": _record_runtime(build)})
+    return out
+
+
 def run_all(mod, rng):
     out = {"mode": [], "topology": [], "config": [], "hybrid": []}
     for value in ["read_write", " Save_Only ", "READ_WRITE", "write", "", None, 3, "save-only"]:

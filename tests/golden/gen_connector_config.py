@@ -29,6 +29,7 @@ _spec.loader.exec_module(cases)
 
 def main():
     out = cases.run_all(ref, random.Random(20260101))
+    out["cache_groups"] = cases.run_cache_groups(ref)
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "connector_config.json")
     with open(path, "w") as f:
         json.dump(out, f, sort_keys=True)
