@@ -1,0 +1,55 @@
+"""bench.py's `roofline` object keeps the keys the measurement contract names, whichever legs ran:
+the kernel-alone leg puts its figure at the top level and moves the in-pipeline figures below it.
+Pure host logic on made-up counters; no GPU."""
+import importlib.util
+import os
+from types import SimpleNamespace
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+_spec = importlib.util.spec_from_file_location("bench_module", os.path.join(ROOT, "bench.py"))
+bench = importlib.util.module_from_spec(_spec)
+_spec.loader.exec_module(bench)
+
+REQUIRED = {"bound", "achieved", "peak", "unit", "frac", "traffic"}
+ARGS = SimpleNamespace(traffic_per_launch=None)
+
+
+def _stats(launches, ms, nbytes, dev_n=0, dev_ms=0.0, link=(0, 0.0, 0)):
+    return {"pack_kernel_launches": launches, "pack_kernel_ms": ms, "pack_kernel_bytes": nbytes,
+            "pack_kernel_device_launches": dev_n, "pack_kernel_device_ms": dev_ms,
+            "link_kernel_launches": link[0], "link_kernel_ms": link[1], "link_kernel_bytes": link[2]}
+
+
+def test_roofline_from_pipeline_counters_only():
+    zero = _stats(0, 0.0, 0)
+    after = _stats(100, 4.0, 100 * 40 << 20, dev_n=100, dev_ms=0.75)
+    r = bench.build_roofline([(zero, after)], ARGS)
+    assert REQUIRED <= set(r) and r["bound"] == "hbm" and r["unit"] == "GB/s"
+    assert r["launches"] == 100 and r["algorithmic_bytes_per_launch"] == 40 << 20
+    assert abs(r["achieved"] - (100 * (40 << 20)) / 1e6 / 4.0) < 0.1
+    assert abs(r["frac"] - r["achieved"] / r["peak"]) < 1e-3
+    assert r["device_clock"]["avg_launch_us"] == 7.5
+    assert r["traffic"] == round((40 << 20) / 2 * (8.398336 / 8.388608))   # one DRAM read per payload byte
+
+
+def test_roofline_headline_is_the_kernel_alone_when_that_leg_ran():
+    zero = _stats(0, 0.0, 0)
+    after = _stats(100, 4.0, 100 * 40 << 20, dev_n=100, dev_ms=0.75)
+    alone = {"ms": 16.0, "launches": 1536, "payload": 1536 * (20 << 20), "passes": 3, "inputs_exceed_l2": True}
+    r = bench.build_roofline([(zero, after)], ARGS, alone)
+    assert REQUIRED <= set(r)
+    assert r["launches"] == 1536 and r["algorithmic_bytes_per_launch"] == 40 << 20
+    assert abs(r["achieved"] - 2 * alone["payload"] / 1e6 / 16.0) < 0.1
+    assert abs(r["frac"] - r["achieved"] / r["peak"]) < 1e-3
+    assert "gather_layers" in r["how"] and r["inputs_exceed_l2"] is True
+    inner = r["in_pipeline"]
+    assert inner["launches"] == 100 and abs(inner["avg_launch_us"] - 40.0) < 1e-6
+    assert inner["device_clock"]["frac"] > inner["frac"]
+    assert "device_clock" not in r and "note" not in r
+
+
+def test_roofline_of_the_zero_copy_route_reports_the_link_kernel():
+    zero = _stats(0, 0.0, 0)
+    after = _stats(0, 0.0, 0, link=(64, 200.0, 10 << 30))
+    r = bench.build_roofline([(zero, after)], ARGS)
+    assert REQUIRED <= set(r) and r["launches"] == 64 and "PCIe" in r["note"]
