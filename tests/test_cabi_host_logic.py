@@ -409,3 +409,49 @@ def test_service_state_recovers_once_the_health_probe_succeeds():
     assert sm.is_available() and Client.asked == 3
     w.registered_layers = []
     w.unregister()          # also stops the probe thread
+
+
+def test_page_layout_and_unit_size_match_the_oracle_on_random_topologies():
+    """Random worker layer sets (disjoint shards, identical replicas, overlapping or empty sets that
+    must be refused) through the product's C ABI and through the oracle: same layout or both refuse."""
+    import numpy as np
+
+    rng = np.random.default_rng(11)
+    SZ = C.c_size_t
+    agreed_ok = agreed_reject = 0
+    for _ in range(300):
+        n = int(rng.integers(1, 12))
+        kind = rng.choice(["split", "replicas", "random"])
+        if kind == "split":
+            cuts = sorted(set(rng.integers(1, n, size=int(rng.integers(0, 3))).tolist())) if n > 1 else []
+            edges = [0] + cuts + [n]
+            sets = [list(range(a, b)) for a, b in zip(edges, edges[1:])]
+            sets = [sets[i] for i in rng.permutation(len(sets))] * int(rng.integers(1, 3))
+        elif kind == "replicas":
+            sets = [list(range(n))] * int(rng.integers(1, 4))
+        else:
+            sets = [sorted(set(rng.integers(0, n + 1, size=int(rng.integers(0, n + 1))).tolist()))
+                    for _ in range(int(rng.integers(1, 4)))]
+        padded = (rng.integers(1, 40, size=n) * 512).tolist()
+        offs, items = [0], []
+        for s in sets:
+            items += s
+            offs.append(len(items))
+        shard, loff, lbytes, pages, nsh = (SZ * n)(), (SZ * n)(), (SZ * n)(), (SZ * len(sets))(), SZ()
+        st = N.lib.pf_build_page_layout((SZ * len(offs))(*offs), (SZ * max(1, len(items)))(*items), len(sets), n,
+                                        (SZ * n)(*padded), shard, loff, lbytes, pages, C.byref(nsh))
+        try:
+            want = po.build_page_layout(sets, n, padded)
+        except po.OracleError:
+            assert st == 3, f"oracle refuses {sets} over {n} layers, the library accepted it"
+            agreed_reject += 1
+            continue
+        assert st == 0, f"oracle accepts {sets} over {n} layers, the library said: {N.lib.pf_last_error().decode()}"
+        assert list(shard) == want["layer_shard"] and list(loff) == want["layer_offsets"]
+        assert list(lbytes) == want["layer_bytes"] and list(pages[: nsh.value]) == want["shard_page_sizes"]
+        agreed_ok += 1
+    assert agreed_ok >= 50 and agreed_reject >= 20, (agreed_ok, agreed_reject)
+    for _ in range(300):
+        pool = int(rng.integers(1, 1 << 46))
+        hint = int(rng.choice([0, 1, 511, 512, 513, 4096, 73728, int(rng.integers(1, 1 << 24))]))
+        assert N.lib.pf_pool_unit_size(pool, hint) == po.pool_unit_size(pool, hint or None)
