@@ -153,6 +153,34 @@ class ShardQuery:
             raise
         return common, tuple(leases)
 
+    def query_group_membership(self, instance_id: str, hashes: List[bytes], req_id: str, group_id: int):
+        """Which of `hashes` one hybrid storage group holds, per shard (tp_shards.py:93-141): a list of
+        (hit positions, lease over exactly those blocks, in that order).  Membership is answered from
+        memory only, so a shard that says Loading is an error; whatever goes wrong, the leases of the
+        shards that had already answered are given back."""
+        answers: List[Tuple[Tuple[int, ...], bytes]] = []
+        try:
+            for index, client in enumerate(self.clients):
+                got = client.query_prefetch(instance_id, hashes, req_id=req_id, group_id=group_id)
+                if isinstance(got, QueryLoading) or type(got).__name__ == "QueryLoading":
+                    raise RuntimeError(f"TP shard {index} membership query for group {group_id} returned Loading; "
+                                       "membership queries are local-only")
+                if not hasattr(got, "num_hit_blocks"):
+                    raise TypeError(f"query_prefetch returned unexpected outcome {type(got)!r}")
+                positions = tuple(got.hit_positions)
+                if len(positions) != got.num_hit_blocks:
+                    raise RuntimeError(f"TP shard {index} reported {got.num_hit_blocks} hits but returned "
+                                       f"{len(positions)} positions")
+                if any(p >= len(hashes) for p in positions):
+                    raise RuntimeError(f"TP shard {index} returned hit positions outside a {len(hashes)}-hash query")
+                if positions and not got.lease:
+                    raise RuntimeError(f"TP shard {index} returned {len(positions)} hits without a lease")
+                answers.append((positions, got.lease))
+        except Exception:
+            self.release([lease for _, lease in answers], req_id)
+            raise
+        return answers
+
     def release(self, leases: Sequence[bytes], req_id: str = "") -> bool:
         ok = True
         for client, lease in zip(self.clients, leases):

@@ -178,3 +178,43 @@ def test_other_group_layouts_are_refused(specs):
 
     with pytest.raises(RuntimeError, match="single"):
         check(_cfg(*specs))
+
+
+# ---- ShardQuery against recorded answers of the reference's TpShardQueryClient -----------------------------
+def test_shard_query_replays_the_reference_in_scripted_scenarios():
+    """tests/golden/shard_query.json holds, for 70 scripted scenarios (shards that answer Ready with
+    varying hit counts, Loading, raise, return malformed answers, or fail to release), what the
+    reference's client returned or raised and every call it made to the shards, in order.  The
+    mirror must do exactly the same: same result, same exception type and text, same queries,
+    same releases."""
+    import json
+    import os
+
+    from pegaflow_b200.connector import QueryLoading, QueryReady
+    from pegaflow_b200.scheduler import ShardQuery
+    from tests import shard_query_cases as cases
+
+    class Adapter:
+        def __init__(self, shards):
+            self.client = ShardQuery(shards)
+
+        def prefix(self, instance_id, hashes, req_id, wait):
+            got = self.client.query(instance_id, hashes, req_id, wait)
+            return None if got is None else [got[0], [lease.decode() for lease in got[1]]]
+
+        def membership(self, instance_id, hashes, req_id, group_id):
+            return [[list(p), lease.decode()]
+                    for p, lease in self.client.query_group_membership(instance_id, hashes, req_id, group_id)]
+
+    here = os.path.dirname(os.path.abspath(__file__))
+    golden = json.load(open(os.path.join(here, "golden", "shard_query.json")))
+    got = json.loads(json.dumps(cases.run_all(Adapter, QueryReady, QueryLoading)))
+    assert len(got) == len(golden) == 70
+    kinds = set()
+    for i, (a, b) in enumerate(zip(got, golden)):
+        assert a["scripts"] == b["scripts"], f"scenario {i}: the scripts differ, regenerate the fixture"
+        assert a["outcome"] == b["outcome"], f"scenario {i} ({a['kind']}): {a['outcome']} != {b['outcome']}"
+        assert a["log"] == b["log"], f"scenario {i} ({a['kind']}): calls differ\n{a['log']}\n{b['log']}"
+        kinds.add((b["kind"], "ok" if "ok" in b["outcome"] else b["outcome"]["error"][0]))
+    assert {("prefix", "ok"), ("prefix", "RuntimeError"), ("prefix", "ConnectionError"), ("membership", "ok"),
+            ("membership", "RuntimeError")} <= kinds
