@@ -19,6 +19,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
+from .config import reconcile_hybrid_hit
 from .connector import QueryLoading, QueryReady
 
 
@@ -103,6 +104,20 @@ def require_single_attention_group(kv_cache_config) -> None:
                        f"grouped MLA layers (got {kind})")
 
 
+@dataclass(frozen=True)
+class HybridHit:
+    """Outcome of `ShardQuery.query_hybrid`: the attention prefix leases (one per shard) and, for a
+    hit, the pinned recurrent checkpoints — `recurrent_leases[g][shard]` over the blocks at
+    `recurrent_positions[g][shard]` — with the chosen checkpoint position and every position the
+    hit may legally end at (common.py:233-249, tp_shards.py:9-19)."""
+    num_hit_blocks: int
+    leases: Tuple[bytes, ...]
+    recurrent_leases: Tuple[Tuple[bytes, ...], ...] = ()
+    recurrent_positions: Tuple[Tuple[Tuple[int, ...], ...], ...] = ()
+    checkpoint: Optional[int] = None
+    usable_positions: Tuple[int, ...] = ()
+
+
 class ShardQuery:
     """Prefix query across node-local TP shards (tp_shards.py:23-97): the usable hit is the prefix
     every shard holds; shards that answered with more are re-leased for exactly that prefix."""
@@ -180,6 +195,53 @@ class ShardQuery:
             self.release([lease for _, lease in answers], req_id)
             raise
         return answers
+
+    def query_hybrid(self, instance_id: str, hashes: List[bytes], req_id: str, wait_for_full_prefix: bool,
+                     recurrent_group_ids: Sequence[int]):
+        """Prefix query for a hybrid (attention + recurrent state) model (scheduler.py:927-1075): the
+        attention prefix only counts as far as every recurrent storage group has a state checkpoint
+        on every shard.  Returns None while a shard is loading, else a `HybridHit`; a hit of 0 blocks
+        means every lease taken on the way has been given back."""
+        answer = self.query(instance_id, hashes, req_id, wait_for_full_prefix)
+        if answer is None:
+            return None
+        hit, leases = answer
+        if hit == 0:
+            return HybridHit(0, leases)
+        members: List[List[Tuple[Tuple[int, ...], bytes]]] = []
+
+        def release_members():
+            for gid, group in zip(recurrent_group_ids, members):
+                self.release([lease for _, lease in group], f"{req_id}:g{gid}")
+
+        try:
+            for gid in recurrent_group_ids:
+                members.append(self.query_group_membership(instance_id, hashes, f"{req_id}:g{gid}", gid))
+            blocks, checkpoint, usable = reconcile_hybrid_hit(
+                hit, tuple(tuple(positions for positions, _ in group) for group in members))
+        except Exception:
+            self.release(leases, req_id)
+            release_members()
+            raise
+        nothing = HybridHit(0, tuple(b"" for _ in leases))
+        if blocks == 0 or checkpoint is None:
+            self.release(leases, req_id)
+            release_members()
+            return nothing
+        if blocks < hit:
+            # the usable prefix is shorter than the leased one: lease exactly what will be loaded
+            exact = self.query(instance_id, hashes[:blocks], f"{req_id}:hma-exact-{blocks}", False)
+            self.release(leases, req_id)
+            if exact is None or exact[0] != blocks:
+                if exact is not None:
+                    self.release(exact[1], req_id)
+                release_members()
+                return nothing
+            leases = exact[1]
+        return HybridHit(blocks, leases,
+                         tuple(tuple(lease for _, lease in group) for group in members),
+                         tuple(tuple(positions for positions, _ in group) for group in members),
+                         checkpoint, tuple(sorted(usable)))
 
     def release(self, leases: Sequence[bytes], req_id: str = "") -> bool:
         ok = True

@@ -76,6 +76,61 @@ def scenarios(rng):
     return out
 
 
+def hybrid_scenarios(rng):
+    """Hybrid lookups: per shard the attention prefix answer, one membership answer per recurrent
+    storage group, then the answer to the exact re-lease of a shortened prefix.  Most scripts are
+    well-formed so that the success paths are reached; some break at each stage."""
+    out = []
+    for _ in range(80):
+        n_shards, n_groups, n_hashes = rng.choice([1, 2]), rng.choice([1, 2]), rng.choice([4, 6, 8])
+        prefix = rng.choice([n_hashes, n_hashes, n_hashes, n_hashes - 1, 2, 0])
+        positions = [[sorted(rng.sample(range(n_hashes), rng.choice([0, 1, n_hashes // 2, n_hashes - 1, n_hashes, n_hashes])))
+                      for _ in range(n_shards)] for _ in range(n_groups)]
+        usable = None
+        for group in positions:
+            for shard_positions in group:
+                inside = {p for p in shard_positions if p < prefix}
+                usable = inside if usable is None else usable & inside
+        reconciled = max(usable) + 1 if usable else 0
+        scripts = []
+        for s in range(n_shards):
+            roll = rng.random()
+            script = [["loading"] if roll < 0.06 else ["raise", f"shard {s} unreachable"] if roll < 0.1
+                      else ["ready", prefix, f"lease-{s}-a", []]]
+            for g in range(n_groups):
+                roll = rng.random()
+                here = positions[g][s]
+                if roll < 0.05:
+                    script.append(["loading"])
+                elif roll < 0.1:
+                    script.append(["ready", len(here) + 1, f"lease-{s}-g{g}", here])
+                elif roll < 0.14:
+                    script.append(["raise", f"shard {s} dropped"])
+                else:
+                    script.append(["ready", len(here), f"lease-{s}-g{g}" if rng.random() > 0.05 else "", here])
+            roll = rng.random()
+            script.append(["loading"] if roll < 0.1 else ["ready", max(0, reconciled - 1), f"lease-{s}-x", []] if roll < 0.2
+                          else ["ready", reconciled, f"lease-{s}-x", []])
+            scripts.append(script)
+        failing = [f"lease-{s}-a" for s in range(n_shards) if rng.random() < 0.08]
+        out.append(["hybrid", n_hashes, scripts, failing, list(range(1, n_groups + 1))])
+    return out
+
+
+def run_hybrid(make_client, ready_cls, loading_cls, seed=78):
+    results = []
+    for kind, n_hashes, scripts, failing, group_ids in hybrid_scenarios(random.Random(seed)):
+        log = []
+        shards = tuple(ScriptedShard(i, [list(step) for step in sc], log, ready_cls, loading_cls, failing)
+                       for i, sc in enumerate(scripts))
+        client = make_client(shards, group_ids)
+        hashes = [b"h%d" % i for i in range(n_hashes)]
+        outcome = _outcome(lambda: client.hybrid("inst", hashes, "req", False))
+        results.append({"kind": kind, "n_hashes": n_hashes, "scripts": scripts, "groups": group_ids, "outcome": outcome,
+                        "log": log})
+    return results
+
+
 def run_all(make_client, ready_cls, loading_cls, seed=77):
     """`make_client(shards)` returns the object under test; its `query` answer is normalised with
     `normalise_query` by the caller's adapter (see the generator and the test)."""

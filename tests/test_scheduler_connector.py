@@ -182,7 +182,7 @@ def test_other_group_layouts_are_refused(specs):
 
 # ---- ShardQuery against recorded answers of the reference's TpShardQueryClient -----------------------------
 def test_shard_query_replays_the_reference_in_scripted_scenarios():
-    """tests/golden/shard_query.json holds, for 70 scripted scenarios (shards that answer Ready with
+    """tests/golden/shard_query.json holds, for 150 scripted scenarios (70 prefix and membership queries, 80 hybrid lookups; shards that answer Ready with
     varying hit counts, Loading, raise, return malformed answers, or fail to release), what the
     reference's client returned or raised and every call it made to the shards, in order.  The
     mirror must do exactly the same: same result, same exception type and text, same queries,
@@ -206,10 +206,25 @@ def test_shard_query_replays_the_reference_in_scripted_scenarios():
             return [[list(p), lease.decode()]
                     for p, lease in self.client.query_group_membership(instance_id, hashes, req_id, group_id)]
 
+    def hybrid_adapter(shards, group_ids):
+        client = ShardQuery(shards)
+
+        class H:
+            def hybrid(self, instance_id, hashes, req_id, wait):
+                got = client.query_hybrid(instance_id, hashes, req_id, wait, group_ids)
+                if got is None:
+                    return None
+                return {"hit": got.num_hit_blocks, "leases": [x.decode() for x in got.leases],
+                        "recurrent_leases": [[x.decode() for x in g] for g in got.recurrent_leases],
+                        "recurrent_positions": [[list(p) for p in g] for g in got.recurrent_positions],
+                        "checkpoint": got.checkpoint, "usable": list(got.usable_positions)}
+        return H()
+
     here = os.path.dirname(os.path.abspath(__file__))
     golden = json.load(open(os.path.join(here, "golden", "shard_query.json")))
-    got = json.loads(json.dumps(cases.run_all(Adapter, QueryReady, QueryLoading)))
-    assert len(got) == len(golden) == 70
+    got = cases.run_all(Adapter, QueryReady, QueryLoading) + cases.run_hybrid(hybrid_adapter, QueryReady, QueryLoading)
+    got = json.loads(json.dumps(got))
+    assert len(got) == len(golden) == 150
     kinds = set()
     for i, (a, b) in enumerate(zip(got, golden)):
         assert a["scripts"] == b["scripts"], f"scenario {i}: the scripts differ, regenerate the fixture"
@@ -217,4 +232,8 @@ def test_shard_query_replays_the_reference_in_scripted_scenarios():
         assert a["log"] == b["log"], f"scenario {i} ({a['kind']}): calls differ\n{a['log']}\n{b['log']}"
         kinds.add((b["kind"], "ok" if "ok" in b["outcome"] else b["outcome"]["error"][0]))
     assert {("prefix", "ok"), ("prefix", "RuntimeError"), ("prefix", "ConnectionError"), ("membership", "ok"),
-            ("membership", "RuntimeError")} <= kinds
+            ("membership", "RuntimeError"), ("hybrid", "ok"), ("hybrid", "RuntimeError"),
+            ("hybrid", "ConnectionError")} <= kinds
+    hybrid_ok = [b["outcome"]["ok"] for b in golden if b["kind"] == "hybrid" and b["outcome"].get("ok")]
+    assert sum(1 for h in hybrid_ok if h["hit"] > 0) >= 10, "the fixture should hold real hybrid hits"
+    assert any(h["hit"] > 0 and h["leases"][0].endswith("-x") for h in hybrid_ok), "and re-leased shortened prefixes"
