@@ -2,12 +2,16 @@
 loads from the host pool and which it saves to it.
 
 Mirrors the reference's ``SchedulerConnector`` (python/pegaflow/connector/scheduler.py) and
-``TpShardQueryClient`` (python/pegaflow/connector/tp_shards.py) for attention-only models with one
-KV-cache group: prefix lookup with query leases, the identity check that protects a lookup
-against a request that moved on while a slower tier was loading, load intents after block
-allocation, incremental save intents as blocks fill up, and the hold on a finished request's
-blocks until its saves have been sent.  Not mirrored: hybrid (recurrent-state) cache groups and
-the prefill/decode tail-block extension.
+``TpShardQueryClient`` (python/pegaflow/connector/tp_shards.py): prefix lookup with query leases,
+the identity check that protects a lookup against a request that moved on while a slower tier
+was loading, load intents after block allocation, incremental save intents as blocks fill up, and
+the hold on a finished request's blocks until its saves have been sent.  With a cache-group
+layout that has recurrent-state groups (hybrid attention + Mamba models) the reference's hybrid
+rules apply: a hit ends at a checkpoint every recurrent group holds on every shard, the recurrent
+groups load only that checkpoint's state block, blocks are saved from vLLM's block pool by hash,
+and the last state block is saved when the request finishes.  Not mirrored: the prefill/decode
+tail-block extension.  (The vLLM plug-in and the worker-side mirror in this package serve one
+attention or MLA group; they do not consume the recurrent holds.)
 
 Everything here is host bookkeeping over block ids, hashes and leases; no KV bytes are touched.
 The objects it reads are vLLM's (``Request.request_id/.block_hashes/.num_tokens``,
@@ -16,11 +20,22 @@ The objects it reads are vLLM's (``Request.request_id/.block_hashes/.num_tokens`
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass, field, replace
 from typing import Dict, List, Optional, Sequence, Tuple
 
-from .config import reconcile_hybrid_hit
+from .config import CacheGroupLayout, reconcile_hybrid_hit
 from .connector import QueryLoading, QueryReady
+
+
+@dataclass(frozen=True)
+class RecurrentLoadHold:
+    """Pinned recurrent-state checkpoints of one hybrid load (common.py:233-249): `leases[g][shard]`
+    is the membership lease over recurrent group g's hit blocks on that shard, `hit_positions[g][shard]`
+    their positions in the query (lease order), `checkpoint` the position the load resumes from —
+    the state stored there covers every token up to the end of that block."""
+    leases: Tuple[Tuple[bytes, ...], ...]
+    hit_positions: Tuple[Tuple[Tuple[int, ...], ...], ...]
+    checkpoint: int
 
 
 @dataclass(frozen=True)
@@ -29,6 +44,7 @@ class LoadIntent:
     block_ids_by_group: Tuple[Tuple[Optional[int], ...], ...]
     leases: Tuple[bytes, ...]
     num_tokens: int
+    recurrent_hold: Optional[RecurrentLoadHold] = None
 
 
 @dataclass(frozen=True)
@@ -60,6 +76,8 @@ class _Probe:
     hashes: Tuple[bytes, ...]
     hit_blocks: Optional[int] = None      # None: the backend is still loading
     leases: Tuple[bytes, ...] = ()
+    hold: Optional[RecurrentLoadHold] = None     # hybrid models: the pinned recurrent checkpoints
+    usable: frozenset = frozenset()              # hybrid models: every position the hit may end at
 
     def same_query(self, computed_blocks: int, hashes: Tuple[bytes, ...]) -> bool:
         return self.computed_blocks == computed_blocks and self.hashes == hashes
@@ -72,7 +90,7 @@ class _Tracked:
     hashes: Tuple[bytes, ...]
     first_local_block: int                 # blocks before this index came from the host pool
     next_to_store: int
-    block_ids: List[int] = field(default_factory=list)
+    block_ids: List[List[int]] = field(default_factory=list)     # per cache group, in request order
     scheduled_tokens: int = 0
 
 
@@ -275,10 +293,16 @@ def _is_loading(answer) -> bool:
 
 class SchedulerConnector:
     def __init__(self, clients: Sequence[object], *, instance_id: str, block_size: int, read_enabled: bool = True,
-                 wait_for_full_prefix: bool = False):
+                 wait_for_full_prefix: bool = False, cache_groups: Optional[CacheGroupLayout] = None):
         self.instance_id, self.block_size = instance_id, block_size
         self.read_enabled, self.wait_for_full_prefix = read_enabled, wait_for_full_prefix
         self._shards = ShardQuery(clients)
+        # one attention (or MLA) group unless told otherwise; a layout with recurrent-state groups turns
+        # on the hybrid rules (lookups gated on a common checkpoint, saves taken from the local cache)
+        self._groups = cache_groups or CacheGroupLayout(((),), 0, False, frozenset(), frozenset())
+        self._recurrent_storage_ids = tuple(self._groups.storage_group_ids[i]
+                                            for i in sorted(self._groups.recurrent_group_indices))
+        self._local_cached_block = None
         self._probes: Dict[str, _Probe] = {}
         self._matched_blocks: Dict[str, int] = {}      # local prefix + blocks to be loaded, per request
         self._tracked: Dict[str, _Tracked] = {}
@@ -286,6 +310,34 @@ class SchedulerConnector:
         self._deferred_saves: Dict[str, SaveIntent] = {}
         self._unsent: set = set()                      # requests with saves the workers have not reported sent
         self._held: set = set()                        # finished requests whose blocks wait for those saves
+
+    def bind_gpu_block_pool(self, gpu_block_pool) -> None:
+        """scheduler.py:197-208.  Hybrid saves name blocks by hash through vLLM's block pool; and with
+        more than one group vLLM's own prefix cache could expose a loaded attention group before the
+        recurrent group has a usable state, so local prefix hits are switched off there."""
+        self._local_cached_block = gpu_block_pool.get_cached_block
+        if self._groups.group_count > 1:
+            gpu_block_pool.get_cached_block = lambda *_a, **_k: None
+
+    def _lookup(self, hashes: List[bytes], req_id: str):
+        """None while loading, else (hit blocks, prefix leases, recurrent hold or None, usable positions)."""
+        if self._groups.has_recurrent_state:
+            got = self._shards.query_hybrid(self.instance_id, hashes, req_id, self.wait_for_full_prefix,
+                                            self._recurrent_storage_ids)
+            if got is None:
+                return None
+            hold = None
+            if got.checkpoint is not None:
+                hold = RecurrentLoadHold(got.recurrent_leases, got.recurrent_positions, got.checkpoint)
+            return got.num_hit_blocks, got.leases, hold, frozenset(got.usable_positions)
+        got = self._shards.query(self.instance_id, hashes, req_id, self.wait_for_full_prefix)
+        return None if got is None else (got[0], got[1], None, frozenset())
+
+    def _release_hold(self, hold: Optional[RecurrentLoadHold], req_id: str) -> bool:
+        ok = True
+        for index, leases in enumerate(hold.leases if hold is not None else ()):
+            ok = self._shards.release(leases, f"{req_id}:g{index}") and ok
+        return ok
 
     # ------------------------------------------------------------------ lookup (scheduler.py:210-407)
     def get_num_new_matched_tokens(self, request, num_computed_tokens: int) -> Tuple[Optional[int], bool]:
@@ -311,22 +363,22 @@ class SchedulerConnector:
         # A lookup that is loading is known to the backend by request id: keep polling with the
         # hashes it was started with, and compare the answer with today's position afterwards.
         moved_on = probe is not None and not probe.same_query(computed, hashes)
-        answer = self._shards.query(self.instance_id, list(probe.hashes if moved_on else hashes), req_id,
-                                    self.wait_for_full_prefix)
+        answer = self._lookup(list(probe.hashes if moved_on else hashes), req_id)
         if answer is None:
             if probe is None:
                 self._probes[req_id] = _Probe(computed, hashes)
             return None, False
-        hit_blocks, leases = answer
+        hit_blocks, leases, hold, usable = answer
         if moved_on:
             self._shards.release(leases, req_id)
+            self._release_hold(hold, req_id)
             self._probes.pop(req_id, None)
             return None, False
         if probe is None:
             probe = self._probes[req_id] = _Probe(computed, hashes)
         if hit_blocks > len(probe.hashes):
             raise RuntimeError(f"invariant violated: server returned {hit_blocks} hits for {len(probe.hashes)} hashes")
-        probe.hit_blocks, probe.leases = hit_blocks, leases
+        probe.hit_blocks, probe.leases, probe.hold, probe.usable = hit_blocks, leases, hold, usable
         return self._answer(req_id, request.num_tokens, probe)
 
     def _answer(self, req_id: str, num_tokens: int, probe: _Probe) -> Tuple[int, bool]:
@@ -334,6 +386,19 @@ class SchedulerConnector:
         hit_tokens = probe.hit_blocks * bs
         # one token is always left for the forward pass that produces the first logits
         hit_tokens = min(hit_tokens, max(0, num_tokens - probe.computed_blocks * bs - 1))
+        if probe.hold is not None:
+            # a recurrent state can only be resumed at the end of its own block: when the clamp cut
+            # into the reconciled span, fall back to the last checkpoint before the cut, or give up
+            boundary = hit_tokens // bs
+            earlier = [p for p in probe.usable if p < boundary]
+            if not earlier:
+                if self._probes.get(req_id) is probe:
+                    self._drop_probe(req_id)
+                return 0, False
+            checkpoint = max(earlier)
+            probe.hit_blocks = checkpoint + 1
+            hit_tokens = probe.hit_blocks * bs
+            probe.hold = replace(probe.hold, checkpoint=checkpoint)
         self._matched_blocks[req_id] = probe.computed_blocks + (hit_tokens + bs - 1) // bs
         if hit_tokens <= 0:
             self._drop_probe(req_id)
@@ -351,20 +416,29 @@ class SchedulerConnector:
         t = self._tracked.get(req_id)
         if t is None:
             first = self._matched_blocks.get(req_id, 0)
-            t = self._tracked[req_id] = _Tracked(request, tuple(request.block_hashes), first, first)
+            t = self._tracked[req_id] = _Tracked(request, tuple(request.block_hashes), first, first,
+                                                 [[] for _ in range(self._groups.group_count)])
         else:
             t.request, t.hashes = request, tuple(request.block_hashes)
         if num_external_tokens <= 0:
             return
-        ids = self._one_group(blocks.get_block_ids()) if blocks else ()
-        already_computed = sum(b.block_hash is not None for b in blocks.blocks[0]) if blocks else 0
+        ids = self._by_group(blocks.get_block_ids()) if blocks else tuple(() for _ in range(self._groups.group_count))
+        hashed = blocks.blocks[self._groups.hash_group_index] if blocks else ()
+        already_computed = sum(b.block_hash is not None for b in hashed)
         n_load = (num_external_tokens + self.block_size - 1) // self.block_size
-        if len(ids) < already_computed + n_load:
+        if any(len(g) < already_computed + n_load for g in ids):
             self._drop_probe(req_id)
-            raise RuntimeError(f"load block mismatch: start={already_computed} count={n_load} available={len(ids)}")
+            raise RuntimeError(f"load block mismatch: start={already_computed} count={n_load} "
+                               f"available_by_group={[len(g) for g in ids]}")
+        destinations = []
+        for index, group in enumerate(ids):
+            dst = group[already_computed:already_computed + n_load]
+            if index in self._groups.recurrent_group_indices and dst:
+                dst = (None,) * (len(dst) - 1) + (dst[-1],)     # only the checkpoint's state is loaded
+            destinations.append(dst)
         probe = self._probes.get(req_id)
-        intent = LoadIntent((tuple(ids[already_computed:already_computed + n_load]),),
-                            probe.leases if probe is not None else (), num_external_tokens)
+        intent = LoadIntent(tuple(destinations), probe.leases if probe is not None else (), num_external_tokens,
+                            probe.hold if probe is not None else None)
         if probe is not None:
             if not probe.same_query(already_computed, tuple(request.block_hashes[already_computed:])):
                 self._drop_probe(req_id)
@@ -390,9 +464,9 @@ class SchedulerConnector:
             t = self._tracked.get(new.req_id)
             assert t is not None, f"req {new.req_id} not initialized in update_state_after_alloc"
             if new.block_ids:
-                t.block_ids = list(self._one_group(new.block_ids))
+                t.block_ids = [list(g) for g in self._by_group(new.block_ids)]
             self._count_tokens(t, new.num_computed_tokens, scheduled.get(new.req_id, 0))
-            intent = self._next_save(t)
+            intent = self._next_save(t, new.num_computed_tokens)
             if intent:
                 saves[new.req_id] = intent
 
@@ -404,11 +478,13 @@ class SchedulerConnector:
             t.hashes = tuple(t.request.block_hashes)      # decode completes new blocks: pick up their hashes
             fresh = running.new_block_ids[i]
             if req_id in running.resumed_req_ids:
-                t.block_ids = list(self._one_group(fresh)) if fresh else []
+                t.block_ids = ([list(g) for g in self._by_group(fresh)] if fresh
+                               else [[] for _ in range(self._groups.group_count)])
             elif fresh:
-                t.block_ids.extend(self._one_group(fresh))
+                for have, more in zip(t.block_ids, self._by_group(fresh)):
+                    have.extend(more)
             self._count_tokens(t, running.num_computed_tokens[i], scheduled.get(req_id, 0))
-            intent = self._next_save(t)
+            intent = self._next_save(t, running.num_computed_tokens[i])
             if intent:
                 saves[req_id] = intent
 
@@ -421,15 +497,63 @@ class SchedulerConnector:
         else:
             t.scheduled_tokens = max(t.scheduled_tokens, computed_before + now)
 
-    def _next_save(self, t: _Tracked) -> Optional[SaveIntent]:
+    def _next_save(self, t: _Tracked, computed_before_step: int) -> Optional[SaveIntent]:
         """Blocks that became full since the last step (scheduler.py:700-770): block ids and hashes
-        are both in request order, and the prefix that was loaded from the pool is never re-saved."""
-        full_local = min(len(t.block_ids), t.scheduled_tokens // self.block_size)
-        end = min(len(t.hashes), t.first_local_block + full_local)
+        are both in request order, and the prefix that was loaded from the pool is never re-saved.
+        Hybrid models save only what was complete before this step and take the block ids from
+        vLLM's block pool by hash (every group's block of a hash, or nothing yet)."""
+        hybrid = self._groups.has_recurrent_state
+        if hybrid:
+            end = min(len(t.hashes), computed_before_step // self.block_size)
+        else:
+            full_local = min(min((len(g) for g in t.block_ids), default=0), t.scheduled_tokens // self.block_size)
+            end = min(len(t.hashes), t.first_local_block + full_local)
         if end <= t.next_to_store:
             return None
-        start, t.next_to_store = t.next_to_store, end
-        return SaveIntent((tuple(t.block_ids[start:end]),), t.hashes[start:end])
+        start = t.next_to_store
+        hashes = t.hashes[start:end]
+        if hybrid:
+            ids = self._local_cached_ids(hashes)
+            if ids is None:
+                return None
+        else:
+            ids = tuple(tuple(g[start:end]) for g in t.block_ids)
+        t.next_to_store = end
+        return SaveIntent(ids, hashes)
+
+    def _local_cached_ids(self, hashes: Sequence[bytes]):
+        """scheduler.py:774-789."""
+        if self._local_cached_block is None:
+            raise RuntimeError("HMA block pool was not bound before building save metadata")
+        group_ids = list(range(self._groups.group_count))
+        out: List[List[int]] = [[] for _ in group_ids]
+        for h in hashes:
+            cached = self._local_cached_block(h, group_ids)
+            if cached is None:
+                return None
+            for ids, block in zip(out, cached):
+                ids.append(block.block_id)
+        return tuple(tuple(ids) for ids in out)
+
+    def _final_hybrid_save(self, t: _Tracked, block_ids, written: int) -> Optional[SaveIntent]:
+        """What a finished hybrid request still has to save (scheduler.py:791-837): the attention
+        blocks not saved yet, and for every recurrent group only the state block that follows the
+        last full block — the null block stands in for the positions before it."""
+        start = t.next_to_store
+        end = min(len(t.hashes), written // self.block_size)
+        if end <= start:
+            return None
+        groups = self._by_group(block_ids)
+        recurrent = self._groups.recurrent_group_indices
+        available = tuple(len(g) for g in groups)
+        required = tuple(end + 1 if i in recurrent else end for i in range(self._groups.group_count))
+        if any(have < need for have, need in zip(available, required)):
+            raise RuntimeError(f"req {t.request.request_id} final HMA block table is shorter than its hash prefix: "
+                               f"saveable={end} available_by_group={available} required_by_group={required}")
+        ids = tuple((0,) * (end - start - 1) + (g[end],) if i in recurrent else g[start:end]
+                    for i, g in enumerate(groups))
+        t.next_to_store = end
+        return SaveIntent(ids, t.hashes[start:end])
 
     # ------------------------------------------------------------------ completion (scheduler.py:874-925)
     def update_connector_output(self, connector_output) -> None:
@@ -442,6 +566,13 @@ class SchedulerConnector:
     def request_finished(self, request, block_ids) -> Tuple[bool, Optional[dict]]:
         """True: the caller must keep the request's blocks until its saves are reported sent."""
         req_id = request.request_id
+        t = self._tracked.get(req_id)
+        if self._groups.has_recurrent_state and t is not None:
+            t.hashes = tuple(request.block_hashes)
+            final = self._final_hybrid_save(t, block_ids, request.num_computed_tokens)
+            if final is not None:
+                self._deferred_saves[req_id] = final
+                self._unsent.add(req_id)
         if req_id in self._unsent:
             self._held.add(req_id)
             return True, None
@@ -462,15 +593,15 @@ class SchedulerConnector:
 
     def _drop_probe(self, req_id: str) -> bool:
         probe = self._probes.pop(req_id, None)
-        if probe is None or not any(probe.leases):
+        if probe is None:
             return True
-        return self._shards.release(probe.leases, req_id)
+        ok = self._shards.release(probe.leases, req_id) if any(probe.leases) else True
+        return self._release_hold(probe.hold, req_id) and ok
 
-    @staticmethod
-    def _one_group(block_ids) -> Tuple[int, ...]:
+    def _by_group(self, block_ids) -> Tuple[Tuple[int, ...], ...]:
         groups = tuple(tuple(g) for g in block_ids)
-        if len(groups) != 1:
-            raise RuntimeError(f"KV cache group count mismatch: expected=1 actual={len(groups)}")
-        if any(b < 0 for b in groups[0]):
+        if len(groups) != self._groups.group_count:
+            raise RuntimeError(f"KV cache group count mismatch: expected={self._groups.group_count} actual={len(groups)}")
+        if any(b < 0 for g in groups for b in g):
             raise RuntimeError("KV cache block IDs must be non-negative")
-        return groups[0]
+        return groups

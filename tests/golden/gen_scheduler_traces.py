@@ -32,7 +32,7 @@ scripts = importlib.util.module_from_spec(_spec)
 _spec.loader.exec_module(scripts)
 
 
-def make_reference_connector(clients, *, block_size, read_enabled, wait_for_full_prefix, group_count):
+def make_reference_connector(clients, *, block_size, read_enabled, wait_for_full_prefix, group_count, recurrent_groups=0):
     ctx = ConnectorContext(
         instance_id="inst", namespace="ns", block_size=block_size, tp_size=1, world_size=1, tp_rank=None, device_id=None,
         engine_client=clients[0], state_manager=MagicMock(),
@@ -42,6 +42,16 @@ def make_reference_connector(clients, *, block_size, read_enabled, wait_for_full
         tp_shards=None if len(clients) == 1 else SimpleNamespace(shard_count=len(clients)))
     kv_cache_config = None
     conn = SchedulerConnector(ctx, engine_clients=tuple(clients), kv_cache_config=kv_cache_config)
+    if recurrent_groups:
+        # one attention group followed by the recurrent-state groups, storage groups 1..n
+        from pegaflow.connector.common import CacheGroupLayout
+
+        names = (("attn",),) + tuple((f"mamba{g}",) for g in range(1, recurrent_groups + 1))
+        conn._cache_groups = CacheGroupLayout(
+            layer_names=names, hash_group_index=0, has_recurrent_state=True,
+            recurrent_group_indices=frozenset(range(1, recurrent_groups + 1)),
+            recurrent_layer_names=frozenset(n for g in names[1:] for n in g),
+            storage_group_ids=tuple(range(recurrent_groups + 1)))
     if group_count != 1:
         # attention-only groups that share the hash cadence: the layout only needs the group count
         object.__setattr__(conn._cache_groups, "layer_names", tuple(() for _ in range(group_count)))

@@ -22,8 +22,26 @@ class FakeClient:
     def __init__(self, name, ready_cls, loading_cls):
         self.name, self.ready_cls, self.loading_cls = name, ready_cls, loading_cls
         self.store, self.loading, self.live, self.log, self.issued = set(), {}, {}, [], 0
+        self.group_store = {}       # storage group id -> hashes whose recurrent state is stored
+
+    def _ready(self, hits, lease, positions):
+        answer = self.ready_cls(hits, lease)      # the reference's test stub takes two arguments
+        answer.hit_positions = list(positions)
+        return answer
 
     def query_prefetch(self, instance_id, block_hashes, req_id, wait_for_full_prefix=False, group_id=0):
+        if group_id != 0:
+            # membership: which of the hashes this storage group holds, wherever they are in the query
+            held = self.group_store.get(group_id, set())
+            positions = [i for i, h in enumerate(block_hashes) if bytes(h) in held]
+            if not positions:
+                self.log.append(["member-miss", self.name, req_id, group_id, len(block_hashes)])
+                return self._ready(0, b"", [])
+            self.issued += 1
+            lease = b"%s-lease-%03d" % (self.name.encode(), self.issued)
+            self.live[lease] = len(positions)
+            self.log.append(["member-lease", self.name, req_id, group_id, len(block_hashes), positions, lease.decode()])
+            return self._ready(len(positions), lease, positions)
         if self.loading.get(req_id, 0) > 0:
             self.loading[req_id] -= 1
             self.log.append(["loading", self.name, req_id, len(block_hashes)])
@@ -35,12 +53,12 @@ class FakeClient:
             n += 1
         if n == 0:
             self.log.append(["miss", self.name, req_id, len(block_hashes)])
-            return self.ready_cls(0, b"")
+            return self._ready(0, b"", [])
         self.issued += 1
         lease = b"%s-lease-%03d" % (self.name.encode(), self.issued)
         self.live[lease] = n
         self.log.append(["lease", self.name, req_id, len(block_hashes), n, lease.decode(), bool(wait_for_full_prefix)])
-        return self.ready_cls(n, lease)
+        return self._ready(n, lease, range(n))
 
     def release(self, lease):
         self.log.append(["release", self.name, bytes(lease).decode()])
@@ -60,13 +78,37 @@ class FakeRequest:
         self.mm_features = None
 
 
+class FakeBlockPool:
+    """vLLM's GPU block pool as the hybrid save path reads it: the blocks (one per cache group) that
+    hold a given block hash locally, or None while some group has none."""
+
+    def __init__(self):
+        self.by_hash = {}
+
+    def get_cached_block(self, block_hash, group_ids):
+        ids = self.by_hash.get(bytes(block_hash))
+        if ids is None:
+            return None
+        return [SimpleNamespace(block_id=ids[g]) for g in group_ids]
+
+
+def _groups_of(ids):
+    """Block ids as vLLM passes them: a tuple of per-group lists (scripts write one flat list for the
+    single-group case)."""
+    if ids and isinstance(ids[0], (list, tuple)):
+        return tuple(list(g) for g in ids)
+    return tuple([list(ids)])
+
+
 class FakeBlocks:
     """`KVCacheBlocks` as the connector sees it: ids per group, and which blocks already carry a
     hash (the locally computed prefix)."""
 
     def __init__(self, block_ids, n_cached):
-        self._ids = [list(block_ids)]
-        self.blocks = [[SimpleNamespace(block_hash=(b"x" if i < n_cached else None)) for i in range(len(block_ids))]]
+        groups = block_ids if block_ids and isinstance(block_ids[0], (list, tuple)) else [block_ids]
+        self._ids = [list(g) for g in groups]
+        self.blocks = [[SimpleNamespace(block_hash=(b"x" if i < n_cached else None)) for i in range(len(g))]
+                       for g in groups]
 
     def get_block_ids(self):
         return tuple(self._ids)
@@ -77,17 +119,25 @@ def _intent(x):
     if hasattr(x, "leases"):
         out["leases"] = [bytes(l).decode() for l in x.leases]
         out["num_tokens"] = x.num_tokens
+        hold = getattr(x, "recurrent_hold", None)
+        if hold is not None:
+            out["hold"] = {"leases": [[bytes(l).decode() for l in g] for g in hold.leases],
+                           "positions": [[list(p) for p in g] for g in hold.hit_positions], "checkpoint": hold.checkpoint}
     else:
         out["hashes"] = [bytes(h).decode() for h in x.block_hashes]
     return out
 
 
 def run_script(script, make_connector, ready_cls, loading_cls):
-    cfg = dict(block_size=BLOCK, read_enabled=True, wait_for_full_prefix=False, shards=1)
+    cfg = dict(block_size=BLOCK, read_enabled=True, wait_for_full_prefix=False, shards=1, recurrent_groups=0)
     cfg.update(script.get("config", {}))
     clients = [FakeClient("shard%d" % i, ready_cls, loading_cls) for i in range(cfg["shards"])]
     conn = make_connector(clients, block_size=cfg["block_size"], read_enabled=cfg["read_enabled"],
-                          wait_for_full_prefix=cfg["wait_for_full_prefix"], group_count=1)
+                          wait_for_full_prefix=cfg["wait_for_full_prefix"], group_count=1,
+                          recurrent_groups=cfg["recurrent_groups"])
+    pool = FakeBlockPool()
+    if cfg["recurrent_groups"]:
+        conn.bind_gpu_block_pool(pool)
     requests, trace = {}, []
     for op in script["ops"]:
         kind, args = op[0], op[1:]
@@ -97,6 +147,12 @@ def run_script(script, make_connector, ready_cls, loading_cls):
                 clients[args[0]].store.update(H(i) for i in args[1])
             elif kind == "evict":
                 clients[args[0]].store.difference_update(H(i) for i in args[1])
+            elif kind == "gstore":
+                clients[args[0]].group_store.setdefault(args[1], set()).update(H(i) for i in args[2])
+            elif kind == "pool":
+                pool.by_hash.update({H(int(i)): list(ids) for i, ids in args[0].items()})
+            elif kind == "computed":
+                requests[args[0]].num_computed_tokens = args[1]
             elif kind == "loading":
                 clients[args[0]].loading[args[1]] = args[2]
             elif kind == "request":
@@ -114,14 +170,14 @@ def run_script(script, make_connector, ready_cls, loading_cls):
                 result = "ok"
             elif kind == "step":
                 spec = args[0]
-                new = [SimpleNamespace(req_id=r, block_ids=(tuple([list(ids)]) if ids is not None else None),
+                new = [SimpleNamespace(req_id=r, block_ids=(_groups_of(ids) if ids is not None else None),
                                        num_computed_tokens=nc) for r, ids, nc, _n in spec.get("new", [])]
                 cached = spec.get("cached", [])
                 out = SimpleNamespace(
                     scheduled_new_reqs=new,
                     scheduled_cached_reqs=SimpleNamespace(
                         req_ids=[c[0] for c in cached],
-                        new_block_ids=[(tuple([list(c[1])]) if c[1] is not None else None) for c in cached],
+                        new_block_ids=[(_groups_of(c[1]) if c[1] is not None else None) for c in cached],
                         num_computed_tokens=[c[2] for c in cached],
                         resumed_req_ids={c[0] for c in cached if len(c) > 4 and c[4]}),
                     num_scheduled_tokens={**{r: n for r, _i, _c, n in spec.get("new", [])},
@@ -133,7 +189,7 @@ def run_script(script, make_connector, ready_cls, loading_cls):
                           "ready_saves": {k: _intent(v) for k, v in sorted(meta.ready_save_intents.items())},
                           "preempted": sorted(meta.preempted_req_ids)}
             elif kind == "finished":
-                held, extra = conn.request_finished(requests[args[0]], tuple([list(args[1])]))
+                held, extra = conn.request_finished(requests[args[0]], _groups_of(args[1]))
                 result = [bool(held), extra]
             elif kind == "sent":
                 conn.update_connector_output(SimpleNamespace(finished_sending=set(args[0]), finished_recving=None))
@@ -356,3 +412,138 @@ SCRIPTS = {
         ("finished", "r", [7, 8, 9, 10]),
     ]},
 }
+
+# ---- hybrid models: one attention cache group and recurrent-state groups ---------------------------------------
+# Block ids are written per group ([attention ids, recurrent ids, ...]); the block pool maps a block hash
+# to the local block of every group ("pool"); "gstore" puts recurrent checkpoints into a storage group.
+HYBRID = {"recurrent_groups": 1}
+
+SCRIPTS.update({
+    # nothing cached: blocks are saved only once they were complete before the step and every group's block
+    # is in vLLM's block pool; the rest, and the recurrent state after the last full block, at the finish
+    "hybrid_cold_saves_from_the_block_pool": {"config": HYBRID, "ops": [
+        ("request", "h", _r(0, 3), 56),
+        ("match", "h", 0),
+        ("alloc", "h", [[10, 11, 12, 13], [30, 31, 32, 33]], 0, 0),
+        ("step", {"new": [["h", [[10, 11, 12, 13], [30, 31, 32, 33]], 0, 40]]}),
+        ("step", {"cached": [["h", None, 40, 16]]}),
+        ("pool", {"0": [10, 30], "1": [11, 31]}),
+        ("step", {"cached": [["h", None, 56, 1]]}),
+        ("pool", {"2": [12, 32]}),
+        ("step", {"cached": [["h", None, 57, 1]]}),
+        ("grow", "h", [3], 65),
+        ("step", {"cached": [["h", [[14], [34]], 58, 6]]}),
+        ("computed", "h", 64),
+        ("finished", "h", [[10, 11, 12, 13, 14], [30, 31, 32, 33, 34]]),
+        ("step", {}),
+        ("sent", ["h"]),
+        ("finished", "h", [[10, 11, 12, 13, 14], [30, 31, 32, 33, 34]]),
+    ]},
+    # attention prefix of four blocks, recurrent checkpoints at positions 1 and 3: the hit ends at 3,
+    # the recurrent group loads only the checkpoint's state block
+    "hybrid_warm_hit": {"config": HYBRID, "ops": [
+        ("store", 0, _r(0, 4)),
+        ("gstore", 0, 1, [1, 3]),
+        ("request", "w", _r(0, 4), 70),
+        ("match", "w", 0),
+        ("match", "w", 0),
+        ("alloc", "w", [[5, 6, 7, 8, 9], [40, 41, 42, 43, 44]], 0, 64),
+        ("step", {"new": [["w", [[5, 6, 7, 8, 9], [40, 41, 42, 43, 44]], 64, 6]]}),
+        ("computed", "w", 70),
+        ("finished", "w", [[5, 6, 7, 8, 9], [40, 41, 42, 43, 44]]),
+    ]},
+    # the whole 64-token prompt is stored: one token must be left to compute, which cuts into the last
+    # block, so the hit falls back to the checkpoint at position 1
+    "hybrid_hit_clamped_to_an_earlier_checkpoint": {"config": HYBRID, "ops": [
+        ("store", 0, _r(0, 4)),
+        ("gstore", 0, 1, [1, 3]),
+        ("request", "c", _r(0, 4), 64),
+        ("match", "c", 0),
+        ("alloc", "c", [[5, 6, 7, 8], [40, 41, 42, 43]], 0, 32),
+        ("step", {"new": [["c", [[5, 6, 7, 8], [40, 41, 42, 43]], 32, 32]]}),
+    ]},
+    # same, but the only checkpoint is the last block's: nothing usable survives the clamp
+    "hybrid_hit_lost_to_the_clamp": {"config": HYBRID, "ops": [
+        ("store", 0, _r(0, 4)),
+        ("gstore", 0, 1, [3]),
+        ("request", "l", _r(0, 4), 64),
+        ("match", "l", 0),
+        ("alloc", "l", [[5, 6, 7, 8], [40, 41, 42, 43]], 0, 0),
+        ("step", {"new": [["l", [[5, 6, 7, 8], [40, 41, 42, 43]], 0, 64]]}),
+    ]},
+    # an attention prefix without any recurrent checkpoint is a miss, and so is a checkpoint beyond the prefix
+    "hybrid_prefix_without_a_checkpoint": {"config": HYBRID, "ops": [
+        ("store", 0, _r(0, 3)),
+        ("request", "n", _r(0, 5), 100),
+        ("match", "n", 0),
+        ("gstore", 0, 1, [4]),
+        ("match", "n", 0),
+        ("gstore", 0, 1, [0]),
+        ("match", "n", 0),
+        ("alloc", "n", [[1, 2, 3, 4, 5, 6, 7], [11, 12, 13, 14, 15, 16, 17]], 0, 16),
+        ("step", {"new": [["n", [[1, 2, 3, 4, 5, 6, 7], [11, 12, 13, 14, 15, 16, 17]], 16, 84]]}),
+    ]},
+    # the checkpoint lies before the end of the attention prefix: the prefix lease is exchanged for
+    # one over exactly the shortened prefix
+    "hybrid_shortened_prefix_is_leased_again": {"config": HYBRID, "ops": [
+        ("store", 0, _r(0, 4)),
+        ("gstore", 0, 1, [1]),
+        ("request", "s", _r(0, 5), 90),
+        ("match", "s", 0),
+        ("alloc", "s", [[1, 2, 3, 4, 5, 6], [11, 12, 13, 14, 15, 16]], 0, 32),
+        ("step", {"new": [["s", [[1, 2, 3, 4, 5, 6], [11, 12, 13, 14, 15, 16]], 32, 58]]}),
+        ("shutdown",),
+    ]},
+    # two TP shards and two recurrent groups: the checkpoint has to exist everywhere
+    "hybrid_two_shards_two_groups": {"config": {"recurrent_groups": 2, "shards": 2}, "ops": [
+        ("store", 0, _r(0, 6)),
+        ("store", 1, _r(0, 5)),
+        ("gstore", 0, 1, [0, 2, 4]),
+        ("gstore", 1, 1, [2, 4]),
+        ("gstore", 0, 2, [2, 3, 4]),
+        ("gstore", 1, 2, [1, 2]),
+        ("request", "t", _r(0, 6), 120),
+        ("match", "t", 0),
+        ("alloc", "t", [[1, 2, 3, 4, 5, 6, 7, 8], [11, 12, 13, 14, 15, 16, 17, 18], [21, 22, 23, 24, 25, 26, 27, 28]], 0, 48),
+        ("step", {"new": [["t", [[1, 2, 3, 4, 5, 6, 7, 8], [11, 12, 13, 14, 15, 16, 17, 18],
+                                 [21, 22, 23, 24, 25, 26, 27, 28]], 48, 72]]}),
+    ]},
+    # a slower tier is loading while the request moves on: the stale answer's prefix and recurrent leases go back
+    "hybrid_drift_while_loading": {"config": HYBRID, "ops": [
+        ("store", 0, _r(0, 4)),
+        ("gstore", 0, 1, [1, 2]),
+        ("request", "d", _r(0, 4), 80),
+        ("loading", 0, "d", 1),
+        ("match", "d", 0),
+        ("match", "d", 16),
+        ("match", "d", 16),
+        ("shutdown",),
+    ]},
+    # a Ready answer is kept between polls, replaced when the request's position changes, and dropped at the finish
+    "hybrid_ready_reuse_and_release": {"config": HYBRID, "ops": [
+        ("store", 0, _r(0, 4)),
+        ("gstore", 0, 1, [0, 1, 2, 3]),
+        ("request", "r", _r(0, 4), 80),
+        ("match", "r", 0),
+        ("match", "r", 0),
+        ("match", "r", 32),
+        ("finished", "r", [[1], [2]]),
+    ]},
+    # refused inputs: a flat block table for a two-group model, a block table shorter than the load, a final
+    # recurrent table without the state block after the last full block
+    "hybrid_errors": {"config": HYBRID, "ops": [
+        ("store", 0, _r(0, 2)),
+        ("gstore", 0, 1, [1]),
+        ("request", "e", _r(0, 3), 50),
+        ("match", "e", 0),
+        ("alloc", "e", [1, 2, 3, 4], 0, 32),
+        ("match", "e", 0),
+        ("alloc", "e", [[1, 2, 3, 4], [11]], 0, 32),
+        ("match", "e", 0),
+        ("alloc", "e", [[1, 2, 3, 4], [11, 12, 13, 14]], 0, 32),
+        ("step", {"new": [["e", [[1, 2, 3, 4], [11, 12, 13, 14]], 32, 18]]}),
+        ("computed", "e", 50),
+        ("finished", "e", [[1, 2, 3, 4], [11, 12, 13]]),
+        ("finished", "e", [[1, 2, 3, 4], [11, 12, 13, 14]]),
+    ]},
+})

@@ -18,12 +18,19 @@ def golden():
         return json.load(f)
 
 
-def _make(clients, *, block_size, read_enabled, wait_for_full_prefix, group_count):
+def _make(clients, *, block_size, read_enabled, wait_for_full_prefix, group_count, recurrent_groups=0):
+    from pegaflow_b200.config import CacheGroupLayout
     from pegaflow_b200.scheduler import SchedulerConnector
 
     assert group_count == 1
+    layout = None
+    if recurrent_groups:
+        # one attention group followed by the recurrent-state groups, storage groups 1..n
+        names = (("attn",),) + tuple((f"mamba{g}",) for g in range(1, recurrent_groups + 1))
+        layout = CacheGroupLayout(names, 0, True, frozenset(range(1, recurrent_groups + 1)),
+                                  frozenset(n for g in names[1:] for n in g), tuple(range(recurrent_groups + 1)))
     return SchedulerConnector(clients, instance_id="inst", block_size=block_size, read_enabled=read_enabled,
-                              wait_for_full_prefix=wait_for_full_prefix)
+                              wait_for_full_prefix=wait_for_full_prefix, cache_groups=layout)
 
 
 def test_every_script_has_a_trace(golden):
