@@ -19,7 +19,7 @@ from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
 from . import _native as N
-from .config import resolve_transfer_backend  # noqa: F401  (re-exported)
+from .config import CacheGroupLayout, resolve_transfer_backend  # noqa: F401  (resolve_transfer_backend is re-exported)
 from .engine import PegaEngine, PyLoadState
 
 CROSS_LAYER_KEY = "ALL_LAYERS"  # worker.py:32
@@ -239,6 +239,46 @@ class ServiceStateManager:
             probe.join(timeout=1.0)
 
 
+def plan_group_loads(load_intents, cache_groups: CacheGroupLayout, shard_index: int = 0, shard_count: int = 1):
+    """Turn the scheduler's load intents into the engine's load requests for one TP shard when the model
+    has several cache groups (worker.py:571-617).  Returns (loads, destination block ids, request ids);
+    a load is (lease, destination ids per cache group, `None` = skip that block).
+
+    The prefix lease pins attention blocks only, so under it the recurrent groups get no destination.
+    Each recurrent group's state travels under its own membership lease, which pins the blocks at
+    `hit_positions`; only the checkpoint among them has a destination — the last block the
+    scheduler allocated for that group."""
+    loads, all_ids, request_ids = [], [], []
+    recurrent = sorted(cache_groups.recurrent_group_indices)
+    for req_id, intent in load_intents.items():
+        if len(intent.leases) != shard_count:
+            raise RuntimeError(f"load intent has {len(intent.leases)} TP shard leases; expected {shard_count}")
+        by_group = [list(g) for g in intent.block_ids_by_group]
+        hold = getattr(intent, "recurrent_hold", None)
+        if hold is not None:
+            for g in recurrent:
+                by_group[g] = [None] * len(by_group[g])
+        for ids in by_group:
+            all_ids.extend(b for b in ids if b is not None)
+        loads.append((intent.leases[shard_index], by_group))
+        if hold is not None:
+            for slot, g in enumerate(recurrent):
+                positions = hold.hit_positions[slot][shard_index]
+                if hold.checkpoint not in positions:
+                    raise RuntimeError(f"req {req_id}: recurrent group {g} shard {shard_index} lease has no checkpoint "
+                                       f"at query position {hold.checkpoint}")
+                destination = next((b for b in reversed(intent.block_ids_by_group[g]) if b is not None), None)
+                if destination is None:
+                    raise RuntimeError(f"req {req_id}: no recurrent destination block in group {g} for checkpoint "
+                                       f"{hold.checkpoint}")
+                vectors = [[None] * len(positions) for _ in range(cache_groups.group_count)]
+                vectors[g][list(positions).index(hold.checkpoint)] = destination
+                loads.append((hold.leases[slot][shard_index], vectors))
+                all_ids.append(destination)
+        request_ids.append(req_id)
+    return loads, all_ids, request_ids
+
+
 def _load_timeout_seconds() -> int:
     """worker.py:34-43: PEGA_LOAD_TIMEOUT_SECONDS, default 120, never below 30; an unparsable value
     falls back to the default (common.py:464-485)."""
@@ -266,8 +306,13 @@ class PegaWorkerConnector:
     def __init__(self, client: InProcEngineClient, engine: PegaEngine, *, instance_id: str, namespace: str,
                  device_id: int, block_size: int, tp_rank: int = 0, pp_rank: int = 0, tp_size: int = 1,
                  world_size: int = 1, is_mla: bool = False, transfer_backend: Optional[str] = None,
-                 page_first: Optional[bool] = None, state_manager: Optional[ServiceStateManager] = None):
+                 page_first: Optional[bool] = None, state_manager: Optional[ServiceStateManager] = None,
+                 cache_groups: Optional[CacheGroupLayout] = None, tp_shard_count: int = 1):
         self.client, self.engine = client, engine
+        # one attention (or MLA) group unless a layout says otherwise (worker.py:196-197)
+        self.cache_groups = cache_groups or CacheGroupLayout(((),), 0, False, frozenset(), frozenset())
+        self._layer_to_group = self.cache_groups.layer_to_group()
+        self.tp_shard_count = tp_shard_count
         self.state_manager = state_manager if state_manager is not None else ServiceStateManager(client)
         self.instance_id, self.namespace, self.device_id = instance_id, namespace, device_id
         self.block_size, self.is_mla = block_size, is_mla
@@ -402,8 +447,42 @@ class PegaWorkerConnector:
     def start_load_kv_from_metadata(self, metadata, shard_index: int = 0):
         """Start every load the scheduler planned for this step (one lease per TP shard: this
         worker's shard consumes `leases[shard_index]`)."""
+        if self.cache_groups.group_count > 1:
+            return self._start_group_loads(metadata.load_intents, shard_index)
         self.start_load_kv([(req_id, intent.leases[shard_index], list(intent.block_ids_by_group[0]))
                             for req_id, intent in metadata.load_intents.items()])
+
+    def layer_groups(self) -> List[List[str]]:
+        """Registered layers by cache group, in registration order (worker.py:624-633)."""
+        groups: List[List[str]] = [[] for _ in range(self.cache_groups.group_count)]
+        for name in self.registered_layers:
+            groups[self._layer_to_group.get(name, 0)].append(name)
+        return groups
+
+    def _start_group_loads(self, load_intents, shard_index: int):
+        """Loads of a model with several cache groups (worker.py:571-684).  vLLM cannot recompute a
+        failed load for several groups, so a load that cannot be submitted raises after its leases went back."""
+        if not load_intents:
+            return
+        loads, all_ids, request_ids = plan_group_loads(load_intents, self.cache_groups, shard_index, self.tp_shard_count)
+        layer_groups = self.layer_groups()
+        if not all_ids or not any(layer_groups):
+            return
+        state = PyLoadState()
+        try:
+            ok, msg = self.client.load(self.instance_id, self.tp_rank, self.device_id, state.shm_name(), layer_groups, loads)
+        except Exception as e:
+            ok, msg = False, str(e)
+        if not ok:
+            for lease, _ in loads:
+                try:
+                    self.client.release(lease)
+                except Exception:
+                    pass
+            self.state_manager.mark_unavailable(f"load rpc failed: {msg}")
+            raise RuntimeError("PegaFlow HMA load failed; vLLM cannot recover failed loads for multiple cache groups: "
+                               f"{msg}")
+        self._pending_loads.append(_PendingLoad(state, request_ids, all_ids, time.perf_counter()))
 
     def wait_for_save_from_metadata(self, metadata):
         """Save what the scheduler marked as newly full this step: every registered layer stores the
@@ -412,8 +491,19 @@ class PegaWorkerConnector:
         intents = list(metadata.ready_save_intents.items()) + list(metadata.save_intents.items())
         saves = []
         for _req_id, intent in intents:
-            ids, hashes = list(intent.block_ids_by_group[0]), list(intent.block_hashes)
-            saves.extend((name, ids, hashes) for name in self.registered_layers)
+            hashes = list(intent.block_hashes)
+            per_group: Dict[int, List[int]] = {}
+            for name in self.registered_layers:
+                # worker.py:850-866: a layer saves the block ids of its own cache group
+                g = self._layer_to_group.get(name, 0)
+                if g not in per_group:
+                    if g >= len(intent.block_ids_by_group):
+                        raise RuntimeError(f"save intent is missing cache group {g} for {name}")
+                    per_group[g] = list(intent.block_ids_by_group[g])
+                    if len(per_group[g]) != len(hashes):
+                        raise RuntimeError(f"save block/hash count mismatch for {name}: blocks={len(per_group[g])} "
+                                           f"hashes={len(hashes)}")
+                saves.append((name, per_group[g], hashes))
         self.wait_for_save(saves)
         return {req_id for req_id, _ in intents}
 

@@ -1,0 +1,83 @@
+"""Loads of models with several cache groups: the worker mirror sends the engine exactly the load
+requests the reference's worker sends (tests/golden/worker_loads.json, recorded by
+tests/golden/gen_worker_loads.py), and refuses what it refuses with the same words.  Host logic
+only: the engine client is a recorder."""
+import json
+import os
+
+import pytest
+
+from tests import worker_load_cases as cases
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _start_load(layout, shard, shards, layers, intents, client):
+    pytest.importorskip("vllm")
+    from pegaflow_b200.config import CacheGroupLayout
+    from pegaflow_b200.connector import PegaWorkerConnector
+    from pegaflow_b200.scheduler import LoadIntent, PegaConnectorMetadata, RecurrentLoadHold
+
+    worker = PegaWorkerConnector(client, None, instance_id="inst", namespace="ns", device_id=0, block_size=16,
+                                 tp_rank=0, tp_size=1, cache_groups=CacheGroupLayout.from_config(cases.kv_cache_config(layout)),
+                                 tp_shard_count=shards)
+    worker.registered_layers = list(layers)
+    meta = PegaConnectorMetadata(load_intents=cases.build_intents(intents, LoadIntent, RecurrentLoadHold))
+    worker.start_load_kv_from_metadata(meta, shard_index=shard)
+    return worker
+
+
+def test_group_loads_match_the_reference_worker():
+    golden = json.load(open(os.path.join(HERE, "golden", "worker_loads.json")))
+    got = json.loads(json.dumps(cases.run_all(_start_load)))
+    assert sorted(got) == sorted(golden) and len(golden) >= 9
+    for name in golden:
+        assert got[name] == golden[name], f"{name}:\n{got[name]}\n{golden[name]}"
+    assert sum(1 for v in golden.values() if "error" in v) == 3
+    two = golden["second_shard_of_two_and_two_recurrent_groups"]["calls"][0]
+    assert [lease for lease, _ in two["loads"]] == ["p-s1", "g0-s1", "g1-s1"], "the second shard's leases"
+
+
+def test_a_group_load_that_cannot_be_submitted_raises_after_giving_the_leases_back():
+    """worker.py:650-684: with several cache groups vLLM cannot recompute a failed load."""
+    class Refusing(cases.RecordingClient):
+        def load(self, *a):
+            super().load(*a)
+            return False, "engine restarting"
+
+    client = Refusing()
+    with pytest.raises(RuntimeError, match="HMA load failed.*engine restarting"):
+        _start_load(*cases.CASES["one_request_with_checkpoint"], client)
+    assert [c["release"] for c in client.calls if "release" in c] == ["prefix-0", "mem-0"]
+
+
+def test_saves_take_each_layer_s_own_group_ids():
+    """worker.py:850-866: a layer saves the ids of its cache group; the null block (id 0) that pads a
+    recurrent group's positions before the state block is never saved."""
+    pytest.importorskip("vllm")
+    from pegaflow_b200.config import CacheGroupLayout
+    from pegaflow_b200.connector import PegaWorkerConnector
+    from pegaflow_b200.scheduler import PegaConnectorMetadata, SaveIntent
+
+    class Saver(cases.RecordingClient):
+        def save(self, instance_id, tp_rank, pp_rank, device_id, saves):
+            self.calls.append({"save": [(n, list(i), [bytes(h).decode() for h in hs]) for n, i, hs in saves]})
+            return True, ""
+
+        def flush_saves(self):
+            return True, ""
+
+    client = Saver()
+    worker = PegaWorkerConnector(client, None, instance_id="inst", namespace="ns", device_id=0, block_size=16,
+                                 cache_groups=CacheGroupLayout.from_config(cases.kv_cache_config("attn_mamba")))
+    worker.registered_layers = ["attn.0", "mamba.0", "attn.1"]
+    intent = SaveIntent(((13, 14, 15), (0, 0, 36)), (b"h3", b"h4", b"h5"))
+    done = worker.wait_for_save_from_metadata(PegaConnectorMetadata(ready_save_intents={"r": intent}))
+    assert done == {"r"}
+    (call,) = [c["save"] for c in client.calls if "save" in c]
+    assert call == [("attn.0", [13, 14, 15], ["h3", "h4", "h5"]), ("mamba.0", [36], ["h5"]),
+                    ("attn.1", [13, 14, 15], ["h3", "h4", "h5"])]
+    with pytest.raises(RuntimeError, match="missing cache group 1"):
+        worker.wait_for_save_from_metadata(PegaConnectorMetadata(save_intents={"r": SaveIntent(((1,),), (b"h",))}))
+    with pytest.raises(RuntimeError, match="count mismatch"):
+        worker.wait_for_save_from_metadata(PegaConnectorMetadata(save_intents={"r": SaveIntent(((1,), (2, 3)), (b"h",))}))
