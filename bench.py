@@ -9,14 +9,16 @@ A step is one pass of the hot path over one batch of synthetic input: the layer-
 Llama-3.1-8B shape of the baseline (32 layers, 8 KV heads x 128, bf16, block 16; 8 requests of
 10240 tokens = 640 blocks each at random block ids among 8192 GPU blocks; 10 GiB each way).
 With N > 1 every rank runs that workload on its own GPU, stream and pool (weak scaling, no
-data-path collective).
+data-path collective), in both arms; the b200 arm then adds a `peer` object: ranks N/2 .. N-1 act as
+a second instance and pull prefix hits from ranks 0 .. N/2-1 over NVLink, across processes.
 
 Prints ONE JSON line:  value = payload GB/s (10^9 B/s) with the KV cache resident in HBM,
 timed with CUDA events; e2e = the same metric through the engine's public API (save with
 hashes, prefix query, lease, load), host wall clock around a synchronised region.
 
 Other modes (each prints one JSON line of its own):
-    --workload W         the other baseline shapes (qwen3-0.6b, llama70b-tp8-rank, mla-bf16, mla-fp8, small)
+    --workload W         the other baseline shapes (qwen3-0.6b, llama70b-tp8-rank, mla-bf16, mla-fp8, small) and
+                         llama3.1-8b-crosslayer (the reference's default registration: one 2 MiB block per block id)
     --duplex             every step saves one set of blocks and loads another at the same time
     --peer [--peer-pairs K | --peer-local]
                          NVLink block copy between instances (GPU pairs, or both on one GPU)
@@ -52,6 +54,11 @@ def workloads():
     # segment); 1 = one segment per block with page-first host pages (one page per block holding every layer).
     return {
         "llama3.1-8b": dict(layers=32, seg_bytes=16 * 8 * 128 * 2, gpu_blocks=8192, requests=8, blocks=640, segments=2),
+        # the same model in the reference's default registration for non-MLA models: vLLM's cross-layer KV cache
+        # [num_blocks, layers, 2, 16, 8, 128] registered as ONE pseudo-layer whose block is every layer's K and V,
+        # 2 MiB (python/pegaflow/connector/__init__.py:67,170-171, worker.py:414-420); not page-first, direct backend
+        "llama3.1-8b-crosslayer": dict(layers=1, seg_bytes=32 * 2 * 16 * 8 * 128 * 2, gpu_blocks=8192, requests=8,
+                                       blocks=640, segments=1, page_first=False, mla=False),
         # Qwen3-0.6B round trip: 256 GPU blocks, 64 saved and loaded back into 64 other ids
         "qwen3-0.6b": dict(layers=28, seg_bytes=16 * 8 * 128 * 2, gpu_blocks=256, requests=1, blocks=64, segments=2),
         "small": dict(layers=4, seg_bytes=16 * 8 * 128 * 2, gpu_blocks=2048, requests=2, blocks=256, segments=2),
@@ -60,8 +67,10 @@ def workloads():
         "llama70b-tp8-rank": dict(layers=80, seg_bytes=16 * 1 * 128 * 2, gpu_blocks=16640, requests=4, blocks=2048,
                                   segments=2),
         # DeepSeek-V3-style latent cache [num_blocks, 64, 576], bf16 and fp8 byte widths
-        "mla-bf16": dict(layers=61, seg_bytes=64 * 576 * 2, gpu_blocks=1024, requests=1, blocks=256, segments=1),
-        "mla-fp8": dict(layers=61, seg_bytes=64 * 576 * 1, gpu_blocks=1024, requests=1, blocks=256, segments=1),
+        "mla-bf16": dict(layers=61, seg_bytes=64 * 576 * 2, gpu_blocks=1024, requests=1, blocks=256, segments=1,
+                         page_first=True, mla=True),
+        "mla-fp8": dict(layers=61, seg_bytes=64 * 576 * 1, gpu_blocks=1024, requests=1, blocks=256, segments=1,
+                        page_first=True, mla=True),
     }
 
 
@@ -138,9 +147,12 @@ def barrier_and_max(value, world, device):
     """Barrier, then the max of `value` over ranks (device-side all-reduce)."""
     if world == 1:
         return value
-    from pegaflow_b200 import sharding
+    import torch
+    import torch.distributed as dist
 
-    return sharding.barrier_and_max(value, device=device)
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
 
 
 def barrier(world):
@@ -293,8 +305,12 @@ def cpu_baseline(wl, seconds_budget=8.0):
     lib.pfr_free.argtypes = [C.c_void_p]
     spec = wl.spec
     seg, nb = spec["seg_bytes"], spec["gpu_blocks"]
-    n_layers = 2
+    n_layers = min(2, spec["layers"])
     ids = np.concatenate(wl.save_ids).astype(np.uint64)
+    # bounded sample: the host shadow of a layer is capped at 1 GiB, block ids wrap around inside it
+    nb_full, nb = nb, max(1, min(nb, (1 << 30) // (spec["segments"] * seg)))
+    if nb < nb_full:
+        ids = ids[: min(len(ids), 1024)] % nb
     n = len(ids)
     rng = np.random.default_rng(1)
     nseg = spec["segments"]
@@ -331,7 +347,9 @@ def cpu_baseline(wl, seconds_budget=8.0):
     lib.pfr_free(descs)
     return {"value": round(out[cores][0], 2), "unit": "GB/s", "cores": cores, "kind": "port",
             "single_core_value": round(out[1][0], 2), "descriptor_build_seconds_per_M": round(secs.value / nd.value * 1e6, 3),
-            "sample": f"{n_layers} of {spec['layers']} layers x {n} blocks (all requests), {nseg} segment(s) per block, "
+            "sample": f"{n_layers} of {spec['layers']} layers x {n} blocks"
+                      + (" (all requests)" if nb == nb_full else f" (ids wrapped into a {nb}-block shadow)")
+                      + f", {nseg} segment(s) per block, "
                       f"{payload / 2**20:.0f} MiB per pass, {out[cores][1]} passes, gather from a host shadow of the KV "
                       "cache into the pool layout with memcpy (save direction)"}
 
@@ -354,13 +372,41 @@ def ref_layer_type():
     return _REF_LAYER
 
 
-def run_reference(args, rank, world, local, launched_world=1):
+class RefPinned:
+    """Pinned, mapped host memory for the reference arm: one cudaHostAlloc(Mapped) region from
+    oracle/ref_path.cu (pinned_mem.rs:153-163) handed out by a bump pointer in 512-byte units
+    (the reference pool's default unit, pinned_pool.rs:135-141).  Nothing of the product is used."""
+
+    def __init__(self, lib, nbytes):
+        lib.pfr_host_alloc.argtypes = [C.c_size_t, C.POINTER(C.c_void_p), C.POINTER(C.c_uint64)]
+        lib.pfr_host_free.argtypes = [C.c_void_p]
+        host, dev = C.c_void_p(), C.c_uint64()
+        rc = lib.pfr_host_alloc(nbytes, C.byref(host), C.byref(dev))
+        if rc:
+            raise RuntimeError(f"cudaHostAlloc of {nbytes} bytes failed with CUDA error {rc}")
+        self.lib, self.host, self.dev, self.size, self.head = lib, host.value, dev.value, nbytes, 0
+
+    def alloc(self, nbytes):
+        off = self.head
+        self.head += -(-nbytes // 512) * 512
+        if self.head > self.size:
+            raise RuntimeError("reference arm: pinned region exhausted")
+        return self.host + off, self.dev + off, off
+
+    def close(self):
+        if self.host:
+            self.lib.pfr_host_free(C.c_void_p(self.host))
+            self.host = None
+
+
+def run_reference(args, rank, world, local):
     """The reference's own transfer path restated (oracle/ref_path.cu): descriptor build on one host
-    thread, its direct backend (one cudaMemcpyAsync per non-mergeable fragment), one sync per task."""
+    thread, its direct backend (one cudaMemcpyAsync per non-mergeable fragment), one sync per task.
+    Every rank of a torchrun launch runs it on its own GPU, as every rank of the reference has its own
+    GPU worker threads (gpu_worker.rs:131-201); the product library is not loaded."""
     import torch
     from oracle import build_ref
     from oracle import pf_oracle as po
-    import pegaflow_b200 as pf
 
     device = torch.device("cuda", local)
     spec = workloads()[args.workload]
@@ -375,7 +421,7 @@ def run_reference(args, rank, world, local, launched_world=1):
     lib.pfr_sync.argtypes = [C.c_void_p]
     seg, L = spec["seg_bytes"], spec["layers"]
     per = spec["blocks"]
-    pool = pf.PinnedPool(wl.payload + (64 << 20))
+    pool = RefPinned(lib, wl.payload + (64 << 20))
     images = alloc_host_images(pool, wl)
     stream = torch.cuda.Stream()
     tasks = []
@@ -420,7 +466,7 @@ def run_reference(args, rank, world, local, launched_world=1):
 
     # the reference picks its kernel backend for MLA models and the direct one otherwise
     # (python/pegaflow/connector/common.py:577-594)
-    use_kernel = wl.segments == 1 and bool(lib.pfr_has_reference_kernel())
+    use_kernel = bool(spec.get("mla")) and bool(lib.pfr_has_reference_kernel())
     for _ in range(args.warmup):
         step(use_kernel)
     torch.cuda.synchronize()
@@ -438,6 +484,8 @@ def run_reference(args, rank, world, local, launched_world=1):
     torch.cuda.synchronize()
     elapsed = barrier_and_max(time.perf_counter() - t0, world, device)
     clocks = sampler.stop() if rank == 0 else None
+    verified = verify_step(wl, lambda: step(use_kernel), torch, device)
+    verified = barrier_and_max(0.0 if verified else 1.0, world, device) == 0.0
     extra = {}
     if lib.pfr_has_reference_kernel() and world == 1:
         ks, kl = step(kernel=not use_kernel)
@@ -449,12 +497,13 @@ def run_reference(args, rank, world, local, launched_world=1):
             other["note"] = ("the reference's own NVRTC kernel source compiled unchanged, 1 CTA x 256 threads per "
                              "fragment, pageable descriptor upload")
             extra["reference_kernel_backend"] = other
+    pool.close()
     if rank != 0:
         return
     value = 2 * wl.payload * args.steps * world / elapsed / 1e9
     line = {
         "impl": "reference", "metric": "kv_save_load_GBps", "value": round(value, 3), "unit": "GB/s",
-        "n_gpus": launched_world, "ranks_measured": 1,
+        "n_gpus": world, "ranks_measured": world, "bit_exact": bool(verified),
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(elapsed / args.steps * 1e3, 3),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
         "config": {"workload": args.workload, **spec, "between_iterations": "inputs (10 GiB per direction) far exceed the 126 MB L2",
@@ -467,13 +516,48 @@ def run_reference(args, rank, world, local, launched_world=1):
         "frac_pcie_gen5_x16": round(value / world / PCIE_GEN5_X16_GBS, 4),
         "memcpy_calls_per_step": stats["calls"] // max(1, args.steps),
         "descriptor_build_ms_per_step": round(stats["build_s"] / max(1, args.steps) * 1e3, 2),
-        "cpu_baseline": {"value": round(value, 3), "unit": "GB/s", "cores": 1, "kind": "port",
-                         "sample": "full workload; the reference drives its copy engines from one host thread per "
-                                   "direction per GPU"},
+        "cpu_baseline": {"value": round(value, 3), "unit": "GB/s", "cores": world, "kind": "port",
+                         "sample": "full workload on every rank; the reference drives its copy engines from one host "
+                                   "thread per direction per GPU"},
         "e2e": {"value": round(value, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0, "clocks": clocks, **extra,
     }
     print(json.dumps(line))
+
+
+def verify_step(wl, run_step, torch, device):
+    """One more pass of the hot path, after the timed region, with every source block of every request
+    and layer snapshotted first: afterwards every destination block must hold its source block's bits."""
+    src = torch.from_numpy(np.concatenate(wl.save_ids).astype(np.int64)).to(device)
+    dst = torch.from_numpy(np.concatenate(wl.load_ids).astype(np.int64)).to(device)
+    snap = [kv[:, src].clone() for kv in wl.kv]
+    torch.cuda.synchronize()
+    run_step()
+    torch.cuda.synchronize()
+    ok = all(torch.equal(kv[:, dst], want) for kv, want in zip(wl.kv, snap))
+    del snap
+    return bool(ok)
+
+
+def pool_images_match_gpu(wl, allocs, torch, device):
+    """After a step's loads: for every request, layer and range, the destination blocks on the GPU equal
+    the host images in the pool (read here through a CPU view of the pinned bytes, not by the library)."""
+    seg, per = wl.spec["seg_bytes"], wl.spec["blocks"]
+    for r, ids in enumerate(wl.load_ids):
+        dst = torch.from_numpy(ids.astype(np.int64)).to(device)
+        for l, ranges in enumerate(allocs[r]):
+            for rng_i, (host, _dev, stride) in enumerate(ranges):
+                span = (per - 1) * stride + seg
+                view = np.ctypeslib.as_array((C.c_uint8 * span).from_address(host))
+                rows = np.lib.stride_tricks.as_strided(view, shape=(per, seg), strides=(stride, 1))
+                image = torch.from_numpy(np.ascontiguousarray(rows)).to(device)
+                if not torch.equal(wl.kv[l][rng_i][dst], image):
+                    return False
+    return True
+
+
+def spread(values):
+    return {"min": round(min(values), 3), "median": round(statistics.median(values), 3), "max": round(max(values), 3)}
 
 
 def time_gather_alone(args, pf, torch, local, route, wl, save_x, stream):
@@ -536,8 +620,8 @@ def build_roofline(stat_pairs, args, alone=None):
                     "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback",
                     "launches": pack_launches, "avg_launch_us": round(pack_ms / pack_launches * 1e3, 2),
                     "algorithmic_bytes_per_launch": pack_bytes // pack_launches,
-                    # DRAM bytes per launch: the ncu capture of a smaller case (8.398 MB read, 0 written per
-                    # 8.389 MB of payload: profiles/copy_group_ldst_small_full_set.md) scaled by payload
+                    # DRAM bytes per launch: an ncu capture of a smaller case of the same kernel (8.398 MB read,
+                    # 0 written per 8.389 MB of payload) scaled by payload
                     "traffic": args.traffic_per_launch if args.traffic_per_launch is not None
                     else round(pack_bytes / pack_launches / 2 * (8.398336 / 8.388608)),
                     "how": "one CUDA event pair around every launch, on the launching stream, inside the timed region"}
@@ -583,9 +667,12 @@ def run_b200(args, rank, world, local):
     import torch
     import pegaflow_b200 as pf
 
+    from pegaflow_b200 import sharding
+
     device = torch.device("cuda", local)
     spec = workloads()[args.workload]
-    wl = Workload(spec, device, 42 + 2 + rank)
+    plan = sharding.rank_plan(rank, world, n_layers=spec["layers"], payload_bytes_per_rank=0, local_rank=local)
+    wl = Workload(spec, device, plan.seed)
     L, seg, per, n_req = spec["layers"], spec["seg_bytes"], spec["blocks"], spec["requests"]
     if args.contiguous_ids:
         wl.save_ids = [np.arange(1 + r * per, 1 + (r + 1) * per, dtype=np.uint32) for r in range(n_req)]
@@ -616,16 +703,6 @@ def run_b200(args, rank, world, local):
         if events:
             events[2].record(stream)
 
-    # bit-exactness of the timed path itself: request 0, layer by layer, src rows == dst rows
-    be.save_layers(save_x[0], s)
-    stream.synchronize()
-    expected = [wl.kv[l][:, torch.from_numpy(wl.save_ids[0].astype(np.int64)).to(device)].clone() for l in (0, L - 1)]
-    be.load_layers(load_x[0], s)
-    stream.synchronize()
-    dst_idx = torch.from_numpy(wl.load_ids[0].astype(np.int64)).to(device)
-    verified = all(torch.equal(wl.kv[l][:, dst_idx], e) for l, e in zip((0, L - 1), expected))
-    del expected
-
     for _ in range(max(3, args.warmup) if not args.allow_short_warmup else args.warmup):
         step()
     stream.synchronize()
@@ -646,6 +723,11 @@ def run_b200(args, rank, world, local):
     load_ms = sum(e[1].elapsed_time(e[2]) for e in evs)
     total_ms = barrier_and_max(total_ms, world, device)
     st1 = be.stats()
+    # Bit-exactness of the timed path, every request and layer.  (a) The last timed step's loads: each
+    # destination block must hold what the pool held for it.  (b) One more step of the same calls with all
+    # source blocks snapshotted first: every destination block must hold its source block's bits.
+    verified = pool_images_match_gpu(wl, allocs, torch, device) and verify_step(wl, step, torch, device)
+    verified = barrier_and_max(0.0 if verified else 1.0, world, device) == 0.0
     # per-layer events on one request (diagnostic, outside the timed region)
     lev = [torch.cuda.Event(enable_timing=True) for _ in range(L + 1)]
     for e in lev:
@@ -664,7 +746,7 @@ def run_b200(args, rank, world, local):
     del save_x, load_x
     pool.close()
 
-    value = 2 * wl.payload * args.steps * world / (total_ms / 1e3) / 1e9
+    value = sharding.aggregate_throughput([2 * wl.payload * args.steps] * world, total_ms / 1e3)
     roofline = build_roofline([(st0, st1)], args, alone)
 
     # ---------------- end-to-end arm: the engine's public API ----------------------------------
@@ -675,6 +757,7 @@ def run_b200(args, rank, world, local):
     concurrent = concurrent_pcie_ceiling(device, world) if world > 1 else None
     barrier(world)
     ceiling = measure_pcie_ceiling(device) if rank == 0 else None
+    peer = peer_phase(args, pf, torch, rank, world, local) if world > 1 and not args.skip_peer else None
     cpu = None
     if rank == 0 and world == 1 and not args.skip_cpu_baseline:
         cpu = cpu_baseline(wl)
@@ -690,7 +773,13 @@ def run_b200(args, rank, world, local):
                    "between_iterations": "inputs (payload per direction per step far exceeds the 126 MB L2) are not "
                                          "re-read from cache; no flush needed",
                    "values": "bf16 N(0,1) from a seeded generator; block ids by seeded permutation without id 0"},
-        "save_gbs": round(save_gbs, 3), "load_gbs": round(load_gbs, 3), "bit_exact": bool(verified),
+        "save_gbs": round(save_gbs, 3), "load_gbs": round(load_gbs, 3),
+        "per_step": {"save_gbs": spread([wl.payload / 1e6 / e[0].elapsed_time(e[1]) for e in evs]),
+                     "load_gbs": spread([wl.payload / 1e6 / e[1].elapsed_time(e[2]) for e in evs]),
+                     "how": "rank 0, CUDA events around each timed step's saves and loads"},
+        "bit_exact": bool(verified),
+        "bit_exact_how": "every request and layer: the last timed step's destination blocks against the pool's host "
+                         "images, then one more step with all source blocks snapshotted first",
         "link": {"bound": "pcie_gen5_x16", "peak_theoretical": round(PCIE_GEN5_X16_GBS, 2),
                  "save_frac": round(save_gbs / PCIE_GEN5_X16_GBS, 4), "load_frac": round(load_gbs / PCIE_GEN5_X16_GBS, 4),
                  "measured_ceiling_d2h": round(ceiling["d2h"], 2), "measured_ceiling_h2d": round(ceiling["h2d"], 2),
@@ -704,7 +793,7 @@ def run_b200(args, rank, world, local):
                            "gbs": round(L * layer_bytes / 1e6 / all_layers_ms, 2),
                            "how": "per-layer completion events of one request: layer 0 is usable after "
                                   "first_layer_ms, the rest stream in behind it"},
-        "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
+        "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "peer": peer,
         "gpu_launches": (st1["kernel_launches"] - st0["kernel_launches"]),
         "dma_copies": (st1["dma_copies"] - st0["dma_copies"]), "device_status": st2["device_status"],
         "clocks": clocks,
@@ -871,7 +960,7 @@ def run_e2e(args, pf, wl, rank, world, local, route, duplex=False):
     eng.register_context_layer_batch_strided(
         "bench", "bench-ns", local, 0, 0, 1, 1, names, [wl.layer_ptr(l) for l in range(L)], [region] * L,
         [spec["gpu_blocks"]] * L, [seg] * L, [wl.kv_stride] * L, [wl.segments] * L, None, None,
-        "direct" if wl.segments == 2 else "kernel", wl.segments == 1)
+        "kernel" if spec.get("mla") else "direct", bool(spec.get("page_first")))
     prepared = []
     for k in range(steps_total):
         reqs = []
@@ -930,6 +1019,195 @@ def run_e2e(args, pf, wl, rank, world, local, route, duplex=False):
                    "arguments marshalled once outside the timed region; saves issued from two caller threads"
                    + ("; each step's saves overlap the loads of the step before" if duplex else ""),
             "evicted_blocks": m["evicted_blocks"], "load_failures": m["load_failures"]}
+
+
+def cuda_memcpy_async(dst_ptr, src_ptr, nbytes, stream):
+    """cudaMemcpyAsync(cudaMemcpyDefault) on raw device addresses (torch cannot wrap a pointer that was
+    opened from another process)."""
+    import torch  # noqa: F401  (has loaded the CUDA runtime this resolves to)
+
+    global _CUDART
+    if _CUDART is None:
+        for name in ("libcudart.so.12", "libcudart.so.13", "libcudart.so"):
+            try:
+                _CUDART = C.CDLL(name)
+                break
+            except OSError:
+                continue
+        else:
+            raise RuntimeError("the CUDA runtime library is not loadable by name")
+        _CUDART.cudaMemcpyAsync.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]
+    rc = _CUDART.cudaMemcpyAsync(C.c_void_p(dst_ptr), C.c_void_p(src_ptr), nbytes, 4, C.c_void_p(stream))
+    if rc:
+        raise RuntimeError(f"cudaMemcpyAsync failed with CUDA error {rc}")
+
+
+_CUDART = None
+
+
+def peer_phase(args, pf, torch, rank, world, local):
+    """Same-box prefix sharing between two instances that live in different processes (the baseline's
+    fifth configuration): ranks 0 .. N/2-1 are instance A, ranks N/2 .. N-1 instance B with the same TP degree.
+    Every A rank owns a Qwen3-32B TP4-shard-shaped KV cache (64 layers, 2 KV heads per rank -> 8 KiB K and
+    V segments, HND inside a block, 8192 blocks) and exports each layer's region (pf_ipc_export); the
+    rank-aligned B rank opens them (pf_ipc_open), and pulls 4096 blocks (50 % of the prefix) of every layer
+    into random block ids of its own cache with the peer-copy kernel - all pairs at the same time, no
+    collective on the data path.  Compared with the same blocks going through a pinned host pool, and with one
+    large device-to-device copy between the same two GPUs.  Returns the `peer` object on rank 0."""
+    import torch.distributed as dist
+    from pegaflow_b200 import _native as N
+
+    from pegaflow_b200 import sharding
+
+    half = world // 2
+    device = torch.device("cuda", local)
+    L, seg, nb, n = 64, 16 * 2 * 128 * 2, 8192, 4096
+    who = sharding.peer_role(rank, world)
+    role, pair = who.role, who.pair
+    payload = L * n * 2 * seg
+    gen = torch.Generator(device=device)
+
+    def source_layers(seed):
+        gen.manual_seed(seed)
+        for _ in range(L):
+            yield torch.randint(0, 256, (2, nb, seg), dtype=torch.uint8, device=device, generator=gen)
+
+    mine, kv, big = None, None, None
+    if role == "A":
+        kv = list(source_layers(5000 + pair))
+        big = torch.empty(1 << 30, dtype=torch.uint8, device=device)
+        regions = []
+        for t in kv + [big]:
+            r = N.IpcRegion()
+            N.check(N.lib.pf_ipc_export(t.data_ptr(), t.numel(), C.byref(r)))
+            regions.append(bytes(r))
+        torch.cuda.synchronize()
+        mine = regions
+    everyone = [None] * world
+    dist.all_gather_object(everyone, mine)
+    result = None
+    if role == "B":
+        regions = [N.IpcRegion.from_buffer_copy(b) for b in everyone[pair]]
+        src_ptrs, src_dev = [], None
+        for r in regions:
+            ptr, dev_id = C.c_uint64(), C.c_int()
+            N.check(N.lib.pf_ipc_open(C.byref(r), C.byref(ptr), C.byref(dev_id)))
+            src_ptrs.append(ptr.value)
+            src_dev = dev_id.value
+        pf.enable_peer_access(local, src_dev)
+        torch.cuda.set_device(local)
+        dst = [torch.zeros((2, nb, seg), dtype=torch.uint8, device=device) for _ in range(L)]
+        rng = np.random.default_rng(4200 + pair)
+        sids = (rng.permutation(nb - 1)[:n] + 1).astype(np.uint32)
+        dids = (rng.permutation(nb - 1)[:n] + 1).astype(np.uint32)
+        si = torch.from_numpy(sids.astype(np.int64)).to(device)
+        di = torch.from_numpy(dids.astype(np.int64)).to(device)
+        be = pf.TransferBackend(local, link_ctas=args.link_ctas)
+        stream = torch.cuda.Stream()
+        sl = [(p_, seg, nb * seg, seg, 2) for p_ in src_ptrs[:L]]
+        dl = [(t.data_ptr(), seg, nb * seg, seg, 2) for t in dst]
+
+        def exact():
+            """Every layer: destination blocks hold the source blocks (regenerated here from A's seed), every
+            other block is still zero."""
+            ok = True
+            for t, want_src in zip(dst, source_layers(5000 + pair)):
+                want = torch.zeros_like(t)
+                want[:, di] = want_src[:, si]
+                ok = ok and torch.equal(t, want)
+                del want, want_src
+            return ok
+
+        for _ in range(3):
+            be.peer_copy_layers(sl, sids, dl, dids, stream.cuda_stream)
+        stream.synchronize()
+    dist.barrier()          # all pairs start their timed copies together
+    if role == "B":
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(args.steps):
+            be.peer_copy_layers(sl, sids, dl, dids, stream.cuda_stream)
+        b.record(stream)
+        b.synchronize()
+        peer_ms = a.elapsed_time(b)
+    dist.barrier()
+    if role == "B":
+        peer_exact = exact()
+        stats = be.stats()
+        # ceiling: one 1 GiB device-to-device copy from the same peer GPU, best of 5, all pairs at once
+        scratch = torch.empty(1 << 30, dtype=torch.uint8, device=device)
+        best = 0.0
+        for _ in range(6):
+            a.record(stream)
+            cuda_memcpy_async(scratch.data_ptr(), src_ptrs[L], 1 << 30, stream.cuda_stream)
+            b.record(stream)
+            b.synchronize()
+            best = max(best, (1 << 30) / 1e6 / a.elapsed_time(b))
+        del scratch
+        # the reference's way: source GPU -> pinned host pool -> destination GPU, driven from this process
+        for t in dst:
+            t.zero_()
+        pool = pf.PinnedPool(payload + (64 << 20), numa_node=pf.numa_node_of_device(local))
+        be_src, be_dst = pf.TransferBackend(src_dev), pf.TransferBackend(local)
+        st_src = torch.cuda.Stream(device=torch.device("cuda", src_dev))
+        lay_s, lay_l = [], []
+        for l in range(L):
+            k, v = pool.alloc(n * seg), pool.alloc(n * seg)
+            runs = [[pf.HostRun(0, n, k[0], k[1], seg)], [pf.HostRun(0, n, v[0], v[1], seg)]]
+            lay_s.append(pf.LayerXfer(src_ptrs[l], seg, nb * seg, seg, 2, sids, runs))
+            lay_l.append(pf.LayerXfer(dst[l].data_ptr(), seg, nb * seg, seg, 2, dids, runs))
+        xs, xl = pf.TransferBackend.make_layers(lay_s), pf.TransferBackend.make_layers(lay_l)
+        t_host = []
+        for _ in range(3):
+            torch.cuda.synchronize(device)
+            t0 = time.perf_counter()
+            be_src.save_layers(xs, st_src.cuda_stream)
+            st_src.synchronize()
+            be_dst.load_layers(xl, stream.cuda_stream)
+            stream.synchronize()
+            t_host.append(time.perf_counter() - t0)
+        host_exact = exact()
+        status = stats["device_status"] | be_src.stats()["device_status"] | be_dst.stats()["device_status"]
+        be.close(), be_src.close(), be_dst.close(), pool.close()
+        for r in regions:
+            N.check(N.lib.pf_ipc_close(C.byref(r)))
+        result = {"pair": [src_dev, local], "ranks": [pair, rank], "GBps": round(payload * args.steps / 1e6 / peer_ms, 2),
+                  "ceiling_GBps": round(best, 1), "via_host_pool_GBps": round(payload / min(t_host) / 1e9, 2),
+                  "bit_exact": bool(peer_exact), "via_host_pool_bit_exact": bool(host_exact),
+                  "ms": peer_ms, "gpu_launches": stats["kernel_launches"], "device_status": status}
+        del dst
+    results = [None] * world
+    dist.all_gather_object(results, result)
+    dist.barrier()          # instance A keeps its memory until every B rank has closed its mappings
+    del kv, big
+    torch.cuda.empty_cache()
+    if rank != 0:
+        return None
+    rs = [r for r in results if r]
+    agg = sum(payload * args.steps for _ in rs) / 1e6 / max(r["ms"] for r in rs)
+    ceil_sum = sum(r["ceiling_GBps"] for r in rs)
+    return {
+        "config": {"workload": "qwen3-32b-tp4-rank prefix hit across instances", "layers": L, "seg_bytes": seg, "gpu_blocks": nb,
+                   "blocks": n, "segments": 2, "payload_bytes_per_pair": payload,
+                   "instances": "A = ranks 0..%d, B = ranks %d..%d, one process per GPU; B reaches A's KV cache through "
+                                "pf_ipc_export / pf_ipc_open" % (half - 1, half, 2 * half - 1),
+                   "kernel_runs_on": "destination GPU (pull)"},
+        "pairs": [r["pair"] for r in rs], "per_pair_GBps": [r["GBps"] for r in rs], "aggregate_GBps": round(agg, 2),
+        "link": {"bound": "nvlink5", "peak_nominal_per_direction": 900.0,
+                 "measured_ceiling_per_pair": [r["ceiling_GBps"] for r in rs],
+                 "frac_of_nominal": round(agg / (900.0 * len(rs)), 4), "frac_of_ceiling": round(agg / ceil_sum, 4),
+                 "ceiling_how": "one 1 GiB device-to-device cudaMemcpyAsync from the same peer GPU, best of 6, every pair's "
+                                "own measurement"},
+        "via_host_pool_GBps": [r["via_host_pool_GBps"] for r in rs],
+        "speedup_vs_host_pool": round(agg / max(1e-9, sum(r["via_host_pool_GBps"] for r in rs)), 2),
+        "bit_exact": all(r["bit_exact"] and r["via_host_pool_bit_exact"] for r in rs),
+        "bit_exact_how": "all 64 layers of every pair, whole destination cache compared (copied blocks against the source "
+                         "regenerated from its seed, all other blocks still zero), after the peer copy and again after the "
+                         "host-pool route",
+        "gpu_launches": sum(r["gpu_launches"] for r in rs), "device_status": max(r["device_status"] for r in rs),
+        "how": "per pair: CUDA events on the destination rank's stream around `steps` calls of pf_backend_peer_copy_layers, "
+               "all pairs released by one barrier; aggregate = all pairs' bytes / the slowest pair's time"}
+
 
 
 def peer_pairs_phase(pf, torch, n_pairs, args, L, seg, nb, n):
@@ -1552,6 +1830,7 @@ def main():
     ap.add_argument("--contiguous-ids", action="store_true", help="diagnostic: block ids in ascending order")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
+    ap.add_argument("--skip-peer", action="store_true", help="N > 1: leave the cross-instance NVLink phase out")
     ap.add_argument("--allow-short-warmup", action="store_true", help="profiling runs only")
     ap.add_argument("--traffic-per-launch", type=float, default=None,
                     help="DRAM bytes per launch of the dominant kernel from an ncu capture (recorded in the line)")
@@ -1596,18 +1875,12 @@ def main():
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
                "--master-addr", "127.0.0.1", "--master-port", "29531", os.path.abspath(__file__)] + sys.argv[1:]
         os.execv(sys.executable, cmd)
-    if args.impl == "reference":
-        # Rank 0 alone runs the reference arm; other ranks of a torchrun launch leave at once.
-        if int(os.environ.get("RANK", "0")) == 0:
-            import torch
-
-            local = int(os.environ.get("LOCAL_RANK", "0"))
-            torch.cuda.set_device(local)
-            run_reference(args, 0, 1, local, launched_world=world_env)
-        return
     rank, world, local = dist_setup(args.gpus)
     try:
-        (run_duplex if args.duplex else run_b200)(args, rank, world, local)
+        if args.impl == "reference":
+            run_reference(args, rank, world, local)
+        else:
+            (run_duplex if args.duplex else run_b200)(args, rank, world, local)
     except BaseException:
         # Leave at once: a clean process-group shutdown would wait for the other ranks, and the
         # launcher only stops them when it sees this rank die.

@@ -182,6 +182,8 @@ typedef struct pf_device_layout {
   size_t kv_stride_bytes;
   size_t range_bytes;
   uint32_t n_ranges;
+  size_t num_blocks; /* blocks in the cache; when non-zero every block id is checked against it
+                        before anything is launched, 0 = the caller vouches for the ids */
 } pf_device_layout;
 int pf_backend_peer_copy(pf_backend *backend, const pf_device_layout *src, const uint32_t *src_ids,
                          const pf_device_layout *dst, const uint32_t *dst_ids, size_t n_blocks,
@@ -217,16 +219,21 @@ int pf_enable_peer_access(int device_id, int peer_device);
  * device-wide synchronisation of cudaMalloc/cudaFree, or code running while a stream is being
  * captured elsewhere in the process.  Blocks block_ids[0..n_blocks) of `layout` (memory of
  * `device_id`) are gathered into a staging area that is part of the library image and copied to
- * host_dst, which must be page-locked for the copy to be asynchronous: range 0 of every block
- * back to back, then range 1 of every block (the image pf_backend_save_layers writes for one
- * dense host run per range).  Everything is enqueued on `stream`; nothing is synchronised.
+ * host_dst: range 0 of every block back to back, then range 1 of every block (the image
+ * pf_backend_save_layers writes for one dense host run per range).  The work is enqueued on
+ * `stream` and the call does not wait for it.  It is fully asynchronous only when both
+ * `block_ids` and `host_dst` are page-locked: from ordinary pageable memory the runtime stages
+ * the id upload itself and may hold the call until earlier work on the stream has finished.
+ * With layout->num_blocks set, an id outside the cache is PF_INVALID_ARGUMENT and nothing is
+ * launched; with 0 the ids are not checked and an id outside the cache reads outside it.
  *
  * No cudaMalloc, cudaFree, stream, event or other allocating call is made.  Limits: at most
  * PF_NOALLOC_MAX_BLOCKS blocks and PF_NOALLOC_MAX_PAYLOAD_BYTES bytes per call, otherwise
  * PF_INVALID_ARGUMENT.  The staging area (PF_NOALLOC_MAX_PAYLOAD_BYTES plus 4 bytes per block
  * id) is static device memory: each GPU that loads the library holds it until the process
- * ends.  The first call on a device looks the area's address up (cudaGetSymbolAddress with
- * that device current), so make that first call before any stream capture starts.  All calls
+ * ends.  The first call on a device (an empty batch counts) looks the area's address up
+ * (cudaGetSymbolAddress with that device current), so make that first call before any stream
+ * capture starts.  All calls
  * on one device share the area and it keeps the previous call's bytes; nothing in it needs
  * clearing between calls, but two calls whose GPU work overlaps (different streams) race. */
 #define PF_NOALLOC_MAX_PAYLOAD_BYTES (8u << 20)
@@ -278,9 +285,40 @@ int pf_pool_release(pf_pool *pool, uint64_t handle);
 /* pinned_pool.rs:293-299 `usage`. */
 int pf_pool_usage(pf_pool *pool, uint64_t *used, uint64_t *total, uint64_t *largest_free);
 
-/* pegaflow-common/src/numa.rs:344-411: NUMA node of a CUDA device (-1 unknown) and node count. */
+/* pinned_mem.rs:378-391 `touch_threads`: workers that pre-touch an mmap-backed pool of `bytes`
+ * bytes (one per GiB, rounded up, at most the CPUs the process may run on); and the kernel's
+ * huge page size in bytes from /proc/meminfo, 0 when unknown (`read_hugepage_size_from_proc`). */
+size_t pf_pool_pre_touch_threads(size_t bytes);
+size_t pf_huge_page_size(void);
+
+/* NUMA helpers (pegaflow-common/src/numa.rs).  Node ids are plain ints, -1 = unknown
+ * (`NumaNode::UNKNOWN`).  The topology is read from sysfs; the tree's root is /sys unless the
+ * environment variable PEGAFLOW_SYSFS_ROOT or pf_numa_set_sysfs_root names another one (NULL or
+ * "" restores /sys) - for containers that mount it elsewhere and for tests. */
+int pf_numa_set_sysfs_root(const char *root);
+/* numa.rs:344-411 `NumaTopology::numa_for_gpu` / `num_nodes`. */
 int pf_numa_node_of_device(int device_id);
 int pf_numa_num_nodes(void);
+/* numa.rs:129-168 `parse_cpulist`: "0-2,8,16-17" -> 0,1,2,8,16,17 (sorted, each once).  *n is
+ * always the number of CPUs; PF_INVALID_ARGUMENT for malformed text or when they do not fit. */
+int pf_numa_parse_cpulist(const char *text, int *cpus_out, size_t capacity, size_t *n);
+/* numa.rs:88-126 `read_cpu_topology_from_sysfs`, one node: empty when the node is unknown. */
+int pf_numa_cpus_of_node(int node, int *cpus_out, size_t capacity, size_t *n);
+/* numa.rs:178-218 `pin_thread_to_numa_node`: restricts the calling thread to the node's CPUs;
+ * PF_INVALID_ARGUMENT with the reference's message ("Cannot pin to unknown NUMA node", "No CPUs
+ * found for NUMA node N", ...) otherwise. */
+int pf_numa_pin_thread_to_node(int node);
+/* Node of a PCI device ("0000:1b:00.0") from <root>/bus/pci/devices/<id>/numa_node; the
+ * reference asks the driver's tool instead (numa.rs:266-291), whose answer this parses
+ * (numa.rs:293-302 `parse_closest_cpu_numa_node`: the first id listed). */
+int pf_numa_node_of_pci_device(const char *bus_id);
+int pf_numa_parse_closest_cpu_node(const char *text);
+/* numa.rs:392-402 `gpu_numa_nodes`: the known entries of a device -> node list, sorted, each
+ * once.  nodes_out needs room for n_devices entries. */
+int pf_numa_distinct_valid_nodes(const int *device_nodes, size_t n_devices, int *nodes_out, size_t *n);
+/* numa.rs:441-497 `query_pages_numa`: node on which the page of each address lives (-1 when it
+ * is not resident or the query fails). */
+int pf_numa_query_pages(const void *const *addrs, size_t n, int *nodes_out);
 
 /* ------------------------------------------------------------------------------------------
  * 3. Engine boundary.  Replaces `PegaEngine` (pegaflow-core/src/lib.rs:113-126).

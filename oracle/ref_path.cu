@@ -146,6 +146,26 @@ int pfr_submit_kernel(const pfo_copy_desc *descs, size_t n, int host_is_src, voi
 #endif
 }
 
+/* pinned_mem.rs:153-163 `allocate_cuda_host_alloc`: the pool's default backing, one
+ * cudaHostAlloc(Mapped) region and its device-visible address.  The reference arm of the
+ * benchmark carves its host images out of this region with a bump pointer, so that it does not
+ * depend on the product library for anything. */
+int pfr_host_alloc(size_t bytes, void **host, uint64_t *host_device) {
+  void *p = NULL, *d = NULL;
+  cudaError_t e = cudaHostAlloc(&p, bytes, cudaHostAllocMapped);
+  if (e != cudaSuccess) return (int)e;
+  e = cudaHostGetDevicePointer(&d, p, 0);
+  if (e != cudaSuccess) {
+    cudaFreeHost(p);
+    return (int)e;
+  }
+  *host = p;
+  *host_device = (uint64_t)(uintptr_t)d;
+  return 0;
+}
+
+int pfr_host_free(void *host) { return (int)cudaFreeHost(host); }
+
 /* gpu_worker.rs:444-449: record an event on the stream and wait for it. */
 int pfr_sync(void *stream) {
   cudaEvent_t ev;

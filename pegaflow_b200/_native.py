@@ -60,7 +60,7 @@ class LayerXfer(C.Structure):
 
 class DeviceLayout(C.Structure):
     _fields_ = [("data_ptr", u64), ("block_stride_bytes", sz), ("kv_stride_bytes", sz), ("range_bytes", sz),
-                ("n_ranges", u32)]
+                ("n_ranges", u32), ("num_blocks", sz)]
 
 
 class BackendStats(C.Structure):
@@ -144,6 +144,16 @@ _sig("pf_pool_release", C.c_int, vp, u64)
 _sig("pf_pool_usage", C.c_int, vp, P(u64), P(u64), P(u64))
 _sig("pf_numa_node_of_device", C.c_int, C.c_int)
 _sig("pf_numa_num_nodes", C.c_int)
+_sig("pf_numa_set_sysfs_root", C.c_int, C.c_char_p)
+_sig("pf_numa_parse_cpulist", C.c_int, C.c_char_p, P(C.c_int), sz, P(sz))
+_sig("pf_numa_cpus_of_node", C.c_int, C.c_int, P(C.c_int), sz, P(sz))
+_sig("pf_numa_pin_thread_to_node", C.c_int, C.c_int)
+_sig("pf_numa_node_of_pci_device", C.c_int, C.c_char_p)
+_sig("pf_numa_parse_closest_cpu_node", C.c_int, C.c_char_p)
+_sig("pf_numa_distinct_valid_nodes", C.c_int, P(C.c_int), sz, P(C.c_int), P(sz))
+_sig("pf_numa_query_pages", C.c_int, P(vp), sz, P(C.c_int))
+_sig("pf_pool_pre_touch_threads", sz, sz)
+_sig("pf_huge_page_size", sz)
 _sig("pf_engine_new", C.c_int, sz, C.c_int, P(StorageConfig), P(vp))
 _sig("pf_engine_free", None, vp)
 _sig("pf_engine_register_context_layer_batch_strided", C.c_int, vp, C.c_char_p, C.c_char_p, C.c_int, sz, sz, sz,

@@ -151,7 +151,7 @@ class TransferBackend:
         N.check(N.lib.pf_backend_gather_layers(self._h, arr, n, C.c_void_p(stream or None)))
 
     def peer_copy(self, src_layout, src_ids, dst_layout, dst_ids, stream: int = 0):
-        """layouts: (data_ptr, block_stride_bytes, kv_stride_bytes, range_bytes, n_ranges)."""
+        """layouts: (data_ptr, block_stride_bytes, kv_stride_bytes, range_bytes, n_ranges[, num_blocks])."""
         import numpy as np
 
         n = len(src_ids)
@@ -204,9 +204,10 @@ def save_blocks_noalloc(device_id: int, layout, block_ids, host_dst: int, host_d
     tolerance for cudaMalloc's device-wide synchronisation, a stream capture in progress).  The
     staging area lives inside the library image; at most ``NOALLOC_MAX_BLOCKS`` blocks and
     ``NOALLOC_MAX_PAYLOAD_BYTES`` bytes per call.  ``layout`` is (data_ptr, block_stride_bytes,
-    kv_stride_bytes, range_bytes, n_ranges); ``host_dst`` should be page-locked.  Calls on one device
-    share the staging area: do not let their GPU work overlap.  Make the first call on a device
-    before any stream capture."""
+    kv_stride_bytes, range_bytes, n_ranges[, num_blocks]); with ``num_blocks`` given, ids outside
+    the cache are rejected before anything is launched.  ``host_dst`` should be page-locked.  Calls
+    on one device share the staging area: do not let their GPU work overlap.  Make the first call
+    on a device (an empty batch will do) before any stream capture."""
     n = len(block_ids)
     ids = (C.c_uint32 * max(1, n))(*[int(b) for b in block_ids])
     lay = N.DeviceLayout(*layout)

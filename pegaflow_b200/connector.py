@@ -523,6 +523,9 @@ class PegaWorkerConnector:
         done, still = [], []
         failed, self._rejected_loads = self._rejected_loads, []
         now = time.perf_counter()
+        multi_group = self.cache_groups.group_count > 1
+        hma_failure = None
+        timed_out = False
         for p in self._pending_loads:
             st = p.state.get_state()
             if st == 0 and now - p.started <= self.LOAD_TIMEOUT_SECONDS:
@@ -530,17 +533,31 @@ class PegaWorkerConnector:
                 continue
             if st == 1:
                 done.extend(p.request_ids)
+            elif multi_group:
+                # worker.py:467-470, 499-503: vLLM cannot recompute a partial load of several cache groups,
+                # so such a failure is not reported as invalid blocks; it ends the step (below)
+                if st == 0:
+                    hma_failure = f"load timed out for requests {sorted(p.request_ids)} after {now - p.started:.1f}s"
+                else:
+                    hma_failure = f"async load failed for requests {sorted(p.request_ids)}: state={st}"
+                done.extend(p.request_ids)
             else:
                 # failed, or (worker.py:454-507) pending for longer than the timeout: the requests are
                 # handed back as received and their blocks are reported invalid, so that vLLM recomputes
                 # them instead of waiting for ever
                 failed.extend(p.request_ids)
                 self._load_errors.update(p.block_ids)
-                if st == 0:
-                    self.state_manager.mark_unavailable("load timeout")   # worker.py:522-523
+            timed_out = timed_out or st == 0
             self.load_history.append((now - p.started, len(p.block_ids), st == 1))
         self._pending_loads = still
         del self.load_history[:-1024]
+        if timed_out:
+            self.state_manager.mark_unavailable("load timeout")   # worker.py:522-523
+        if hma_failure is not None:
+            # worker.py:534-539
+            self.state_manager.mark_unavailable(hma_failure)
+            raise RuntimeError("PegaFlow HMA load failed; vLLM cannot recover failed loads for multiple cache groups: "
+                               f"{hma_failure}")
         return done, failed
 
     def get_block_ids_with_load_errors(self) -> set:

@@ -134,8 +134,58 @@ int pf_pool_usage(pf_pool *pool, uint64_t *used, uint64_t *total, uint64_t *larg
   });
 }
 
+size_t pf_pool_pre_touch_threads(size_t bytes) { return pre_touch_threads(bytes); }
+size_t pf_huge_page_size(void) { return huge_page_size(); }
+
+// ---- NUMA ----------------------------------------------------------------------------------------
+namespace {
+void copy_ints(const std::vector<int> &v, int *out, size_t capacity, size_t *n) {
+  if (!n) throw Error::invalid("n is null");
+  *n = v.size();
+  if (v.size() > capacity) throw Error::invalid(strf("%zu entries do not fit a buffer of %zu", v.size(), capacity));
+  for (size_t i = 0; i < v.size(); ++i) out[i] = v[i];
+}
+}  // namespace
+
 int pf_numa_node_of_device(int device_id) { return numa::node_of_device(device_id); }
 int pf_numa_num_nodes(void) { return (int)numa::online_nodes().size(); }
+int pf_numa_set_sysfs_root(const char *root) {
+  return guarded([&] { numa::set_sysfs_root(root ? root : ""); });
+}
+int pf_numa_parse_cpulist(const char *text, int *cpus_out, size_t capacity, size_t *n) {
+  return guarded([&] {
+    if (!text) throw Error::invalid("text is null");
+    try {
+      copy_ints(numa::parse_cpulist(text), cpus_out, capacity, n);
+    } catch (const std::invalid_argument &e) {
+      throw Error::invalid(e.what());
+    }
+  });
+}
+int pf_numa_cpus_of_node(int node, int *cpus_out, size_t capacity, size_t *n) {
+  return guarded([&] { copy_ints(numa::cpus_of_node(node), cpus_out, capacity, n); });
+}
+int pf_numa_pin_thread_to_node(int node) {
+  return guarded([&] {
+    const std::string why = numa::pin_thread_to_node_why(node);
+    if (!why.empty()) throw Error::invalid(why);
+  });
+}
+int pf_numa_node_of_pci_device(const char *bus_id) { return bus_id ? numa::node_of_pci_device(bus_id) : numa::kUnknown; }
+int pf_numa_parse_closest_cpu_node(const char *text) { return text ? numa::parse_closest_cpu_node(text) : numa::kUnknown; }
+int pf_numa_distinct_valid_nodes(const int *device_nodes, size_t n_devices, int *nodes_out, size_t *n) {
+  return guarded([&] {
+    if (n_devices && !device_nodes) throw Error::invalid("device_nodes is null");
+    copy_ints(numa::distinct_valid_nodes(std::vector<int>(device_nodes, device_nodes + n_devices)), nodes_out, n_devices, n);
+  });
+}
+int pf_numa_query_pages(const void *const *addrs, size_t n, int *nodes_out) {
+  return guarded([&] {
+    if (n && (!addrs || !nodes_out)) throw Error::invalid("null argument");
+    const std::vector<int> nodes = numa::query_pages(std::vector<const void *>(addrs, addrs + n));
+    for (size_t i = 0; i < n; ++i) nodes_out[i] = nodes[i];
+  });
+}
 
 // ---- engine --------------------------------------------------------------------------------------
 int pf_engine_new(size_t pool_bytes, int use_hugepages, const pf_storage_config *config, pf_engine **out) {

@@ -631,6 +631,9 @@ void Engine::batch_save(const std::string &instance_id, size_t tp_rank, size_t p
   const bool blockwise = cfg_.blockwise_alloc != 0 && !page_first;
   auto work = std::make_shared<std::vector<LayerWork>>();
   auto all_allocs = std::make_shared<std::vector<std::shared_ptr<PinnedAllocation>>>();
+  // Everything the GPU copy writes into: the worker's task holds it, so the pool ranges outlive the
+  // copy even when this call unwinds early.
+  auto copy_targets = std::make_shared<std::vector<std::shared_ptr<PinnedAllocation>>>();
   std::vector<std::shared_ptr<PinnedAllocation>> pages;
   // allocs[c][a] = (K-or-whole, V) allocation a of layer context c
   std::vector<std::vector<std::array<std::shared_ptr<PinnedAllocation>, 2>>> layer_allocs(ctxs.size());
@@ -657,6 +660,7 @@ void Engine::batch_save(const std::string &instance_id, size_t tp_rank, size_t p
     if (page_size == 0) throw Error::storage("page size is zero");
     pages.reserve(ctxs[0].ids.size());
     for (size_t i = 0; i < ctxs[0].ids.size(); ++i) pages.push_back(allocate(page_size, numa_node, "page"));
+    *copy_targets = pages;
     for (auto &c : ctxs) {
       const size_t layer_id = topo->layer_id(c.name);
       const size_t offset = topo->page->layer_offsets[layer_id];
@@ -701,6 +705,8 @@ void Engine::batch_save(const std::string &instance_id, size_t tp_rank, size_t p
           else
             runs.push_back(pf_host_run{a * per, per, pair[r]->host(), pair[r]->device(), stride});
         }
+        copy_targets->push_back(pair[0]);
+        if (split) copy_targets->push_back(pair[1]);
         if (!blockwise) {
           all_allocs->push_back(pair[0]);
           if (split) all_allocs->push_back(pair[1]);
@@ -751,6 +757,7 @@ void Engine::batch_save(const std::string &instance_id, size_t tp_rank, size_t p
       if (ready_event) cuda_or_storage(cudaStreamWaitEvent(stream, ready_event, 0), "cudaStreamWaitEvent");
       backend.move_layers(xf.data(), xf.size(), false, stream, nullptr);
       cuda_or_storage(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
+      (void)copy_targets;
       if (async) hand_over();
       done->set_value();
     } catch (const std::exception &e) {
@@ -1228,8 +1235,10 @@ void Engine::peer_load(const std::string &src_instance, int src_device, const st
         throw Error::invalid(strf("block_id %zu out of range (num_blocks=%zu) for layer %s", dst_ids[i], b.num_blocks(),
                                   kv.first.c_str()));
     }
-    pairs->push_back(Pair{{a.data_ptr(), a.block_stride_bytes(), a.kv_stride_bytes(), a.range_bytes(), a.n_ranges()},
-                          {b.data_ptr(), b.block_stride_bytes(), b.kv_stride_bytes(), b.range_bytes(), b.n_ranges()}});
+    pairs->push_back(Pair{{a.data_ptr(), a.block_stride_bytes(), a.kv_stride_bytes(), a.range_bytes(), a.n_ranges(),
+                           a.num_blocks()},
+                          {b.data_ptr(), b.block_stride_bytes(), b.kv_stride_bytes(), b.range_bytes(), b.n_ranges(),
+                           b.num_blocks()}});
   }
   if (pairs->empty()) throw Error::invalid("the two instances share no layer name");
   for (size_t v : src_ids) sids->push_back((uint32_t)v);

@@ -1,10 +1,14 @@
 #include "pinned_pool.h"
 
 #include <cuda_runtime.h>
+#include <sched.h>
 #include <sys/mman.h>
 #include <unistd.h>
 
 #include <algorithm>
+#include <cstdio>
+#include <fstream>
+#include <string>
 #include <thread>
 
 #include "layout.h"
@@ -17,26 +21,50 @@ std::string cuda_msg(const char *what, cudaError_t e) {
   return strf("%s failed: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
 }
 
-// Touch one byte per page from several threads bound to `node`, so that the kernel places
-// the pages there before cudaHostRegister pins them (pinned_mem.rs:343-391: about one thread
-// per GiB, never more than the CPUs available).
+// Touch one byte per page (and the last byte) from several threads bound to `node`, so that the
+// kernel places the pages there before cudaHostRegister pins them (pinned_mem.rs:343-391).
 void parallel_pre_touch(char *ptr, size_t bytes, size_t page, int node) {
-  size_t want = std::max<size_t>(1, bytes >> 30);
-  size_t cpus = node >= 0 ? numa::cpus_of_node(node).size() : 0;
-  if (cpus == 0) cpus = std::max<long>(1, sysconf(_SC_NPROCESSORS_ONLN));
-  const size_t n_threads = std::min(want, cpus);
-  const size_t pages = (bytes + page - 1) / page;
+  const size_t n_threads = pre_touch_threads(bytes);
+  const size_t chunk = (bytes + n_threads - 1) / n_threads;
   std::vector<std::thread> threads;
   for (size_t t = 0; t < n_threads; ++t) {
+    const size_t off = t * chunk;
+    if (off >= bytes) break;
+    const size_t len = std::min(chunk, bytes - off);
     threads.emplace_back([=] {
       if (node >= 0) numa::pin_thread_to_node(node);
-      const size_t first = pages * t / n_threads, last = pages * (t + 1) / n_threads;
-      for (size_t p = first; p < last; ++p) ((volatile char *)ptr)[p * page] = 0;
+      volatile char *p = ptr + off;
+      for (size_t o = 0; o < len; o += page) p[o] = 0;
+      p[len - 1] = 0;
     });
   }
   for (auto &t : threads) t.join();
 }
 }  // namespace
+
+// pinned_mem.rs:378-391 `touch_threads`: one worker per GiB (rounded up), never more than the
+// CPUs this process may run on.
+size_t pre_touch_threads(size_t bytes) {
+  const size_t by_size = std::max<size_t>(1, (bytes + (1ull << 30) - 1) >> 30);
+  cpu_set_t set;
+  size_t by_cpu = 0;
+  if (sched_getaffinity(0, sizeof set, &set) == 0) by_cpu = (size_t)CPU_COUNT(&set);
+  if (by_cpu == 0) by_cpu = 8;
+  return std::min(by_size, by_cpu);
+}
+
+// `Hugepagesize:    2048 kB` of /proc/meminfo in bytes, 0 when the line is absent
+// (pinned_mem.rs `read_hugepage_size_from_proc`).
+size_t huge_page_size() {
+  std::ifstream f("/proc/meminfo");
+  std::string line;
+  while (std::getline(f, line)) {
+    if (line.rfind("Hugepagesize:", 0) != 0) continue;
+    unsigned long long kb = 0;
+    if (sscanf(line.c_str() + 13, "%llu", &kb) == 1 && kb) return (size_t)kb << 10;
+  }
+  return 0;
+}
 
 PinnedMemory::PinnedMemory(size_t bytes, Strategy strategy, int numa_node) : size_(bytes), strategy_(strategy) {
   if (bytes == 0) throw Error::storage("pinned memory size must be greater than zero");
@@ -58,14 +86,15 @@ PinnedMemory::PinnedMemory(size_t bytes, Strategy strategy, int numa_node) : siz
     host_ = static_cast<char *>(p);
   } else {
     const bool huge = strategy == Strategy::HugePages;
-    const size_t page = huge ? (2u << 20) : (size_t)sysconf(_SC_PAGESIZE);
+    const size_t page = huge ? huge_page_size() : (size_t)sysconf(_SC_PAGESIZE);
+    if (page == 0) throw Error::storage("huge page size is not available from /proc/meminfo");
     size_ = (bytes + page - 1) / page * page;
     int flags = MAP_PRIVATE | MAP_ANONYMOUS | (huge ? MAP_HUGETLB : 0);
     void *p = mmap(nullptr, size_, PROT_READ | PROT_WRITE, flags, -1, 0);
     if (p == MAP_FAILED)
       throw Error::storage(strf("mmap of %zu bytes failed%s", size_, huge ? " (are huge pages reserved?)" : ""));
     host_ = static_cast<char *>(p);
-    parallel_pre_touch(host_, size_, page, numa_node);
+    parallel_pre_touch(host_, size_, (size_t)sysconf(_SC_PAGESIZE), numa_node);
     cudaError_t e = cudaHostRegister(host_, size_, cudaHostRegisterMapped | cudaHostRegisterPortable);
     if (e != cudaSuccess) {
       munmap(host_, size_);

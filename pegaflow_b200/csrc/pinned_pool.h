@@ -37,6 +37,11 @@ class PinnedMemory {
   Strategy strategy_;
 };
 
+// Workers used to pre-touch a mapping of `bytes` bytes, and the kernel's huge page size (0 when
+// unknown): pinned_mem.rs:378-391 and `read_hugepage_size_from_proc`.
+size_t pre_touch_threads(size_t bytes);
+size_t huge_page_size();
+
 // Best-fit offset allocator with neighbour coalescing, in units of `unit` bytes.
 // Same observable rules as the reference's wrapper (allocator.rs:66-141): sizes round up to
 // the unit, capacity rounds down, the first allocation of a fresh range sits at offset 0,

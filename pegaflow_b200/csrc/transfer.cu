@@ -1290,6 +1290,16 @@ void TransferBackend::peer_copy_layers(const pf_device_layout *src, const pf_dev
       throw Error::invalid("peer copy: unsupported block geometry");
   }
   if (n_blocks > 0xFFFFFFFFull) throw Error::invalid("peer copy: too many blocks");
+  for (size_t l = 0; l < n_layers; ++l)
+    for (int side = 0; side < 2; ++side) {
+      const pf_device_layout &lay = side ? dst[l] : src[l];
+      const uint32_t *ids = side ? dst_ids : src_ids;
+      if (!lay.num_blocks) continue;  // not stated: the ids are trusted
+      for (size_t i = 0; i < n_blocks; ++i)
+        if (ids[i] >= lay.num_blocks)
+          throw Error::invalid(strf("peer copy: block_id %u out of range (num_blocks=%zu) for layer %zu", ids[i],
+                                    lay.num_blocks, l));
+    }
   // one upload of the ids serves every layer
   const size_t ids_bytes = align_up(n_blocks * sizeof(uint32_t), 256);
   const size_t base = meta_alloc(2 * ids_bytes);
@@ -1417,6 +1427,9 @@ extern "C" int pf_save_blocks_noalloc(int device_id, const pf_device_layout *lay
     if (!layout || (!block_ids && n_blocks) || (!host_dst && n_blocks)) throw Error::invalid("null argument");
     if (layout->n_ranges < 1 || layout->n_ranges > 2 || layout->range_bytes == 0)
       throw Error::invalid("unsupported block geometry");
+    // Any first call on a device, an empty one included, resolves the staging area's address there.
+    DeviceGuard on_device(device_id);
+    const NoAllocDevice &dev = noalloc_device(device_id);
     if (n_blocks == 0) return;
     if (n_blocks > PF_NOALLOC_MAX_BLOCKS)
       throw Error::invalid(strf("%zu blocks exceed the built-in staging area's limit of %d blocks; use "
@@ -1430,8 +1443,11 @@ extern "C" int pf_save_blocks_noalloc(int device_id, const pf_device_layout *lay
                                 total, kNoAllocPayload));
     if (host_dst_bytes < total)
       throw Error::invalid(strf("destination holds %zu bytes, the blocks need %zu", host_dst_bytes, total));
-    DeviceGuard on_device(device_id);
-    const NoAllocDevice &dev = noalloc_device(device_id);
+    // The kernel trusts the ids: a caller that states how many blocks the cache has gets them checked here.
+    if (layout->num_blocks)
+      for (size_t i = 0; i < n_blocks; ++i)
+        if (block_ids[i] >= layout->num_blocks)
+          throw Error::invalid(strf("block_id %u out of range (num_blocks=%zu)", block_ids[i], layout->num_blocks));
     cudaStream_t s = (cudaStream_t)stream;
     uint32_t *ids_dev = reinterpret_cast<uint32_t *>(dev.scratch + kNoAllocPayload);
     PF_CUDA(cudaMemcpyAsync(ids_dev, block_ids, n_blocks * sizeof(uint32_t), cudaMemcpyHostToDevice, s));

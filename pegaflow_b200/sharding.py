@@ -3,12 +3,14 @@
 Rank r owns GPU r of the node, its own transfer workers and stream, a pinned pool on that GPU's
 NUMA node, and the storage slots ``(layer, tp_rank = r)`` (pegaflow-core/src/instance.rs:251-269,
 gpu_worker.rs:131-201).  The only collective is the one that times a run: a barrier and a
-max-over-ranks of the elapsed time.
+max-over-ranks of the elapsed time.  Where two instances share a box (same-box prefix hits over
+NVLink), the first half of the ranks is one instance and the second half the other, paired rank
+by rank.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, List, Sequence
+from typing import List, Optional, Sequence
 
 
 @dataclass(frozen=True)
@@ -30,6 +32,27 @@ def rank_plan(rank: int, world: int, *, n_layers: int, payload_bytes_per_rank: i
                     pool_bytes=payload_bytes_per_rank + (64 << 20))
 
 
+@dataclass(frozen=True)
+class PeerRole:
+    role: Optional[str]     # "A" (owns the prefix), "B" (pulls it), None (odd rank out)
+    pair: int               # index of the rank-aligned pair
+    partner: Optional[int]  # rank of the other side
+
+
+def peer_role(rank: int, world: int) -> PeerRole:
+    """Two instances of the same TP degree on one box: ranks 0 .. world/2-1 are instance A, ranks
+    world/2 .. 2*(world/2)-1 instance B; B's rank i pulls from A's rank i (rank-aligned shards, so no
+    exchange between pairs).  With an odd world the last rank takes no part."""
+    if not 0 <= rank < world:
+        raise ValueError(f"rank {rank} out of range (world {world})")
+    half = world // 2
+    if rank < half:
+        return PeerRole("A", rank, rank + half)
+    if rank < 2 * half:
+        return PeerRole("B", rank - half, rank - half)
+    return PeerRole(None, -1, None)
+
+
 def aggregate_throughput(bytes_per_rank: Sequence[int], elapsed_max_seconds: float) -> float:
     """Whole-job GB/s: everything all ranks moved, over the slowest rank's time."""
     return sum(bytes_per_rank) / elapsed_max_seconds / 1e9
@@ -45,14 +68,3 @@ def barrier_and_max(value: float, group=None, device=None) -> float:
     t = torch.tensor([value], dtype=torch.float64, device=device or "cpu")
     dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
     return float(t.item())
-
-
-def numa_assignment(device_nodes: Dict[int, int], nodes: Sequence[int]) -> Dict[int, List[int]]:
-    """Which devices allocate from which node's pool (pinned_pool.rs:464-605): every GPU uses the
-    pool of its own node; a GPU whose node is unknown is an error when per-node pools are on."""
-    out: Dict[int, List[int]] = {n: [] for n in nodes}
-    for dev, node in sorted(device_nodes.items()):
-        if node not in out:
-            raise ValueError(f"GPU {dev} NUMA affinity is unknown")
-        out[node].append(dev)
-    return out

@@ -98,6 +98,15 @@ class PegaKVConnector(KVConnectorBase_V1):
         # every factor that changes a stored block's layout, hashed as the reference does (common.py:519-565)
         self._namespace = derive_namespace(vllm_config, vllm_config.parallel_config.tensor_parallel_size)
         self._is_mla = bool(getattr(model, "use_mla", False))
+        # Scheduler and worker share one in-process engine and the worker registers as rank 0 of 1: with
+        # several workers every one of them would save into a private pool as rank 0 and every lookup
+        # would miss.  Refused like the group layouts this plug-in cannot serve.
+        parallel = vllm_config.parallel_config
+        n_workers = int(getattr(parallel, "world_size", 1) or 1) * int(getattr(parallel, "data_parallel_size", 1) or 1)
+        if n_workers > 1:
+            raise ValueError(
+                "pegaflow_b200's vLLM plug-in runs scheduler and worker in one process with one worker "
+                f"(tensor/pipeline/data parallel world of 1); this configuration has {n_workers} workers")
         self._engine = shared_engine(self._instance_id, int(extra("pegaflow.pool_bytes", 4 << 30)))
         self._client = _connector.InProcEngineClient(self._engine)
         self._scheduler: Optional[SchedulerConnector] = None

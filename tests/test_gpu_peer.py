@@ -64,6 +64,67 @@ def test_peer_load_over_nvlink(env):
     _peer_roundtrip(pf, torch, 1, 0)
 
 
+def test_prefix_hit_between_instances_in_two_processes_over_nvlink(env):
+    """The way instances really meet: each is its own process.  This process is instance A (GPU 0); it
+    exports its layers' regions like the reference ships KV handles (python/pegaflow/ipc_wrapper.py:101-163);
+    a child process is instance B on GPU 1, opens them and pulls blocks across NVLink."""
+    import ctypes as C
+    import json
+    import os
+    import pickle
+    import subprocess
+    import sys
+    import tempfile
+
+    pf, torch = env
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from pegaflow_b200 import _native as N
+
+    nb, seg, n_layers, seed = 256, 16 * 2 * 128 * 2, 5, 600
+    dev = torch.device("cuda", 0)
+    layers = [torch.from_numpy(np.random.default_rng(seed + l).integers(0, 256, size=(2, nb, seg), dtype=np.uint8)).to(dev)
+              for l in range(n_layers)]
+    torch.cuda.synchronize()
+    regions = []
+    for t in layers:
+        r = N.IpcRegion()
+        N.check(N.lib.pf_ipc_export(t.data_ptr(), t.numel(), C.byref(r)))
+        regions.append(bytes(r))
+    rng = np.random.default_rng(9)
+    job = dict(regions=regions, dst_device=1, num_blocks=nb, seg=seg, seed=seed,
+               src_ids=(rng.permutation(nb - 1)[:100] + 1).tolist(), dst_ids=(rng.permutation(nb - 1)[:100] + 1).tolist())
+    with tempfile.NamedTemporaryFile(suffix=".pkl", delete=False) as f:
+        pickle.dump(job, f)
+        path = f.name
+    try:
+        proc = subprocess.run([sys.executable, os.path.join(os.path.dirname(os.path.abspath(__file__)), "peer_child.py"), path],
+                              stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=300)
+    finally:
+        os.unlink(path)
+    lines = [ln for ln in proc.stdout.splitlines() if ln.startswith("{")]
+    assert proc.returncode == 0 and lines, proc.stderr[-3000:]
+    out = json.loads(lines[-1])
+    assert out["bit_exact"] and out["device_status"] == 0
+    assert out["bytes_peer"] == n_layers * 100 * 2 * seg and out["kernel_launches"] == 1
+    del layers
+
+
+def test_peer_copy_rejects_ids_outside_a_stated_cache_size(env):
+    pf, torch = env
+    mem = CudaMem(0)
+    a, b = mem.alloc(8 * 4096), mem.alloc(8 * 4096)
+    be = pf.TransferBackend(0)
+    try:
+        with pytest.raises(pf.PegaflowInvalidArgument, match="block_id 8 out of range"):
+            be.peer_copy((a.data_ptr(), 4096, 0, 4096, 1, 8), [1, 8], (b.data_ptr(), 4096, 0, 4096, 1, 8), [2, 3], 0)
+        with pytest.raises(pf.PegaflowInvalidArgument, match="block_id 9 out of range"):
+            be.peer_copy((a.data_ptr(), 4096, 0, 4096, 1), [1, 2], (b.data_ptr(), 4096, 0, 4096, 1, 8), [2, 9], 0)
+        assert be.stats()["kernel_launches"] == 0
+    finally:
+        be.close()
+
+
 def test_backend_peer_copy_unaligned_geometry(env):
     """Block sizes that are not a multiple of 16 fall back to the ld/st kernel."""
     pf, torch = env

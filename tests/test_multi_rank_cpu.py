@@ -33,6 +33,14 @@ def _worker(rank, world, port, out_dir):
         elapsed = sharding.barrier_and_max(0.5 + rank, device="cpu")
         assert elapsed == 0.5 + (world - 1)
         agg = sharding.aggregate_throughput([10 ** 9] * world, elapsed)
+        # two instances on one box: rank 0 is instance A and hands its "regions" to rank 1, its partner
+        who = sharding.peer_role(rank, world)
+        everyone = [None] * world
+        dist.all_gather_object(everyone, [b"region-of-%d" % rank] if who.role == "A" else None)
+        if who.role == "B":
+            assert everyone[who.partner] == [b"region-of-%d" % who.partner] and who.pair == who.partner
+        else:
+            assert who.role == "A" and everyone[who.partner] is None
         np.save(os.path.join(out_dir, f"r{rank}.npy"), np.array([agg]))
     finally:
         dist.destroy_process_group()
@@ -45,12 +53,14 @@ def test_two_gloo_ranks_plan_disjoint_shards_and_time_like_the_bench(tmp_path):
     assert vals[0] == vals[1] == pytest.approx(2 / 1.5)
 
 
-def test_numa_assignment_rules():
-    assert sharding.numa_assignment({0: 0, 1: 0, 2: 1, 3: 1}, [0, 1]) == {0: [0, 1], 1: [2, 3]}
-    with pytest.raises(ValueError, match="unknown"):
-        sharding.numa_assignment({0: -1}, [0, 1])
+def test_rank_plan_and_peer_roles():
     with pytest.raises(ValueError):
         sharding.rank_plan(2, 2, n_layers=1, payload_bytes_per_rank=1)
+    roles = [sharding.peer_role(r, 8) for r in range(8)]
+    assert [x.role for x in roles] == ["A"] * 4 + ["B"] * 4
+    assert [x.partner for x in roles] == [4, 5, 6, 7, 0, 1, 2, 3] and [x.pair for x in roles] == [0, 1, 2, 3] * 2
+    assert [sharding.peer_role(r, 3).role for r in range(3)] == ["A", "B", None]
+    assert sharding.peer_role(0, 1).role is None
 
 
 def test_tp2_block_seals_only_when_both_ranks_saved_and_loads_per_rank():

@@ -81,3 +81,26 @@ def test_saves_take_each_layer_s_own_group_ids():
         worker.wait_for_save_from_metadata(PegaConnectorMetadata(save_intents={"r": SaveIntent(((1,),), (b"h",))}))
     with pytest.raises(RuntimeError, match="count mismatch"):
         worker.wait_for_save_from_metadata(PegaConnectorMetadata(save_intents={"r": SaveIntent(((1,), (2, 3)), (b"h",))}))
+
+
+@pytest.mark.parametrize("how", ["error", "timeout"])
+def test_a_group_load_that_fails_later_ends_the_step_like_the_reference(how):
+    """worker.py:467-470, 499-503, 534-539: when the load state of a multi-group load reports an error,
+    or the load outlives the timeout, the service is marked unavailable and get_finished raises; the
+    blocks are not reported as invalid (vLLM could not recompute them for several groups)."""
+    client = cases.RecordingClient()
+    worker = _start_load(*cases.CASES["one_request_with_checkpoint"], client)
+    (pending,) = worker._pending_loads
+    assert worker.get_finished() == ([], [])            # still pending, within the timeout
+    if how == "error":
+        pending.state.set_error()
+        match = r"HMA load failed.*async load failed for requests \[.*\]: state=-1"
+    else:
+        worker.LOAD_TIMEOUT_SECONDS = 0.0
+        match = r"HMA load failed.*load timed out for requests \[.*\] after"
+    with pytest.raises(RuntimeError, match=match):
+        worker.get_finished()
+    assert not worker.state_manager.is_available()
+    assert worker.get_block_ids_with_load_errors() == set()
+    assert worker._pending_loads == [] and worker.get_finished() == ([], [])   # reported once
+    assert worker.load_history[-1][2] is False
