@@ -27,6 +27,8 @@ Other modes (each prints one JSON line of its own):
     --vllm-ttft [--after-forward]
                          the same shape under a real vLLM engine with this library as KV connector
     --pool-coldstart     pinned-pool allocation strategies
+    --placement-probe    (with --gpus N) where in host memory a GPU's pool should lie: copy rates into chunks
+                         allocated in different ways, one rank at a time and all ranks at once
 """
 from __future__ import annotations
 
@@ -750,9 +752,10 @@ def run_b200(args, rank, world, local):
     roofline = build_roofline([(st0, st1)], args, alone)
 
     # ---------------- end-to-end arm: the engine's public API ----------------------------------
-    e2e = None
+    e2e, e2e_breakdown = None, None
     if not args.skip_e2e:
         e2e = run_e2e(args, pf, wl, rank, world, local, route)
+        e2e_breakdown = e2e.pop("e2e_breakdown")
 
     concurrent = concurrent_pcie_ceiling(device, world) if world > 1 else None
     barrier(world)
@@ -793,7 +796,7 @@ def run_b200(args, rank, world, local):
                            "gbs": round(L * layer_bytes / 1e6 / all_layers_ms, 2),
                            "how": "per-layer completion events of one request: layer 0 is usable after "
                                   "first_layer_ms, the rest stream in behind it"},
-        "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "peer": peer,
+        "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "e2e_breakdown": e2e_breakdown, "peer": peer,
         "gpu_launches": (st1["kernel_launches"] - st0["kernel_launches"]),
         "dma_copies": (st1["dma_copies"] - st0["dma_copies"]), "device_status": st2["device_status"],
         "clocks": clocks,
@@ -910,6 +913,7 @@ def run_duplex(args, rank, world, local):
     e2e = None
     if not args.skip_e2e:
         e2e = run_e2e(args, pf, wl, rank, world, local, route, duplex=True)
+        e2e.pop("e2e_breakdown")
     concurrent = concurrent_pcie_ceiling(device, world) if world > 1 else None
     barrier(world)
     ceiling = measure_pcie_ceiling(device) if rank == 0 else None
@@ -1004,11 +1008,21 @@ def run_e2e(args, pf, wl, rank, world, local, route, duplex=False):
         step(k)
     torch.cuda.synchronize()
     barrier(world)
+    ph0 = eng.phase_times()
     t0 = time.perf_counter()
     for k in range(args.steps):
         step(max(1, args.warmup) + k)
     torch.cuda.synchronize()
-    elapsed = barrier_and_max(time.perf_counter() - t0, world, device)
+    mine = time.perf_counter() - t0
+    elapsed = barrier_and_max(mine, world, device)
+    ph1 = eng.phase_times()
+    breakdown = {name: {"us_per_step": round((ph1[name][0] - ph0[name][0]) / args.steps * 1e6, 1),
+                        "calls_per_step": round((ph1[name][1] - ph0[name][1]) / args.steps, 2)} for name in ph1}
+    breakdown["step_us"] = round(mine / args.steps * 1e6, 1)
+    breakdown["how"] = ("engine-side timers (pf_engine_get_phase_times), this rank, summed over the calls of a step; saves come "
+                        "from two caller threads and loads are issued before any is awaited, so phases overlap and do not "
+                        "add up to step_us; gpu.save_task / gpu.load_task are the workers' time from picking a task up to the "
+                        "GPU being done, *.enqueue and *.queue_wait are parts of what their name prefixes")
     m = eng.metrics()
     callers.shutdown()
     eng.close()
@@ -1018,7 +1032,7 @@ def run_e2e(args, pf, wl, rank, world, local, route, duplex=False):
             "api": "pf_engine_batch_save / flush_saves / query_prefix / create_query_lease / batch_load_inproc, "
                    "arguments marshalled once outside the timed region; saves issued from two caller threads"
                    + ("; each step's saves overlap the loads of the step before" if duplex else ""),
-            "evicted_blocks": m["evicted_blocks"], "load_failures": m["load_failures"]}
+            "evicted_blocks": m["evicted_blocks"], "load_failures": m["load_failures"], "e2e_breakdown": breakdown}
 
 
 def cuda_memcpy_async(dst_ptr, src_ptr, nbytes, stream):
@@ -1207,6 +1221,114 @@ def peer_phase(args, pf, torch, rank, world, local):
         "gpu_launches": sum(r["gpu_launches"] for r in rs), "device_status": max(r["device_status"] for r in rs),
         "how": "per pair: CUDA events on the destination rank's stream around `steps` calls of pf_backend_peer_copy_layers, "
                "all pairs released by one barrier; aggregate = all pairs' bytes / the slowest pair's time"}
+
+
+
+def first_page_frame(addr):
+    """Guest-physical page frame of the page at `addr` from /proc/self/pagemap (None when the kernel hides it)."""
+    try:
+        page = os.sysconf("SC_PAGESIZE")
+        with open("/proc/self/pagemap", "rb") as f:
+            f.seek(addr // page * 8)
+            entry = int.from_bytes(f.read(8), "little")
+        return (entry & ((1 << 55) - 1)) if entry >> 63 else None
+    except OSError:
+        return None
+
+
+def run_placement_probe(args, rank, world, local):
+    """Does it matter where in host memory a GPU's pinned pool lies?  On a guest that shows a single NUMA
+    node the kernel gives no answer, so this measures it: every rank allocates candidate chunks in several
+    ways (cudaHostAlloc or mmap + pre-touch + cudaHostRegister; from threads restricted to each quarter of the
+    CPUs; early and late in the process's life), then times plain cudaMemcpyAsync copies between its GPU and
+    each chunk - one rank at a time, and with all ranks copying at once - and finally all ranks at once into
+    each rank's best chunk.  Prints one JSON line with the whole table."""
+    import torch
+    import torch.distributed as dist
+    import pegaflow_b200 as pf
+
+    device = torch.device("cuda", local)
+    chunk = args.probe_chunk_mib << 20
+    piece = min(chunk, 256 << 20)
+    cpus = sorted(os.sched_getaffinity(0))
+    quarters = [cpus[i * len(cpus) // 4:(i + 1) * len(cpus) // 4] or cpus for i in range(4)]
+    kinds = [("cudaHostAlloc", q, {}) for q in range(4)] + [("mmap+register", q, {"use_mmap": True}) for q in range(4)] \
+        + [("cudaHostAlloc-late", None, {}) for _ in range(args.probe_late_chunks)]
+    if args.probe_hugepages:
+        kinds.append(("hugepages", None, {"use_hugepages": True}))
+    chunks = []
+    for name, q, kw in kinds:
+        os.sched_setaffinity(0, quarters[q] if q is not None else cpus)
+        try:
+            pool = pf.PinnedPool(chunk + (1 << 20), **kw)
+            host, host_dev, _ = pool.alloc(chunk)
+            chunks.append({"kind": name, "cpu_quarter": q, "pool": pool, "host": host, "pfn": first_page_frame(host)})
+        except pf.PegaFlowError as e:
+            chunks.append({"kind": name, "cpu_quarter": q, "pool": None, "unavailable": str(e)[:100]})
+    os.sched_setaffinity(0, cpus)
+    dev = torch.empty(piece, dtype=torch.uint8, device=device)
+    stream = torch.cuda.Stream()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def copy_rate(c, to_host, reps):
+        """GB/s of `reps` passes over the chunk in pieces of 256 MiB."""
+        a.record(stream)
+        for _ in range(reps):
+            for off in range(0, chunk, piece):
+                if to_host:
+                    cuda_memcpy_async(c["host"] + off, dev.data_ptr(), piece, stream.cuda_stream)
+                else:
+                    cuda_memcpy_async(dev.data_ptr(), c["host"] + off, piece, stream.cuda_stream)
+        b.record(stream)
+        b.synchronize()
+        return reps * chunk / 1e6 / a.elapsed_time(b)
+
+    live = [c for c in chunks if c["pool"] is not None]
+    for c in live:                       # first use of every chunk, untimed
+        copy_rate(c, True, 1), copy_rate(c, False, 1)
+    for turn in range(world):            # one rank at a time
+        barrier(world)
+        if turn == rank:
+            for c in live:
+                c["solo_d2h"], c["solo_h2d"] = round(copy_rate(c, True, 1), 2), round(copy_rate(c, False, 1), 2)
+    for i, c in enumerate(chunks):       # every rank at once, chunk i of each
+        for key, to_host in (("all_d2h", True), ("all_h2d", False)):
+            barrier(world)
+            if c["pool"] is not None:
+                c[key] = round(copy_rate(c, to_host, args.probe_reps), 2)
+    best = {k: max(live, key=lambda c: c[k]) for k in ("all_d2h", "all_h2d")}
+    final = {}
+    for key, to_host in (("all_d2h", True), ("all_h2d", False)):     # every rank at once, each into its best chunk
+        barrier(world)
+        final[key] = round(copy_rate(best[key], to_host, args.probe_reps), 2)
+        barrier(world)
+        final[key + "_first_chunk"] = round(copy_rate(live[0], to_host, args.probe_reps), 2)
+    mine = {"rank": rank, "gpu": local,
+            "chunks": [{k: v for k, v in c.items() if k not in ("pool", "host")} for c in chunks],
+            "best_chunk": {k: chunks.index(v) for k, v in best.items()}, "all_ranks_best_chunk": final}
+    for c in live:
+        c["pool"].close()
+    every = [None] * world
+    if world > 1:
+        dist.all_gather_object(every, mine)
+    else:
+        every = [mine]
+    if rank != 0:
+        return
+
+    def total(key):
+        return round(sum(r["all_ranks_best_chunk"][key] for r in every), 2)
+
+    print(json.dumps({
+        "metric": "pinned_pool_placement_probe", "unit": "GB/s", "n_gpus": world, "host_cpus": len(cpus),
+        "numa_nodes_visible": pf._native.lib.pf_numa_num_nodes(), "chunk_mib": args.probe_chunk_mib,
+        "how": "plain cudaMemcpyAsync in 256 MiB pieces between each rank's GPU and each of its candidate chunks; solo_* = "
+               "one rank at a time, all_* = every rank at once on its chunk of the same index; all_ranks_best_chunk = every "
+               "rank at once, each on the chunk that was fastest for it under load (and on its first chunk, for comparison)",
+        "sum_all_ranks_best_chunk": {"d2h": total("all_d2h"), "h2d": total("all_h2d"),
+                                     "d2h_first_chunk": total("all_d2h_first_chunk"),
+                                     "h2d_first_chunk": total("all_h2d_first_chunk")},
+        "ranks": every}))
 
 
 
@@ -1853,6 +1975,12 @@ def main():
     ap.add_argument("--after-forward", action="store_true",
                     help="with --vllm-ttft: the reference's hook behaviour instead of the layer-wise hooks")
     ap.add_argument("--peer", action="store_true", help="measure the NVLink peer-copy path (one process, two GPUs)")
+    ap.add_argument("--placement-probe", action="store_true",
+                    help="time copies into pinned chunks allocated in different ways, alone and with all ranks at once")
+    ap.add_argument("--probe-chunk-mib", type=int, default=1024)
+    ap.add_argument("--probe-late-chunks", type=int, default=4)
+    ap.add_argument("--probe-reps", type=int, default=2)
+    ap.add_argument("--probe-hugepages", action="store_true")
     args = ap.parse_args()
     if args.peer:
         run_peer(args)
@@ -1877,7 +2005,9 @@ def main():
         os.execv(sys.executable, cmd)
     rank, world, local = dist_setup(args.gpus)
     try:
-        if args.impl == "reference":
+        if args.placement_probe:
+            run_placement_probe(args, rank, world, local)
+        elif args.impl == "reference":
             run_reference(args, rank, world, local)
         else:
             (run_duplex if args.duplex else run_b200)(args, rank, world, local)

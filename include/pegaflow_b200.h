@@ -469,6 +469,20 @@ typedef struct pf_engine_metrics {
 } pf_engine_metrics;
 int pf_engine_get_metrics(pf_engine *engine, pf_engine_metrics *out);
 
+/* Where a save and a load spend their time on the host side, accumulated since the engine was
+ * created: seconds and number of samples per phase.  Phases that the reference traces carry its
+ * span names (pf_engine_phase_name: "save.resolve_metadata", "save.hash_filter",
+ * "save.pinned_alloc", "save.gpu_copy", "gpu.save_task", "load.cache_lookup", "load.build_tasks",
+ * "gpu.load_task"; offload.rs:311,391,428,532, lib.rs:775,835, gpu_worker.rs:433,488); the others
+ * split those further.  The same names mark NVTX ranges on the calling and worker threads. */
+#define PF_PHASE_COUNT 17
+typedef struct pf_engine_phase_times {
+  double seconds[PF_PHASE_COUNT];
+  uint64_t calls[PF_PHASE_COUNT];
+} pf_engine_phase_times;
+int pf_engine_get_phase_times(pf_engine *engine, pf_engine_phase_times *out);
+const char *pf_engine_phase_name(int phase); /* NULL when out of range */
+
 /* ------------------------------------------------------------------------------------------
  * 4. LoadState.  Replaces `LoadState` (pegaflow-core/src/sync_state.rs:104-188); the segment
  *    layout is bit-compatible, so either side may be the reference's.

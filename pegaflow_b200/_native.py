@@ -103,6 +103,13 @@ class EngineMetrics(C.Structure):
                 ("transfer", BackendStats)]
 
 
+PHASE_COUNT = 17
+
+
+class PhaseTimes(C.Structure):
+    _fields_ = [("seconds", C.c_double * PHASE_COUNT), ("calls", u64 * PHASE_COUNT)]
+
+
 def _sig(name, restype, *argtypes):
     fn = getattr(lib, name)
     fn.restype = restype
@@ -182,6 +189,8 @@ _sig("pf_stream_wait_event", C.c_int, vp, vp)
 _sig("pf_engine_save_layers_async", C.c_int, vp, C.c_char_p, sz, sz, C.c_int, sz, P(LayerSave), vp)
 _sig("pf_engine_peer_load", C.c_int, vp, C.c_char_p, C.c_int, C.c_char_p, C.c_int, sz, P(sz), P(sz))
 _sig("pf_engine_get_metrics", C.c_int, vp, P(EngineMetrics))
+_sig("pf_engine_get_phase_times", C.c_int, vp, P(PhaseTimes))
+_sig("pf_engine_phase_name", C.c_char_p, C.c_int)
 _sig("pf_load_state_new", C.c_int, P(vp))
 _sig("pf_load_state_attach", C.c_int, C.c_char_p, P(vp))
 _sig("pf_load_state_shm_name", C.c_char_p, vp)

@@ -396,6 +396,15 @@ int pf_engine_peer_load(pf_engine *engine, const char *src_instance, int src_dev
   });
 }
 
+int pf_engine_get_phase_times(pf_engine *engine, pf_engine_phase_times *out) {
+  return guarded([&] {
+    if (!engine || !out) throw Error::invalid("null argument");
+    engine->impl.phase_times(out);
+  });
+}
+
+const char *pf_engine_phase_name(int phase) { return phase_name(phase); }
+
 int pf_engine_get_metrics(pf_engine *engine, pf_engine_metrics *out) {
   return guarded([&] {
     if (!engine || !out) throw Error::invalid("null argument");

@@ -5,11 +5,22 @@
 #include <random>
 #include <set>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "numa.h"
 
 namespace pf {
 
 namespace {
+// NVTX range named like the reference's trace span for the same stretch of work.
+struct Range {
+  explicit Range(const char *name) { nvtxRangePushA(name); }
+  ~Range() { nvtxRangePop(); }
+  Range(const Range &) = delete;
+  Range &operator=(const Range &) = delete;
+};
+using Clock = std::chrono::steady_clock;
+
 constexpr size_t kReclaimBatch = 64;                       // blocks evicted per reclaim step
 constexpr auto kLeaseTtl = std::chrono::seconds(600);      // lease.rs:11
 constexpr uint64_t kMaxRunStride = 1ull << 30;             // 2D DMA pitch stays far below its limit
@@ -20,6 +31,30 @@ void cuda_or_storage(cudaError_t e, const char *what) {
   if (e != cudaSuccess) throw Error::storage(strf("%s failed: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e)));
 }
 }  // namespace
+
+const char *phase_name(int phase) {
+  static const char *const names[kPhaseCount] = {
+      "save.resolve_metadata", "save.hash_filter", "save.pinned_alloc", "save.gpu_copy", "save.queue_wait",
+      "gpu.save_task", "gpu.save_task.enqueue", "save.insert_build", "save.insert", "save.flush_wait",
+      "query.prefix", "query.create_lease", "load.cache_lookup", "load.build_tasks", "load.queue_wait",
+      "gpu.load_task", "gpu.load_task.enqueue"};
+  return phase >= 0 && phase < kPhaseCount ? names[phase] : nullptr;
+}
+
+Clock::time_point Engine::lap(Phase p, Clock::time_point since) {
+  const auto now = Clock::now();
+  phase_nanos_[p].fetch_add((uint64_t)std::chrono::duration_cast<std::chrono::nanoseconds>(now - since).count(),
+                            std::memory_order_relaxed);
+  phase_calls_[p].fetch_add(1, std::memory_order_relaxed);
+  return now;
+}
+
+void Engine::phase_times(pf_engine_phase_times *out) {
+  for (int i = 0; i < kPhaseCount; ++i) {
+    out->seconds[i] = phase_nanos_[i].load() * 1e-9;
+    out->calls[i] = phase_calls_[i].load();
+  }
+}
 
 std::string group_hash(const std::string &hash, uint32_t group) {
   if (group == 0) return hash;
@@ -532,6 +567,7 @@ void Engine::batch_save(const std::string &instance_id, size_t tp_rank, size_t p
   auto topo = sealed_topology(*inst);
 
   // ---- phase 0: resolve layout / slot / group, validate ids (offload.rs:313-378)
+  nvtxRangePushA("save.resolve_metadata");
   std::shared_ptr<GpuContext> gpu;
   {
     std::lock_guard<std::mutex> g(inst->mu);
@@ -570,13 +606,15 @@ void Engine::batch_save(const std::string &instance_id, size_t tp_rank, size_t p
     if (s.block_ids.empty()) continue;
     ctxs.push_back(Ctx{s.layer_name, &lit->second, slot, group, std::move(s.block_ids), s.block_hashes, {}});
   }
+  nvtxRangePop();
   if (ctxs.empty()) return;
-  const auto t1 = std::chrono::steady_clock::now();
+  const auto t1 = lap(kSaveResolve, t0);
 
   // ---- phase 1: drop blocks whose (group, hash) is already resident (offload.rs:393-424).
   // Layers of one save normally share one hash list: each distinct (list, group) is encoded and
   // looked up once and the result is shared.
   {
+    Range nvtx("save.hash_filter");
     struct Filtered {
       HashList hashes;                 // group-encoded, resident ones removed
       std::vector<uint32_t> kept;      // positions that survive (empty + all_kept: every position)
@@ -621,11 +659,18 @@ void Engine::batch_save(const std::string &instance_id, size_t tp_rank, size_t p
     ctxs.erase(std::remove_if(ctxs.begin(), ctxs.end(), [](const Ctx &c) { return c.ids.empty(); }), ctxs.end());
     if (total == 0 || ctxs.empty()) return;
   }
-  const auto t2 = std::chrono::steady_clock::now();
+  const auto t2 = lap(kSaveHashFilter, t1);
 
   // ---- phase 2: host placement (offload.rs:428-527, 182-282).  Only what the GPU copy needs is
   // built here (allocations, block ids, host runs); the per-block bookkeeping for the cache is
   // built after the copy has been submitted, while it runs.
+  nvtxRangePushA("save.pinned_alloc");
+  struct PopRange {
+    bool armed = true;
+    ~PopRange() {
+      if (armed) nvtxRangePop();
+    }
+  } alloc_range;
   const int numa_node = gpu->numa_node;
   const bool page_first = topo->page.has_value();
   const bool blockwise = cfg_.blockwise_alloc != 0 && !page_first;
@@ -717,7 +762,9 @@ void Engine::batch_save(const std::string &instance_id, size_t tp_rank, size_t p
       work->push_back(std::move(w));
     }
   }
-  const auto t3 = std::chrono::steady_clock::now();
+  nvtxRangePop();
+  alloc_range.armed = false;
+  const auto t3 = lap(kSavePinnedAlloc, t2);
 
   // ---- phase 3: one GPU batch (offload.rs:532-536 -> gpu_worker.rs:482-523)
   auto done = std::make_shared<std::promise<void>>();
@@ -746,6 +793,8 @@ void Engine::batch_save(const std::string &instance_id, size_t tp_rank, size_t p
     insert_idle_cv_.notify_all();
   };
   gpu->save_worker->submit([=](TransferBackend &backend, cudaStream_t stream) {
+    Range nvtx("gpu.save_task");
+    const auto w0 = lap(kSaveQueueWait, t3);
     try {
       std::vector<pf_layer_xfer> xf(work->size());
       for (size_t i = 0; i < work->size(); ++i) {
@@ -756,7 +805,9 @@ void Engine::batch_save(const std::string &instance_id, size_t tp_rank, size_t p
       }
       if (ready_event) cuda_or_storage(cudaStreamWaitEvent(stream, ready_event, 0), "cudaStreamWaitEvent");
       backend.move_layers(xf.data(), xf.size(), false, stream, nullptr);
+      lap(kSaveEnqueue, w0);
       cuda_or_storage(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
+      lap(kSaveTask, w0);
       (void)copy_targets;
       if (async) hand_over();
       done->set_value();
@@ -776,6 +827,7 @@ void Engine::batch_save(const std::string &instance_id, size_t tp_rank, size_t p
   // ---- phase 4 input, built while the copy runs: one RawBlock per (layer, block) and the
   // batches the insert worker will seal (offload.rs:594-656).
   try {
+    Range nvtx("save.insert_build");
     auto batches = std::make_shared<std::vector<RawSaveBatch>>();
     if (page_first) {
       const size_t slot = ctxs[0].slot;
@@ -827,6 +879,7 @@ void Engine::batch_save(const std::string &instance_id, size_t tp_rank, size_t p
       for (auto &kv : by_group) batches->push_back(std::move(kv.second));
     }
     batches_ready->set_value(std::move(batches));
+    lap(kSaveInsertBuild, t3);
   } catch (...) {
     batches_ready->set_value(nullptr);
     if (!async) {
@@ -844,6 +897,7 @@ void Engine::batch_save(const std::string &instance_id, size_t tp_rank, size_t p
     return;
   }
   try {
+    Range nvtx("save.gpu_copy");
     finished.get();
   } catch (...) {
     abandon();
@@ -851,7 +905,7 @@ void Engine::batch_save(const std::string &instance_id, size_t tp_rank, size_t p
   }
   save_bytes_.fetch_add(padded_total);
   save_batches_.fetch_add(1);
-  const auto t4 = std::chrono::steady_clock::now();
+  const auto t4 = lap(kSaveGpuCopy, t3);
   save_nanos_.fetch_add((uint64_t)std::chrono::duration_cast<std::chrono::nanoseconds>(t4 - t0).count());
   hand_over();
   if (trace_) {
@@ -862,8 +916,10 @@ void Engine::batch_save(const std::string &instance_id, size_t tp_rank, size_t p
 }
 
 void Engine::flush_saves() {
+  const auto t0 = Clock::now();
   std::unique_lock<std::mutex> g(insert_mu_);
   insert_idle_cv_.wait(g, [&] { return insert_pending_ == 0; });
+  lap(kFlushWait, t0);
   if (!async_error_.empty()) {
     std::string msg;
     msg.swap(async_error_);
@@ -882,7 +938,11 @@ void Engine::insert_loop() {
       batch = std::move(insert_queue_.front());
       insert_queue_.pop_front();
     }
-    process_insert(batch);
+    {
+      const auto t0 = Clock::now();
+      process_insert(batch);
+      lap(kSaveInsert, t0);
+    }
     {
       std::lock_guard<std::mutex> g(insert_mu_);
       --insert_pending_;
@@ -963,6 +1023,7 @@ void Engine::insert_slot(const BlockKey &key, size_t slot, RawBlock block, size_
 
 void Engine::query_prefix(const std::string &instance_id, const std::vector<std::string> &hashes,
                           std::vector<BlockRef> *blocks, size_t *missing) {
+  const auto t0 = Clock::now();
   auto inst = get_instance(instance_id);
   blocks->clear();
   for (auto &h : hashes) {
@@ -971,6 +1032,7 @@ void Engine::query_prefix(const std::string &instance_id, const std::vector<std:
     blocks->push_back(std::move(b));
   }
   *missing = hashes.size() - blocks->size();
+  lap(kQueryPrefix, t0);
 }
 
 std::vector<BlockRef> Engine::query_group_membership(const std::string &instance_id, uint32_t group,
@@ -990,6 +1052,7 @@ void Engine::sweep_leases() {
 }
 
 std::array<uint8_t, 16> Engine::create_query_lease(const std::string &instance_id, std::vector<BlockRef> blocks) {
+  const auto t0 = Clock::now();
   auto inst = get_instance(instance_id);
   if (blocks.empty()) throw Error::invalid("query lease requires at least one block");
   sweep_leases();
@@ -1002,6 +1065,7 @@ std::array<uint8_t, 16> Engine::create_query_lease(const std::string &instance_i
   std::lock_guard<std::mutex> g(leases_mu_);
   leases_[token] = Lease{instance_id, std::move(blocks), std::max<size_t>(1, inst->world_size),
                          std::chrono::steady_clock::now() + kLeaseTtl};
+  lap(kCreateLease, t0);
   return token;
 }
 
@@ -1102,7 +1166,9 @@ void Engine::batch_load(const std::string &instance_id, size_t tp_rank, int devi
       }
       for (auto &b : blocks) block_cache.push_back(std::move(b));
     }
+    const auto t_lookup = lap(kLoadCacheLookup, t_begin);
     // per layer work (lib.rs:836-888 + gpu_worker.rs:353-423 pairing)
+    Range nvtx_build("load.build_tasks");
     auto work = std::make_shared<std::vector<LayerWork>>();
     for (size_t gi = 0; gi < layer_groups.size(); ++gi) {
       for (auto &name : layer_groups[gi]) {
@@ -1151,8 +1217,10 @@ void Engine::batch_load(const std::string &instance_id, size_t tp_rank, int devi
     if (trace_)
       fprintf(stderr, "[pegaflow_b200] load %s: build_tasks %.2f ms\n", instance_id.c_str(),
               std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t_begin).count());
+    const auto t_submit = lap(kLoadBuildTasks, t_lookup);
     gpu->load_worker->submit([=](TransferBackend &backend, cudaStream_t stream) {
-      const auto t0 = std::chrono::steady_clock::now();
+      Range nvtx("gpu.load_task");
+      const auto t0 = lap(kLoadQueueWait, t_submit);
       try {
         std::vector<pf_layer_xfer> xf(work->size());
         std::vector<void *> events(work->size(), nullptr);
@@ -1167,8 +1235,10 @@ void Engine::batch_load(const std::string &instance_id, size_t tp_rank, int devi
           bytes += w.payload_bytes();
         }
         backend.move_layers(xf.data(), xf.size(), true, stream, events.data());
+        lap(kLoadEnqueue, t0);
         gpu_raw->load_worker->mark_enqueued(gpu_raw->load_worker->current_ticket());
         cuda_or_storage(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
+        lap(kLoadTask, t0);
         load_bytes_.fetch_add(bytes);
         load_tasks_.fetch_add(1);
         load_nanos_.fetch_add((uint64_t)std::chrono::duration_cast<std::chrono::nanoseconds>(

@@ -34,6 +34,32 @@
 
 namespace pf {
 
+// Phases of a save and a load whose time the engine accumulates (pf_engine_get_phase_times).  Where
+// the reference has a trace span for the same stretch, the phase carries its name (offload.rs:311,
+// 391,428,532; lib.rs:775,835; gpu_worker.rs:433,488), and the same names mark NVTX ranges.
+enum Phase {
+  kSaveResolve = 0,   // save.resolve_metadata
+  kSaveHashFilter,    // save.hash_filter
+  kSavePinnedAlloc,   // save.pinned_alloc
+  kSaveGpuCopy,       // save.gpu_copy: caller's wait from submit until the worker reports the copy done
+  kSaveQueueWait,     //   of which: the task sat in the save worker's queue
+  kSaveTask,          // gpu.save_task: the worker's time in the task (enqueue + wait for the GPU)
+  kSaveEnqueue,       //   of which: building and enqueueing the transfers
+  kSaveInsertBuild,   // per-block bookkeeping for the cache, built on the caller while the copy runs
+  kSaveInsert,        // sealing and inserting blocks on the insert thread
+  kFlushWait,         // flush_saves: waiting for the insert thread
+  kQueryPrefix,       // prefix lookup
+  kCreateLease,
+  kLoadCacheLookup,   // load.cache_lookup: leases consumed, targets mapped
+  kLoadBuildTasks,    // load.build_tasks
+  kLoadQueueWait,     // the task sat in the load worker's queue
+  kLoadTask,          // gpu.load_task
+  kLoadEnqueue,       //   of which: building and enqueueing the transfers
+  kPhaseCount
+};
+static_assert(kPhaseCount == PF_PHASE_COUNT, "phase list and C ABI disagree");
+const char *phase_name(int phase);
+
 // ---- stored blocks (block.rs) --------------------------------------------------------------
 struct Segment {
   char *host = nullptr;
@@ -254,8 +280,13 @@ class Engine {
   void peer_load(const std::string &src_instance, int src_device, const std::string &dst_instance, int dst_device,
                  const std::vector<size_t> &src_ids, const std::vector<size_t> &dst_ids);
   void metrics(pf_engine_metrics *out);
+  void phase_times(pf_engine_phase_times *out);
 
  private:
+  // Adds the time since `since` to a phase and returns now.
+  std::chrono::steady_clock::time_point lap(Phase p, std::chrono::steady_clock::time_point since);
+  std::atomic<uint64_t> phase_nanos_[kPhaseCount] = {}, phase_calls_[kPhaseCount] = {};
+
   struct RawSaveLayer {
     size_t slot_id;
     std::vector<RawBlock> blocks;

@@ -40,9 +40,10 @@ constexpr uint32_t kPackChunk = 16384;   // bytes one CTA iteration of the ld/st
 constexpr int kStages = 4;               // ring depth of the TMA kernels
 constexpr uint32_t kStageBytes = 32768;  // bytes per ring stage
 constexpr unsigned kStatusWaitExpired = 0x57A17u;
-constexpr size_t kSmallTaskBytes = 2u << 20;
+constexpr size_t kSmallTaskBytes = 2u << 20;      // multi-layer tasks up to this size take one zero-copy launch
 constexpr size_t kFirstGroupBytes = 4u << 20;     // size limit of a call's first staging group, doubled per group
-constexpr size_t kMinEventGroupBytes = 8u << 20;  // a layer with fewer staged bytes shares the DMA of the next ones  // multi-layer tasks up to this size take one launch
+constexpr size_t kMinEventGroupBytes = 8u << 20;  // a layer with fewer staged bytes shares the DMA of the next ones
+constexpr size_t kMinLinkLaunchBytes = 32u << 20; // ... and one with fewer zero-copy bytes the launch of the next ones
 
 __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t t;
@@ -392,6 +393,112 @@ copy_descs_tma(const uint64_t *__restrict__ triples, uint32_t n, uint32_t stage_
   tma_ring(gen, ring, bars, stage_bytes, status);
 }
 
+
+// ---- zero-copy over PCIe, one launch for a whole task ---------------------------------------------
+// A unit is one host run of one device range of one layer: item i lives at
+// kv_base + ids[i] * kv_stride on the GPU and at host_base + i * host_stride in the (mapped) pool.
+// The unit table and the ids lie in device memory, so a launch covers any number of layers.  One
+// thread per CTA drives a ring of bulk copies; the PCIe side of a ring stage is one large bulk copy
+// whenever the host side of the chunk is dense, whatever the block size: blocks of 2-16 KiB are
+// batched kLinkItemsMax to a stage (several bulk loads from scattered HBM blocks fill the stage, one
+// bulk store drains it to the pool; the mirror image for a load).
+constexpr uint32_t kLinkItemsMax = 16;
+struct LinkUnit {
+  uint64_t kv_base, kv_stride;
+  uint64_t host_base, host_stride;
+  const uint32_t *ids;
+  uint64_t chunk_end;        // exclusive prefix sum of chunks over the units of the call
+  uint32_t n_items, item_bytes;
+  uint32_t items_per_chunk;  // >= 2: a chunk is that many whole items; otherwise an item is cut
+  uint32_t chunks_per_item;  //      into this many chunks of at most kStageBytes
+};
+
+__global__ void __launch_bounds__(32)
+copy_units_tma(const LinkUnit *__restrict__ units, uint32_t n_units, uint64_t chunk_begin, int to_host,
+               unsigned int *status) {
+  extern __shared__ __align__(128) char ring[];
+  __shared__ uint64_t bars[kStages];
+  if (threadIdx.x != 0) return;
+  for (int s = 0; s < kStages; ++s) mbar_init(&bars[s], 1);
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+
+  // what each ring stage holds: `count` pieces of `len` bytes, piece j = bytes [off, off + len) of item item0 + j
+  uint32_t st_unit[kStages], st_item0[kStages], st_count[kStages], st_off[kStages], st_len[kStages];
+  const uint64_t total_end = units[n_units - 1].chunk_end;
+  uint64_t cursor = chunk_begin + blockIdx.x, unit_begin = chunk_begin;
+  uint32_t k = 0;
+  uint64_t produced = 0, consumed = 0;
+
+  auto produce = [&]() -> bool {
+    if (cursor >= total_end) return false;
+    while (cursor >= units[k].chunk_end) {  // chunks are visited in ascending order
+      unit_begin = units[k].chunk_end;
+      ++k;
+    }
+    const LinkUnit &u = units[k];
+    const uint64_t local = cursor - unit_begin;
+    uint32_t item0, count, off, len;
+    if (u.items_per_chunk >= 2) {
+      item0 = (uint32_t)local * u.items_per_chunk;
+      count = min(u.items_per_chunk, u.n_items - item0);
+      off = 0;
+      len = u.item_bytes;
+    } else {
+      item0 = (uint32_t)(local / u.chunks_per_item);
+      count = 1;
+      off = (uint32_t)(local - (uint64_t)item0 * u.chunks_per_item) * kStageBytes;
+      len = min(kStageBytes, u.item_bytes - off);
+    }
+    const int st = (int)(produced % kStages);
+    st_unit[st] = k, st_item0[st] = item0, st_count[st] = count, st_off[st] = off, st_len[st] = len;
+    char *stage = ring + (size_t)st * kStageBytes;
+    mbar_expect_tx(&bars[st], count * len);
+    if (to_host) {
+      for (uint32_t j = 0; j < count; ++j)
+        bulk_g2s(stage + (size_t)j * len, u.kv_base + (uint64_t)u.ids[item0 + j] * u.kv_stride + off, len, &bars[st]);
+    } else if (u.host_stride == len) {  // whole items, back to back in the pool: one read across the link
+      bulk_g2s(stage, u.host_base + (uint64_t)item0 * u.host_stride, count * len, &bars[st]);
+    } else {
+      for (uint32_t j = 0; j < count; ++j)
+        bulk_g2s(stage + (size_t)j * len, u.host_base + (uint64_t)(item0 + j) * u.host_stride + off, len, &bars[st]);
+    }
+    ++produced;
+    cursor += gridDim.x;
+    return true;
+  };
+
+  bool more = true;
+  for (int s = 0; s < kStages && more; ++s) more = produce();
+  while (consumed < produced) {
+    const int st = (int)(consumed % kStages);
+    if (!wait_stage(&bars[st], (uint32_t)((consumed / kStages) & 1))) {
+      *status = kStatusWaitExpired;
+      bulk_wait_all();
+      return;
+    }
+    const LinkUnit &u = units[st_unit[st]];
+    const uint32_t item0 = st_item0[st], count = st_count[st], off = st_off[st], len = st_len[st];
+    const char *stage = ring + (size_t)st * kStageBytes;
+    if (!to_host) {
+      for (uint32_t j = 0; j < count; ++j)
+        bulk_s2g(u.kv_base + (uint64_t)u.ids[item0 + j] * u.kv_stride + off, stage + (size_t)j * len, len);
+    } else if (u.host_stride == len) {  // one write across the link
+      bulk_s2g(u.host_base + (uint64_t)item0 * u.host_stride, stage, count * len);
+    } else {
+      for (uint32_t j = 0; j < count; ++j)
+        bulk_s2g(u.host_base + (uint64_t)(item0 + j) * u.host_stride + off, stage + (size_t)j * len, len);
+    }
+    bulk_commit();
+    ++consumed;
+    if (more && consumed >= 2) {
+      bulk_wait_read_1();  // every store group but the newest has finished reading shared memory
+      more = produce();    // lands in the stage of chunk consumed-2
+    }
+  }
+  bulk_wait_all();
+}
+
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 }  // namespace
@@ -436,6 +543,7 @@ TransferBackend::TransferBackend(int device, const pf_backend_config *config) : 
   PF_CUDA(cudaHostGetDevicePointer(&status_dev_, status_host_, 0));
   PF_CUDA(cudaFuncSetAttribute(copy_items_tma, cudaFuncAttributeMaxDynamicSharedMemorySize, kStages * kStageBytes));
   PF_CUDA(cudaFuncSetAttribute(copy_descs_tma, cudaFuncAttributeMaxDynamicSharedMemorySize, kStages * kStageBytes));
+  PF_CUDA(cudaFuncSetAttribute(copy_units_tma, cudaFuncAttributeMaxDynamicSharedMemorySize, kStages * kStageBytes));
   meta_grow(1u << 20);
   if (cfg_.time_kernels) {
     stamps_host_.assign(2 * (size_t)kStampRing, 0);
@@ -869,16 +977,20 @@ void TransferBackend::gather_layers(const pf_layer_xfer *layers, size_t n_layers
 void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, bool host_is_src,
                                   cudaStream_t stream, void *const *layer_done) {
   DeviceGuard on_device(device_);
-  // ---- validate and plan the meta upload: block ids of every layer, plus an address table
-  // for each (layer, range) whose zero-copy part spans more than one host run.
-  struct RangePlan {
-    std::vector<size_t> zc_runs;  // indices of runs taking the zero-copy route
-    size_t zc_blocks = 0;
-    size_t table_off = 0, zc_ids_off = 0;  // valid when zc_runs.size() > 1
-  };
+  // ---- validate and plan.  Every host run takes one of three routes: staged (gather kernel + copy
+  // engine), one pitched DMA (consecutive block ids), or zero-copy.  Zero-copy runs become units of
+  // the task's unit table; a whole task's units go into one launch unless layer events cut it.
+  size_t total_bytes = 0;
+  for (size_t li = 0; li < n_layers; ++li) total_bytes += layers[li].n_blocks * layers[li].range_bytes * layers[li].n_ranges;
+  // Small tasks (a few blocks of every layer, e.g. the tail blocks saved while decoding): launches,
+  // not bytes, are what they cost, so everything goes into the one zero-copy launch.
+  const bool small_task = cfg_.route != PF_ROUTE_STAGED && n_layers > 1 && total_bytes <= kSmallTaskBytes;
   std::vector<size_t> ids_off(n_layers, 0);
-  std::vector<RangePlan> plans(n_layers * 2);
+  std::vector<LinkUnit> units;               // `ids` holds a byte offset into the meta region until it is known
+  std::vector<uint32_t> unit_of_run;         // per (layer, range, run) in visiting order: unit index, kStaged or kLdst
+  constexpr uint32_t kStaged = 0xFFFFFFFFu, kLdst = 0xFFFFFFFEu;
   size_t meta_bytes = 0;
+  uint64_t chunk_total = 0;
   for (size_t li = 0; li < n_layers; ++li) {
     const pf_layer_xfer &L = layers[li];
     if (L.n_blocks == 0) continue;
@@ -890,8 +1002,8 @@ void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, 
     ids_off[li] = meta_bytes;
     meta_bytes += align_up(L.n_blocks * sizeof(uint32_t), 256);
     for (uint32_t r = 0; r < L.n_ranges; ++r) {
-      RangePlan &P = plans[li * 2 + r];
       size_t covered = 0;
+      const uint64_t dev_base = L.data_ptr + (uint64_t)r * L.kv_stride_bytes;
       for (size_t j = 0; j < L.n_runs[r]; ++j) {
         const pf_host_run &run = L.runs[r][j];
         if (run.first_block != covered)
@@ -901,22 +1013,40 @@ void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, 
         if (run.n_blocks > 1 && run.stride_bytes < L.range_bytes)
           throw Error::invalid(strf("layer %zu range %u: host stride smaller than the range", li, r));
         covered += run.n_blocks;
+        if (run.n_blocks == 0) {
+          unit_of_run.push_back(kStaged);
+          continue;
+        }
         const size_t bytes = run.n_blocks * L.range_bytes;
         bool staged = cfg_.route == PF_ROUTE_STAGED || (cfg_.route == PF_ROUTE_AUTO && bytes >= cfg_.min_dma_bytes);
-        if (L.range_bytes > cfg_.staging_slot_bytes) staged = false;
-        if (!staged && run.n_blocks) {
-          P.zc_runs.push_back(j);
-          P.zc_blocks += run.n_blocks;
+        if (L.range_bytes > cfg_.staging_slot_bytes || small_task) staged = false;
+        if (staged) {
+          unit_of_run.push_back(kStaged);
+          continue;
         }
+        // bulk copies need 16-byte aligned addresses and sizes; anything else takes the ld/st kernel
+        if ((dev_base | L.block_stride_bytes | run.host_device | run.stride_bytes | L.range_bytes) & 15ull) {
+          unit_of_run.push_back(kLdst);
+          continue;
+        }
+        LinkUnit u;
+        u.kv_base = dev_base;
+        u.kv_stride = L.block_stride_bytes;
+        u.host_base = run.host_device;
+        u.host_stride = run.n_blocks > 1 ? run.stride_bytes : L.range_bytes;
+        u.ids = reinterpret_cast<const uint32_t *>(ids_off[li] + run.first_block * sizeof(uint32_t));
+        u.n_items = (uint32_t)run.n_blocks;
+        u.item_bytes = (uint32_t)L.range_bytes;
+        u.items_per_chunk = (uint32_t)std::min<size_t>(kLinkItemsMax, kStageBytes / L.range_bytes);
+        u.chunks_per_item = (uint32_t)((L.range_bytes + kStageBytes - 1) / kStageBytes);
+        chunk_total += u.items_per_chunk >= 2 ? (run.n_blocks + u.items_per_chunk - 1) / u.items_per_chunk
+                                              : (uint64_t)run.n_blocks * u.chunks_per_item;
+        u.chunk_end = chunk_total;
+        unit_of_run.push_back((uint32_t)units.size());
+        units.push_back(u);
       }
       if (covered != L.n_blocks)
         throw Error::invalid(strf("layer %zu range %u: host runs cover %zu of %zu blocks", li, r, covered, L.n_blocks));
-      if (P.zc_runs.size() > 1) {
-        P.table_off = meta_bytes;
-        meta_bytes += align_up(P.zc_blocks * sizeof(uint64_t), 256);
-        P.zc_ids_off = meta_bytes;
-        meta_bytes += align_up(P.zc_blocks * sizeof(uint32_t), 256);
-      }
     }
   }
   if (meta_bytes == 0) {
@@ -925,71 +1055,15 @@ void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, 
         if (layer_done[li]) PF_CUDA(cudaEventRecord((cudaEvent_t)layer_done[li], stream));
     return;
   }
-  // ---- small tasks (a few blocks of every layer, e.g. the tail blocks saved while decoding):
-  // launches, not bytes, are what they cost.  Everything goes into one descriptor-driven
-  // zero-copy launch, whatever the number of layers.
-  {
-    size_t total_bytes = 0, total_items = 0;
-    for (size_t li = 0; li < n_layers; ++li) {
-      total_bytes += layers[li].n_blocks * layers[li].range_bytes * layers[li].n_ranges;
-      total_items += layers[li].n_blocks * layers[li].n_ranges;
-    }
-    if (cfg_.route != PF_ROUTE_STAGED && n_layers > 1 && total_bytes <= kSmallTaskBytes && total_items <= 65536) {
-      const size_t tb = align_up(total_items * 3 * sizeof(uint64_t), 256);
-      const size_t tbase = meta_alloc(tb);
-      uint64_t *triples = reinterpret_cast<uint64_t *>(meta_host_ + tbase);
-      bool aligned = true;
-      size_t q = 0;
-      for (size_t li = 0; li < n_layers; ++li) {
-        const pf_layer_xfer &L = layers[li];
-        for (uint32_t r = 0; r < (L.n_blocks ? L.n_ranges : 0); ++r)
-          for (size_t j = 0; j < L.n_runs[r]; ++j) {
-            const pf_host_run &run = L.runs[r][j];
-            for (size_t i = 0; i < run.n_blocks; ++i, ++q) {
-              const uint64_t dev = L.data_ptr + (uint64_t)L.block_ids[run.first_block + i] * L.block_stride_bytes +
-                                   (uint64_t)r * L.kv_stride_bytes;
-              const uint64_t host = run.host_device + (uint64_t)i * run.stride_bytes;
-              triples[3 * q] = host_is_src ? dev : host;
-              triples[3 * q + 1] = host_is_src ? host : dev;
-              triples[3 * q + 2] = L.range_bytes;
-              if ((dev | host | L.range_bytes) & 15ull) aligned = false;
-            }
-          }
-      }
-      meta_upload(tbase, tb, stream);
-      launch_descs(reinterpret_cast<const uint64_t *>(meta_dev_ + tbase), q, aligned, stream);
-      stats_.bytes_zero_copy += total_bytes;
-      if (layer_done)
-        for (size_t li = 0; li < n_layers; ++li)
-          if (layer_done[li]) PF_CUDA(cudaEventRecord((cudaEvent_t)layer_done[li], stream));
-      cudaEvent_t ev = take_event();
-      PF_CUDA(cudaEventRecord(ev, stream));
-      meta_inflight_.push_back({tbase, tbase + tb, ev});
-      return;
-    }
-  }
+  const size_t units_off = meta_bytes;
+  meta_bytes += align_up(units.size() * sizeof(LinkUnit), 256);
   const size_t base = meta_alloc(meta_bytes);
-  tables_aligned_ = true;
-  for (size_t li = 0; li < n_layers; ++li) {
-    const pf_layer_xfer &L = layers[li];
-    if (L.n_blocks == 0) continue;
-    std::memcpy(meta_host_ + base + ids_off[li], L.block_ids, L.n_blocks * sizeof(uint32_t));
-    for (uint32_t r = 0; r < L.n_ranges; ++r) {
-      RangePlan &P = plans[li * 2 + r];
-      if (P.zc_runs.size() <= 1) continue;
-      uint64_t *table = reinterpret_cast<uint64_t *>(meta_host_ + base + P.table_off);
-      uint32_t *zids = reinterpret_cast<uint32_t *>(meta_host_ + base + P.zc_ids_off);
-      size_t k = 0;
-      for (size_t j : P.zc_runs) {
-        const pf_host_run &run = L.runs[r][j];
-        for (size_t i = 0; i < run.n_blocks; ++i, ++k) {
-          table[k] = run.host_device + (uint64_t)i * run.stride_bytes;
-          zids[k] = L.block_ids[run.first_block + i];
-          if (table[k] & 15ull) tables_aligned_ = false;
-        }
-      }
-    }
-  }
+  for (size_t li = 0; li < n_layers; ++li)
+    if (layers[li].n_blocks)
+      std::memcpy(meta_host_ + base + ids_off[li], layers[li].block_ids, layers[li].n_blocks * sizeof(uint32_t));
+  for (LinkUnit &u : units) u.ids = reinterpret_cast<const uint32_t *>(meta_dev_ + base + reinterpret_cast<uintptr_t>(u.ids));
+  if (!units.empty()) std::memcpy(meta_host_ + base + units_off, units.data(), units.size() * sizeof(LinkUnit));
+  const LinkUnit *units_dev = reinterpret_cast<const LinkUnit *>(meta_dev_ + base + units_off);
   meta_upload(base, meta_bytes, stream);
 
   // ---- enqueue, layer by layer.
@@ -997,9 +1071,29 @@ void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, 
   std::fill(aux_task_dirty_.begin(), aux_task_dirty_.end(), 0);
   std::fill(aux_forked_.begin(), aux_forked_.end(), 0);
   if (host_is_src) PF_CUDA(cudaEventRecord(fork_, stream));
-  // Events of layers whose bytes are still in an open (small) group wait here until it is flushed.
+  // Zero-copy units not launched yet: [link_first, link_end) of the table.
+  size_t link_first = 0, link_end = 0;
+  uint64_t link_bytes = 0;
+  auto flush_link = [&]() {
+    if (link_end == link_first) return;
+    const uint64_t chunk_begin = link_first ? units[link_first - 1].chunk_end : 0;
+    const uint64_t chunks = units[link_end - 1].chunk_end - chunk_begin;
+    const int ctas = cfg_.link_ctas > 0 ? cfg_.link_ctas : 16;
+    cudaEvent_t t0;
+    time_begin(stream, &t0);
+    copy_units_tma<<<(int)std::min<uint64_t>(chunks, (uint64_t)ctas), 32, (size_t)kStages * kStageBytes, stream>>>(
+        units_dev + link_first, (uint32_t)(link_end - link_first), chunk_begin, host_is_src ? 0 : 1, status_dev_);
+    PF_CUDA(cudaGetLastError());
+    time_end(stream, t0, link_bytes, true, -1);
+    ++stats_.kernel_launches;
+    stats_.bytes_zero_copy += link_bytes;
+    link_first = link_end;
+    link_bytes = 0;
+  };
+  // Events of layers whose bytes are still in an open (small) group or launch wait here until it is flushed.
   std::vector<cudaEvent_t> deferred;
   bool layer_stream = false;
+  size_t run_cursor = 0;
   for (size_t li = 0; li < n_layers; ++li) {
     const pf_layer_xfer &L = layers[li];
     if (deferred.empty()) {
@@ -1009,23 +1103,21 @@ void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, 
     if (L.n_blocks) {
       const uint32_t *ids_dev = reinterpret_cast<const uint32_t *>(meta_dev_ + base + ids_off[li]);
       for (uint32_t r = 0; r < L.n_ranges; ++r) {
-        RangePlan &P = plans[li * 2 + r];
         const uint64_t dev_base = L.data_ptr + (uint64_t)r * L.kv_stride_bytes;
-        size_t zc_cursor = 0;
         for (size_t j = 0; j < L.n_runs[r]; ++j) {
           const pf_host_run &run = L.runs[r][j];
+          const uint32_t how = unit_of_run[run_cursor++];
           if (run.n_blocks == 0) continue;
-          const bool is_zc = zc_cursor < P.zc_runs.size() && P.zc_runs[zc_cursor] == j;
-          if (is_zc) {
-            ++zc_cursor;
-            if (P.zc_runs.size() > 1) continue;  // handled below in one table-driven launch
+          if (how == kLdst) {
             const Side dev{dev_base, L.block_stride_bytes, ids_dev + run.first_block, nullptr};
             const Side host{run.host_device, run.stride_bytes, nullptr, nullptr};
-            if (host_is_src)
-              launch_link(host, dev, run.n_blocks, L.range_bytes, stream, false);
-            else
-              launch_link(dev, host, run.n_blocks, L.range_bytes, stream, false);
+            if (host_is_src) launch_link(host, dev, run.n_blocks, L.range_bytes, stream, false);
+            else launch_link(dev, host, run.n_blocks, L.range_bytes, stream, false);
             stats_.bytes_zero_copy += run.n_blocks * L.range_bytes;
+            layer_stream = true;
+          } else if (how != kStaged) {
+            link_end = (size_t)how + 1;   // units were numbered in this visiting order
+            link_bytes += run.n_blocks * L.range_bytes;
             layer_stream = true;
           } else {
             // Consecutive block ids (a fresh prompt usually gets them from an ordered free list) are
@@ -1056,26 +1148,18 @@ void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, 
             staged_run(dev, run, L.range_bytes, host_is_src, stream);
           }
         }
-        if (P.zc_runs.size() > 1) {
-          const Side dev{dev_base, L.block_stride_bytes,
-                         reinterpret_cast<const uint32_t *>(meta_dev_ + base + P.zc_ids_off), nullptr};
-          const Side host{0, 0, nullptr, reinterpret_cast<const uint64_t *>(meta_dev_ + base + P.table_off)};
-          if (host_is_src)
-            launch_link(host, dev, P.zc_blocks, L.range_bytes, stream, false);
-          else
-            launch_link(dev, host, P.zc_blocks, L.range_bytes, stream, false);
-          stats_.bytes_zero_copy += P.zc_blocks * L.range_bytes;
-          layer_stream = true;
-        }
       }
     }
     cudaEvent_t done = layer_done ? (cudaEvent_t)layer_done[li] : nullptr;
     if (done) deferred.push_back(done);
-    // A layer's event should not wait for later layers - unless its bytes are so few that a DMA
-    // of its own would waste the link: then it shares the group, and the event, of its successors.
-    const bool keep_open = !group_.empty() && group_bytes_ < kMinEventGroupBytes && li + 1 < n_layers;
+    // A layer's event should not wait for later layers - unless its bytes are so few that a DMA or a
+    // launch of its own would waste the link: then it shares the group, and the event, of its successors.
+    const bool last = li + 1 == n_layers;
+    const bool keep_open = !last && ((!group_.empty() && group_bytes_ < kMinEventGroupBytes) ||
+                                     (link_end > link_first && link_bytes < kMinLinkLaunchBytes));
     if (!deferred.empty() && !keep_open) {
       flush_group();
+      flush_link();
       // Saved layers are complete when their DMAs (copy streams) and zero-copy kernels (caller's
       // stream) are; loaded layers always end with a scatter on the caller's stream.
       const bool layer_aux = std::find(aux_layer_dirty_.begin(), aux_layer_dirty_.end(), 1) != aux_layer_dirty_.end();
@@ -1092,6 +1176,7 @@ void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, 
     }
   }
   flush_group();
+  flush_link();
   if (!host_is_src) join_copy_streams(stream, aux_task_dirty_, -1);
   // The meta region is free once everything enqueued above has run.
   cudaEvent_t ev = take_event();

@@ -347,6 +347,13 @@ class PegaEngine:
         out["transfer"] = {f: getattr(m.transfer, f) for f, _ in N.BackendStats._fields_}
         return out
 
+    def phase_times(self) -> dict:
+        """{phase name: (seconds, samples)} accumulated since the engine was created; phases the
+        reference traces carry its span names (``save.pinned_alloc``, ``gpu.save_task``, ...)."""
+        t = N.PhaseTimes()
+        N.check(N.lib.pf_engine_get_phase_times(self._h, C.byref(t)))
+        return {N.lib.pf_engine_phase_name(i).decode(): (t.seconds[i], t.calls[i]) for i in range(N.PHASE_COUNT)}
+
     def block_slot_image(self, instance_id, raw_hash: bytes, slot: int, group: int = 0):
         """Host image of one stored slot, or None when the block is not resident."""
         (b,) = self.query_group_membership(instance_id, group, [raw_hash])
