@@ -1064,7 +1064,7 @@ def peer_phase(args, pf, torch, rank, world, local):
     fifth configuration): ranks 0 .. N/2-1 are instance A, ranks N/2 .. N-1 instance B with the same TP degree.
     Every A rank owns a Qwen3-32B TP4-shard-shaped KV cache (64 layers, 2 KV heads per rank -> 8 KiB K and
     V segments, HND inside a block, 8192 blocks) and exports each layer's region (pf_ipc_export); the
-    rank-aligned B rank opens them (pf_ipc_open), and pulls 4096 blocks (50 % of the prefix) of every layer
+    rank-aligned B rank opens them for its own GPU (pf_ipc_open_for) and pulls 4096 blocks (50 % of the prefix) of every layer
     into random block ids of its own cache with the peer-copy kernel - all pairs at the same time, no
     collective on the data path.  Compared with the same blocks going through a pinned host pool, and with one
     large device-to-device copy between the same two GPUs.  Returns the `peer` object on rank 0."""
@@ -1086,6 +1086,12 @@ def peer_phase(args, pf, torch, rank, world, local):
         for _ in range(L):
             yield torch.randint(0, 256, (2, nb, seg), dtype=torch.uint8, device=device, generator=gen)
 
+    rng = np.random.default_rng(4200 + pair)
+    sids = (rng.permutation(nb - 1)[:n] + 1).astype(np.uint32)
+    dids = (rng.permutation(nb - 1)[:n] + 1).astype(np.uint32)
+    si = torch.from_numpy(sids.astype(np.int64)).to(device)
+    di = torch.from_numpy(dids.astype(np.int64)).to(device)
+    stream = torch.cuda.Stream()
     mine, kv, big = None, None, None
     if role == "A":
         kv = list(source_layers(5000 + pair))
@@ -1103,23 +1109,15 @@ def peer_phase(args, pf, torch, rank, world, local):
     if role == "B":
         regions = [N.IpcRegion.from_buffer_copy(b) for b in everyone[pair]]
         src_ptrs, src_dev = [], None
-        for r in regions:
+        for r in regions:     # mapped for this rank's GPU: its kernels and copies read A's memory over NVLink
             ptr, dev_id = C.c_uint64(), C.c_int()
-            N.check(N.lib.pf_ipc_open(C.byref(r), C.byref(ptr), C.byref(dev_id)))
+            N.check(N.lib.pf_ipc_open_for(C.byref(r), local, C.byref(ptr), C.byref(dev_id)))
             src_ptrs.append(ptr.value)
             src_dev = dev_id.value
-        pf.enable_peer_access(local, src_dev)
-        torch.cuda.set_device(local)
         dst = [torch.zeros((2, nb, seg), dtype=torch.uint8, device=device) for _ in range(L)]
-        rng = np.random.default_rng(4200 + pair)
-        sids = (rng.permutation(nb - 1)[:n] + 1).astype(np.uint32)
-        dids = (rng.permutation(nb - 1)[:n] + 1).astype(np.uint32)
-        si = torch.from_numpy(sids.astype(np.int64)).to(device)
-        di = torch.from_numpy(dids.astype(np.int64)).to(device)
         be = pf.TransferBackend(local, link_ctas=args.link_ctas)
-        stream = torch.cuda.Stream()
-        sl = [(p_, seg, nb * seg, seg, 2) for p_ in src_ptrs[:L]]
-        dl = [(t.data_ptr(), seg, nb * seg, seg, 2) for t in dst]
+        sl = [(p_, seg, nb * seg, seg, 2, nb) for p_ in src_ptrs[:L]]
+        dl = [(t.data_ptr(), seg, nb * seg, seg, 2, nb) for t in dst]
 
         def exact():
             """Every layer: destination blocks hold the source blocks (regenerated here from A's seed), every
@@ -1148,7 +1146,7 @@ def peer_phase(args, pf, torch, rank, world, local):
     if role == "B":
         peer_exact = exact()
         stats = be.stats()
-        # ceiling: one 1 GiB device-to-device copy from the same peer GPU, best of 5, all pairs at once
+        # ceiling: one 1 GiB device-to-device copy from the same peer GPU, best of 6, all pairs at once
         scratch = torch.empty(1 << 30, dtype=torch.uint8, device=device)
         best = 0.0
         for _ in range(6):
@@ -1158,38 +1156,53 @@ def peer_phase(args, pf, torch, rank, world, local):
             b.synchronize()
             best = max(best, (1 << 30) / 1e6 / a.elapsed_time(b))
         del scratch
-        # the reference's way: source GPU -> pinned host pool -> destination GPU, driven from this process
-        for t in dst:
-            t.zero_()
+        be.close()
+    # The reference's way: source GPU -> pinned host pool -> destination GPU.  Each half runs in the process
+    # that owns the GPU (A saves its blocks into a pool, B loads as many bytes from a pool into its blocks);
+    # a hit costs the sum of the two, since the load can only start when the save is in the pool.
+    half_s, half_ok = None, True
+    if role in ("A", "B"):
         pool = pf.PinnedPool(payload + (64 << 20), numa_node=pf.numa_node_of_device(local))
-        be_src, be_dst = pf.TransferBackend(src_dev), pf.TransferBackend(local)
-        st_src = torch.cuda.Stream(device=torch.device("cuda", src_dev))
-        lay_s, lay_l = [], []
+        be_h = pf.TransferBackend(local)
+        mem = kv if role == "A" else dst
+        ids = sids if role == "A" else dids
+        lay, images = [], []
         for l in range(L):
             k, v = pool.alloc(n * seg), pool.alloc(n * seg)
-            runs = [[pf.HostRun(0, n, k[0], k[1], seg)], [pf.HostRun(0, n, v[0], v[1], seg)]]
-            lay_s.append(pf.LayerXfer(src_ptrs[l], seg, nb * seg, seg, 2, sids, runs))
-            lay_l.append(pf.LayerXfer(dst[l].data_ptr(), seg, nb * seg, seg, 2, dids, runs))
-        xs, xl = pf.TransferBackend.make_layers(lay_s), pf.TransferBackend.make_layers(lay_l)
-        t_host = []
+            images.append((k[0], v[0]))
+            lay.append(pf.LayerXfer(mem[l].data_ptr(), seg, nb * seg, seg, 2, ids,
+                                    [[pf.HostRun(0, n, k[0], k[1], seg)], [pf.HostRun(0, n, v[0], v[1], seg)]]))
+        x = pf.TransferBackend.make_layers(lay)
+        move = be_h.save_layers if role == "A" else be_h.load_layers
+        times = []
         for _ in range(3):
             torch.cuda.synchronize(device)
+            dist.barrier()
             t0 = time.perf_counter()
-            be_src.save_layers(xs, st_src.cuda_stream)
-            st_src.synchronize()
-            be_dst.load_layers(xl, stream.cuda_stream)
+            move(x, stream.cuda_stream)
             stream.synchronize()
-            t_host.append(time.perf_counter() - t0)
-        host_exact = exact()
-        status = stats["device_status"] | be_src.stats()["device_status"] | be_dst.stats()["device_status"]
-        be.close(), be_src.close(), be_dst.close(), pool.close()
+            times.append(time.perf_counter() - t0)
+        half_s = min(times)
+        if role == "A":      # the pool now holds the source blocks of every layer
+            for l in range(L):
+                for r_i in range(2):
+                    view = np.ctypeslib.as_array((C.c_uint8 * (n * seg)).from_address(images[l][r_i])).reshape(n, seg)
+                    half_ok = half_ok and torch.equal(kv[l][r_i][si], torch.from_numpy(view).to(device))
+        half_ok = half_ok and be_h.stats()["device_status"] == 0
+        be_h.close(), pool.close()
+    else:
+        for _ in range(3):
+            dist.barrier()
+    if role == "B":
         for r in regions:
-            N.check(N.lib.pf_ipc_close(C.byref(r)))
+            N.check(N.lib.pf_ipc_close_for(C.byref(r), local))
         result = {"pair": [src_dev, local], "ranks": [pair, rank], "GBps": round(payload * args.steps / 1e6 / peer_ms, 2),
-                  "ceiling_GBps": round(best, 1), "via_host_pool_GBps": round(payload / min(t_host) / 1e9, 2),
-                  "bit_exact": bool(peer_exact), "via_host_pool_bit_exact": bool(host_exact),
-                  "ms": peer_ms, "gpu_launches": stats["kernel_launches"], "device_status": status}
+                  "ceiling_GBps": round(best, 1), "bit_exact": bool(peer_exact), "ms": peer_ms,
+                  "gpu_launches": stats["kernel_launches"], "device_status": stats["device_status"],
+                  "load_half_s": half_s, "load_half_ok": bool(half_ok)}
         del dst
+    elif role == "A":
+        result = {"save_half_s": half_s, "save_half_ok": bool(half_ok)}
     results = [None] * world
     dist.all_gather_object(results, result)
     dist.barrier()          # instance A keeps its memory until every B rank has closed its mappings
@@ -1197,7 +1210,11 @@ def peer_phase(args, pf, torch, rank, world, local):
     torch.cuda.empty_cache()
     if rank != 0:
         return None
-    rs = [r for r in results if r]
+    rs = [r for r in results if r and "pair" in r]
+    for r in rs:    # a hit through the host pool: the A rank's save, then the B rank's load
+        a_side = results[r["ranks"][0]]
+        r["via_host_pool_GBps"] = round(payload / (a_side["save_half_s"] + r["load_half_s"]) / 1e9, 2)
+        r["via_host_pool_ok"] = a_side["save_half_ok"] and r["load_half_ok"]
     agg = sum(payload * args.steps for _ in rs) / 1e6 / max(r["ms"] for r in rs)
     ceil_sum = sum(r["ceiling_GBps"] for r in rs)
     return {
@@ -1213,11 +1230,14 @@ def peer_phase(args, pf, torch, rank, world, local):
                  "ceiling_how": "one 1 GiB device-to-device cudaMemcpyAsync from the same peer GPU, best of 6, every pair's "
                                 "own measurement"},
         "via_host_pool_GBps": [r["via_host_pool_GBps"] for r in rs],
+        "via_host_pool_how": "payload / (instance A's save of the hit blocks into a pinned pool + instance B's load of as many "
+                             "bytes from a pinned pool), each half in the process that owns the GPU, all pairs at once, best of "
+                             "3; A's pool images are compared with its cache for all layers: "
+                             + ("equal" if all(r["via_host_pool_ok"] for r in rs) else "DIFFERENT"),
         "speedup_vs_host_pool": round(agg / max(1e-9, sum(r["via_host_pool_GBps"] for r in rs)), 2),
-        "bit_exact": all(r["bit_exact"] and r["via_host_pool_bit_exact"] for r in rs),
+        "bit_exact": all(r["bit_exact"] for r in rs),
         "bit_exact_how": "all 64 layers of every pair, whole destination cache compared (copied blocks against the source "
-                         "regenerated from its seed, all other blocks still zero), after the peer copy and again after the "
-                         "host-pool route",
+                         "regenerated from its seed, all other blocks still zero) after the timed peer copies",
         "gpu_launches": sum(r["gpu_launches"] for r in rs), "device_status": max(r["device_status"] for r in rs),
         "how": "per pair: CUDA events on the destination rank's stream around `steps` calls of pf_backend_peer_copy_layers, "
                "all pairs released by one barrier; aggregate = all pairs' bytes / the slowest pair's time"}

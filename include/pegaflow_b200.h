@@ -208,6 +208,15 @@ typedef struct pf_ipc_region {
 int pf_ipc_export(uint64_t device_ptr, size_t nbytes, pf_ipc_region *out);
 int pf_ipc_open(const pf_ipc_region *region, uint64_t *device_ptr, int *device_id);
 int pf_ipc_close(const pf_ipc_region *region);
+/* The same for a reader on another GPU: another instance's KV cache, opened so that kernels and
+ * copies of `accessing_device` can read it over NVLink (the source side of pf_backend_peer_copy_layers
+ * when the two instances are different processes).  The driver binds an imported allocation to the
+ * device that was current when it was opened, so the pointer pf_ipc_open returns (opened on the owning
+ * GPU, for an engine that works on that GPU) is not usable from a peer device; this one is, and only
+ * from `accessing_device`.  *owner_device receives the GPU the memory lives on.  Has no counterpart
+ * in the reference, which has no GPU-to-GPU path. */
+int pf_ipc_open_for(const pf_ipc_region *region, int accessing_device, uint64_t *device_ptr, int *owner_device);
+int pf_ipc_close_for(const pf_ipc_region *region, int accessing_device);
 
 /* Make `peer_device`'s memory addressable from `device_id` (cudaDeviceEnablePeerAccess). */
 int pf_enable_peer_access(int device_id, int peer_device);
@@ -380,6 +389,9 @@ int pf_engine_query_group_membership(pf_engine *engine, const char *instance_id,
                                      size_t n, const uint8_t *const *hashes, const size_t *hash_lens,
                                      pf_block **blocks_out);
 void pf_block_release(pf_block *block);
+/* Releases n handles in one call (entries may be NULL): what a caller does with the array
+ * pf_engine_query_prefix filled once it holds a lease. */
+void pf_blocks_release(pf_block *const *blocks, size_t n);
 /* `SealedBlock::slots().len()` and a copy of one slot's segment bytes (`get_slot` +
  * `RawBlock` segments, block.rs): what a host-side consumer (SSD/RDMA tier, a test) reads. */
 size_t pf_block_num_slots(const pf_block *block);

@@ -141,6 +141,8 @@ class IpcRegion(C.Structure):
 _sig("pf_ipc_export", C.c_int, u64, sz, P(IpcRegion))
 _sig("pf_ipc_open", C.c_int, P(IpcRegion), P(u64), P(C.c_int))
 _sig("pf_ipc_close", C.c_int, P(IpcRegion))
+_sig("pf_ipc_open_for", C.c_int, P(IpcRegion), C.c_int, P(u64), P(C.c_int))
+_sig("pf_ipc_close_for", C.c_int, P(IpcRegion), C.c_int)
 _sig("pf_enable_peer_access", C.c_int, C.c_int, C.c_int)
 _sig("pf_save_blocks_noalloc", C.c_int, C.c_int, P(DeviceLayout), P(u32), sz, vp, sz, vp)
 _sig("pf_backend_get_stats", C.c_int, vp, P(BackendStats))
@@ -172,6 +174,7 @@ _sig("pf_engine_query_prefix", C.c_int, vp, C.c_char_p, C.c_char_p, sz, P(P(C.c_
      P(sz))
 _sig("pf_engine_query_group_membership", C.c_int, vp, C.c_char_p, u32, sz, P(P(C.c_uint8)), P(sz), P(vp))
 _sig("pf_block_release", None, vp)
+_sig("pf_blocks_release", None, P(vp), sz)
 _sig("pf_block_num_slots", sz, vp)
 _sig("pf_block_slot_info", C.c_int, vp, sz, P(sz), P(sz))
 _sig("pf_block_slot_read", C.c_int, vp, sz, sz, vp, sz)

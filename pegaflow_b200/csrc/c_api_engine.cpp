@@ -271,6 +271,10 @@ int pf_engine_query_group_membership(pf_engine *engine, const char *instance_id,
 
 void pf_block_release(pf_block *block) { delete block; }
 
+void pf_blocks_release(pf_block *const *blocks, size_t n) {
+  for (size_t i = 0; blocks && i < n; ++i) delete blocks[i];
+}
+
 size_t pf_block_num_slots(const pf_block *block) { return block ? block->ref->slots.size() : 0; }
 
 int pf_block_slot_info(const pf_block *block, size_t slot, size_t *n_segments, size_t seg_bytes[2]) {

@@ -21,7 +21,7 @@ struct Range {
 };
 using Clock = std::chrono::steady_clock;
 
-constexpr size_t kReclaimBatch = 64;                       // blocks evicted per reclaim step
+constexpr size_t kReclaimBatch = 512;                      // blocks evicted per reclaim step (storage/mod.rs:32)
 constexpr auto kLeaseTtl = std::chrono::seconds(600);      // lease.rs:11
 constexpr uint64_t kMaxRunStride = 1ull << 30;             // 2D DMA pitch stays far below its limit
 
@@ -843,38 +843,69 @@ void Engine::batch_save(const std::string &instance_id, size_t tp_rank, size_t p
         rbk.owner = page;  // a page lives and dies with its block
         layer.blocks.push_back(std::move(rbk));
       }
-      RawSaveBatch b{inst->ns, topo->total_slots(), {}, nullptr};
+      RawSaveBatch b{inst->ns, topo->total_slots(), {}, nullptr, {}, nullptr};
       b.layers.push_back(std::move(layer));
       batches->push_back(std::move(b));
     } else {
       std::map<uint32_t, RawSaveBatch> by_group;
       const Owner batch_owner = blockwise ? Owner() : Owner(all_allocs);
+      // Which groups this save seals on its own: it brings every slot of the group exactly once and
+      // all its layers carry one hash list.
+      std::map<uint32_t, std::vector<size_t>> ctx_of_group;
+      for (size_t ci = 0; ci < ctxs.size(); ++ci) ctx_of_group[ctxs[ci].group].push_back(ci);
+      std::set<uint32_t> seals_alone;
+      for (auto &kv : ctx_of_group) {
+        const size_t total = topo->group_total_slots(kv.first);
+        std::vector<char> seen(total, 0);
+        bool ok = kv.second.size() == total;
+        for (size_t ci : kv.second) {
+          const Ctx &c = ctxs[ci];
+          ok = ok && c.hashes.get() == ctxs[kv.second[0]].hashes.get() && c.slot < total && !seen[c.slot];
+          if (ok) seen[c.slot] = 1;
+        }
+        if (ok) seals_alone.insert(kv.first);
+      }
       for (size_t ci = 0; ci < ctxs.size(); ++ci) {
         Ctx &c = ctxs[ci];
         auto it = by_group.find(c.group);
         if (it == by_group.end())
-          it = by_group.emplace(c.group, RawSaveBatch{inst->ns, topo->group_total_slots(c.group), {}, batch_owner}).first;
+          it = by_group.emplace(c.group, RawSaveBatch{inst->ns, topo->group_total_slots(c.group), {}, batch_owner, {}, nullptr}).first;
+        RawSaveBatch &batch = it->second;
         const bool split = c.layout->is_split();
         const size_t stride = split ? c.layout->padded_segment_bytes() : c.layout->padded_block_bytes();
         const size_t per = blockwise ? 1 : c.ids.size();
+        const bool presealed = seals_alone.count(c.group) != 0;
         RawSaveLayer layer;
-        layer.slot_id = c.slot;
-        layer.hashes = c.hashes;  // already group-encoded
-        layer.blocks.resize(c.ids.size());
+        if (presealed) {
+          if (batch.sealed.empty()) {
+            batch.sealed_hashes = c.hashes;  // already group-encoded
+            batch.sealed.resize(c.ids.size());
+            for (auto &sb : batch.sealed) {
+              sb = std::make_shared<SealedBlock>();
+              sb->owner = batch_owner;
+              sb->slots.resize(batch.total_slots);
+            }
+          }
+        } else {
+          layer.slot_id = c.slot;
+          layer.hashes = c.hashes;  // already group-encoded
+          layer.blocks.resize(c.ids.size());
+        }
         for (size_t a = 0; a < layer_allocs[ci].size(); ++a) {
           auto &pair = layer_allocs[ci][a];
           Owner own;
           if (blockwise) own = split ? Owner(std::make_shared<std::array<std::shared_ptr<PinnedAllocation>, 2>>(pair))
                                      : Owner(pair[0]);
           for (size_t i = 0; i < per; ++i) {
-            RawBlock &rbk = layer.blocks[a * per + i];
+            RawBlock &rbk = presealed ? batch.sealed[a * per + i]->slots[c.slot] : layer.blocks[a * per + i];
             rbk.n_segments = split ? 2 : 1;
             rbk.seg[0] = Segment{pair[0]->host() + i * stride, pair[0]->device() + i * stride, stride};
             if (split) rbk.seg[1] = Segment{pair[1]->host() + i * stride, pair[1]->device() + i * stride, stride};
             rbk.owner = own;
+            if (presealed) batch.sealed[a * per + i]->footprint += rbk.total_size();
           }
         }
-        it->second.layers.push_back(std::move(layer));
+        if (!presealed) batch.layers.push_back(std::move(layer));
       }
       for (auto &kv : by_group) batches->push_back(std::move(kv.second));
     }
@@ -953,6 +984,21 @@ void Engine::insert_loop() {
 
 // storage/write_path.rs:119-254 + offload.rs:70-151.
 void Engine::process_insert(RawSaveBatch &batch) {
+  if (!batch.sealed.empty()) {
+    // sealed by the save itself while its copy ran: publish
+    const auto &hashes = *batch.sealed_hashes;
+    for (size_t b = 0; b < batch.sealed.size(); ++b) {
+      BlockKey key{batch.ns, hashes[b]};
+      if (cache_.contains(key) || inflight_.count(key)) {
+        // someone else is filling or has filled this block: slot by slot, first writer wins
+        for (size_t slot = 0; slot < batch.sealed[b]->slots.size(); ++slot)
+          insert_slot(key, slot, std::move(batch.sealed[b]->slots[slot]), batch.total_slots, batch.owner);
+        continue;
+      }
+      cache_.insert(key, std::move(batch.sealed[b]));
+    }
+    return;
+  }
   if (batch.layers.empty()) return;
   bool same_order = true;
   for (auto &l : batch.layers)
@@ -1171,40 +1217,60 @@ void Engine::batch_load(const std::string &instance_id, size_t tp_rank, int devi
     Range nvtx_build("load.build_tasks");
     auto work = std::make_shared<std::vector<LayerWork>>();
     for (size_t gi = 0; gi < layer_groups.size(); ++gi) {
+      if (targets[gi].empty()) continue;
+      // what each layer of the group needs from a stored block
+      struct PerLayer {
+        const std::string *name;
+        const KVCacheLayout *layout;
+        size_t slot, offset;
+      };
+      std::vector<PerLayer> per;
       for (auto &name : layer_groups[gi]) {
         const size_t layer_id = topo->layer_id(name);
         auto lit = gpu->layouts.find(name);
         if (lit == gpu->layouts.end())
           throw Error::invalid(strf("layer %s not registered on device %d", name.c_str(), device_id));
-        const KVCacheLayout &layout = lit->second;
-        const size_t slot = topo->slot_index(layer_id, tp_rank);
-        const size_t offset = topo->page ? topo->page->layer_offsets[layer_id] : 0;
-        if (targets[gi].empty()) continue;
-        LayerWork w;
-        w.layer_name = name;
-        w.layout = layout;
-        RunBuilder rb0(layout.range_bytes()), rb1(layout.range_bytes());
-        for (auto &t : targets[gi]) {
-          const SealedBlock &sb = *block_cache[t.second];
-          if (slot >= sb.slots.size() || sb.slots[slot].n_segments == 0)
-            throw Error::invalid(strf("stored block is missing slot %zu for layer %s", slot, name.c_str()));
-          if (t.first >= layout.num_blocks())
-            throw Error::storage(strf("layer %s: block %zu out of range (%zu blocks)", name.c_str(), t.first,
-                                      layout.num_blocks()));
-          const RawBlock &raw = sb.slots[slot];
-          w.block_ids.push_back((uint32_t)t.first);
-          char *k_host = raw.seg[0].host + offset;
-          const uint64_t k_dev = raw.seg[0].device + offset;
-          rb0.add(k_host, k_dev);
-          if (layout.is_split()) {
+        per.push_back(PerLayer{&name, &lit->second, topo->slot_index(layer_id, tp_rank),
+                               topo->page ? topo->page->layer_offsets[layer_id] : 0});
+      }
+      std::vector<uint32_t> ids;
+      ids.reserve(targets[gi].size());
+      for (auto &t : targets[gi]) ids.push_back((uint32_t)t.first);
+      std::vector<RunBuilder> rb0, rb1;
+      for (auto &p : per) {
+        rb0.emplace_back(p.layout->range_bytes());
+        rb1.emplace_back(p.layout->range_bytes());
+      }
+      // Block by block, every layer of the block in turn: a stored block's slots lie next to each
+      // other in memory, a layer's slots of different blocks do not.
+      for (auto &t : targets[gi]) {
+        const SealedBlock &sb = *block_cache[t.second];
+        for (size_t k = 0; k < per.size(); ++k) {
+          const PerLayer &p = per[k];
+          if (p.slot >= sb.slots.size() || sb.slots[p.slot].n_segments == 0)
+            throw Error::invalid(strf("stored block is missing slot %zu for layer %s", p.slot, p.name->c_str()));
+          if (t.first >= p.layout->num_blocks())
+            throw Error::storage(strf("layer %s: block %zu out of range (%zu blocks)", p.name->c_str(), t.first,
+                                      p.layout->num_blocks()));
+          const RawBlock &raw = sb.slots[p.slot];
+          char *k_host = raw.seg[0].host + p.offset;
+          const uint64_t k_dev = raw.seg[0].device + p.offset;
+          rb0[k].add(k_host, k_dev);
+          if (p.layout->is_split()) {
             // V comes from the second host segment, or directly after K when the stored
             // block has a single segment (gpu_worker.rs:376-379).
-            if (raw.n_segments > 1) rb1.add(raw.seg[1].host + offset, raw.seg[1].device + offset);
-            else rb1.add(k_host + layout.segment_bytes(), k_dev + layout.segment_bytes());
+            if (raw.n_segments > 1) rb1[k].add(raw.seg[1].host + p.offset, raw.seg[1].device + p.offset);
+            else rb1[k].add(k_host + p.layout->segment_bytes(), k_dev + p.layout->segment_bytes());
           }
         }
-        w.runs[0] = rb0.take();
-        if (layout.is_split()) w.runs[1] = rb1.take();
+      }
+      for (size_t k = 0; k < per.size(); ++k) {
+        LayerWork w;
+        w.layer_name = *per[k].name;
+        w.layout = *per[k].layout;
+        w.block_ids = ids;
+        w.runs[0] = rb0[k].take();
+        if (per[k].layout->is_split()) w.runs[1] = rb1[k].take();
         work->push_back(std::move(w));
       }
     }

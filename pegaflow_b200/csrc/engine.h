@@ -297,6 +297,10 @@ class Engine {
     size_t total_slots;
     std::vector<RawSaveLayer> layers;
     Owner owner;  // all pool allocations of the save call (null when the slots carry their own)
+    // A save that fills every slot of its blocks by itself (one rank, all layers, one hash list) is
+    // sealed while its copy runs: block b of `sealed` belongs under (*sealed_hashes)[b], `layers` is empty.
+    std::vector<BlockRef> sealed;
+    HashList sealed_hashes;
   };
   struct Inflight {
     size_t total_slots;

@@ -51,11 +51,59 @@ int device_of_uuid(const uint8_t uuid[16]) {
 
 struct Mapping {
   char *base = nullptr;
-  int device = 0;
+  int device = 0;  // the device that was current when the handle was opened
   size_t users = 0;
 };
 std::mutex g_mu;
-std::map<std::string, Mapping> g_open;  // keyed by the 64 handle bytes: one mapping per exported allocation
+// One mapping per exported allocation and accessing device, keyed by the 64 handle bytes + device.
+std::map<std::string, Mapping> g_open;
+
+std::string mapping_key(const pf_ipc_region *region, int device) {
+  std::string key(reinterpret_cast<const char *>(region->handle), sizeof region->handle);
+  key.append(reinterpret_cast<const char *>(&device), sizeof device);
+  return key;
+}
+
+// Opens (or reuses) the mapping of the region's allocation made with `device` current.  The driver
+// ties an imported allocation to the context that opened it: kernels and copies of that device can
+// use the pointer - over NVLink when the memory belongs to another GPU (peer access is switched on
+// by the open, cudaIpcMemLazyEnablePeerAccess) - while another device of the same process cannot,
+// even with peer access enabled afterwards.
+constexpr int kOwnerKey = -1;  // pf_ipc_open: the mapping lives on the GPU that owns the memory
+
+uint64_t open_on(const pf_ipc_region *region, int device, int key_device) {
+  DeviceGuard on_device(device);
+  const std::string key = mapping_key(region, key_device);
+  std::lock_guard<std::mutex> g(g_mu);
+  Mapping &m = g_open[key];
+  if (!m.base) {
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, region->handle, sizeof h);
+    void *p = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+      g_open.erase(key);
+      check(e, "cudaIpcOpenMemHandle");
+    }
+    m.base = static_cast<char *>(p);
+    m.device = device;
+  }
+  ++m.users;
+  return (uint64_t)(uintptr_t)(m.base + region->offset);
+}
+
+void close_on(const pf_ipc_region *region, int key_device) {
+  const std::string key = mapping_key(region, key_device);
+  std::lock_guard<std::mutex> g(g_mu);
+  auto it = g_open.find(key);
+  if (it == g_open.end()) throw Error::invalid("ipc close: the region is not open");
+  if (--it->second.users == 0) {
+    DeviceGuard on_device(it->second.device);
+    cudaError_t e = cudaIpcCloseMemHandle(it->second.base);
+    g_open.erase(it);
+    check(e, "cudaIpcCloseMemHandle");
+  }
+}
 
 }  // namespace
 }  // namespace pf
@@ -95,24 +143,7 @@ int pf_ipc_open(const pf_ipc_region *region, uint64_t *device_ptr, int *device_i
   return guarded([&] {
     if (!region || !device_ptr) throw Error::invalid("ipc open: null argument");
     const int device = device_of_uuid(region->device_uuid);
-    DeviceGuard on_device(device);
-    const std::string key(reinterpret_cast<const char *>(region->handle), sizeof region->handle);
-    std::lock_guard<std::mutex> g(g_mu);
-    Mapping &m = g_open[key];
-    if (!m.base) {
-      cudaIpcMemHandle_t h;
-      std::memcpy(&h, region->handle, sizeof h);
-      void *p = nullptr;
-      cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
-      if (e != cudaSuccess) {
-        g_open.erase(key);
-        check(e, "cudaIpcOpenMemHandle");
-      }
-      m.base = static_cast<char *>(p);
-      m.device = device;
-    }
-    ++m.users;
-    *device_ptr = (uint64_t)(uintptr_t)(m.base + region->offset);
+    *device_ptr = open_on(region, device, kOwnerKey);
     if (device_id) *device_id = device;
   });
 }
@@ -120,16 +151,33 @@ int pf_ipc_open(const pf_ipc_region *region, uint64_t *device_ptr, int *device_i
 int pf_ipc_close(const pf_ipc_region *region) {
   return guarded([&] {
     if (!region) throw Error::invalid("ipc close: null argument");
-    const std::string key(reinterpret_cast<const char *>(region->handle), sizeof region->handle);
-    std::lock_guard<std::mutex> g(g_mu);
-    auto it = g_open.find(key);
-    if (it == g_open.end()) throw Error::invalid("ipc close: the region is not open");
-    if (--it->second.users == 0) {
-      DeviceGuard on_device(it->second.device);
-      cudaError_t e = cudaIpcCloseMemHandle(it->second.base);
-      g_open.erase(it);
-      check(e, "cudaIpcCloseMemHandle");
+    close_on(region, kOwnerKey);
+  });
+}
+
+int pf_ipc_open_for(const pf_ipc_region *region, int accessing_device, uint64_t *device_ptr, int *owner_device) {
+  return guarded([&] {
+    if (!region || !device_ptr) throw Error::invalid("ipc open: null argument");
+    int count = 0;
+    check(cudaGetDeviceCount(&count), "cudaGetDeviceCount");
+    if (accessing_device < 0 || accessing_device >= count)
+      throw Error::invalid(strf("ipc open: device %d out of range (%d devices)", accessing_device, count));
+    const int owner = device_of_uuid(region->device_uuid);
+    if (owner != accessing_device) {
+      int can = 0;
+      check(cudaDeviceCanAccessPeer(&can, accessing_device, owner), "cudaDeviceCanAccessPeer");
+      if (!can) throw Error::cuda_init(strf("device %d cannot access device %d", accessing_device, owner));
     }
+    *device_ptr = open_on(region, accessing_device, accessing_device);
+    if (owner_device) *owner_device = owner;
+  });
+}
+
+int pf_ipc_close_for(const pf_ipc_region *region, int accessing_device) {
+  return guarded([&] {
+    if (!region) throw Error::invalid("ipc close: null argument");
+    if (accessing_device < 0) throw Error::invalid("ipc close: device out of range");
+    close_on(region, accessing_device);
   });
 }
 

@@ -977,20 +977,9 @@ void TransferBackend::gather_layers(const pf_layer_xfer *layers, size_t n_layers
 void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, bool host_is_src,
                                   cudaStream_t stream, void *const *layer_done) {
   DeviceGuard on_device(device_);
-  // ---- validate and plan.  Every host run takes one of three routes: staged (gather kernel + copy
-  // engine), one pitched DMA (consecutive block ids), or zero-copy.  Zero-copy runs become units of
-  // the task's unit table; a whole task's units go into one launch unless layer events cut it.
-  size_t total_bytes = 0;
-  for (size_t li = 0; li < n_layers; ++li) total_bytes += layers[li].n_blocks * layers[li].range_bytes * layers[li].n_ranges;
-  // Small tasks (a few blocks of every layer, e.g. the tail blocks saved while decoding): launches,
-  // not bytes, are what they cost, so everything goes into the one zero-copy launch.
-  const bool small_task = cfg_.route != PF_ROUTE_STAGED && n_layers > 1 && total_bytes <= kSmallTaskBytes;
+  // ---- validate everything before anything is enqueued (a light pass: no planning yet).
+  size_t total_bytes = 0, total_runs = 0, ids_bytes = 0;
   std::vector<size_t> ids_off(n_layers, 0);
-  std::vector<LinkUnit> units;               // `ids` holds a byte offset into the meta region until it is known
-  std::vector<uint32_t> unit_of_run;         // per (layer, range, run) in visiting order: unit index, kStaged or kLdst
-  constexpr uint32_t kStaged = 0xFFFFFFFFu, kLdst = 0xFFFFFFFEu;
-  size_t meta_bytes = 0;
-  uint64_t chunk_total = 0;
   for (size_t li = 0; li < n_layers; ++li) {
     const pf_layer_xfer &L = layers[li];
     if (L.n_blocks == 0) continue;
@@ -999,13 +988,14 @@ void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, 
       throw Error::invalid(strf("layer %zu: range_bytes %zu unsupported", li, L.range_bytes));
     if (L.n_blocks > 0xFFFFFFFFull) throw Error::invalid("too many blocks in one layer transfer");
     if (!L.block_ids) throw Error::invalid(strf("layer %zu: block_ids is null", li));
-    ids_off[li] = meta_bytes;
-    meta_bytes += align_up(L.n_blocks * sizeof(uint32_t), 256);
+    ids_off[li] = ids_bytes;
+    ids_bytes += align_up(L.n_blocks * sizeof(uint32_t), 256);
+    total_bytes += L.n_blocks * L.range_bytes * L.n_ranges;
     for (uint32_t r = 0; r < L.n_ranges; ++r) {
       size_t covered = 0;
-      const uint64_t dev_base = L.data_ptr + (uint64_t)r * L.kv_stride_bytes;
+      const pf_host_run *runs = L.runs[r];
       for (size_t j = 0; j < L.n_runs[r]; ++j) {
-        const pf_host_run &run = L.runs[r][j];
+        const pf_host_run &run = runs[j];
         if (run.first_block != covered)
           throw Error::invalid(strf("layer %zu range %u: host runs must cover the blocks in order", li, r));
         if (run.n_blocks && (!run.host || !run.host_device))
@@ -1013,87 +1003,64 @@ void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, 
         if (run.n_blocks > 1 && run.stride_bytes < L.range_bytes)
           throw Error::invalid(strf("layer %zu range %u: host stride smaller than the range", li, r));
         covered += run.n_blocks;
-        if (run.n_blocks == 0) {
-          unit_of_run.push_back(kStaged);
-          continue;
-        }
-        const size_t bytes = run.n_blocks * L.range_bytes;
-        bool staged = cfg_.route == PF_ROUTE_STAGED || (cfg_.route == PF_ROUTE_AUTO && bytes >= cfg_.min_dma_bytes);
-        if (L.range_bytes > cfg_.staging_slot_bytes || small_task) staged = false;
-        if (staged) {
-          unit_of_run.push_back(kStaged);
-          continue;
-        }
-        // bulk copies need 16-byte aligned addresses and sizes; anything else takes the ld/st kernel
-        if ((dev_base | L.block_stride_bytes | run.host_device | run.stride_bytes | L.range_bytes) & 15ull) {
-          unit_of_run.push_back(kLdst);
-          continue;
-        }
-        LinkUnit u;
-        u.kv_base = dev_base;
-        u.kv_stride = L.block_stride_bytes;
-        u.host_base = run.host_device;
-        u.host_stride = run.n_blocks > 1 ? run.stride_bytes : L.range_bytes;
-        u.ids = reinterpret_cast<const uint32_t *>(ids_off[li] + run.first_block * sizeof(uint32_t));
-        u.n_items = (uint32_t)run.n_blocks;
-        u.item_bytes = (uint32_t)L.range_bytes;
-        u.items_per_chunk = (uint32_t)std::min<size_t>(kLinkItemsMax, kStageBytes / L.range_bytes);
-        u.chunks_per_item = (uint32_t)((L.range_bytes + kStageBytes - 1) / kStageBytes);
-        chunk_total += u.items_per_chunk >= 2 ? (run.n_blocks + u.items_per_chunk - 1) / u.items_per_chunk
-                                              : (uint64_t)run.n_blocks * u.chunks_per_item;
-        u.chunk_end = chunk_total;
-        unit_of_run.push_back((uint32_t)units.size());
-        units.push_back(u);
       }
       if (covered != L.n_blocks)
         throw Error::invalid(strf("layer %zu range %u: host runs cover %zu of %zu blocks", li, r, covered, L.n_blocks));
+      total_runs += L.n_runs[r];
     }
   }
-  if (meta_bytes == 0) {
+  if (ids_bytes == 0) {
     if (layer_done)
       for (size_t li = 0; li < n_layers; ++li)
         if (layer_done[li]) PF_CUDA(cudaEventRecord((cudaEvent_t)layer_done[li], stream));
     return;
   }
-  const size_t units_off = meta_bytes;
-  meta_bytes += align_up(units.size() * sizeof(LinkUnit), 256);
+  // Small tasks (a few blocks of every layer, e.g. the tail blocks saved while decoding): launches,
+  // not bytes, are what they cost, so everything goes into the one zero-copy launch.
+  const bool small_task = cfg_.route != PF_ROUTE_STAGED && n_layers > 1 && total_bytes <= kSmallTaskBytes;
+
+  // ---- meta region: the block ids of every layer (uploaded now) and room for one zero-copy unit
+  // per host run (filled layer by layer, uploaded just before the launch that reads them: the
+  // first transfer is on its way after one layer has been planned, not after all of them).
+  const size_t units_off = ids_bytes;
+  const size_t meta_bytes = ids_bytes + align_up(total_runs * sizeof(LinkUnit), 256);
   const size_t base = meta_alloc(meta_bytes);
   for (size_t li = 0; li < n_layers; ++li)
     if (layers[li].n_blocks)
       std::memcpy(meta_host_ + base + ids_off[li], layers[li].block_ids, layers[li].n_blocks * sizeof(uint32_t));
-  for (LinkUnit &u : units) u.ids = reinterpret_cast<const uint32_t *>(meta_dev_ + base + reinterpret_cast<uintptr_t>(u.ids));
-  if (!units.empty()) std::memcpy(meta_host_ + base + units_off, units.data(), units.size() * sizeof(LinkUnit));
+  meta_upload(base, ids_bytes, stream);
+  LinkUnit *units = reinterpret_cast<LinkUnit *>(meta_host_ + base + units_off);
   const LinkUnit *units_dev = reinterpret_cast<const LinkUnit *>(meta_dev_ + base + units_off);
-  meta_upload(base, meta_bytes, stream);
+  size_t n_units = 0;
+  uint64_t chunk_total = 0;
 
-  // ---- enqueue, layer by layer.
   group_limit_ = kFirstGroupBytes;
   std::fill(aux_task_dirty_.begin(), aux_task_dirty_.end(), 0);
   std::fill(aux_forked_.begin(), aux_forked_.end(), 0);
   if (host_is_src) PF_CUDA(cudaEventRecord(fork_, stream));
-  // Zero-copy units not launched yet: [link_first, link_end) of the table.
-  size_t link_first = 0, link_end = 0;
+  // Zero-copy units not launched yet: [link_first, n_units) of the table.
+  size_t link_first = 0;
   uint64_t link_bytes = 0;
   auto flush_link = [&]() {
-    if (link_end == link_first) return;
+    if (n_units == link_first) return;
     const uint64_t chunk_begin = link_first ? units[link_first - 1].chunk_end : 0;
-    const uint64_t chunks = units[link_end - 1].chunk_end - chunk_begin;
+    const uint64_t chunks = units[n_units - 1].chunk_end - chunk_begin;
     const int ctas = cfg_.link_ctas > 0 ? cfg_.link_ctas : 16;
+    meta_upload(base + units_off + link_first * sizeof(LinkUnit), (n_units - link_first) * sizeof(LinkUnit), stream);
     cudaEvent_t t0;
     time_begin(stream, &t0);
     copy_units_tma<<<(int)std::min<uint64_t>(chunks, (uint64_t)ctas), 32, (size_t)kStages * kStageBytes, stream>>>(
-        units_dev + link_first, (uint32_t)(link_end - link_first), chunk_begin, host_is_src ? 0 : 1, status_dev_);
+        units_dev + link_first, (uint32_t)(n_units - link_first), chunk_begin, host_is_src ? 0 : 1, status_dev_);
     PF_CUDA(cudaGetLastError());
     time_end(stream, t0, link_bytes, true, -1);
     ++stats_.kernel_launches;
     stats_.bytes_zero_copy += link_bytes;
-    link_first = link_end;
+    link_first = n_units;
     link_bytes = 0;
   };
   // Events of layers whose bytes are still in an open (small) group or launch wait here until it is flushed.
   std::vector<cudaEvent_t> deferred;
   bool layer_stream = false;
-  size_t run_cursor = 0;
   for (size_t li = 0; li < n_layers; ++li) {
     const pf_layer_xfer &L = layers[li];
     if (deferred.empty()) {
@@ -1106,47 +1073,65 @@ void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, 
         const uint64_t dev_base = L.data_ptr + (uint64_t)r * L.kv_stride_bytes;
         for (size_t j = 0; j < L.n_runs[r]; ++j) {
           const pf_host_run &run = L.runs[r][j];
-          const uint32_t how = unit_of_run[run_cursor++];
           if (run.n_blocks == 0) continue;
-          if (how == kLdst) {
-            const Side dev{dev_base, L.block_stride_bytes, ids_dev + run.first_block, nullptr};
-            const Side host{run.host_device, run.stride_bytes, nullptr, nullptr};
-            if (host_is_src) launch_link(host, dev, run.n_blocks, L.range_bytes, stream, false);
-            else launch_link(dev, host, run.n_blocks, L.range_bytes, stream, false);
-            stats_.bytes_zero_copy += run.n_blocks * L.range_bytes;
-            layer_stream = true;
-          } else if (how != kStaged) {
-            link_end = (size_t)how + 1;   // units were numbered in this visiting order
-            link_bytes += run.n_blocks * L.range_bytes;
-            layer_stream = true;
-          } else {
-            // Consecutive block ids (a fresh prompt usually gets them from an ordered free list) are
-            // one strided region on the device as well: a single pitched DMA, nothing to gather.  It
-            // runs on the caller's stream like the zero-copy launches, which keeps the layer's event
-            // and the ordering rules unchanged.
-            const uint32_t *ids = L.block_ids + run.first_block;
-            const bool linear = L.block_stride_bytes == L.range_bytes && run.stride_bytes == L.range_bytes;
-            // (pitched rows are only worth a DMA of their own when they are long: the staged route
-            // already turns short padded rows into large linear copies)
-            bool consecutive = run.n_blocks >= 2 && L.block_stride_bytes >= L.range_bytes &&
-                               run.stride_bytes >= L.range_bytes && (linear || L.range_bytes >= (32u << 10));
-            for (size_t k = 1; k < run.n_blocks && consecutive; ++k) consecutive = ids[k] == ids[k - 1] + 1;
-            if (consecutive) {
-              char *device_first = reinterpret_cast<char *>(dev_base + (uint64_t)ids[0] * L.block_stride_bytes);
-              if (host_is_src)
-                PF_CUDA(cudaMemcpy2DAsync(device_first, L.block_stride_bytes, run.host, run.stride_bytes, L.range_bytes,
-                                          run.n_blocks, cudaMemcpyHostToDevice, stream));
-              else
-                PF_CUDA(cudaMemcpy2DAsync(run.host, run.stride_bytes, device_first, L.block_stride_bytes, L.range_bytes,
-                                          run.n_blocks, cudaMemcpyDeviceToHost, stream));
-              ++stats_.dma_copies;
-              stats_.bytes_staged += run.n_blocks * L.range_bytes;
-              layer_stream = true;
-              continue;
+          // Every host run takes one of three routes: staged (gather kernel + copy engine), one pitched
+          // DMA (consecutive block ids), or zero-copy.
+          const size_t bytes = run.n_blocks * L.range_bytes;
+          bool staged = cfg_.route == PF_ROUTE_STAGED || (cfg_.route == PF_ROUTE_AUTO && bytes >= cfg_.min_dma_bytes);
+          if (L.range_bytes > cfg_.staging_slot_bytes || small_task) staged = false;
+          if (!staged) {
+            // bulk copies need 16-byte aligned addresses and sizes; anything else takes the ld/st kernel
+            if ((dev_base | L.block_stride_bytes | run.host_device | run.stride_bytes | L.range_bytes) & 15ull) {
+              const Side dev{dev_base, L.block_stride_bytes, ids_dev + run.first_block, nullptr};
+              const Side host{run.host_device, run.stride_bytes, nullptr, nullptr};
+              if (host_is_src) launch_link(host, dev, run.n_blocks, L.range_bytes, stream, false);
+              else launch_link(dev, host, run.n_blocks, L.range_bytes, stream, false);
+              stats_.bytes_zero_copy += bytes;
+            } else {
+              LinkUnit &u = units[n_units++];
+              u.kv_base = dev_base;
+              u.kv_stride = L.block_stride_bytes;
+              u.host_base = run.host_device;
+              u.host_stride = run.n_blocks > 1 ? run.stride_bytes : L.range_bytes;
+              u.ids = ids_dev + run.first_block;
+              u.n_items = (uint32_t)run.n_blocks;
+              u.item_bytes = (uint32_t)L.range_bytes;
+              u.items_per_chunk = (uint32_t)std::min<size_t>(kLinkItemsMax, kStageBytes / L.range_bytes);
+              u.chunks_per_item = (uint32_t)((L.range_bytes + kStageBytes - 1) / kStageBytes);
+              chunk_total += u.items_per_chunk >= 2 ? (run.n_blocks + u.items_per_chunk - 1) / u.items_per_chunk
+                                                    : (uint64_t)run.n_blocks * u.chunks_per_item;
+              u.chunk_end = chunk_total;
+              link_bytes += bytes;
             }
-            const Side dev{dev_base, L.block_stride_bytes, ids_dev + run.first_block, nullptr};
-            staged_run(dev, run, L.range_bytes, host_is_src, stream);
+            layer_stream = true;
+            continue;
           }
+          // Consecutive block ids (a fresh prompt usually gets them from an ordered free list) are
+          // one strided region on the device as well: a single pitched DMA, nothing to gather.  It
+          // runs on the caller's stream like the zero-copy launches, which keeps the layer's event
+          // and the ordering rules unchanged.
+          const uint32_t *ids = L.block_ids + run.first_block;
+          const bool linear = L.block_stride_bytes == L.range_bytes && run.stride_bytes == L.range_bytes;
+          // (pitched rows are only worth a DMA of their own when they are long: the staged route
+          // already turns short padded rows into large linear copies)
+          bool consecutive = run.n_blocks >= 2 && L.block_stride_bytes >= L.range_bytes &&
+                             run.stride_bytes >= L.range_bytes && (linear || L.range_bytes >= (32u << 10));
+          for (size_t k = 1; k < run.n_blocks && consecutive; ++k) consecutive = ids[k] == ids[k - 1] + 1;
+          if (consecutive) {
+            char *device_first = reinterpret_cast<char *>(dev_base + (uint64_t)ids[0] * L.block_stride_bytes);
+            if (host_is_src)
+              PF_CUDA(cudaMemcpy2DAsync(device_first, L.block_stride_bytes, run.host, run.stride_bytes, L.range_bytes,
+                                        run.n_blocks, cudaMemcpyHostToDevice, stream));
+            else
+              PF_CUDA(cudaMemcpy2DAsync(run.host, run.stride_bytes, device_first, L.block_stride_bytes, L.range_bytes,
+                                        run.n_blocks, cudaMemcpyDeviceToHost, stream));
+            ++stats_.dma_copies;
+            stats_.bytes_staged += bytes;
+            layer_stream = true;
+            continue;
+          }
+          const Side dev{dev_base, L.block_stride_bytes, ids_dev + run.first_block, nullptr};
+          staged_run(dev, run, L.range_bytes, host_is_src, stream);
         }
       }
     }
@@ -1156,7 +1141,7 @@ void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, 
     // launch of its own would waste the link: then it shares the group, and the event, of its successors.
     const bool last = li + 1 == n_layers;
     const bool keep_open = !last && ((!group_.empty() && group_bytes_ < kMinEventGroupBytes) ||
-                                     (link_end > link_first && link_bytes < kMinLinkLaunchBytes));
+                                     (n_units > link_first && link_bytes < kMinLinkLaunchBytes));
     if (!deferred.empty() && !keep_open) {
       flush_group();
       flush_link();

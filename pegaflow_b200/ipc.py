@@ -45,6 +45,18 @@ class CudaIPCWrapper:
         region = N.IpcRegion.from_buffer_copy(self.region)
         N.check(N.lib.pf_ipc_close(C.byref(region)))
 
+    def open_for(self, accessing_device: int) -> Tuple[int, int, int]:
+        """(data_ptr, nbytes, owner_device) for a reader on another GPU of this process: the pointer is
+        valid for kernels and copies of ``accessing_device`` only (the source of a peer copy)."""
+        region = N.IpcRegion.from_buffer_copy(self.region)
+        ptr, owner = C.c_uint64(), C.c_int()
+        N.check(N.lib.pf_ipc_open_for(C.byref(region), accessing_device, C.byref(ptr), C.byref(owner)))
+        return ptr.value, int(region.nbytes), owner.value
+
+    def close_for(self, accessing_device: int) -> None:
+        region = N.IpcRegion.from_buffer_copy(self.region)
+        N.check(N.lib.pf_ipc_close_for(C.byref(region), accessing_device))
+
     def to_bytes(self) -> bytes:
         return pickle.dumps(self)
 

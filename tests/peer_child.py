@@ -25,10 +25,9 @@ def main():
     ptrs, src_dev = [], None
     for r in regions:
         ptr, dev = C.c_uint64(), C.c_int()
-        N.check(N.lib.pf_ipc_open(C.byref(r), C.byref(ptr), C.byref(dev)))
+        N.check(N.lib.pf_ipc_open_for(C.byref(r), dst_dev, C.byref(ptr), C.byref(dev)))
         ptrs.append(ptr.value)
         src_dev = dev.value
-    pf.enable_peer_access(dst_dev, src_dev)
     dst = [torch.zeros((2, nb, seg), dtype=torch.uint8, device=device) for _ in range(L)]
     be = pf.TransferBackend(dst_dev)
     stream = torch.cuda.Stream()
@@ -45,7 +44,7 @@ def main():
     st = be.stats()
     be.close()
     for r in regions:
-        N.check(N.lib.pf_ipc_close(C.byref(r)))
+        N.check(N.lib.pf_ipc_close_for(C.byref(r), dst_dev))
     print(json.dumps({"bit_exact": bool(ok), "src_device": src_dev, "bytes_peer": st["bytes_peer"],
                       "device_status": st["device_status"], "kernel_launches": st["kernel_launches"]}))
     sys.stdout.flush()
