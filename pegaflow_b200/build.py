@@ -20,7 +20,7 @@ LIB_PATH = os.path.join(PKG_DIR, "libpegaflow_b200.so")
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",
-    "-Xcompiler", "-fPIC,-Wall,-Wextra,-Wno-unused-parameter",
+    "-Xcompiler", "-fPIC,-g,-Wall,-Wextra,-Wno-unused-parameter",
     "--shared",
 ]
 LINK_FLAGS = ["-lpthread", "-ldl", "-lrt"]

@@ -185,7 +185,8 @@ def test_prefix_dedup_and_partial_layer_semantics(pf):
         eng.flush_saves()
         assert eng.metrics()["pool_used_bytes"] == used_before, "a save of resident blocks must not allocate"
         # gap breaks the prefix
-        sc.register(eng, mem, "gap", "ns2", [sc.Layer("layer_0", 3, 1024)])
+        gap_layers = [sc.Layer("layer_0", 3, 1024)]      # kept: registered memory must outlive its use
+        sc.register(eng, mem, "gap", "ns2", gap_layers)
         allh = sc.make_block_hashes(4, 20)
         eng.batch_save("gap", 0, 0, 0, [("layer_0", [0, 1, 2], [allh[0], allh[2], allh[3]])])
         eng.flush_saves()
@@ -213,8 +214,10 @@ def test_error_behaviour_matches_the_oracle(pf):
         both(lambda e, m: sc.register(e, m, "bad", "ns", [sc.Layer("l", 4, 1024, segments=2, kv_stride=512)]),
              "overlap")
         both(lambda e, m: sc.register(e, m, "bad2", "ns", [sc.Layer("l", 10, 1024, region_bytes=5120)]), "too small")
+        keep = []   # registered memory must outlive the engines: the oracle's is plain numpy
         for e, m in ((eng, gmem), (ora, nmem)):
-            sc.register(e, m, "v", "ns", [sc.Layer("layer_0", 4, 1024), sc.Layer("layer_1", 4, 1024)])
+            keep.append([sc.Layer("layer_0", 4, 1024), sc.Layer("layer_1", 4, 1024)])
+            sc.register(e, m, "v", "ns", keep[-1])
         both(lambda e, m: sc.register(e, m, "v", "ns", [sc.Layer("layer_0", 4, 1024)]), "already exists")
         both(lambda e, m: sc.register(e, m, "v", "ns", [sc.Layer("layer_0", 4, 1024)], device_id=1),
              "already fully registered")
@@ -230,7 +233,8 @@ def test_error_behaviour_matches_the_oracle(pf):
         both(lambda e, m: e.batch_load("v", 0, 0, [["layer_0"]], [(b"\0" * 16, [[0]])]), "unknown or expired")
         # page-first partial save (engine_basic.rs:131-158)
         for e, m in ((eng, gmem), (ora, nmem)):
-            sc.register(e, m, "pf", "ns3", [sc.Layer(n, 4, 512) for n in ("layer_a", "layer_b", "layer_c")],
+            keep.append([sc.Layer(n, 4, 512) for n in ("layer_a", "layer_b", "layer_c")])
+            sc.register(e, m, "pf", "ns3", keep[-1],
                         page_first=True)
         both(lambda e, m: e.batch_save("pf", 0, 0, 0, [("layer_a", [0, 1, 2, 3], sc.make_block_hashes(4, 0xCD))]),
              "must cover all")

@@ -93,7 +93,8 @@ def test_multi_layer_partial_save_is_not_a_hit_and_dedup():
 
 def test_prefix_semantics_gap_breaks_prefix():
     eng, mem = _engine(), sc.NumpyMem()
-    sc.register(eng, mem, "gap", "ns", [sc.Layer("layer_0", 3, 1024)])
+    layers = [sc.Layer("layer_0", 3, 1024)]      # kept: registered memory must outlive its use
+    sc.register(eng, mem, "gap", "ns", layers)
     allh = sc.make_block_hashes(4, 20)
     eng.batch_save("gap", 0, 0, 0, [("layer_0", [0, 1, 2], [allh[0], allh[2], allh[3]])])
     blocks, missing = eng.query_prefix("gap", allh)
