@@ -986,7 +986,10 @@ def run_e2e(args, pf, wl, rank, world, local, route, duplex=False):
             saving = [callers.submit(eng.batch_save, "bench", 0, 0, local, req[0]) for req in prepared[k]]
             load_from = k - 1
         else:
-            list(callers.map(lambda req: eng.batch_save("bench", 0, 0, local, req[0]), prepared[k]))
+            if n_req == 1:      # one request: no second caller to overlap with
+                eng.batch_save("bench", 0, 0, local, prepared[k][0][0])
+            else:
+                list(callers.map(lambda req: eng.batch_save("bench", 0, 0, local, req[0]), prepared[k]))
             eng.flush_saves()
             load_from = k
         pending = []
@@ -1030,7 +1033,8 @@ def run_e2e(args, pf, wl, rank, world, local, route, duplex=False):
             "h2d_bytes_per_step": wl.payload, "d2h_bytes_per_step": wl.payload,
             "ms_per_step": round(elapsed / args.steps * 1e3, 3), "clock": "host wall clock around a synchronised region",
             "api": "pf_engine_batch_save / flush_saves / query_prefix / create_query_lease / batch_load_inproc, "
-                   "arguments marshalled once outside the timed region; saves issued from two caller threads"
+                   "arguments marshalled once outside the timed region; saves issued from two caller threads (one request per "
+                   "step: from the calling thread)"
                    + ("; each step's saves overlap the loads of the step before" if duplex else ""),
             "evicted_blocks": m["evicted_blocks"], "load_failures": m["load_failures"], "e2e_breakdown": breakdown}
 
@@ -1244,6 +1248,14 @@ def peer_phase(args, pf, torch, rank, world, local):
 
 
 
+def read_first_line(path):
+    try:
+        with open(path) as f:
+            return f.readline().strip()
+    except OSError:
+        return None
+
+
 def first_page_frame(addr):
     """Guest-physical page frame of the page at `addr` from /proc/self/pagemap (None when the kernel hides it)."""
     try:
@@ -1273,6 +1285,7 @@ def run_placement_probe(args, rank, world, local):
     cpus = sorted(os.sched_getaffinity(0))
     quarters = [cpus[i * len(cpus) // 4:(i + 1) * len(cpus) // 4] or cpus for i in range(4)]
     kinds = [("cudaHostAlloc", q, {}) for q in range(4)] + [("mmap+register", q, {"use_mmap": True}) for q in range(4)] \
+        + [("mmap+madvise(HUGEPAGE)+register", None, {"transparent_huge": True})] \
         + [("cudaHostAlloc-late", None, {}) for _ in range(args.probe_late_chunks)]
     if args.probe_hugepages:
         kinds.append(("hugepages", None, {"use_hugepages": True}))
@@ -1342,6 +1355,8 @@ def run_placement_probe(args, rank, world, local):
     print(json.dumps({
         "metric": "pinned_pool_placement_probe", "unit": "GB/s", "n_gpus": world, "host_cpus": len(cpus),
         "numa_nodes_visible": pf._native.lib.pf_numa_num_nodes(), "chunk_mib": args.probe_chunk_mib,
+        "transparent_hugepage": read_first_line("/sys/kernel/mm/transparent_hugepage/enabled"),
+        "nr_hugepages": read_first_line("/proc/sys/vm/nr_hugepages"),
         "how": "plain cudaMemcpyAsync in 256 MiB pieces between each rank's GPU and each of its candidate chunks; solo_* = "
                "one rank at a time, all_* = every rank at once on its chunk of the same index; all_ranks_best_chunk = every "
                "rank at once, each on the chunk that was fastest for it under load (and on its first chunk, for comparison)",

@@ -285,6 +285,8 @@ typedef struct pf_pool_config {
   int numa_node;          /* first-touch node for the mmap strategies; -1 = caller's affinity */
   uint64_t unit_hint;     /* allocator granularity hint (0 = 512 B) */
   int shards;             /* independent allocators (0/1 = one) */
+  int transparent_huge;   /* with use_mmap: madvise(MADV_HUGEPAGE) before the pre-touch, so that a kernel with
+                             transparent huge pages in "madvise" or "always" mode backs the pool with 2 MiB pages */
 } pf_pool_config;
 int pf_pool_new(size_t bytes, const pf_pool_config *config, pf_pool **out);
 void pf_pool_free(pf_pool *pool);

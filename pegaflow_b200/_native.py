@@ -73,7 +73,7 @@ class BackendStats(C.Structure):
 
 class PoolConfig(C.Structure):
     _fields_ = [("use_hugepages", C.c_int), ("use_mmap", C.c_int), ("numa_node", C.c_int), ("unit_hint", u64),
-                ("shards", C.c_int)]
+                ("shards", C.c_int), ("transparent_huge", C.c_int)]
 
 
 class StorageConfig(C.Structure):

@@ -42,8 +42,10 @@ class LayerXfer:
 class PinnedPool:
     """`PinnedAllocator` of the reference (pinned_pool.rs:616-715) through the C ABI."""
 
-    def __init__(self, nbytes: int, *, use_hugepages=False, use_mmap=False, numa_node=-1, unit_hint=0, shards=1):
-        cfg = N.PoolConfig(int(use_hugepages), int(use_mmap), numa_node, unit_hint, shards)
+    def __init__(self, nbytes: int, *, use_hugepages=False, use_mmap=False, numa_node=-1, unit_hint=0, shards=1,
+                 transparent_huge=False):
+        cfg = N.PoolConfig(int(use_hugepages), int(use_mmap or transparent_huge), numa_node, unit_hint, shards,
+                           int(transparent_huge))
         h = C.c_void_p()
         N.check(N.lib.pf_pool_new(nbytes, C.byref(cfg), C.byref(h)))
         self._h = h

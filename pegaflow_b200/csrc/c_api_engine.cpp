@@ -87,10 +87,11 @@ int pf_pool_new(size_t bytes, const pf_pool_config *config, pf_pool **out) {
   return guarded([&] {
     if (!out) throw Error::invalid("out is null");
     if (bytes == 0) throw Error::storage("Pinned memory pool size must be greater than zero");
-    pf_pool_config c = config ? *config : pf_pool_config{0, 0, -1, 0, 1};
-    PinnedMemory::Strategy st = c.use_hugepages ? PinnedMemory::Strategy::HugePages
-                                : c.use_mmap    ? PinnedMemory::Strategy::MmapRegister
-                                                : PinnedMemory::Strategy::CudaHostAlloc;
+    pf_pool_config c = config ? *config : pf_pool_config{0, 0, -1, 0, 1, 0};
+    PinnedMemory::Strategy st = c.use_hugepages      ? PinnedMemory::Strategy::HugePages
+                                : c.transparent_huge ? PinnedMemory::Strategy::MmapTransparentHuge
+                                : c.use_mmap         ? PinnedMemory::Strategy::MmapRegister
+                                                     : PinnedMemory::Strategy::CudaHostAlloc;
     auto pool = std::make_unique<pf_pool>();
     std::vector<int> nodes;
     if (c.numa_node >= 0) nodes.push_back(c.numa_node);

@@ -86,7 +86,8 @@ PinnedMemory::PinnedMemory(size_t bytes, Strategy strategy, int numa_node) : siz
     host_ = static_cast<char *>(p);
   } else {
     const bool huge = strategy == Strategy::HugePages;
-    const size_t page = huge ? huge_page_size() : (size_t)sysconf(_SC_PAGESIZE);
+    const bool thp = strategy == Strategy::MmapTransparentHuge;
+    const size_t page = huge || thp ? huge_page_size() : (size_t)sysconf(_SC_PAGESIZE);
     if (page == 0) throw Error::storage("huge page size is not available from /proc/meminfo");
     size_ = (bytes + page - 1) / page * page;
     int flags = MAP_PRIVATE | MAP_ANONYMOUS | (huge ? MAP_HUGETLB : 0);
@@ -94,6 +95,9 @@ PinnedMemory::PinnedMemory(size_t bytes, Strategy strategy, int numa_node) : siz
     if (p == MAP_FAILED)
       throw Error::storage(strf("mmap of %zu bytes failed%s", size_, huge ? " (are huge pages reserved?)" : ""));
     host_ = static_cast<char *>(p);
+    // Advice only: a kernel whose transparent huge pages are off ignores it and the pool is backed by
+    // ordinary pages.  (The mapping is not 2 MiB aligned; the kernel uses huge pages for the aligned part.)
+    if (thp) madvise(host_, size_, MADV_HUGEPAGE);
     parallel_pre_touch(host_, size_, (size_t)sysconf(_SC_PAGESIZE), numa_node);
     cudaError_t e = cudaHostRegister(host_, size_, cudaHostRegisterMapped | cudaHostRegisterPortable);
     if (e != cudaSuccess) {

@@ -21,7 +21,7 @@ namespace pf {
 // (Registered memory may map at a different device address, transfer/mod.rs:30-35.)
 class PinnedMemory {
  public:
-  enum class Strategy { CudaHostAlloc, MmapRegister, HugePages };
+  enum class Strategy { CudaHostAlloc, MmapRegister, HugePages, MmapTransparentHuge };
   PinnedMemory(size_t bytes, Strategy strategy, int numa_node);
   ~PinnedMemory();
   PinnedMemory(const PinnedMemory &) = delete;

@@ -405,12 +405,15 @@ copy_descs_tma(const uint64_t *__restrict__ triples, uint32_t n, uint32_t stage_
 constexpr uint32_t kLinkItemsMax = 16;
 struct LinkUnit {
   uint64_t kv_base, kv_stride;
-  uint64_t host_base, host_stride;
+  uint64_t host_base, host_stride;   // pool side when host_table is null
+  const uint64_t *host_table;        // else: the pool address of every item (host runs that do not line up)
   const uint32_t *ids;
   uint64_t chunk_end;        // exclusive prefix sum of chunks over the units of the call
   uint32_t n_items, item_bytes;
   uint32_t items_per_chunk;  // >= 2: a chunk is that many whole items; otherwise an item is cut
-  uint32_t chunks_per_item;  //      into this many chunks of at most kStageBytes
+  uint32_t chunks_per_item;  //      into this many chunks of chunk_bytes (the last one may be shorter)
+  uint32_t chunk_bytes;
+  uint32_t pad_;
 };
 
 __global__ void __launch_bounds__(32)
@@ -430,6 +433,12 @@ copy_units_tma(const LinkUnit *__restrict__ units, uint32_t n_units, uint64_t ch
   uint32_t k = 0;
   uint64_t produced = 0, consumed = 0;
 
+  auto host_addr = [](const LinkUnit &u, uint32_t item) -> uint64_t {
+    return u.host_table ? u.host_table[item] : u.host_base + (uint64_t)item * u.host_stride;
+  };
+  // whole items that lie back to back in the pool cross the link as one bulk copy
+  auto host_dense = [](const LinkUnit &u, uint32_t len) -> bool { return !u.host_table && u.host_stride == len; };
+
   auto produce = [&]() -> bool {
     if (cursor >= total_end) return false;
     while (cursor >= units[k].chunk_end) {  // chunks are visited in ascending order
@@ -447,8 +456,8 @@ copy_units_tma(const LinkUnit *__restrict__ units, uint32_t n_units, uint64_t ch
     } else {
       item0 = (uint32_t)(local / u.chunks_per_item);
       count = 1;
-      off = (uint32_t)(local - (uint64_t)item0 * u.chunks_per_item) * kStageBytes;
-      len = min(kStageBytes, u.item_bytes - off);
+      off = (uint32_t)(local - (uint64_t)item0 * u.chunks_per_item) * u.chunk_bytes;
+      len = min(u.chunk_bytes, u.item_bytes - off);
     }
     const int st = (int)(produced % kStages);
     st_unit[st] = k, st_item0[st] = item0, st_count[st] = count, st_off[st] = off, st_len[st] = len;
@@ -457,11 +466,10 @@ copy_units_tma(const LinkUnit *__restrict__ units, uint32_t n_units, uint64_t ch
     if (to_host) {
       for (uint32_t j = 0; j < count; ++j)
         bulk_g2s(stage + (size_t)j * len, u.kv_base + (uint64_t)u.ids[item0 + j] * u.kv_stride + off, len, &bars[st]);
-    } else if (u.host_stride == len) {  // whole items, back to back in the pool: one read across the link
+    } else if (host_dense(u, len)) {
       bulk_g2s(stage, u.host_base + (uint64_t)item0 * u.host_stride, count * len, &bars[st]);
     } else {
-      for (uint32_t j = 0; j < count; ++j)
-        bulk_g2s(stage + (size_t)j * len, u.host_base + (uint64_t)(item0 + j) * u.host_stride + off, len, &bars[st]);
+      for (uint32_t j = 0; j < count; ++j) bulk_g2s(stage + (size_t)j * len, host_addr(u, item0 + j) + off, len, &bars[st]);
     }
     ++produced;
     cursor += gridDim.x;
@@ -483,11 +491,10 @@ copy_units_tma(const LinkUnit *__restrict__ units, uint32_t n_units, uint64_t ch
     if (!to_host) {
       for (uint32_t j = 0; j < count; ++j)
         bulk_s2g(u.kv_base + (uint64_t)u.ids[item0 + j] * u.kv_stride + off, stage + (size_t)j * len, len);
-    } else if (u.host_stride == len) {  // one write across the link
+    } else if (host_dense(u, len)) {
       bulk_s2g(u.host_base + (uint64_t)item0 * u.host_stride, stage, count * len);
     } else {
-      for (uint32_t j = 0; j < count; ++j)
-        bulk_s2g(u.host_base + (uint64_t)(item0 + j) * u.host_stride + off, stage + (size_t)j * len, len);
+      for (uint32_t j = 0; j < count; ++j) bulk_s2g(host_addr(u, item0 + j) + off, stage + (size_t)j * len, len);
     }
     bulk_commit();
     ++consumed;
@@ -977,8 +984,23 @@ void TransferBackend::gather_layers(const pf_layer_xfer *layers, size_t n_layers
 void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, bool host_is_src,
                                   cudaStream_t stream, void *const *layer_done) {
   DeviceGuard on_device(device_);
-  // ---- validate everything before anything is enqueued (a light pass: no planning yet).
-  size_t total_bytes = 0, total_runs = 0, ids_bytes = 0;
+  size_t total_bytes = 0;
+  for (size_t li = 0; li < n_layers; ++li) total_bytes += layers[li].n_blocks * layers[li].range_bytes * layers[li].n_ranges;
+  // Small tasks (a few blocks of every layer, e.g. the tail blocks saved while decoding): launches,
+  // not bytes, are what they cost, so everything goes into the one zero-copy launch.
+  const bool small_task = cfg_.route != PF_ROUTE_STAGED && n_layers > 1 && total_bytes <= kSmallTaskBytes;
+  // Every host run takes one of three routes: staged (gather kernel + copy engine; consecutive block
+  // ids: one pitched DMA instead) or zero-copy.
+  auto takes_staged_route = [&](const pf_layer_xfer &L, const pf_host_run &run) {
+    if (L.range_bytes > cfg_.staging_slot_bytes || small_task) return false;
+    return cfg_.route == PF_ROUTE_STAGED ||
+           (cfg_.route == PF_ROUTE_AUTO && run.n_blocks * L.range_bytes >= cfg_.min_dma_bytes);
+  };
+
+  // ---- validate everything before anything is enqueued, and size the meta region: the block ids of
+  // every layer, one zero-copy unit per device range, and for ranges whose zero-copy runs do not form
+  // one strided sequence a table of their blocks' pool addresses (8 B) and ids (4 B).
+  size_t ids_bytes = 0, table_items = 0;
   std::vector<size_t> ids_off(n_layers, 0);
   for (size_t li = 0; li < n_layers; ++li) {
     const pf_layer_xfer &L = layers[li];
@@ -990,9 +1012,8 @@ void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, 
     if (!L.block_ids) throw Error::invalid(strf("layer %zu: block_ids is null", li));
     ids_off[li] = ids_bytes;
     ids_bytes += align_up(L.n_blocks * sizeof(uint32_t), 256);
-    total_bytes += L.n_blocks * L.range_bytes * L.n_ranges;
     for (uint32_t r = 0; r < L.n_ranges; ++r) {
-      size_t covered = 0;
+      size_t covered = 0, zc_runs = 0, zc_items = 0;
       const pf_host_run *runs = L.runs[r];
       for (size_t j = 0; j < L.n_runs[r]; ++j) {
         const pf_host_run &run = runs[j];
@@ -1003,10 +1024,14 @@ void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, 
         if (run.n_blocks > 1 && run.stride_bytes < L.range_bytes)
           throw Error::invalid(strf("layer %zu range %u: host stride smaller than the range", li, r));
         covered += run.n_blocks;
+        if (run.n_blocks && !takes_staged_route(L, run)) {
+          ++zc_runs;
+          zc_items += run.n_blocks;
+        }
       }
       if (covered != L.n_blocks)
         throw Error::invalid(strf("layer %zu range %u: host runs cover %zu of %zu blocks", li, r, covered, L.n_blocks));
-      total_runs += L.n_runs[r];
+      if (zc_runs > 1) table_items += zc_items;
     }
   }
   if (ids_bytes == 0) {
@@ -1015,23 +1040,25 @@ void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, 
         if (layer_done[li]) PF_CUDA(cudaEventRecord((cudaEvent_t)layer_done[li], stream));
     return;
   }
-  // Small tasks (a few blocks of every layer, e.g. the tail blocks saved while decoding): launches,
-  // not bytes, are what they cost, so everything goes into the one zero-copy launch.
-  const bool small_task = cfg_.route != PF_ROUTE_STAGED && n_layers > 1 && total_bytes <= kSmallTaskBytes;
 
-  // ---- meta region: the block ids of every layer (uploaded now) and room for one zero-copy unit
-  // per host run (filled layer by layer, uploaded just before the launch that reads them: the
-  // first transfer is on its way after one layer has been planned, not after all of them).
+  // The ids go up now; units and tables are filled layer by layer and uploaded just before the launch
+  // that reads them, so the first transfer is on its way after one layer has been planned.
   const size_t units_off = ids_bytes;
-  const size_t meta_bytes = ids_bytes + align_up(total_runs * sizeof(LinkUnit), 256);
+  const size_t tables_off = units_off + align_up(2 * n_layers * sizeof(LinkUnit), 256);
+  const size_t zids_off = tables_off + align_up(table_items * sizeof(uint64_t), 256);
+  const size_t meta_bytes = zids_off + align_up(table_items * sizeof(uint32_t), 256);
   const size_t base = meta_alloc(meta_bytes);
   for (size_t li = 0; li < n_layers; ++li)
     if (layers[li].n_blocks)
       std::memcpy(meta_host_ + base + ids_off[li], layers[li].block_ids, layers[li].n_blocks * sizeof(uint32_t));
   meta_upload(base, ids_bytes, stream);
   LinkUnit *units = reinterpret_cast<LinkUnit *>(meta_host_ + base + units_off);
+  uint64_t *table = reinterpret_cast<uint64_t *>(meta_host_ + base + tables_off);
+  uint32_t *zids = reinterpret_cast<uint32_t *>(meta_host_ + base + zids_off);
   const LinkUnit *units_dev = reinterpret_cast<const LinkUnit *>(meta_dev_ + base + units_off);
-  size_t n_units = 0;
+  const uint64_t *table_dev = reinterpret_cast<const uint64_t *>(meta_dev_ + base + tables_off);
+  const uint32_t *zids_dev = reinterpret_cast<const uint32_t *>(meta_dev_ + base + zids_off);
+  size_t n_units = 0, n_table = 0, table_uploaded = 0;
   uint64_t chunk_total = 0;
 
   group_limit_ = kFirstGroupBytes;
@@ -1047,6 +1074,11 @@ void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, 
     const uint64_t chunks = units[n_units - 1].chunk_end - chunk_begin;
     const int ctas = cfg_.link_ctas > 0 ? cfg_.link_ctas : 16;
     meta_upload(base + units_off + link_first * sizeof(LinkUnit), (n_units - link_first) * sizeof(LinkUnit), stream);
+    if (n_table > table_uploaded) {
+      meta_upload(base + tables_off + table_uploaded * sizeof(uint64_t), (n_table - table_uploaded) * sizeof(uint64_t), stream);
+      meta_upload(base + zids_off + table_uploaded * sizeof(uint32_t), (n_table - table_uploaded) * sizeof(uint32_t), stream);
+      table_uploaded = n_table;
+    }
     cudaEvent_t t0;
     time_begin(stream, &t0);
     copy_units_tma<<<(int)std::min<uint64_t>(chunks, (uint64_t)ctas), 32, (size_t)kStages * kStageBytes, stream>>>(
@@ -1057,6 +1089,28 @@ void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, 
     stats_.bytes_zero_copy += link_bytes;
     link_first = n_units;
     link_bytes = 0;
+  };
+  // Appends the unit of one device range; `n_items` items of `item_bytes`.
+  auto add_unit = [&](uint64_t dev_base, uint64_t dev_stride, const uint32_t *ids_dev_ptr, size_t n_items, size_t item_bytes,
+                      uint64_t host_base, uint64_t host_stride, const uint64_t *host_table_dev) {
+    LinkUnit &u = units[n_units++];
+    u.kv_base = dev_base;
+    u.kv_stride = dev_stride;
+    u.host_base = host_base;
+    u.host_stride = host_stride;
+    u.host_table = host_table_dev;
+    u.ids = ids_dev_ptr;
+    u.n_items = (uint32_t)n_items;
+    u.item_bytes = (uint32_t)item_bytes;
+    u.items_per_chunk = (uint32_t)std::min<size_t>(kLinkItemsMax, kStageBytes / item_bytes);
+    u.chunks_per_item = (uint32_t)((item_bytes + kStageBytes - 1) / kStageBytes);
+    // an item larger than a ring stage is cut into equal chunks (a multiple of 128 bytes each)
+    u.chunk_bytes = (uint32_t)std::min<size_t>(kStageBytes, align_up((item_bytes + u.chunks_per_item - 1) / u.chunks_per_item, 128));
+    u.pad_ = 0;
+    chunk_total += u.items_per_chunk >= 2 ? (n_items + u.items_per_chunk - 1) / u.items_per_chunk
+                                          : (uint64_t)n_items * u.chunks_per_item;
+    u.chunk_end = chunk_total;
+    link_bytes += n_items * item_bytes;
   };
   // Events of layers whose bytes are still in an open (small) group or launch wait here until it is flushed.
   std::vector<cudaEvent_t> deferred;
@@ -1071,37 +1125,36 @@ void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, 
       const uint32_t *ids_dev = reinterpret_cast<const uint32_t *>(meta_dev_ + base + ids_off[li]);
       for (uint32_t r = 0; r < L.n_ranges; ++r) {
         const uint64_t dev_base = L.data_ptr + (uint64_t)r * L.kv_stride_bytes;
+        // how this range's zero-copy runs travel: one strided unit, one table-driven unit, or (an
+        // address or size that is not a multiple of 16) the ld/st kernel run by run
+        size_t zc_runs = 0;
+        bool zc_aligned = ((dev_base | L.block_stride_bytes | L.range_bytes) & 15ull) == 0;
+        for (size_t j = 0; j < L.n_runs[r]; ++j) {
+          const pf_host_run &run = L.runs[r][j];
+          if (run.n_blocks == 0 || takes_staged_route(L, run)) continue;
+          ++zc_runs;
+          if ((run.host_device | (run.n_blocks > 1 ? run.stride_bytes : 0)) & 15ull) zc_aligned = false;
+        }
+        const size_t table_first = n_table;
         for (size_t j = 0; j < L.n_runs[r]; ++j) {
           const pf_host_run &run = L.runs[r][j];
           if (run.n_blocks == 0) continue;
-          // Every host run takes one of three routes: staged (gather kernel + copy engine), one pitched
-          // DMA (consecutive block ids), or zero-copy.
           const size_t bytes = run.n_blocks * L.range_bytes;
-          bool staged = cfg_.route == PF_ROUTE_STAGED || (cfg_.route == PF_ROUTE_AUTO && bytes >= cfg_.min_dma_bytes);
-          if (L.range_bytes > cfg_.staging_slot_bytes || small_task) staged = false;
-          if (!staged) {
-            // bulk copies need 16-byte aligned addresses and sizes; anything else takes the ld/st kernel
-            if ((dev_base | L.block_stride_bytes | run.host_device | run.stride_bytes | L.range_bytes) & 15ull) {
+          if (!takes_staged_route(L, run)) {
+            if (!zc_aligned) {
               const Side dev{dev_base, L.block_stride_bytes, ids_dev + run.first_block, nullptr};
               const Side host{run.host_device, run.stride_bytes, nullptr, nullptr};
               if (host_is_src) launch_link(host, dev, run.n_blocks, L.range_bytes, stream, false);
               else launch_link(dev, host, run.n_blocks, L.range_bytes, stream, false);
               stats_.bytes_zero_copy += bytes;
+            } else if (zc_runs == 1) {
+              add_unit(dev_base, L.block_stride_bytes, ids_dev + run.first_block, run.n_blocks, L.range_bytes,
+                       run.host_device, run.n_blocks > 1 ? run.stride_bytes : L.range_bytes, nullptr);
             } else {
-              LinkUnit &u = units[n_units++];
-              u.kv_base = dev_base;
-              u.kv_stride = L.block_stride_bytes;
-              u.host_base = run.host_device;
-              u.host_stride = run.n_blocks > 1 ? run.stride_bytes : L.range_bytes;
-              u.ids = ids_dev + run.first_block;
-              u.n_items = (uint32_t)run.n_blocks;
-              u.item_bytes = (uint32_t)L.range_bytes;
-              u.items_per_chunk = (uint32_t)std::min<size_t>(kLinkItemsMax, kStageBytes / L.range_bytes);
-              u.chunks_per_item = (uint32_t)((L.range_bytes + kStageBytes - 1) / kStageBytes);
-              chunk_total += u.items_per_chunk >= 2 ? (run.n_blocks + u.items_per_chunk - 1) / u.items_per_chunk
-                                                    : (uint64_t)run.n_blocks * u.chunks_per_item;
-              u.chunk_end = chunk_total;
-              link_bytes += bytes;
+              for (size_t i = 0; i < run.n_blocks; ++i, ++n_table) {
+                table[n_table] = run.host_device + (uint64_t)i * run.stride_bytes;
+                zids[n_table] = L.block_ids[run.first_block + i];
+              }
             }
             layer_stream = true;
             continue;
@@ -1133,6 +1186,9 @@ void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, 
           const Side dev{dev_base, L.block_stride_bytes, ids_dev + run.first_block, nullptr};
           staged_run(dev, run, L.range_bytes, host_is_src, stream);
         }
+        if (n_table > table_first)
+          add_unit(dev_base, L.block_stride_bytes, zids_dev + table_first, n_table - table_first, L.range_bytes, 0, 0,
+                   table_dev + table_first);
       }
     }
     cudaEvent_t done = layer_done ? (cudaEvent_t)layer_done[li] : nullptr;

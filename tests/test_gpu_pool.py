@@ -45,7 +45,8 @@ def pf():
     return pegaflow_b200
 
 
-STRATEGIES = {"cuda_host_alloc": {}, "mmap_register": {"use_mmap": True}, "hugepages": {"use_hugepages": True}}
+STRATEGIES = {"cuda_host_alloc": {}, "mmap_register": {"use_mmap": True}, "hugepages": {"use_hugepages": True},
+              "mmap_transparent_huge": {"transparent_huge": True}}
 
 
 @pytest.mark.gpu
