@@ -570,7 +570,7 @@ def time_gather_alone(args, pf, torch, local, route, wl, save_x, stream):
     if route == 2 or args.contiguous_ids:
         return None
     be = pf.TransferBackend(local, route=route, time_kernels=False, staging_slot_bytes=args.slot_mib << 20,
-                            staging_slots=args.slots, pack_ctas=args.pack_ctas)
+                            staging_slots=args.slots, pack_ctas=args.pack_ctas, gather_slots=args.gather_slots)
     s = stream.cuda_stream
     try:
         for x in save_x:   # warm-up pass; also proves every run is a gathered one
@@ -687,7 +687,7 @@ def run_b200(args, rank, world, local):
     allocs = alloc_host_images(pool, wl)
     be = pf.TransferBackend(local, route=route, time_kernels=not args.no_kernel_timing, link_ctas=args.link_ctas,
                             staging_slot_bytes=args.slot_mib << 20, staging_slots=args.slots,
-                            copy_streams=args.copy_streams, pack_ctas=args.pack_ctas)
+                            copy_streams=args.copy_streams, pack_ctas=args.pack_ctas, gather_slots=args.gather_slots)
     save_x = make_layer_xfers(pf, wl, allocs, wl.save_ids)
     load_x = make_layer_xfers(pf, wl, allocs, wl.load_ids)
     stream = torch.cuda.Stream()
@@ -1983,6 +1983,7 @@ def main():
     ap.add_argument("--slots", type=int, default=0)
     ap.add_argument("--copy-streams", type=int, default=0)
     ap.add_argument("--pack-ctas", type=int, default=0)
+    ap.add_argument("--gather-slots", type=int, default=0, help="staging slots one gather launch of a save fills")
     ap.add_argument("--no-kernel-timing", action="store_true", help="diagnostic: no event pairs around kernels")
     ap.add_argument("--contiguous-ids", action="store_true", help="diagnostic: block ids in ascending order")
     ap.add_argument("--skip-e2e", action="store_true")

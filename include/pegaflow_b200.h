@@ -108,13 +108,15 @@ enum pf_route {
 
 typedef struct pf_backend_config {
   size_t staging_slot_bytes; /* bytes per HBM staging slot (0 = 32 MiB) */
-  int staging_slots;         /* ring depth (0 = 4) */
+  int staging_slots;         /* ring depth (0 = 6) */
   int pack_ctas;             /* CTAs of the HBM gather/scatter kernel (0 = 8 per SM) */
   int link_ctas;             /* CTAs of the zero-copy / peer kernel (0 = 16 for PCIe, 8 per SM for NVLink) */
   size_t min_dma_bytes;      /* smallest host-contiguous run sent through the copy engine (0 = 256 KiB) */
   int route;                 /* enum pf_route */
   int time_kernels;          /* 1: bracket every kernel launch with CUDA events (see pf_backend_stats) */
-  int copy_streams;          /* copy-engine streams the staged route alternates between (0 = 2) */
+  int copy_streams;          /* copy-engine streams the staged route alternates between (0 = 1) */
+  int gather_slots;          /* staging slots one gather launch of a save may fill (0 = 3, at most half the ring;
+                                1 = one launch per slot) */
 } pf_backend_config;
 
 /* Replaces `KernelBackend::new` (transfer/kernel.rs:63-77) / `build_backend`

@@ -45,7 +45,7 @@ class CopyDesc(C.Structure):
 class BackendConfig(C.Structure):
     _fields_ = [("staging_slot_bytes", sz), ("staging_slots", C.c_int), ("pack_ctas", C.c_int),
                 ("link_ctas", C.c_int), ("min_dma_bytes", sz), ("route", C.c_int), ("time_kernels", C.c_int),
-                ("copy_streams", C.c_int)]
+                ("copy_streams", C.c_int), ("gather_slots", C.c_int)]
 
 
 class HostRun(C.Structure):

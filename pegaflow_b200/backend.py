@@ -75,9 +75,9 @@ class PinnedPool:
 class TransferBackend:
     def __init__(self, device_id: int = 0, *, route: int = N.ROUTE_AUTO, staging_slot_bytes: int = 0,
                  staging_slots: int = 0, pack_ctas: int = 0, link_ctas: int = 0, min_dma_bytes: int = 0,
-                 time_kernels: bool = False, copy_streams: int = 0):
+                 time_kernels: bool = False, copy_streams: int = 0, gather_slots: int = 0):
         cfg = N.BackendConfig(staging_slot_bytes, staging_slots, pack_ctas, link_ctas, min_dma_bytes, route,
-                              int(time_kernels), copy_streams)
+                              int(time_kernels), copy_streams, gather_slots)
         h = C.c_void_p()
         N.check(N.lib.pf_backend_new(device_id, C.byref(cfg), C.byref(h)))
         self._h = h

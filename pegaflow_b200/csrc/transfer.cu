@@ -43,6 +43,8 @@ constexpr unsigned kStatusWaitExpired = 0x57A17u;
 constexpr size_t kSmallTaskBytes = 2u << 20;      // multi-layer tasks up to this size take one zero-copy launch
 constexpr size_t kFirstGroupBytes = 4u << 20;     // size limit of a call's first staging group, doubled per group
 constexpr size_t kMinEventGroupBytes = 8u << 20;  // a layer with fewer staged bytes shares the DMA of the next ones
+constexpr size_t kMinPairBytes = 8u << 20;        // a save group at least this large waits for a partner to share a launch
+constexpr int kHeldGroupsDefault = 3;             // staging slots one gather launch of a save fills
 constexpr size_t kMinLinkLaunchBytes = 32u << 20; // ... and one with fewer zero-copy bytes the launch of the next ones
 
 __device__ __forceinline__ uint64_t global_timer_ns() {
@@ -517,9 +519,14 @@ static_assert(kStages >= 2, "ring needs two stages");
 TransferBackend::TransferBackend(int device, const pf_backend_config *config) : device_(device) {
   cfg_ = config ? *config : pf_backend_config{};
   if (cfg_.staging_slot_bytes == 0) cfg_.staging_slot_bytes = 32u << 20;
-  if (cfg_.staging_slots <= 0) cfg_.staging_slots = 4;
-  if (cfg_.copy_streams <= 0) cfg_.copy_streams = 2;
+  if (cfg_.staging_slots <= 0) cfg_.staging_slots = 6;
+  // One copy stream: DMAs of consecutive slots run back to back.  Two streams let two DMAs share the
+  // link; measured, that is never faster, spreads more from step to step and doubles the time until
+  // the first layer of a save is in the pool.
+  if (cfg_.copy_streams <= 0) cfg_.copy_streams = 1;
   if (cfg_.copy_streams > 8) cfg_.copy_streams = 8;
+  if (cfg_.gather_slots <= 0) cfg_.gather_slots = kHeldGroupsDefault;
+  cfg_.gather_slots = std::min(cfg_.gather_slots, std::max(1, cfg_.staging_slots / 2));
   if (cfg_.min_dma_bytes == 0) cfg_.min_dma_bytes = 256u << 10;
   int count = 0;
   cudaError_t e = cudaGetDeviceCount(&count);
@@ -746,18 +753,20 @@ TransferBackend::Slot &TransferBackend::next_slot() {
   return s;
 }
 
-// Gathers (to_staging) or scatters the units [first, first + count) of the open group in one launch.
-void TransferBackend::launch_group(char *slot_ptr, size_t first, size_t count, bool to_staging, cudaStream_t s) {
+// Gathers (to_staging) or scatters `count` staged units in one launch; unit i lies at
+// slot_ptrs[i] + units[i].slot_offset of the staging ring (the units may sit in different slots).
+void TransferBackend::launch_group(const StagedUnit *units, char *const *slot_ptrs, size_t count, bool to_staging,
+                                   cudaStream_t s) {
   GroupParams p;
   p.n_units = (uint32_t)count;
   p.chunk_bytes = kPackChunk;
   uint64_t chunks = 0, payload = 0;
   bool aligned = true;
   for (size_t i = 0; i < count; ++i) {
-    const StagedUnit &u = group_[first + i];
+    const StagedUnit &u = units[i];
     GroupUnit &g = p.unit[i];
     g.kv = u.dev;
-    g.slot_addr = (uint64_t)(uintptr_t)(slot_ptr + u.slot_offset);
+    g.slot_addr = (uint64_t)(uintptr_t)(slot_ptrs[i] + u.slot_offset);
     g.item_bytes = (uint32_t)u.item_bytes;
     g.chunks_per_item = (uint32_t)((u.item_bytes + kPackChunk - 1) / kPackChunk);
     aligned = aligned && !u.dev.table && (u.dev.base | u.dev.stride | g.slot_addr | u.item_bytes) % 16 == 0;
@@ -779,6 +788,19 @@ void TransferBackend::launch_group(char *slot_ptr, size_t first, size_t count, b
   PF_CUDA(cudaGetLastError());
   time_end(s, t0, 2 * payload, false, stamp_idx);
   ++stats_.kernel_launches;
+}
+
+// All units of the groups in `held` (each in its own staging slot), kMaxGroupUnits per launch.
+void TransferBackend::launch_held(const std::vector<HeldGroup> &held, bool to_staging, cudaStream_t s) {
+  std::vector<StagedUnit> units;
+  std::vector<char *> ptrs;
+  for (const HeldGroup &h : held)
+    for (const StagedUnit &u : h.units) {
+      units.push_back(u);
+      ptrs.push_back(h.slot->ptr);
+    }
+  for (size_t i = 0; i < units.size(); i += kMaxGroupUnits)
+    launch_group(units.data() + i, ptrs.data() + i, std::min<size_t>(kMaxGroupUnits, units.size() - i), to_staging, s);
 }
 
 void TransferBackend::launch_link(const Side &src, const Side &dst, size_t n_items, size_t item_bytes,
@@ -823,8 +845,7 @@ void TransferBackend::launch_descs(const uint64_t *triples_dev, size_t n, bool a
   ++stats_.kernel_launches;
 }
 
-// Copy streams take the DMAs of consecutive staging slots in turn, so that the fixed cost at
-// the start and end of one DMA overlaps the body of the next.
+// With more than one copy stream configured, the streams take the DMAs of consecutive staging slots in turn.
 int TransferBackend::next_aux() {
   const int i = (int)(aux_cursor_++ % aux_.size());
   aux_layer_dirty_[i] = 1;
@@ -872,7 +893,7 @@ void TransferBackend::staged_run(const Side &dev_side, const pf_host_run &run, s
                        group_bytes_ + bytes <= std::min(cfg_.staging_slot_bytes, group_limit_) &&
                        (group_bytes_ & 15u) == 0;
     if (!joins) {
-      flush_group();
+      flush_group(true);
       group_dense_ = dense;
       group_host_is_src_ = host_is_src;
       group_stream_ = stream;
@@ -886,40 +907,36 @@ void TransferBackend::staged_run(const Side &dev_side, const pf_host_run &run, s
   }
 }
 
-// Enqueues the open group: gather kernels then one DMA out (save), or one DMA in then scatter
-// kernels (load).
-void TransferBackend::flush_group() {
-  if (group_.empty()) return;
-  ensure_staging();
-  cudaStream_t stream = group_stream_;
-  Slot &slot = next_slot();
-  const int copy_index = next_aux();
-  cudaStream_t copy = aux_[copy_index];
-  const StagedUnit &first = group_.front();
-  if (gather_only_) {
-    // gather_layers: the kernels alone, back to back.  A slot that an earlier real save still
-    // drains is waited for as usual; slots this mode filled are never handed to a copy stream.
-    if (slot.used) PF_CUDA(cudaStreamWaitEvent(stream, slot.drained, 0));
-    for (size_t i = 0; i < group_.size(); i += kMaxGroupUnits)
-      launch_group(slot.ptr, i, std::min<size_t>(kMaxGroupUnits, group_.size() - i), true, stream);
-    group_.clear();
-    group_bytes_ = 0;
-    group_limit_ = std::min(group_limit_ * 2, cfg_.staging_slot_bytes);
+// Closes the open group.  Load: one DMA into a staging slot, then the scatter kernel.  Save: the
+// group gets its slot and waits in `held_`; emit_held() gathers every held group with ONE launch and
+// sends one DMA per slot after it.  With `may_hold` a full-size group waits for its successor, so that
+// in the steady state a launch fills two slots (K and V of a layer): half the launches for the same
+// DMAs.  Call sites that need the bytes on their way (a layer's event, the end of a call) pass false.
+void TransferBackend::flush_group(bool may_hold) {
+  if (group_.empty()) {
+    if (!may_hold) emit_held();
     return;
   }
-  if (!group_host_is_src_) {
-    if (slot.used) PF_CUDA(cudaStreamWaitEvent(stream, slot.drained, 0));
-    for (size_t i = 0; i < group_.size(); i += kMaxGroupUnits)
-      launch_group(slot.ptr, i, std::min<size_t>(kMaxGroupUnits, group_.size() - i), true, stream);
-    PF_CUDA(cudaEventRecord(slot.filled, stream));
-    PF_CUDA(cudaStreamWaitEvent(copy, slot.filled, 0));
-    if (group_dense_)
-      PF_CUDA(cudaMemcpyAsync(group_host_begin_, slot.ptr, group_bytes_, cudaMemcpyDeviceToHost, copy));
-    else
-      PF_CUDA(cudaMemcpy2DAsync(first.host, first.host_stride, slot.ptr, first.item_bytes, first.item_bytes,
-                                first.n_items, cudaMemcpyDeviceToHost, copy));
-    PF_CUDA(cudaEventRecord(slot.drained, copy));
+  ensure_staging();
+  cudaStream_t stream = group_stream_;
+  if (!group_host_is_src_ || gather_only_) {
+    if (!held_.empty() && held_.front().stream != stream) emit_held();
+    HeldGroup h;
+    h.slot = &next_slot();
+    h.copy_index = gather_only_ ? -1 : next_aux();
+    h.units.swap(group_);
+    h.bytes = group_bytes_;
+    h.dense = group_dense_;
+    h.host_begin = group_host_begin_;
+    h.stream = stream;
+    held_.push_back(std::move(h));
+    const bool hold = may_hold && held_.size() < (size_t)cfg_.gather_slots && held_.back().bytes >= kMinPairBytes;
+    if (!hold) emit_held();
   } else {
+    Slot &slot = next_slot();
+    const int copy_index = next_aux();
+    cudaStream_t copy = aux_[copy_index];
+    const StagedUnit &first = group_.front();
     // The DMA reads host memory that earlier work on the caller's stream may still be writing
     // (a save enqueued just before): each copy stream joins the caller's stream once per call.
     if (!aux_forked_[copy_index]) {
@@ -934,16 +951,46 @@ void TransferBackend::flush_group() {
                                 first.n_items, cudaMemcpyHostToDevice, copy));
     PF_CUDA(cudaEventRecord(slot.filled, copy));
     PF_CUDA(cudaStreamWaitEvent(stream, slot.filled, 0));
+    std::vector<char *> ptrs(group_.size(), slot.ptr);
     for (size_t i = 0; i < group_.size(); i += kMaxGroupUnits)
-      launch_group(slot.ptr, i, std::min<size_t>(kMaxGroupUnits, group_.size() - i), false, stream);
+      launch_group(group_.data() + i, ptrs.data() + i, std::min<size_t>(kMaxGroupUnits, group_.size() - i), false, stream);
     PF_CUDA(cudaEventRecord(slot.drained, stream));
+    slot.used = true;
+    ++stats_.dma_copies;
+    stats_.bytes_staged += group_bytes_;
+    group_.clear();
   }
-  slot.used = true;
-  ++stats_.dma_copies;
-  stats_.bytes_staged += group_bytes_;
-  group_.clear();
   group_bytes_ = 0;
   group_limit_ = std::min(group_limit_ * 2, cfg_.staging_slot_bytes);  // ramp up: the first DMAs start early
+}
+
+// One gather launch for every held save group, then one DMA per group on its copy stream.
+void TransferBackend::emit_held() {
+  if (held_.empty()) return;
+  cudaStream_t stream = held_.front().stream;
+  // A slot that an earlier save still drains is waited for first.
+  for (const HeldGroup &h : held_)
+    if (h.slot->used) PF_CUDA(cudaStreamWaitEvent(stream, h.slot->drained, 0));
+  launch_held(held_, true, stream);
+  if (held_.front().copy_index >= 0) {   // (gather_layers: the kernels alone, nothing leaves the ring)
+    cudaEvent_t filled = held_.front().slot->filled;
+    PF_CUDA(cudaEventRecord(filled, stream));
+    for (const HeldGroup &h : held_) {
+      cudaStream_t copy = aux_[h.copy_index];
+      const StagedUnit &first = h.units.front();
+      PF_CUDA(cudaStreamWaitEvent(copy, filled, 0));
+      if (h.dense)
+        PF_CUDA(cudaMemcpyAsync(h.host_begin, h.slot->ptr, h.bytes, cudaMemcpyDeviceToHost, copy));
+      else
+        PF_CUDA(cudaMemcpy2DAsync(first.host, first.host_stride, h.slot->ptr, first.item_bytes, first.item_bytes,
+                                  first.n_items, cudaMemcpyDeviceToHost, copy));
+      PF_CUDA(cudaEventRecord(h.slot->drained, copy));
+      h.slot->used = true;
+      ++stats_.dma_copies;
+      stats_.bytes_staged += h.bytes;
+    }
+  }
+  held_.clear();
 }
 
 void TransferBackend::gather_layers(const pf_layer_xfer *layers, size_t n_layers, cudaStream_t stream) {
@@ -1199,7 +1246,7 @@ void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, 
     const bool keep_open = !last && ((!group_.empty() && group_bytes_ < kMinEventGroupBytes) ||
                                      (n_units > link_first && link_bytes < kMinLinkLaunchBytes));
     if (!deferred.empty() && !keep_open) {
-      flush_group();
+      flush_group(false);
       flush_link();
       // Saved layers are complete when their DMAs (copy streams) and zero-copy kernels (caller's
       // stream) are; loaded layers always end with a scatter on the caller's stream.
@@ -1216,7 +1263,7 @@ void TransferBackend::move_layers(const pf_layer_xfer *layers, size_t n_layers, 
       deferred.clear();
     }
   }
-  flush_group();
+  flush_group(false);
   flush_link();
   if (!host_is_src) join_copy_streams(stream, aux_task_dirty_, -1);
   // The meta region is free once everything enqueued above has run.
@@ -1295,7 +1342,7 @@ void TransferBackend::copy_descs(const pf_copy_desc *copies, size_t n, bool host
         if (host_is_src) PF_CUDA(cudaEventRecord(fork_, stream));
         const Side dev{0, 0, nullptr, reinterpret_cast<const uint64_t *>(meta_dev_ + base)};
         staged_run(dev, pf_host_run{0, n, host_lo, host_dev_lo, sz}, sz, host_is_src, stream);
-        flush_group();
+        flush_group(false);
         if (!host_is_src) join_copy_streams(stream, aux_task_dirty_, -1);
         cudaEvent_t ev = take_event();
         PF_CUDA(cudaEventRecord(ev, stream));
@@ -1391,7 +1438,7 @@ void TransferBackend::copy_descs(const pf_copy_desc *copies, size_t n, bool host
     staged_run(dev, run, c0.size, host_is_src, stream);
     table_cursor += r.count;
   }
-  flush_group();
+  flush_group(false);
   launch_descs(reinterpret_cast<const uint64_t *>(meta_dev_ + base + table_bytes), n_direct, aligned, stream);
   if (!host_is_src) join_copy_streams(stream, aux_task_dirty_, -1);
   cudaEvent_t ev = take_event();

@@ -85,7 +85,10 @@ class TransferBackend {
   void ensure_staging();
 
   // Kernel launchers (transfer.cu).
-  void launch_group(char *slot_ptr, size_t first, size_t count, bool to_staging, cudaStream_t s);
+  struct StagedUnit;
+  struct HeldGroup;
+  void launch_group(const StagedUnit *units, char *const *slot_ptrs, size_t count, bool to_staging, cudaStream_t s);
+  void launch_held(const std::vector<HeldGroup> &held, bool to_staging, cudaStream_t s);
   void launch_link(const Side &src, const Side &dst, size_t n_items, size_t item_bytes, cudaStream_t s,
                    bool peer);
   void launch_descs(const uint64_t *triples_dev, size_t n, bool aligned, cudaStream_t s);
@@ -93,7 +96,8 @@ class TransferBackend {
   // One run of one range of one layer through the staged route.
   void staged_run(const Side &dev_side, const pf_host_run &run, size_t item_bytes, bool host_is_src,
                   cudaStream_t stream);
-  void flush_group();
+  void flush_group(bool may_hold);
+  void emit_held();
   int next_aux();
   void join_copy_streams(cudaStream_t target, std::vector<char> &dirty, int skip);
 
@@ -108,6 +112,17 @@ class TransferBackend {
     size_t host_stride;
   };
   std::vector<StagedUnit> group_;
+  // Closed save groups whose gather has not been launched yet (see flush_group).
+  struct HeldGroup {
+    Slot *slot = nullptr;
+    int copy_index = -1;       // copy stream of the group's DMA; -1: no DMA (gather_layers)
+    std::vector<StagedUnit> units;
+    size_t bytes = 0;
+    bool dense = true;
+    char *host_begin = nullptr;
+    cudaStream_t stream = nullptr;
+  };
+  std::vector<HeldGroup> held_;
   size_t group_bytes_ = 0;
   size_t group_limit_ = ~(size_t)0;  // current size limit of a group (ramps up within a call)
   char *group_host_begin_ = nullptr, *group_host_end_ = nullptr;

@@ -171,7 +171,7 @@ class PegaEngine:
                  blockwise_alloc: bool = False, hint_value_size: int = 0, pool_shards: int = 1,
                  host_alignment: int = 0, use_mmap_pool: bool = False, route: int = N.ROUTE_AUTO,
                  staging_slot_bytes: int = 0, staging_slots: int = 0, min_dma_bytes: int = 0, link_ctas: int = 0,
-                 pack_ctas: int = 0, time_kernels: bool = False, copy_streams: int = 0):
+                 pack_ctas: int = 0, time_kernels: bool = False, copy_streams: int = 0, gather_slots: int = 0):
         cfg = N.StorageConfig()
         cfg.enable_numa_affinity = int(enable_numa_affinity)
         cfg.blockwise_alloc = int(blockwise_alloc)
@@ -187,6 +187,7 @@ class PegaEngine:
         cfg.backend.pack_ctas = pack_ctas
         cfg.backend.time_kernels = int(time_kernels)
         cfg.backend.copy_streams = copy_streams
+        cfg.backend.gather_slots = gather_slots
         h = C.c_void_p()
         N.check(N.lib.pf_engine_new(pool_bytes, int(use_hugepages), C.byref(cfg), C.byref(h)))
         self._h = h
