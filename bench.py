@@ -486,6 +486,7 @@ def run_reference(args, rank, world, local):
     torch.cuda.synchronize()
     elapsed = barrier_and_max(time.perf_counter() - t0, world, device)
     clocks = sampler.stop() if rank == 0 else None
+    timed_calls, timed_build_s = stats["calls"], stats["build_s"]
     verified = verify_step(wl, lambda: step(use_kernel), torch, device)
     verified = barrier_and_max(0.0 if verified else 1.0, world, device) == 0.0
     extra = {}
@@ -516,8 +517,8 @@ def run_reference(args, rank, world, local):
                     "fragment + one sync per task (gpu_worker.rs:428-523, transfer/memcpy.rs:25-97)")},
         "save_gbs": round(wl.payload * args.steps / t_save / 1e9, 3), "load_gbs": round(wl.payload * args.steps / t_load / 1e9, 3),
         "frac_pcie_gen5_x16": round(value / world / PCIE_GEN5_X16_GBS, 4),
-        "memcpy_calls_per_step": stats["calls"] // max(1, args.steps),
-        "descriptor_build_ms_per_step": round(stats["build_s"] / max(1, args.steps) * 1e3, 2),
+        "memcpy_calls_per_step": timed_calls // max(1, args.steps),
+        "descriptor_build_ms_per_step": round(timed_build_s / max(1, args.steps) * 1e3, 2),
         "cpu_baseline": {"value": round(value, 3), "unit": "GB/s", "cores": world, "kind": "port",
                          "sample": "full workload on every rank; the reference drives its copy engines from one host "
                                    "thread per direction per GPU"},
