@@ -64,6 +64,10 @@ def workloads():
         # Qwen3-0.6B round trip: 256 GPU blocks, 64 saved and loaded back into 64 other ids
         "qwen3-0.6b": dict(layers=28, seg_bytes=16 * 8 * 128 * 2, gpu_blocks=256, requests=1, blocks=64, segments=2),
         "small": dict(layers=4, seg_bytes=16 * 8 * 128 * 2, gpu_blocks=2048, requests=2, blocks=256, segments=2),
+        # four layers of the llama3.1-8b shape with full-length requests: the same launches (20 MiB runs, three
+        # to a gather launch) on 512 MiB of KV, small enough for a full ncu capture
+        "llama3.1-8b-4layers": dict(layers=4, seg_bytes=16 * 8 * 128 * 2, gpu_blocks=2048, requests=2, blocks=640,
+                                    segments=2),
         # one rank of Llama-3.1-70B TP=8: 1 KV head per rank -> 4 KiB segments, 4 prompts of 32768 tokens
         # (gpu_blocks leaves room for disjoint save and load ids when both directions run at once)
         "llama70b-tp8-rank": dict(layers=80, seg_bytes=16 * 1 * 128 * 2, gpu_blocks=16640, requests=4, blocks=2048,
@@ -657,11 +661,14 @@ def build_roofline(stat_pairs, args, alone=None):
                        f"peak is the burst copy figure",
                 "inputs_exceed_l2": alone["inputs_exceed_l2"],
                 "in_pipeline": in_pipeline})
+            if args.traffic_per_launch is None:     # per launch of THIS leg: one DRAM read per payload byte
+                roofline["traffic"] = round(alone["payload"] / alone["launches"] * (8.398336 / 8.388608))
     else:
         ach = link_bytes / 1e6 / link_ms if link_ms > 0 else 0.0
-        roofline = {"kernel": "copy_items_tma (zero-copy over PCIe)", "bound": "hbm", "achieved": round(ach, 1),
+        roofline = {"kernel": "copy_units_tma (zero-copy over PCIe)", "bound": "hbm", "achieved": round(ach, 1),
                     "peak": hbm_peak, "unit": "GB/s", "frac": round(ach / hbm_peak, 4),
-                    "note": "this kernel is bound by the PCIe link, not HBM: see the `link` object",
+                    "note": "this kernel is bound by the PCIe link (128-byte TLPs: 53.1 of the 63.0 GB/s raw rate), not "
+                            "HBM: see the `link` object",
                     "launches": link_launches, "traffic": args.traffic_per_launch}
     return roofline
 
