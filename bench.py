@@ -1076,13 +1076,15 @@ def peer_phase(args, pf, torch, rank, world, local):
     fifth configuration): ranks 0 .. N/2-1 are instance A, ranks N/2 .. N-1 instance B with the same TP degree.
     Every A rank owns a Qwen3-32B TP4-shard-shaped KV cache (64 layers, 2 KV heads per rank -> 8 KiB K and
     V segments, HND inside a block, 8192 blocks) and exports each layer's region (pf_ipc_export); the
-    rank-aligned B rank opens them for its own GPU (pf_ipc_open_for) and pulls 4096 blocks (50 % of the prefix) of every layer
-    into random block ids of its own cache with the peer-copy kernel - all pairs at the same time, no
-    collective on the data path.  Compared with the same blocks going through a pinned host pool, and with one
-    large device-to-device copy between the same two GPUs.  Returns the `peer` object on rank 0."""
+    rank-aligned B rank opens them for its own GPU (pf_ipc_open_for) and pulls 4096 blocks (50 % of the prefix)
+    of every layer into random block ids of its own cache with the peer-copy kernel - all pairs at the same
+    time, no collective on the data path.  Compared with the same blocks going through a pinned host pool, and
+    with one large device-to-device copy between the same two GPUs.  Returns the `peer` object on rank 0.
+
+    Every rank takes part in every barrier whatever happens to it: a rank whose step fails (no peer access on
+    this box, say) remembers why and skips its remaining work, and the object then says `unavailable`."""
     import torch.distributed as dist
     from pegaflow_b200 import _native as N
-
     from pegaflow_b200 import sharding
 
     half = world // 2
@@ -1092,6 +1094,14 @@ def peer_phase(args, pf, torch, rank, world, local):
     role, pair = who.role, who.pair
     payload = L * n * 2 * seg
     gen = torch.Generator(device=device)
+    st = {"error": None}      # this rank's state across the stages
+
+    def stage(fn):
+        if st["error"] is None:
+            try:
+                fn()
+            except Exception as e:      # remembered; the barriers below still happen
+                st["error"] = f"rank {rank}: {type(e).__name__}: {e}"[:300]
 
     def source_layers(seed):
         gen.manual_seed(seed)
@@ -1104,124 +1114,159 @@ def peer_phase(args, pf, torch, rank, world, local):
     si = torch.from_numpy(sids.astype(np.int64)).to(device)
     di = torch.from_numpy(dids.astype(np.int64)).to(device)
     stream = torch.cuda.Stream()
-    mine, kv, big = None, None, None
-    if role == "A":
-        kv = list(source_layers(5000 + pair))
-        big = torch.empty(1 << 30, dtype=torch.uint8, device=device)
+
+    def exact():
+        """Every layer: destination blocks hold the source blocks (regenerated here from A's seed), every
+        other block is still zero."""
+        ok = True
+        for t, want_src in zip(st["dst"], source_layers(5000 + pair)):
+            want = torch.zeros_like(t)
+            want[:, di] = want_src[:, si]
+            ok = ok and torch.equal(t, want)
+            del want, want_src
+        return ok
+
+    # ---- A exports, B opens
+    def a_export():
+        st["kv"] = list(source_layers(5000 + pair))
+        st["big"] = torch.empty(1 << 30, dtype=torch.uint8, device=device)
         regions = []
-        for t in kv + [big]:
+        for t in st["kv"] + [st["big"]]:
             r = N.IpcRegion()
             N.check(N.lib.pf_ipc_export(t.data_ptr(), t.numel(), C.byref(r)))
             regions.append(bytes(r))
         torch.cuda.synchronize()
-        mine = regions
+        st["mine"] = regions
+
+    if role == "A":
+        stage(a_export)
     everyone = [None] * world
-    dist.all_gather_object(everyone, mine)
-    result = None
-    if role == "B":
-        regions = [N.IpcRegion.from_buffer_copy(b) for b in everyone[pair]]
-        src_ptrs, src_dev = [], None
-        for r in regions:     # mapped for this rank's GPU: its kernels and copies read A's memory over NVLink
+    dist.all_gather_object(everyone, st.get("mine"))
+
+    def b_open_and_warm():
+        if everyone[pair] is None:
+            raise RuntimeError("the partner rank exported nothing")
+        st["regions"] = [N.IpcRegion.from_buffer_copy(b) for b in everyone[pair]]
+        st["src_ptrs"] = []
+        for r in st["regions"]:     # mapped for this rank's GPU: its kernels and copies read A's memory over NVLink
             ptr, dev_id = C.c_uint64(), C.c_int()
             N.check(N.lib.pf_ipc_open_for(C.byref(r), local, C.byref(ptr), C.byref(dev_id)))
-            src_ptrs.append(ptr.value)
-            src_dev = dev_id.value
-        dst = [torch.zeros((2, nb, seg), dtype=torch.uint8, device=device) for _ in range(L)]
-        be = pf.TransferBackend(local, link_ctas=args.link_ctas)
-        sl = [(p_, seg, nb * seg, seg, 2, nb) for p_ in src_ptrs[:L]]
-        dl = [(t.data_ptr(), seg, nb * seg, seg, 2, nb) for t in dst]
-
-        def exact():
-            """Every layer: destination blocks hold the source blocks (regenerated here from A's seed), every
-            other block is still zero."""
-            ok = True
-            for t, want_src in zip(dst, source_layers(5000 + pair)):
-                want = torch.zeros_like(t)
-                want[:, di] = want_src[:, si]
-                ok = ok and torch.equal(t, want)
-                del want, want_src
-            return ok
-
+            st["src_ptrs"].append(ptr.value)
+            st["src_dev"] = dev_id.value
+        st["dst"] = [torch.zeros((2, nb, seg), dtype=torch.uint8, device=device) for _ in range(L)]
+        st["be"] = pf.TransferBackend(local, link_ctas=args.link_ctas)
+        st["sl"] = [(p_, seg, nb * seg, seg, 2, nb) for p_ in st["src_ptrs"][:L]]
+        st["dl"] = [(t.data_ptr(), seg, nb * seg, seg, 2, nb) for t in st["dst"]]
         for _ in range(3):
-            be.peer_copy_layers(sl, sids, dl, dids, stream.cuda_stream)
+            st["be"].peer_copy_layers(st["sl"], sids, st["dl"], dids, stream.cuda_stream)
         stream.synchronize()
-    dist.barrier()          # all pairs start their timed copies together
+
     if role == "B":
+        stage(b_open_and_warm)
+    dist.barrier()          # all pairs start their timed copies together
+
+    def b_timed():
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record(stream)
         for _ in range(args.steps):
-            be.peer_copy_layers(sl, sids, dl, dids, stream.cuda_stream)
+            st["be"].peer_copy_layers(st["sl"], sids, st["dl"], dids, stream.cuda_stream)
         b.record(stream)
         b.synchronize()
-        peer_ms = a.elapsed_time(b)
-    dist.barrier()
+        st["peer_ms"] = a.elapsed_time(b)
+
     if role == "B":
-        peer_exact = exact()
-        stats = be.stats()
+        stage(b_timed)
+    dist.barrier()
+
+    def b_check_and_ceiling():
+        st["peer_exact"] = exact()
+        st["stats"] = st["be"].stats()
         # ceiling: one 1 GiB device-to-device copy from the same peer GPU, best of 6, all pairs at once
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         scratch = torch.empty(1 << 30, dtype=torch.uint8, device=device)
         best = 0.0
         for _ in range(6):
             a.record(stream)
-            cuda_memcpy_async(scratch.data_ptr(), src_ptrs[L], 1 << 30, stream.cuda_stream)
+            cuda_memcpy_async(scratch.data_ptr(), st["src_ptrs"][L], 1 << 30, stream.cuda_stream)
             b.record(stream)
             b.synchronize()
             best = max(best, (1 << 30) / 1e6 / a.elapsed_time(b))
-        del scratch
-        be.close()
-    # The reference's way: source GPU -> pinned host pool -> destination GPU.  Each half runs in the process
-    # that owns the GPU (A saves its blocks into a pool, B loads as many bytes from a pool into its blocks);
-    # a hit costs the sum of the two, since the load can only start when the save is in the pool.
-    half_s, half_ok = None, True
-    if role in ("A", "B"):
-        pool = pf.PinnedPool(payload + (64 << 20), numa_node=pf.numa_node_of_device(local))
-        be_h = pf.TransferBackend(local)
-        mem = kv if role == "A" else dst
-        ids = sids if role == "A" else dids
-        lay, images = [], []
+        st["ceiling"] = best
+        st["be"].close()
+
+    if role == "B":
+        stage(b_check_and_ceiling)
+
+    # ---- the reference's way: source GPU -> pinned host pool -> destination GPU.  Each half runs in the
+    # process that owns the GPU (A saves its blocks into a pool, B loads as many bytes from a pool into its
+    # blocks); a hit costs the sum of the two, since the load can only start when the save is in the pool.
+    def half_setup():
+        st["pool"] = pf.PinnedPool(payload + (64 << 20), numa_node=pf.numa_node_of_device(local))
+        st["be_h"] = pf.TransferBackend(local)
+        mem, ids = (st["kv"], sids) if role == "A" else (st["dst"], dids)
+        lay, st["images"] = [], []
         for l in range(L):
-            k, v = pool.alloc(n * seg), pool.alloc(n * seg)
-            images.append((k[0], v[0]))
+            k, v = st["pool"].alloc(n * seg), st["pool"].alloc(n * seg)
+            st["images"].append((k[0], v[0]))
             lay.append(pf.LayerXfer(mem[l].data_ptr(), seg, nb * seg, seg, 2, ids,
                                     [[pf.HostRun(0, n, k[0], k[1], seg)], [pf.HostRun(0, n, v[0], v[1], seg)]]))
-        x = pf.TransferBackend.make_layers(lay)
-        move = be_h.save_layers if role == "A" else be_h.load_layers
-        times = []
-        for _ in range(3):
-            torch.cuda.synchronize(device)
-            dist.barrier()
-            t0 = time.perf_counter()
-            move(x, stream.cuda_stream)
-            stream.synchronize()
-            times.append(time.perf_counter() - t0)
-        half_s = min(times)
+        st["x"] = pf.TransferBackend.make_layers(lay)
+        st["times"] = []
+
+    def half_move():
+        move = st["be_h"].save_layers if role == "A" else st["be_h"].load_layers
+        torch.cuda.synchronize(device)
+        t0 = time.perf_counter()
+        move(st["x"], stream.cuda_stream)
+        stream.synchronize()
+        st["times"].append(time.perf_counter() - t0)
+
+    def half_finish():
+        st["half_s"], ok = min(st["times"]), True
         if role == "A":      # the pool now holds the source blocks of every layer
             for l in range(L):
                 for r_i in range(2):
-                    view = np.ctypeslib.as_array((C.c_uint8 * (n * seg)).from_address(images[l][r_i])).reshape(n, seg)
-                    half_ok = half_ok and torch.equal(kv[l][r_i][si], torch.from_numpy(view).to(device))
-        half_ok = half_ok and be_h.stats()["device_status"] == 0
-        be_h.close(), pool.close()
-    else:
-        for _ in range(3):
-            dist.barrier()
-    if role == "B":
-        for r in regions:
+                    view = np.ctypeslib.as_array((C.c_uint8 * (n * seg)).from_address(st["images"][l][r_i])).reshape(n, seg)
+                    ok = ok and torch.equal(st["kv"][l][r_i][si], torch.from_numpy(view).to(device))
+        st["half_ok"] = ok and st["be_h"].stats()["device_status"] == 0
+        st["be_h"].close(), st["pool"].close()
+
+    if role:
+        stage(half_setup)
+    for _ in range(3):
+        dist.barrier()
+        if role:
+            stage(half_move)
+    if role:
+        stage(half_finish)
+
+    def b_close():
+        for r in st["regions"]:
             N.check(N.lib.pf_ipc_close_for(C.byref(r), local))
-        result = {"pair": [src_dev, local], "ranks": [pair, rank], "GBps": round(payload * args.steps / 1e6 / peer_ms, 2),
-                  "ceiling_GBps": round(best, 1), "bit_exact": bool(peer_exact), "ms": peer_ms,
-                  "gpu_launches": stats["kernel_launches"], "device_status": stats["device_status"],
-                  "load_half_s": half_s, "load_half_ok": bool(half_ok)}
-        del dst
-    elif role == "A":
-        result = {"save_half_s": half_s, "save_half_ok": bool(half_ok)}
+
+    result = {"error": st["error"]}
+    if role == "B":
+        stage(b_close)
+        if st["error"] is None:
+            result = {"pair": [st["src_dev"], local], "ranks": [pair, rank],
+                      "GBps": round(payload * args.steps / 1e6 / st["peer_ms"], 2), "ceiling_GBps": round(st["ceiling"], 1),
+                      "bit_exact": bool(st["peer_exact"]), "ms": st["peer_ms"], "gpu_launches": st["stats"]["kernel_launches"],
+                      "device_status": st["stats"]["device_status"], "load_half_s": st["half_s"],
+                      "load_half_ok": bool(st["half_ok"]), "error": None}
+        else:
+            result = {"error": st["error"]}
+    elif role == "A" and st["error"] is None:
+        result = {"save_half_s": st["half_s"], "save_half_ok": bool(st["half_ok"]), "error": None}
     results = [None] * world
     dist.all_gather_object(results, result)
     dist.barrier()          # instance A keeps its memory until every B rank has closed its mappings
-    del kv, big
+    st.clear()
     torch.cuda.empty_cache()
     if rank != 0:
         return None
+    errors = [r["error"] for r in results if r and r.get("error")]
+    if errors:
+        return {"unavailable": "; ".join(errors)}
     rs = [r for r in results if r and "pair" in r]
     for r in rs:    # a hit through the host pool: the A rank's save, then the B rank's load
         a_side = results[r["ranks"][0]]
@@ -1233,7 +1278,7 @@ def peer_phase(args, pf, torch, rank, world, local):
         "config": {"workload": "qwen3-32b-tp4-rank prefix hit across instances", "layers": L, "seg_bytes": seg, "gpu_blocks": nb,
                    "blocks": n, "segments": 2, "payload_bytes_per_pair": payload,
                    "instances": "A = ranks 0..%d, B = ranks %d..%d, one process per GPU; B reaches A's KV cache through "
-                                "pf_ipc_export / pf_ipc_open" % (half - 1, half, 2 * half - 1),
+                                "pf_ipc_export / pf_ipc_open_for" % (half - 1, half, 2 * half - 1),
                    "kernel_runs_on": "destination GPU (pull)"},
         "pairs": [r["pair"] for r in rs], "per_pair_GBps": [r["GBps"] for r in rs], "aggregate_GBps": round(agg, 2),
         "link": {"bound": "nvlink5", "peak_nominal_per_direction": 900.0,
@@ -1253,7 +1298,6 @@ def peer_phase(args, pf, torch, rank, world, local):
         "gpu_launches": sum(r["gpu_launches"] for r in rs), "device_status": max(r["device_status"] for r in rs),
         "how": "per pair: CUDA events on the destination rank's stream around `steps` calls of pf_backend_peer_copy_layers, "
                "all pairs released by one barrier; aggregate = all pairs' bytes / the slowest pair's time"}
-
 
 
 def read_first_line(path):
@@ -1311,8 +1355,8 @@ def run_placement_probe(args, rank, world, local):
     stream = torch.cuda.Stream()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
-    def copy_rate(c, to_host, reps):
-        """GB/s of `reps` passes over the chunk in pieces of 256 MiB."""
+    def copy_rate(c, to_host, reps, piece=piece):
+        """GB/s of `reps` passes over the chunk in pieces of 256 MiB (or of `piece` bytes)."""
         a.record(stream)
         for _ in range(reps):
             for off in range(0, chunk, piece):
@@ -1344,9 +1388,30 @@ def run_placement_probe(args, rank, world, local):
         final[key] = round(copy_rate(best[key], to_host, args.probe_reps), 2)
         barrier(world)
         final[key + "_first_chunk"] = round(copy_rate(live[0], to_host, args.probe_reps), 2)
+    # how the rate of one GPU falls as more GPUs copy at once: ranks 0..k-1 copy, the others wait
+    ladder = {}
+    counts = sorted({k for k in (1, 2, 3, 4, 6, 8, world) if k <= world})
+    for key, to_host in (("d2h", True), ("h2d", False)):
+        for k in counts:
+            barrier(world)
+            ladder[f"{key}_{k}_at_once"] = round(copy_rate(live[0], to_host, args.probe_reps), 2) if rank < k else None
+            barrier(world)
+    # even ranks write host memory while odd ranks read it, then the other way round
+    mixed = {}
+    for name, flip in (("even_d2h_odd_h2d", 0), ("even_h2d_odd_d2h", 1)):
+        barrier(world)
+        to_host = (rank + flip) % 2 == 0
+        mixed[name] = {"dir": "d2h" if to_host else "h2d", "gbs": round(copy_rate(live[0], to_host, args.probe_reps), 2)}
+    # the sizes the engine's own copies have: one staging slot, and one block-sized item
+    by_piece = {}
+    for mib in (32, 2):
+        for key, to_host in (("d2h", True), ("h2d", False)):
+            barrier(world)
+            by_piece[f"all_{key}_{mib}mib_pieces"] = round(copy_rate(live[0], to_host, 1, mib << 20), 2)
     mine = {"rank": rank, "gpu": local,
             "chunks": [{k: v for k, v in c.items() if k not in ("pool", "host")} for c in chunks],
-            "best_chunk": {k: chunks.index(v) for k, v in best.items()}, "all_ranks_best_chunk": final}
+            "best_chunk": {k: chunks.index(v) for k, v in best.items()}, "all_ranks_best_chunk": final,
+            "ranks_at_once": ladder, "mixed_directions": mixed, "piece_size": by_piece}
     for c in live:
         c["pool"].close()
     every = [None] * world
@@ -1368,6 +1433,11 @@ def run_placement_probe(args, rank, world, local):
         "how": "plain cudaMemcpyAsync in 256 MiB pieces between each rank's GPU and each of its candidate chunks; solo_* = "
                "one rank at a time, all_* = every rank at once on its chunk of the same index; all_ranks_best_chunk = every "
                "rank at once, each on the chunk that was fastest for it under load (and on its first chunk, for comparison)",
+        "ranks_at_once_sum": {k: round(sum(r["ranks_at_once"][k] or 0.0 for r in every), 2) for k in every[0]["ranks_at_once"]},
+        "piece_size_sum": {k: round(sum(r["piece_size"][k] for r in every), 2) for k in every[0]["piece_size"]},
+        "mixed_directions_sum": {name: {d: round(sum(r["mixed_directions"][name]["gbs"] for r in every
+                                                     if r["mixed_directions"][name]["dir"] == d), 2) for d in ("d2h", "h2d")}
+                                 for name in every[0]["mixed_directions"]},
         "sum_all_ranks_best_chunk": {"d2h": total("all_d2h"), "h2d": total("all_h2d"),
                                      "d2h_first_chunk": total("all_d2h_first_chunk"),
                                      "h2d_first_chunk": total("all_h2d_first_chunk")},
