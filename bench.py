@@ -277,6 +277,39 @@ def measure_pcie_ceiling(device, nbytes=1 << 30, iters=5, sustained=False, world
     return res
 
 
+def duplex_pcie_ceiling(device, world, nbytes=1 << 30, iters=5):
+    """Both directions at once: `iters` x 1 GiB pinned->device on one stream while as many go device->pinned on
+    another, on every rank at the same time.  Per-rank GB/s of each direction (its own bytes over its own
+    span) and of the pair (all bytes over the span from the first copy's start to the last one's end)."""
+    import torch
+
+    hosts = [torch.empty(nbytes, dtype=torch.uint8, pin_memory=True) for _ in range(2)]
+    devs = [torch.empty(nbytes, dtype=torch.uint8, device=device) for _ in range(2)]
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    pairs = [(hosts[0], devs[0]), (devs[1], hosts[1])]       # (dst, src): d2h on stream 0, h2d on stream 1
+    for (dst, src), s in zip(pairs, streams):
+        with torch.cuda.stream(s):
+            dst.copy_(src, non_blocking=True)
+    torch.cuda.synchronize()
+    barrier(world)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(2)]
+    go = torch.cuda.Event()
+    go.record()
+    for (dst, src), s, (a, b) in zip(pairs, streams, ev):
+        s.wait_event(go)
+        with torch.cuda.stream(s):
+            a.record()
+            for _ in range(iters):
+                dst.copy_(src, non_blocking=True)
+            b.record()
+    torch.cuda.synchronize()
+    d2h = iters * nbytes / 1e6 / ev[0][0].elapsed_time(ev[0][1])
+    h2d = iters * nbytes / 1e6 / ev[1][0].elapsed_time(ev[1][1])
+    span = max(ev[0][0].elapsed_time(ev[0][1]), ev[0][0].elapsed_time(ev[1][1]), ev[1][0].elapsed_time(ev[0][1]),
+               ev[1][0].elapsed_time(ev[1][1]))
+    return {"d2h": d2h, "h2d": h2d, "pair": 2 * iters * nbytes / 1e6 / span}
+
+
 def concurrent_pcie_ceiling(device, world):
     """What the host platform gives when every rank copies at once: per-rank sustained GB/s per
     direction, gathered on all ranks.  Several GPUs can share a root port, a socket link or the
@@ -923,6 +956,16 @@ def run_duplex(args, rank, world, local):
         e2e = run_e2e(args, pf, wl, rank, world, local, route, duplex=True)
         e2e.pop("e2e_breakdown")
     concurrent = concurrent_pcie_ceiling(device, world) if world > 1 else None
+    both = duplex_pcie_ceiling(device, world)
+    if world > 1:
+        import torch.distributed as dist
+
+        t = torch.tensor([both["d2h"], both["h2d"], both["pair"]], dtype=torch.float64, device=device)
+        every = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(every, t)
+        both = {k: [round(float(x[i]), 2) for x in every] for i, k in enumerate(("d2h", "h2d", "pair"))}
+    else:
+        both = {k: [round(v, 2)] for k, v in both.items()}
     barrier(world)
     ceiling = measure_pcie_ceiling(device) if rank == 0 else None
     if rank != 0:
@@ -944,7 +987,14 @@ def run_duplex(args, rank, world, local):
                  "value_frac_of_sum_of_ceilings": round(value / world / (ceiling["d2h"] + ceiling["h2d"]), 4),
                  "ceiling_how": "one 1 GiB pinned<->device cudaMemcpyAsync per direction, best of 5, one direction "
                                 "at a time, rank 0 alone",
-                 "all_ranks_at_once": concurrent},
+                 "all_ranks_at_once": concurrent,
+                 "both_directions_at_once": {
+                     "d2h_per_rank": both["d2h"], "h2d_per_rank": both["h2d"], "pair_per_rank": both["pair"],
+                     "pair_sum": round(sum(both["pair"]), 2),
+                     "value_frac": round(value / (world * min(both["pair"])), 4),
+                     "how": "every rank runs 5 x 1 GiB plain cudaMemcpyAsync device->pinned on one stream and 5 x 1 GiB "
+                            "pinned->device on another at the same time; value_frac = value / (ranks x the slowest "
+                            "rank's pair rate), the max-over-ranks rule of `value`"}},
         "roofline": roofline, "cpu_baseline": None, "e2e": e2e,
         "gpu_launches": sum(b["kernel_launches"] - a["kernel_launches"] for a, b in zip(st0, st1)),
         "dma_copies": sum(b["dma_copies"] - a["dma_copies"] for a, b in zip(st0, st1)), "device_status": status,
@@ -1320,6 +1370,45 @@ def first_page_frame(addr):
         return None
 
 
+class WideChunk:
+    """A 1 GiB anonymous mapping (2 MiB pages where the kernel grants them), touched, whose place in guest-physical
+    memory is sampled at 16 points; pinned with cudaHostRegister only if it is kept."""
+
+    def __init__(self, nbytes):
+        import mmap
+
+        self.nbytes = nbytes
+        self.map = mmap.mmap(-1, nbytes, flags=mmap.MAP_PRIVATE | mmap.MAP_ANONYMOUS)
+        if hasattr(mmap, "MADV_HUGEPAGE"):
+            try:
+                self.map.madvise(mmap.MADV_HUGEPAGE)
+            except OSError:
+                pass
+        self.view = np.frombuffer(self.map, dtype=np.uint8)
+        self.view[::4096] = 1
+        self.addr = self.view.ctypes.data
+        frames = [first_page_frame(self.addr + i * (nbytes // 16)) for i in range(16)]
+        frames = sorted(f for f in frames if f is not None)
+        self.frames_gib = [round(f * 4096 / 2 ** 30, 1) for f in frames]
+        self.median_gib = self.frames_gib[len(frames) // 2] if frames else -1.0
+        self.registered = False
+
+    def register(self, torch):
+        rc = torch.cuda.cudart().cudaHostRegister(self.addr, self.nbytes, 0)
+        if int(rc) != 0:
+            raise RuntimeError(f"cudaHostRegister failed with {int(rc)}")
+        self.registered = True
+
+    def close(self, torch=None):
+        if self.registered:
+            import torch as _torch
+
+            _torch.cuda.cudart().cudaHostUnregister(self.addr)
+            self.registered = False
+        self.view = None
+        self.map.close()
+
+
 def run_placement_probe(args, rank, world, local):
     """Does it matter where in host memory a GPU's pinned pool lies?  On a guest that shows a single NUMA
     node the kernel gives no answer, so this measures it: every rank allocates candidate chunks in several
@@ -1351,6 +1440,24 @@ def run_placement_probe(args, rank, world, local):
         except pf.PegaFlowError as e:
             chunks.append({"kind": name, "cpu_quarter": q, "pool": None, "unavailable": str(e)[:100]})
     os.sched_setaffinity(0, cpus)
+    # a sweep over guest-physical memory: every rank fills `probe_wide_gib` GiB at the same time (together
+    # they reach far into the guest's memory), keeps the chunks that lie lowest, highest and in between, and
+    # gives the rest back before anything is pinned
+    wide = []
+    if args.probe_wide_gib > 0:
+        wide = [WideChunk(chunk) for _ in range(args.probe_wide_gib * (1 << 30) // chunk)]
+        barrier(world)
+        wide.sort(key=lambda w: w.median_gib)
+        picks = sorted({round(i * (len(wide) - 1) / 3) for i in range(4)})
+        for i, w in enumerate(wide):
+            if i not in picks:
+                w.close()
+        wide = [wide[i] for i in picks]
+        for w in wide:
+            w.register(torch)
+            chunks.append({"kind": "mmap(2 MiB pages)+register, sweep", "cpu_quarter": None, "pool": w, "host": w.addr,
+                           "pfn": first_page_frame(w.addr), "frames_gib_min_median_max":
+                               [w.frames_gib[0], w.median_gib, w.frames_gib[-1]] if w.frames_gib else None})
     dev = torch.empty(piece, dtype=torch.uint8, device=device)
     stream = torch.cuda.Stream()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -2095,6 +2202,8 @@ def main():
     ap.add_argument("--probe-late-chunks", type=int, default=4)
     ap.add_argument("--probe-reps", type=int, default=2)
     ap.add_argument("--probe-hugepages", action="store_true")
+    ap.add_argument("--probe-wide-gib", type=int, default=24,
+                    help="GiB every rank fills to find chunks far apart in guest-physical memory (0 = skip)")
     args = ap.parse_args()
     if args.peer:
         run_peer(args)
