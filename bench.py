@@ -636,6 +636,10 @@ def time_gather_alone(args, pf, torch, local, route, wl, save_x, stream):
             "inputs_exceed_l2": wl.payload > 126e6}
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum (MB) of one 60 MiB save launch of copy_group_ldst under ncu
+SAVE_LAUNCH_DRAM_MB = 62.929152 + 10.871808
+
+
 def build_roofline(stat_pairs, args, alone=None):
     """The `roofline` object.  `alone` (time_gather_alone) gives the headline figure: the kernel timed
     by itself with CUDA events.  The backend counters taken before and after the timed region (summed
@@ -694,8 +698,14 @@ def build_roofline(stat_pairs, args, alone=None):
                        f"peak is the burst copy figure",
                 "inputs_exceed_l2": alone["inputs_exceed_l2"],
                 "in_pipeline": in_pipeline})
-            if args.traffic_per_launch is None:     # per launch of THIS leg: one DRAM read per payload byte
-                roofline["traffic"] = round(alone["payload"] / alone["launches"] * (8.398336 / 8.388608))
+            if args.traffic_per_launch is None:
+                # per launch of THIS leg, from an ncu capture of two 60 MiB save launches of the same kernel
+                # (62.915 MB of payload each: 62.93 MB read; 9.49 and 12.25 MB written back while the launch ran,
+                # the rest of the staging writes still being in L2 at its end), scaled by payload
+                roofline["traffic"] = round(alone["payload"] / alone["launches"] * (SAVE_LAUNCH_DRAM_MB / 62.914560))
+                roofline["traffic_how"] = ("dram__bytes_read.sum + dram__bytes_write.sum of a 60 MiB launch under ncu, "
+                                           "scaled by payload: one read per payload byte, and the 0.15-0.19 of the "
+                                           "staging writes that leave L2 before the launch ends")
     else:
         ach = link_bytes / 1e6 / link_ms if link_ms > 0 else 0.0
         roofline = {"kernel": "copy_units_tma (zero-copy over PCIe)", "bound": "hbm", "achieved": round(ach, 1),

@@ -42,7 +42,9 @@ def test_roofline_headline_is_the_kernel_alone_when_that_leg_ran():
     assert abs(r["achieved"] - 2 * alone["payload"] / 1e6 / 16.0) < 0.1
     assert abs(r["frac"] - r["achieved"] / r["peak"]) < 1e-3
     assert "gather_layers" in r["how"] and r["inputs_exceed_l2"] is True
-    assert r["traffic"] == round((20 << 20) * (8.398336 / 8.388608))      # per launch of the headline leg
+    # per launch of the headline leg: the reads of the payload plus the write-backs seen during a launch
+    assert r["traffic"] == round((20 << 20) * (bench.SAVE_LAUNCH_DRAM_MB / 62.914560))
+    assert (20 << 20) < r["traffic"] < r["algorithmic_bytes_per_launch"]
     inner = r["in_pipeline"]
     assert inner["launches"] == 100 and abs(inner["avg_launch_us"] - 40.0) < 1e-6
     assert inner["device_clock"]["frac"] > inner["frac"]
