@@ -49,13 +49,18 @@ def needs_build() -> bool:
 def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not needs_build():
         return LIB_PATH
-    cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-I", INCLUDE, "-o", LIB_PATH] + \
+    # linked under another name and renamed, so that a reader never sees a half-written library
+    tmp = os.path.join(PKG_DIR, f".libpegaflow_b200.{os.getpid()}.tmp")
+    cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-I", INCLUDE, "-o", tmp] + \
         sources() + LINK_FLAGS
     if verbose:
         print(" ".join(cmd))
     proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if proc.returncode != 0:
+        if os.path.exists(tmp):
+            os.remove(tmp)
         raise RuntimeError("nvcc failed:\n" + proc.stdout)
+    os.replace(tmp, LIB_PATH)
     if verbose:
         print(proc.stdout)
     return LIB_PATH

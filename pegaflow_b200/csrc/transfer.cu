@@ -251,6 +251,11 @@ struct GroupParams {
 template <bool kAligned>
 __global__ void __launch_bounds__(kLdstThreads, kLdstCtasPerSm)
 copy_group_ldst(const __grid_constant__ GroupParams p, int to_staging, unsigned long long *stamp) {
+  // Programmatic dependent launch: the next kernel of the stream may be scheduled onto the SMs as
+  // this one's CTAs leave them, and this one touches memory only when everything enqueued before it
+  // has completed and is visible.  Both instructions do nothing in a launch without the attribute.
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (stamp && threadIdx.x == 0) atomicMin(&stamp[0], (unsigned long long)global_timer_ns());
   // 32-bit chunk arithmetic: a group holds at most one staging slot of bytes
   const uint32_t total = (uint32_t)p.unit[p.n_units - 1].chunk_end;
@@ -783,8 +788,24 @@ void TransferBackend::launch_group(const StagedUnit *units, char *const *slot_pt
     stamp_idx = (int)stamps_used_++;
     stamp = stamps_dev_ + 2 * (size_t)stamp_idx;
   }
-  if (aligned) copy_group_ldst<true><<<grid, kLdstThreads, 0, s>>>(p, to_staging ? 1 : 0, stamp);
-  else copy_group_ldst<false><<<grid, kLdstThreads, 0, s>>>(p, to_staging ? 1 : 0, stamp);
+  // Back-to-back launches overlap their launch latency with the tail of the kernel before them
+  // (PEGAFLOW_B200_PDL=1 turns the attribute on).
+  static const bool dependent_launch = [] {
+    const char *e = getenv("PEGAFLOW_B200_PDL");
+    return e && atoi(e) != 0;
+  }();
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = dim3((unsigned)grid);
+  lc.blockDim = dim3(kLdstThreads);
+  lc.stream = s;
+  lc.attrs = attr;
+  lc.numAttrs = dependent_launch ? 1 : 0;
+  const int dir = to_staging ? 1 : 0;
+  if (aligned) PF_CUDA(cudaLaunchKernelEx(&lc, copy_group_ldst<true>, p, dir, stamp));
+  else PF_CUDA(cudaLaunchKernelEx(&lc, copy_group_ldst<false>, p, dir, stamp));
   PF_CUDA(cudaGetLastError());
   time_end(s, t0, 2 * payload, false, stamp_idx);
   ++stats_.kernel_launches;

@@ -56,3 +56,12 @@ def test_roofline_of_the_zero_copy_route_reports_the_link_kernel():
     after = _stats(0, 0.0, 0, link=(64, 200.0, 10 << 30))
     r = bench.build_roofline([(zero, after)], ARGS)
     assert REQUIRED <= set(r) and r["launches"] == 64 and "PCIe" in r["note"]
+
+
+def test_sweep_chunk_reports_where_it_lies_and_releases_its_mapping():
+    w = bench.WideChunk(8 << 20)
+    assert w.addr % 4096 == 0 and w.view[0] == 1 and w.view[4096] == 1 and w.view[1] == 0
+    assert w.frames_gib == sorted(w.frames_gib)            # empty where the kernel hides page frames
+    assert (w.median_gib in w.frames_gib) if w.frames_gib else w.median_gib == -1.0
+    w.close()
+    assert w.view is None and w.map.closed
