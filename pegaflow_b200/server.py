@@ -164,6 +164,8 @@ class EngineService:
         self.registry = registry or TensorRegistry()
         self.sessions = SessionRegistry()
         self.shutdown_requested = threading.Event()
+        self._instances_lock = threading.Lock()
+        self._instances: Dict[str, None] = {}       # registered instance ids, in registration order
 
     # ---- helpers
     @staticmethod
@@ -179,11 +181,17 @@ class EngineService:
     def cleanup_instance(self, instance_id: str) -> int:
         """service.rs:59-82: drop the instance's mapped tensors, then the instance (a missing instance is fine)."""
         removed = self.registry.drop_instance(instance_id)
+        with self._instances_lock:
+            self._instances.pop(instance_id, None)
         try:
             self.engine.unregister_instance(instance_id)
         except Exception:
             pass
         return removed
+
+    def instance_ids(self) -> List[str]:
+        with self._instances_lock:
+            return list(self._instances)
 
     # ---- RPCs
     def RegisterContextBatch(self, req, context):
@@ -218,6 +226,8 @@ class EngineService:
         except Exception as e:
             self.registry.drop_context(key)      # service.rs:318-330
             context.abort(_status_of(e), str(e))
+        with self._instances_lock:
+            self._instances[req.instance_id] = None
         return pb.RegisterContextResponse(status=self._ok())
 
     def Save(self, req, context):
@@ -341,6 +351,98 @@ def serve(engine, address: str = "127.0.0.1:0", *, version: str = R.PROTOCOL_VER
     return EngineServer(service, server, port)
 
 
+def prometheus_text(metrics: dict) -> str:
+    """The engine's transfer and pool counters in the Prometheus text format, under the reference's
+    instrument names (pegaflow-core/src/metrics.rs:229-241,325-349).  Its two duration histograms are
+    given as their sum and count; counters carry the `_total` suffix the exposition format asks for."""
+    rows = [
+        ("pegaflow_save_bytes_total", "counter", "Total bytes saved from GPU to CPU storage", metrics["save_bytes"]),
+        ("pegaflow_save_duration_sum", "untyped", "Save operation latency in seconds (sum)", metrics["save_duration_seconds"]),
+        ("pegaflow_save_duration_count", "untyped", "Save operations", metrics["save_batches"]),
+        ("pegaflow_load_bytes_total", "counter", "Total bytes loaded from CPU storage to GPU", metrics["load_bytes"]),
+        ("pegaflow_load_duration_sum", "untyped", "Load operation latency in seconds (sum)", metrics["load_duration_seconds"]),
+        ("pegaflow_load_duration_count", "untyped", "Load operations", metrics["load_tasks"]),
+        ("pegaflow_load_failures_total", "counter", "Load operation failures (e.g., transfer errors)", metrics["load_failures"]),
+        ("pegaflow_pool_capacity_bytes", "gauge", "Pinned pool capacity", metrics["pool_capacity_bytes"]),
+        ("pegaflow_pool_used_bytes", "gauge", "Pinned pool bytes in use", metrics["pool_used_bytes"]),
+        ("pegaflow_pool_alloc_failures_total", "counter", "Pinned pool allocation failures", metrics["pool_alloc_failures"]),
+    ]
+    out = []
+    for name, kind, text, value in rows:
+        out += [f"# HELP {name} {text}", f"# TYPE {name} {kind}", f"{name} {value}"]
+    return "\n".join(out) + "\n"
+
+
+class HttpEndpoints:
+    """pegaflow-server/src/http_server.rs:22-196: `GET /health`, `GET /metrics` (when enabled),
+    `GET /instances`, `POST /instances/cleanup[?id=<instance_id>]`, on a thread of their own."""
+
+    def __init__(self, service: EngineService, address: str = "127.0.0.1:0", enable_prometheus: bool = True):
+        import json
+        from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+        from urllib.parse import parse_qs, urlsplit
+
+        class Handler(BaseHTTPRequestHandler):
+            def _send(self, code, body, kind="text/plain; charset=utf-8"):
+                data = body.encode()
+                self.send_response(code)
+                self.send_header("Content-Type", kind)
+                self.send_header("Content-Length", str(len(data)))
+                self.end_headers()
+                self.wfile.write(data)
+
+            def _json(self, code, obj):
+                self._send(code, json.dumps(obj), "application/json")
+
+            def do_GET(self):
+                path = urlsplit(self.path).path
+                if path == "/health":
+                    self._send(200, "ok")
+                elif path == "/metrics" and enable_prometheus:
+                    try:
+                        self._send(200, prometheus_text(service.engine.metrics()), "text/plain; version=0.0.4")
+                    except Exception as e:
+                        self._send(200, f"# Error encoding metrics: {e}\n")
+                elif path == "/instances":
+                    self._json(200, {"instances": service.instance_ids()})
+                else:
+                    self._send(404, "metrics not enabled" if path == "/metrics" else "not found")
+
+            def do_POST(self):
+                url = urlsplit(self.path)
+                if url.path != "/instances/cleanup":
+                    self._send(404, "not found")
+                    return
+                wanted = parse_qs(url.query).get("id")
+                if wanted is None:        # every instance and every mapped tensor
+                    ids = service.instance_ids()
+                    tensors = sum(service.cleanup_instance(i) for i in ids)
+                    self._json(200, {"removed_instances": ids, "removed_tensors": tensors})
+                    return
+                instance_id = wanted[0]
+                known = instance_id in service.instance_ids()
+                tensors = service.cleanup_instance(instance_id)
+                if known or tensors > 0:
+                    self._json(200, {"removed_instances": [instance_id], "removed_tensors": tensors})
+                else:
+                    self._send(404, f"instance {instance_id} not found")
+
+            def log_message(self, fmt, *args):     # quiet: requests are not logged to stderr
+                pass
+
+        host, _, port = address.rpartition(":")
+        self._httpd = ThreadingHTTPServer((host or "127.0.0.1", int(port)), Handler)
+        self._httpd.daemon_threads = True
+        self.port = self._httpd.server_address[1]
+        self._thread = threading.Thread(target=self._httpd.serve_forever, name="pf-http", daemon=True)
+        self._thread.start()
+
+    def stop(self):
+        self._httpd.shutdown()
+        self._httpd.server_close()
+        self._thread.join(2.0)
+
+
 def main(argv=None):
     """``python -m pegaflow_b200.server --addr 127.0.0.1:50055 --pool-size 32gb`` (pegaflow-server's flags
     of the same names)."""
@@ -352,17 +454,21 @@ def main(argv=None):
     ap.add_argument("--addr", default="127.0.0.1:50055")
     ap.add_argument("--pool-size", default="30gb")
     ap.add_argument("--use-hugepages", action="store_true")
+    ap.add_argument("--http-addr", default="0.0.0.0:9091", help="health check, metrics and instance management")
+    ap.add_argument("--enable-prometheus", default="true", choices=["true", "false"])
     args = ap.parse_args(argv)
     units = {"kb": 1 << 10, "mb": 1 << 20, "gb": 1 << 30, "tb": 1 << 40}
     text = args.pool_size.lower()
     pool = int(float(text[:-2]) * units[text[-2:]]) if text[-2:] in units else int(text)
     engine = PegaEngine(pool, args.use_hugepages)
     server = serve(engine, args.addr)
-    print(f"pegaflow_b200 engine server listening on port {server.port}", flush=True)
+    http = HttpEndpoints(server.service, args.http_addr, args.enable_prometheus == "true")
+    print(f"pegaflow_b200 engine server listening on port {server.port}, HTTP on port {http.port}", flush=True)
     try:
         server.wait_for_shutdown_request()
     except KeyboardInterrupt:
         pass
+    http.stop()
     server.stop()
     engine.close()
 

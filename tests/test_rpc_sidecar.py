@@ -216,3 +216,60 @@ def test_wire_contract_field_numbers():
     assert pb.QueryResponse(loading=pb.QueryLoading()).SerializeToString() == b"\x0a\x00"
     assert pb.QueryReady(num_hit_blocks=2, lease=b"ab", hit_positions=[1, 5]).SerializeToString() == b"\x08\x02\x12\x02ab\x1a\x02\x01\x05"
     assert rpc_proto.method_path("QueryPrefetch") == "/pegaflow.Engine/QueryPrefetch"
+
+
+def test_http_health_metrics_and_instance_management(sidecar):
+    """pegaflow-server/src/http_server.rs:22-196: /health, /metrics, /instances, /instances/cleanup[?id=]."""
+    import json
+    import urllib.error
+    import urllib.request
+
+    from pegaflow_b200.server import HttpEndpoints, prometheus_text
+
+    engine, registry, buffers, server, client = sidecar
+    counters = dict(save_bytes=4096, save_duration_seconds=0.5, save_batches=2, load_bytes=1024,
+                    load_duration_seconds=0.25, load_tasks=1, load_failures=0, pool_capacity_bytes=16 << 20,
+                    pool_used_bytes=8192, pool_alloc_failures=3)
+    engine.metrics = lambda: counters
+    http = HttpEndpoints(server.service, "127.0.0.1:0")
+    base = f"http://127.0.0.1:{http.port}"
+
+    def get(path):
+        with urllib.request.urlopen(base + path, timeout=10) as r:
+            return r.status, r.read().decode()
+
+    def post(path):
+        try:
+            with urllib.request.urlopen(urllib.request.Request(base + path, data=b"", method="POST"), timeout=10) as r:
+                return r.status, r.read().decode()
+        except urllib.error.HTTPError as e:
+            return e.code, e.read().decode()
+
+    try:
+        assert get("/health") == (200, "ok")
+        assert json.loads(get("/instances")[1]) == {"instances": []}
+        _register(client, buffers, "a", 0, 2, tp_size=1, world=1)
+        _register(client, buffers, "b", 0, 3, tp_size=1, world=1)
+        assert json.loads(get("/instances")[1]) == {"instances": ["a", "b"]}
+        code, text = get("/metrics")
+        assert code == 200 and text == prometheus_text(counters)
+        for line in ("pegaflow_save_bytes_total 4096", "pegaflow_load_bytes_total 1024", "pegaflow_load_failures_total 0",
+                     "pegaflow_save_duration_sum 0.5", "pegaflow_load_duration_count 1",
+                     "pegaflow_pool_used_bytes 8192", "pegaflow_pool_alloc_failures_total 3"):
+            assert line in text.splitlines()
+        assert post("/instances/cleanup?id=nobody")[0] == 404
+        assert json.loads(post("/instances/cleanup?id=a")[1]) == {"removed_instances": ["a"], "removed_tensors": 2}
+        assert json.loads(get("/instances")[1]) == {"instances": ["b"]}
+        assert json.loads(post("/instances/cleanup")[1]) == {"removed_instances": ["b"], "removed_tensors": 3}
+        assert json.loads(get("/instances")[1]) == {"instances": []} and registry.contexts == {}
+        with pytest.raises(urllib.error.HTTPError):
+            get("/nothing")
+    finally:
+        http.stop()
+    quiet = HttpEndpoints(server.service, "127.0.0.1:0", enable_prometheus=False)
+    try:
+        with pytest.raises(urllib.error.HTTPError) as e:
+            urllib.request.urlopen(f"http://127.0.0.1:{quiet.port}/metrics", timeout=10)
+        assert e.value.code == 404 and e.value.read() == b"metrics not enabled"
+    finally:
+        quiet.stop()
