@@ -1110,6 +1110,16 @@ def run_e2e(args, pf, wl, rank, world, local, route, duplex=False):
 def cuda_memcpy_async(dst_ptr, src_ptr, nbytes, stream):
     """cudaMemcpyAsync(cudaMemcpyDefault) on raw device addresses (torch cannot wrap a pointer that was
     opened from another process)."""
+    rc = cudart().cudaMemcpyAsync(C.c_void_p(dst_ptr), C.c_void_p(src_ptr), nbytes, 4, C.c_void_p(stream))
+    if rc:
+        raise RuntimeError(f"cudaMemcpyAsync failed with CUDA error {rc}")
+
+
+_CUDART = None
+
+
+def cudart():
+    """The CUDA runtime library torch has loaded, by ctypes."""
     import torch  # noqa: F401  (has loaded the CUDA runtime this resolves to)
 
     global _CUDART
@@ -1123,12 +1133,26 @@ def cuda_memcpy_async(dst_ptr, src_ptr, nbytes, stream):
         else:
             raise RuntimeError("the CUDA runtime library is not loadable by name")
         _CUDART.cudaMemcpyAsync.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]
-    rc = _CUDART.cudaMemcpyAsync(C.c_void_p(dst_ptr), C.c_void_p(src_ptr), nbytes, 4, C.c_void_p(stream))
-    if rc:
-        raise RuntimeError(f"cudaMemcpyAsync failed with CUDA error {rc}")
+        _CUDART.cudaHostAlloc.argtypes = [C.POINTER(C.c_void_p), C.c_size_t, C.c_uint]
+        _CUDART.cudaFreeHost.argtypes = [C.c_void_p]
+    return _CUDART
 
 
-_CUDART = None
+class WriteCombinedChunk:
+    """cudaHostAlloc(cudaHostAllocWriteCombined | cudaHostAllocPortable): host memory the CPU maps write-combining,
+    which the device may then write without snooping the CPU's caches."""
+
+    def __init__(self, nbytes):
+        p = C.c_void_p()
+        rc = cudart().cudaHostAlloc(C.byref(p), nbytes, 0x04 | 0x01)
+        if rc:
+            raise RuntimeError(f"cudaHostAlloc(WriteCombined) failed with CUDA error {rc}")
+        self.addr = p.value
+
+    def close(self):
+        if self.addr:
+            cudart().cudaFreeHost(C.c_void_p(self.addr))
+            self.addr = None
 
 
 def peer_phase(args, pf, torch, rank, world, local):
@@ -1450,6 +1474,12 @@ def run_placement_probe(args, rank, world, local):
         except pf.PegaFlowError as e:
             chunks.append({"kind": name, "cpu_quarter": q, "pool": None, "unavailable": str(e)[:100]})
     os.sched_setaffinity(0, cpus)
+    try:
+        w = WriteCombinedChunk(chunk)
+        chunks.append({"kind": "cudaHostAlloc(WriteCombined)", "cpu_quarter": None, "pool": w, "host": w.addr,
+                       "pfn": first_page_frame(w.addr)})
+    except RuntimeError as e:
+        chunks.append({"kind": "cudaHostAlloc(WriteCombined)", "cpu_quarter": None, "pool": None, "unavailable": str(e)[:100]})
     # a sweep over guest-physical memory: every rank fills `probe_wide_gib` GiB at the same time (together
     # they reach far into the guest's memory), keeps the chunks that lie lowest, highest and in between, and
     # gives the rest back before anything is pinned
