@@ -789,10 +789,10 @@ void TransferBackend::launch_group(const StagedUnit *units, char *const *slot_pt
     stamp = stamps_dev_ + 2 * (size_t)stamp_idx;
   }
   // Back-to-back launches overlap their launch latency with the tail of the kernel before them
-  // (PEGAFLOW_B200_PDL=1 turns the attribute on).
+  // (PEGAFLOW_B200_PDL=0 turns the attribute off).
   static const bool dependent_launch = [] {
     const char *e = getenv("PEGAFLOW_B200_PDL");
-    return e && atoi(e) != 0;
+    return !e || atoi(e) != 0;
   }();
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
