@@ -640,6 +640,50 @@ def time_gather_alone(args, pf, torch, local, route, wl, save_x, stream):
 SAVE_LAUNCH_DRAM_MB = 62.929152 + 10.871808
 
 
+def run_pair_overhead(args):
+    """What a CUDA event pair around one gather or scatter launch measures beside the kernel: the same launches
+    timed by event pairs and by the kernel's own clock, back to back (pf_backend_gather_layers) and inside the
+    save and load pipelines, where every launch follows a wait for another stream's event."""
+    import torch
+    import pegaflow_b200 as pf
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    wl = Workload(workloads()[args.workload], device, 42)
+    pool = pf.PinnedPool(wl.payload + (64 << 20))
+    allocs = alloc_host_images(pool, wl)
+    stream = torch.cuda.Stream()
+    s = stream.cuda_stream
+    save_x = make_layer_xfers(pf, wl, allocs, wl.save_ids)
+    load_x = make_layer_xfers(pf, wl, allocs, wl.load_ids)
+    cases = [("gather launches back to back, no DMA", "gather_layers", save_x, {}),
+             ("saves", "save_layers", save_x, {}), ("loads", "load_layers", load_x, {}),
+             ("saves, one staging slot per launch", "save_layers", save_x, {"gather_slots": 1})]
+    rows = []
+    for name, method, xs, kw in cases:
+        be = pf.TransferBackend(0, route=1, time_kernels=True, **kw)
+        before = None
+        for _ in range(3):              # one pass untimed, two counted
+            for x in xs:
+                getattr(be, method)(x, s)
+            stream.synchronize()
+            before = before or be.stats()
+        after = be.stats()
+        be.close()
+        n = after["pack_kernel_launches"] - before["pack_kernel_launches"]
+        dn = after["pack_kernel_device_launches"] - before["pack_kernel_device_launches"]
+        pair_us = (after["pack_kernel_ms"] - before["pack_kernel_ms"]) / n * 1e3
+        dev_us = (after["pack_kernel_device_ms"] - before["pack_kernel_device_ms"]) / max(1, dn) * 1e3
+        rows.append({"case": name, "launches": n, "event_pair_us": round(pair_us, 2), "kernel_clock_us": round(dev_us, 2),
+                     "pair_minus_kernel_us": round(pair_us - dev_us, 2),
+                     "payload_mib_per_launch": round((after["pack_kernel_bytes"] - before["pack_kernel_bytes"]) / n / 2 / 2 ** 20, 1)})
+    pool.close()
+    print(json.dumps({"metric": "event_pair_overhead", "unit": "us", "workload": args.workload, "rows": rows,
+                      "how": "per launch: one CUDA event pair on the launching stream (pf_backend_stats pack_kernel_ms) "
+                             "against the kernel's own %globaltimer stamps, first CTA start to last CTA end "
+                             "(pack_kernel_device_ms), over two passes of the workload's requests"}))
+
+
 def build_roofline(stat_pairs, args, alone=None):
     """The `roofline` object.  `alone` (time_gather_alone) gives the headline figure: the kernel timed
     by itself with CUDA events.  The backend counters taken before and after the timed region (summed
@@ -2236,6 +2280,8 @@ def main():
     ap.add_argument("--after-forward", action="store_true",
                     help="with --vllm-ttft: the reference's hook behaviour instead of the layer-wise hooks")
     ap.add_argument("--peer", action="store_true", help="measure the NVLink peer-copy path (one process, two GPUs)")
+    ap.add_argument("--pair-overhead", action="store_true",
+                    help="event pairs against the kernel's own clock, back to back and inside the pipelines")
     ap.add_argument("--placement-probe", action="store_true",
                     help="time copies into pinned chunks allocated in different ways, alone and with all ranks at once")
     ap.add_argument("--probe-chunk-mib", type=int, default=1024)
@@ -2259,6 +2305,9 @@ def main():
         return
     if args.pool_coldstart:
         run_pool_coldstart(args)
+        return
+    if args.pair_overhead:
+        run_pair_overhead(args)
         return
     world_env = int(os.environ.get("WORLD_SIZE", "1"))
     if args.gpus != world_env and world_env == 1 and args.gpus > 1:

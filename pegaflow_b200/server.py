@@ -463,7 +463,8 @@ def main(argv=None):
     engine = PegaEngine(pool, args.use_hugepages)
     server = serve(engine, args.addr)
     http = HttpEndpoints(server.service, args.http_addr, args.enable_prometheus == "true")
-    print(f"pegaflow_b200 engine server listening on port {server.port}, HTTP on port {http.port}", flush=True)
+    print(f"pegaflow_b200 engine server listening on port {server.port}", flush=True)
+    print(f"pegaflow_b200 HTTP endpoints on port {http.port}", flush=True)
     try:
         server.wait_for_shutdown_request()
     except KeyboardInterrupt:

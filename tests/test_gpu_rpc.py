@@ -56,13 +56,17 @@ def test_worker_and_sidecar_in_two_processes():
     from pegaflow_b200.ipc import CudaIPCWrapper
     from pegaflow_b200.rpc_client import EngineRpcClient
 
-    server = subprocess.Popen([sys.executable, "-m", "pegaflow_b200.server", "--addr", "127.0.0.1:0", "--pool-size", "64mb"],
+    server = subprocess.Popen([sys.executable, "-m", "pegaflow_b200.server", "--addr", "127.0.0.1:0", "--pool-size", "64mb",
+                               "--http-addr", "127.0.0.1:0"],
                               cwd=ROOT, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
     try:
         line = server.stdout.readline()
         assert "listening on port" in line, line + server.stderr.read()[-2000:]
         client = EngineRpcClient(f"http://127.0.0.1:{int(line.split()[-1])}", timeout=60)
         assert client.health() == (True, "")
+        http_line = server.stdout.readline()
+        assert "HTTP endpoints on port" in http_line, http_line
+        http_base = f"http://127.0.0.1:{int(http_line.split()[-1])}"
 
         dev = torch.device("cuda", 0)
         nb, seg = 64, 16 * 2 * 128 * 2
@@ -94,6 +98,18 @@ def test_worker_and_sidecar_in_two_processes():
             assert np.array_equal(t.cpu().numpy(), want)
         with pytest.raises(ValueError, match="out of range"):
             client.save("w", 0, 0, 0, [(names[0], [nb], [b"x"])])
+        # the HTTP side of the same process: the real engine's counters under the reference's metric names
+        import json
+        import urllib.request
+
+        assert urllib.request.urlopen(http_base + "/health", timeout=10).read() == b"ok"
+        assert json.loads(urllib.request.urlopen(http_base + "/instances", timeout=10).read()) == {"instances": ["w"]}
+        metrics = dict(line.split() for line in urllib.request.urlopen(http_base + "/metrics", timeout=10).read().decode()
+                       .splitlines() if not line.startswith("#"))
+        moved = 2 * 2 * 5 * seg                      # two layers, K and V, five blocks
+        assert int(metrics["pegaflow_save_bytes_total"]) >= moved and int(metrics["pegaflow_load_bytes_total"]) == moved
+        assert int(metrics["pegaflow_load_failures_total"]) == 0 and int(metrics["pegaflow_pool_capacity_bytes"]) >= 60 << 20
+        assert 0 < int(metrics["pegaflow_pool_used_bytes"]) <= int(metrics["pegaflow_pool_capacity_bytes"])
         # this process "dies": the stream closes and the server lets the instance and its mappings go
         client.close()
         probe = EngineRpcClient(f"http://127.0.0.1:{int(line.split()[-1])}", timeout=60)
