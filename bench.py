@@ -729,8 +729,11 @@ def build_roofline(stat_pairs, args, alone=None):
             for k in ("note", "device_clock"):
                 if k in roofline:
                     in_pipeline[k] = roofline.pop(k)
-            in_pipeline["how"] += (" (the stream is idle between launches there - the copy engine is the bottleneck - so "
-                                   "a pair also brackets launch latency and both event records)")
+            in_pipeline["how"] += (" (every launch there follows a wait for an event of the copy stream, and the copy "
+                                   "engine bounds the step, so the stream is blocked when the launch comes up: a pair also "
+                                   "brackets the 25-31 us the stream takes to resume after the wait, whatever the kernel's "
+                                   "size, against 6 us of records and launch when launches are back to back; "
+                                   "`bench.py --pair-overhead` measures both)")
             ach = 2 * alone["payload"] / 1e6 / alone["ms"]
             roofline.update({
                 "achieved": round(ach, 1), "frac": round(ach / hbm_peak, 4), "launches": alone["launches"],
