@@ -341,6 +341,11 @@ class PegaWorkerConnector:
             bpb.append(info.bytes_per_block)
             kvs.append(info.kv_stride_bytes)
             segs.append(info.segments)
+        if not isinstance(self.client, InProcEngineClient):
+            # an engine in another process gets the tensors as pickled CUDA IPC wrappers (worker.py:326-349)
+            from .ipc import CudaIPCWrapper
+
+            tensors = [CudaIPCWrapper(t).to_bytes() for t in tensors]
         ok, msg = self.client.register_context_batch(self.instance_id, self.namespace, self.tp_rank, self.pp_rank,
                                                      self.tp_size, self.world_size, self.device_id, names, tensors,
                                                      nb, bpb, kvs, segs, self.transfer_backend, self.page_first)

@@ -1,8 +1,9 @@
 """vLLM v1 KV-connector plug-in on top of this library: ``PegaKVConnector``.
 
 Takes the place of the reference's ``pegaflow.connector.PegaKVConnector``
-(python/pegaflow/connector/__init__.py) for the case this library covers: one node, the engine
-in the vLLM process (no sidecar), attention-only models with one KV-cache group.  Configure it as
+(python/pegaflow/connector/__init__.py) for the case this library covers: one node, attention-only
+models with one KV-cache group; the engine in the vLLM process, or behind the sidecar
+(``python -m pegaflow_b200.server``) like the reference's.  Configure it as
 
     KVTransferConfig(kv_connector="PegaKVConnector",
                      kv_connector_module_path="pegaflow_b200.vllm_connector",
@@ -16,10 +17,17 @@ from the scheduler's point of view and every attention layer waits on the stream
 layer's bytes, saves are queued per layer behind the layer's compute; false: the reference's
 behaviour — asynchronous request-level loads, one batch save after the forward pass).
 
-The scheduler role and the worker role of one vLLM process share one engine (looked up by
-instance id), so this works with the in-process engine core and the uniprocess executor
-(``VLLM_ENABLE_V1_MULTIPROCESSING=0``, tensor_parallel_size 1); tensor-parallel workers in other
-processes would need the reference's sidecar, which this library does not provide.
+Without a server address the scheduler role and the worker role of one vLLM process share one
+engine (looked up by instance id), so that form works with the in-process engine core and the
+uniprocess executor (``VLLM_ENABLE_V1_MULTIPROCESSING=0``, tensor_parallel_size 1).
+
+With ``pegaflow.host`` / ``pegaflow.port`` (or ``PEGAFLOW_HOST`` / ``PEGAFLOW_PORT``, which win, as in
+connector/__init__.py:96-103) both roles talk to the sidecar over gRPC instead: the worker sends its
+KV-cache tensors as CUDA IPC wrappers with its own tensor-parallel and pipeline rank, the scheduler
+role queries and holds the session's liveness stream (connector/__init__.py:200-211).  That is the
+reference's deployment, workers in other processes included; loads are asynchronous request-level
+loads and saves one batch after the forward pass, as there (the per-layer hooks need the engine's
+CUDA events in the worker's process, so ``pegaflow.layerwise`` cannot be combined with a server).
 """
 from __future__ import annotations
 
@@ -57,6 +65,15 @@ def close_shared_engines() -> None:
         _ENGINES.clear()
 
 
+def global_device_id(local_index: int) -> int:
+    """The device's index as a process without CUDA_VISIBLE_DEVICES sees it (the server), from this
+    process's index among its visible devices (connector/__init__.py:475-497)."""
+    visible = [v.strip() for v in os.environ.get("CUDA_VISIBLE_DEVICES", "").split(",") if v.strip()]
+    if local_index < len(visible) and visible[local_index].isdigit():
+        return int(visible[local_index])
+    return local_index
+
+
 class _Metadata(PegaConnectorMetadata, KVConnectorMetadata):
     """The scheduler connector's metadata, typed for vLLM."""
 
@@ -92,7 +109,13 @@ class PegaKVConnector(KVConnectorBase_V1):
         configured = cfg.engine_id or getattr(vllm_config, "instance_id", "") or os.environ.get("PEGAFLOW_INSTANCE_ID")
         self._instance_id = resolve_instance_id(vllm_config) if configured else "vllm"
         self._block_size = vllm_config.cache_config.block_size
-        self._layerwise = bool(extra("pegaflow.layerwise", True))
+        host = os.environ.get("PEGAFLOW_HOST") or extra("pegaflow.host", None)
+        port = os.environ.get("PEGAFLOW_PORT") or extra("pegaflow.port", None)
+        self._remote = host is not None or port is not None
+        self._layerwise = bool(extra("pegaflow.layerwise", not self._remote))
+        if self._remote and self._layerwise:
+            raise ValueError("pegaflow.layerwise needs the engine in the vLLM process: it cannot be combined with "
+                             "pegaflow.host / pegaflow.port")
         self._read_enabled = PegaConnectorMode.from_config(extra("pegaflow.mode", "read_write")) is PegaConnectorMode.READ_WRITE
         model = vllm_config.model_config
         # every factor that changes a stored block's layout, hashed as the reference does (common.py:519-565)
@@ -102,23 +125,43 @@ class PegaKVConnector(KVConnectorBase_V1):
         # several workers every one of them would save into a private pool as rank 0 and every lookup
         # would miss.  Refused like the group layouts this plug-in cannot serve.
         parallel = vllm_config.parallel_config
-        n_workers = int(getattr(parallel, "world_size", 1) or 1) * int(getattr(parallel, "data_parallel_size", 1) or 1)
-        if n_workers > 1:
-            raise ValueError(
-                "pegaflow_b200's vLLM plug-in runs scheduler and worker in one process with one worker "
-                f"(tensor/pipeline/data parallel world of 1); this configuration has {n_workers} workers")
-        self._engine = shared_engine(self._instance_id, int(extra("pegaflow.pool_bytes", 4 << 30)))
-        self._client = _connector.InProcEngineClient(self._engine)
+        tp_size = int(getattr(parallel, "tensor_parallel_size", 1) or 1)
+        world_size = int(getattr(parallel, "world_size", 1) or 1)
+        n_workers = world_size * int(getattr(parallel, "data_parallel_size", 1) or 1)
+        if self._remote:
+            from .rpc_client import EngineRpcClient
+
+            self._engine = None
+            self._client = EngineRpcClient(f"{host or 'http://127.0.0.1'}:{port or 50055}")
+        else:
+            if n_workers > 1:
+                raise ValueError(
+                    "pegaflow_b200's vLLM plug-in with the engine in the vLLM process runs scheduler and worker in one "
+                    f"process with one worker (tensor/pipeline/data parallel world of 1); this configuration has {n_workers} "
+                    "workers: start the sidecar and set pegaflow.host / pegaflow.port")
+            self._engine = shared_engine(self._instance_id, int(extra("pegaflow.pool_bytes", 4 << 30)))
+            self._client = _connector.InProcEngineClient(self._engine)
         self._scheduler: Optional[SchedulerConnector] = None
         self._worker: Optional[_connector.PegaWorkerConnector] = None
         if role == KVConnectorRole.SCHEDULER:
             self._scheduler = SchedulerConnector([self._client], instance_id=self._instance_id, block_size=self._block_size,
                                                  read_enabled=self._read_enabled)
+            if self._remote:
+                # one liveness stream per vLLM replica, from the scheduler's process: when it goes away the
+                # server drops the instance and its CUDA IPC mappings (connector/__init__.py:200-211)
+                self._client.start_session_watcher(self._instance_id, self._namespace, tp_size, world_size)
         else:
             device = torch.cuda.current_device()
+            ranks = {}
+            if self._remote:
+                from vllm.distributed.parallel_state import get_pp_group, get_tensor_model_parallel_rank
+
+                device = global_device_id(device)
+                ranks = dict(tp_rank=get_tensor_model_parallel_rank(), pp_rank=get_pp_group().rank_in_group,
+                             tp_size=tp_size, world_size=world_size)
             self._worker = _connector.PegaWorkerConnector(
                 self._client, self._engine, instance_id=self._instance_id, namespace=self._namespace, device_id=device,
-                block_size=self._block_size, is_mla=self._is_mla,
+                block_size=self._block_size, is_mla=self._is_mla, **ranks,
                 # "direct" / "kernel", validated like the reference (common.py:577-594); both name this library's
                 # one transfer path
                 transfer_backend=extra("pegaflow.transfer_backend", None))

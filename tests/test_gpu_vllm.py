@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-@pytest.mark.parametrize("mode", ["layerwise", "after-forward"])
+@pytest.mark.parametrize("mode", ["layerwise", "after-forward", "sidecar"])
 def test_vllm_serves_prompts_from_the_host_pool(mode):
     pytest.importorskip("vllm")
     if os.environ.get("PEGAFLOW_TEST_VLLM", "1") == "0":
@@ -22,7 +22,9 @@ def test_vllm_serves_prompts_from_the_host_pool(mode):
 
     if not torch.cuda.is_available():
         pytest.fail("this test needs a CUDA device")
-    cmd = [sys.executable, os.path.join(HERE, "vllm_scenario.py")] + (["--after-forward"] if mode == "after-forward" else [])
+    # "sidecar": the engine in a server process of its own, reached over gRPC and CUDA IPC like the reference's
+    cmd = [sys.executable, os.path.join(HERE, "vllm_scenario.py")] + {"after-forward": ["--after-forward"],
+                                                                       "sidecar": ["--sidecar"]}.get(mode, [])
     proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=900)
     lines = [ln for ln in proc.stdout.splitlines() if ln.startswith("{")]
     assert proc.returncode == 0 and lines, proc.stderr[-3000:]

@@ -17,8 +17,33 @@ os.environ.setdefault("VLLM_LOGGING_LEVEL", "WARNING")
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
+class Sidecar:
+    """``python -m pegaflow_b200.server`` as a child process; its counters are read over HTTP."""
+
+    def __init__(self):
+        import subprocess
+
+        root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+        self.proc = subprocess.Popen([sys.executable, "-m", "pegaflow_b200.server", "--addr", "127.0.0.1:0", "--http-addr",
+                                      "127.0.0.1:0", "--pool-size", "1gb"], cwd=root, stdout=subprocess.PIPE, text=True)
+        self.port = int(self.proc.stdout.readline().split()[-1])
+        self.http = f"http://127.0.0.1:{int(self.proc.stdout.readline().split()[-1])}"
+
+    def metrics(self):
+        import urllib.request
+
+        text = urllib.request.urlopen(self.http + "/metrics", timeout=30).read().decode()
+        raw = dict(line.split() for line in text.splitlines() if not line.startswith("#"))
+        return {"save_bytes": int(raw["pegaflow_save_bytes_total"]), "load_bytes": int(raw["pegaflow_load_bytes_total"]),
+                "load_failures": int(raw["pegaflow_load_failures_total"]), "cache_blocks": None}
+
+    def stop(self):
+        self.proc.kill()
+
+
 def main():
-    layerwise = "--after-forward" not in sys.argv
+    sidecar = Sidecar() if "--sidecar" in sys.argv else None
+    layerwise = "--after-forward" not in sys.argv and sidecar is None
     import numpy as np
     from transformers import LlamaConfig
     from vllm import LLM, SamplingParams
@@ -31,7 +56,7 @@ def main():
                 num_key_value_heads=2, head_dim=64, max_position_embeddings=4096, torch_dtype="bfloat16",
                 architectures=["LlamaForCausalLM"]).save_pretrained(model_dir)
     try:
-        llm = _start(LLM, KVTransferConfig, model_dir, layerwise)
+        llm = _start(LLM, KVTransferConfig, model_dir, layerwise, sidecar)
     except Exception:
         import traceback
 
@@ -40,20 +65,25 @@ def main():
         # memory, an incompatible vLLM build) is not a verdict on the connector
         print(json.dumps({"engine_start_failed": True, "ours": "pegaflow_b200" in tb, "traceback": tb[-2000:]}))
         sys.stdout.flush()
+        if sidecar:
+            sidecar.stop()
         os._exit(0)
-    _scenario(llm, SamplingParams, vllm_connector, layerwise, np)
+    _scenario(llm, SamplingParams, vllm_connector, layerwise, np, sidecar)
 
 
-def _start(LLM, KVTransferConfig, model_dir, layerwise):
+def _start(LLM, KVTransferConfig, model_dir, layerwise, sidecar=None):
+    extra = {"pegaflow.pool_bytes": 1 << 30, "pegaflow.layerwise": layerwise}
+    if sidecar:
+        extra = {"pegaflow.host": "http://127.0.0.1", "pegaflow.port": sidecar.port}
     return LLM(model=model_dir, load_format="dummy", skip_tokenizer_init=True,
                enforce_eager="--cuda-graphs" not in sys.argv, max_model_len=2048,
               gpu_memory_utilization=0.10, dtype="bfloat16", seed=0, enable_prefix_caching=True, block_size=16,
               kv_transfer_config=KVTransferConfig(
                   kv_connector="PegaKVConnector", kv_connector_module_path="pegaflow_b200.vllm_connector", kv_role="kv_both",
-                  kv_connector_extra_config={"pegaflow.pool_bytes": 1 << 30, "pegaflow.layerwise": layerwise}))
+                  kv_connector_extra_config=extra))
 
 
-def _scenario(llm, SamplingParams, vllm_connector, layerwise, np):
+def _scenario(llm, SamplingParams, vllm_connector, layerwise, np, sidecar=None):
     rng = np.random.default_rng(3)
     prompts = [{"prompt_token_ids": rng.integers(1, 2000, size=n).tolist()} for n in (200, 333, 64, 1000)]
     params = SamplingParams(temperature=0.0, max_tokens=6, detokenize=False, logprobs=1)
@@ -63,7 +93,7 @@ def _scenario(llm, SamplingParams, vllm_connector, layerwise, np):
         return [[(int(t), float(next(iter(lp.values())).logprob)) for t, lp in zip(o.outputs[0].token_ids, o.outputs[0].logprobs)]
                 for o in outs]
 
-    engine = next(iter(vllm_connector._ENGINES.values()))
+    engine = sidecar or next(iter(vllm_connector._ENGINES.values()))
     cold = run()
     after_cold = engine.metrics()
     gpu_cache = run()
@@ -76,7 +106,8 @@ def _scenario(llm, SamplingParams, vllm_connector, layerwise, np):
     host_pool = run()
     after_host = engine.metrics()
     print(json.dumps({
-        "layerwise": layerwise, "cuda_graphs": "--cuda-graphs" in sys.argv, "prefix_cache_reset": bool(reset_ok),
+        "layerwise": layerwise, "sidecar": sidecar is not None, "cuda_graphs": "--cuda-graphs" in sys.argv,
+        "prefix_cache_reset": bool(reset_ok),
         "warm_runs_identical": gpu_cache == host_pool, "cold_equals_warm_tokens": [[t for t, _ in a] for a in cold] ==
         [[t for t, _ in a] for a in host_pool],
         "saved_bytes_cold": after_cold["save_bytes"], "loaded_bytes_gpu_cache_run": after_gpu_cache["load_bytes"],
@@ -85,6 +116,8 @@ def _scenario(llm, SamplingParams, vllm_connector, layerwise, np):
         "tokens": [[t for t, _ in a] for a in host_pool]}))
     sys.stdout.flush()
     vllm_connector.close_shared_engines()
+    if sidecar:
+        sidecar.stop()
     os._exit(0)      # vLLM's own teardown is not what this scenario tests
 
 
