@@ -67,15 +67,27 @@ def main():
         sys.stdout.flush()
         if sidecar:
             sidecar.stop()
+        import multiprocessing
+
+        for child in multiprocessing.active_children():
+            child.terminate()
         os._exit(0)
     _scenario(llm, SamplingParams, vllm_connector, layerwise, np, sidecar)
+
+
+def _tp_size():
+    return int(sys.argv[sys.argv.index("--tp") + 1]) if "--tp" in sys.argv else 1
 
 
 def _start(LLM, KVTransferConfig, model_dir, layerwise, sidecar=None):
     extra = {"pegaflow.pool_bytes": 1 << 30, "pegaflow.layerwise": layerwise}
     if sidecar:
         extra = {"pegaflow.host": "http://127.0.0.1", "pegaflow.port": sidecar.port}
-    return LLM(model=model_dir, load_format="dummy", skip_tokenizer_init=True,
+    parallel = {}
+    if _tp_size() > 1:
+        # worker processes, one per GPU; vLLM's own all-reduce goes through NCCL only
+        parallel = dict(tensor_parallel_size=_tp_size(), distributed_executor_backend="mp", disable_custom_all_reduce=True)
+    return LLM(**parallel, model=model_dir, load_format="dummy", skip_tokenizer_init=True,
                enforce_eager="--cuda-graphs" not in sys.argv, max_model_len=2048,
               gpu_memory_utilization=0.10, dtype="bfloat16", seed=0, enable_prefix_caching=True, block_size=16,
               kv_transfer_config=KVTransferConfig(
@@ -106,7 +118,7 @@ def _scenario(llm, SamplingParams, vllm_connector, layerwise, np, sidecar=None):
     host_pool = run()
     after_host = engine.metrics()
     print(json.dumps({
-        "layerwise": layerwise, "sidecar": sidecar is not None, "cuda_graphs": "--cuda-graphs" in sys.argv,
+        "layerwise": layerwise, "sidecar": sidecar is not None, "tp": _tp_size(), "cuda_graphs": "--cuda-graphs" in sys.argv,
         "prefix_cache_reset": bool(reset_ok),
         "warm_runs_identical": gpu_cache == host_pool, "cold_equals_warm_tokens": [[t for t, _ in a] for a in cold] ==
         [[t for t, _ in a] for a in host_pool],
@@ -116,9 +128,25 @@ def _scenario(llm, SamplingParams, vllm_connector, layerwise, np, sidecar=None):
         "tokens": [[t for t, _ in a] for a in host_pool]}))
     sys.stdout.flush()
     vllm_connector.close_shared_engines()
+    if _tp_size() > 1:
+        _stop_workers(llm)
     if sidecar:
         sidecar.stop()
     os._exit(0)      # vLLM's own teardown is not what this scenario tests
+
+
+def _stop_workers(llm):
+    """Worker processes must not outlive this one: ask the executor to stop them, then make sure."""
+    import multiprocessing
+
+    try:
+        llm.llm_engine.engine_core.shutdown()
+    except Exception:
+        pass
+    for child in multiprocessing.active_children():
+        child.terminate()
+    for child in multiprocessing.active_children():
+        child.join(10)
 
 
 if __name__ == "__main__":
