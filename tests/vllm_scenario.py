@@ -39,6 +39,10 @@ class Sidecar:
 
     def stop(self):
         self.proc.kill()
+        try:
+            self.proc.wait(10)
+        except Exception:
+            pass
 
 
 def main():
