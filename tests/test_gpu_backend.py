@@ -488,3 +488,17 @@ def test_gather_layers_runs_the_kernel_and_moves_nothing_to_the_host(env):
     be.close()
     for a in allocs:
         pool.release(a[2])
+
+
+def test_staged_route_without_the_dependent_launch_attribute():
+    """PEGAFLOW_B200_PDL=0 (read once per process) launches the gather/scatter kernel as a plain launch: the
+    layer cases of the staged route, against the oracle, in a process that has the switch set."""
+    import os
+    import subprocess
+    import sys
+
+    proc = subprocess.run([sys.executable, "-m", "pytest", "-q", "-x", "-m", "gpu", os.path.abspath(__file__), "-k",
+                           "test_layer_save_load_matches_oracle and staged"],
+                          env=dict(os.environ, PEGAFLOW_B200_PDL="0"), cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+                          stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
+    assert proc.returncode == 0 and " passed" in proc.stdout, proc.stdout[-2000:]
