@@ -205,6 +205,42 @@ LAYER_CASES = [
 ]
 
 
+def _random_layer_cases(count, seed):
+    """Seeded random geometries on top of the named ones: segment sizes that are and are not multiples of 16,
+    K/V split and interleaved, block strides wider than the block (aligned or not), padded host strides, few and
+    many blocks, scattered and consecutive ids.  Geometries the layout rules refuse are drawn again."""
+    rng = np.random.default_rng(seed)
+    sizes = [16, 48, 528, 1001, 2048, 4096, 4112, 8848, 9216, 32768, 36864, 73728, 100000]
+    out = []
+    while len(out) < count:
+        segments = int(rng.integers(1, 3))
+        seg = int(rng.choice(sizes))
+        num_blocks = int(rng.choice([2, 3, 17, 64, 300, 600]))
+        if num_blocks * seg * segments > 48 << 20:
+            continue
+        split = segments == 2 and rng.random() < 0.7
+        kv_stride = (num_blocks * seg + int(rng.choice([0, 0, 48, 4096]))) if split else (seg if segments == 2 else 0)
+        block = seg if split else seg * segments
+        block_stride = 0 if rng.random() < 0.6 else block + int(rng.choice([16, 4, 1, block, 512]))
+        if split and block_stride:
+            kv_stride = (num_blocks - 1) * block_stride + seg + int(rng.choice([0, 64]))
+        n_move = int(rng.integers(1, num_blocks + 1))
+        case = _layer_case(f"random_{len(out)}_seg{seg}x{segments}_nb{num_blocks}", num_blocks, seg, segments, kv_stride,
+                           block_stride, n_move, int(rng.choice([0, 0, 16, 368, 512, 3])), 100 + len(out),
+                           consecutive=bool(rng.random() < 0.25))
+        try:
+            lay = po.KVCacheLayout(0x10000, 1 << 40, num_blocks, seg, kv_stride, segments)
+            if block_stride:
+                lay.with_block_stride(block_stride)
+        except Exception:
+            continue
+        out.append(case)
+    return out
+
+
+LAYER_CASES += _random_layer_cases(24, 2024)
+
+
 @pytest.mark.parametrize("route", list(ROUTES))
 @pytest.mark.parametrize("case", LAYER_CASES, ids=[c["name"] for c in LAYER_CASES])
 def test_layer_save_load_matches_oracle(env, case, route):
