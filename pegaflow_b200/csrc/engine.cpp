@@ -199,6 +199,15 @@ void GpuWorker::submit(Task task) {
   cv_.notify_one();
 }
 
+void GpuWorker::expect_task() {
+  {
+    std::lock_guard<std::mutex> g(mu_);
+    if (!queue_.empty() || expected_) return;  // awake already, or about to be
+    expected_ = true;
+  }
+  cv_.notify_one();
+}
+
 void GpuWorker::mark_enqueued(uint64_t ticket) {
   {
     std::lock_guard<std::mutex> g(mu_);
@@ -239,7 +248,17 @@ void GpuWorker::loop(int device, int numa_node, pf_backend_config cfg, std::prom
     Task task;
     {
       std::unique_lock<std::mutex> g(mu_);
-      cv_.wait(g, [&] { return stop_ || !queue_.empty(); });
+      cv_.wait(g, [&] { return stop_ || !queue_.empty() || expected_; });
+      if (queue_.empty() && expected_ && !stop_) {
+        // Woken ahead of a task: poll for it without the lock, for half a millisecond at most.
+        expected_ = false;
+        g.unlock();
+        const auto until = std::chrono::steady_clock::now() + std::chrono::microseconds(500);
+        while (submitted_.load(std::memory_order_acquire) == ticket && std::chrono::steady_clock::now() < until)
+          __builtin_ia32_pause();
+        continue;
+      }
+      expected_ = false;
       if (queue_.empty()) break;
       task = std::move(queue_.front());
       queue_.pop_front();
@@ -575,6 +594,7 @@ void Engine::batch_save(const std::string &instance_id, size_t tp_rank, size_t p
     if (it == inst->gpus.end()) throw Error::worker_missing(instance_id, device_id);
     gpu = it->second;
   }
+  gpu->save_worker->expect_task();
   if (gpu->tp_rank != tp_rank || gpu->pp_rank != pp_rank)
     throw Error::invalid(strf("device_id %d is registered for tp_rank %zu, pp_rank %zu, but save requested tp_rank "
                               "%zu, pp_rank %zu",
@@ -1162,6 +1182,7 @@ void Engine::batch_load(const std::string &instance_id, size_t tp_rank, int devi
       if (it == inst->gpus.end()) throw Error::worker_missing(instance_id, device_id);
       gpu = it->second;
     }
+    gpu->load_worker->expect_task();
     if (layer_groups.empty()) throw Error::invalid("load requires at least one layer group");
     {
       std::unordered_set<std::string> unique;

@@ -173,6 +173,9 @@ class GpuWorker {
   GpuWorker(const std::string &name, int device, int numa_node, const pf_backend_config &cfg);
   ~GpuWorker();
   void submit(Task task);
+  // A task is about to be submitted: have the thread awake and polling for it (for a bounded
+  // time) by then, so that its wake-up overlaps the caller's preparation instead of following it.
+  void expect_task();
   // Number of tasks submitted so far; task k (1-based) carries ticket k.
   uint64_t submitted() const { return submitted_.load(); }
   // Ticket of the task the worker thread is running (valid inside a task only).
@@ -192,6 +195,7 @@ class GpuWorker {
   std::condition_variable cv_, enq_cv_;
   std::deque<Task> queue_;
   bool stop_ = false;
+  bool expected_ = false;
   std::atomic<uint64_t> submitted_{0};
   uint64_t enqueued_ = 0;
   uint64_t current_ticket_ = 0;
