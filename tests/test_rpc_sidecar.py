@@ -273,3 +273,22 @@ def test_http_health_metrics_and_instance_management(sidecar):
         assert e.value.code == 404 and e.value.read() == b"metrics not enabled"
     finally:
         quiet.stop()
+
+
+def test_rpc_client_surface_matches_the_reference_stub():
+    """python/pegaflow/pegaflow.pyi through tests/golden/engine_client_surface.json: every method of the reference's
+    EngineRpcClient exists here with the same parameters in the same order, the constructor included."""
+    import inspect
+    import json
+    import os
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = json.load(open(os.path.join(root, "tests", "golden", "engine_client_surface.json")))["classes"]["EngineRpcClient"]
+    for method, params in spec["methods"].items():
+        assert hasattr(EngineRpcClient, method), f"EngineRpcClient.{method} is missing"
+        sig = inspect.signature(getattr(EngineRpcClient, method))
+        got = [(p.name, p.default is not inspect.Parameter.empty) for p in sig.parameters.values()
+               if p.name != "self" and p.kind not in (p.VAR_POSITIONAL, p.VAR_KEYWORD, p.KEYWORD_ONLY)]
+        want = [tuple(x) for x in params]
+        assert got[:len(want)] == want, f"EngineRpcClient.{method}: {got} != {want}"
+        assert all(has_default for _, has_default in got[len(want):]), f"{method}: extra parameters must be optional"
