@@ -485,6 +485,18 @@ typedef struct pf_engine_metrics {
 } pf_engine_metrics;
 int pf_engine_get_metrics(pf_engine *engine, pf_engine_metrics *out);
 
+/* Drop every block from the resident cache (PegaEngine::cleanup_memory_cache, lib.rs:636-639,
+ * storage/mod.rs:395-445).  Blocks that a lease, a load in flight or a caller's handle still holds
+ * leave the cache too but keep their pool memory until the holder lets go: evicted_bytes is the
+ * footprint that left the cache, reclaimed_bytes what the pool got back at once. */
+typedef struct pf_cache_cleanup_stats {
+  uint64_t evicted_blocks;
+  uint64_t evicted_bytes;
+  uint64_t reclaimed_bytes;
+  uint64_t still_referenced_blocks;
+} pf_cache_cleanup_stats;
+int pf_engine_cleanup_memory_cache(pf_engine *engine, pf_cache_cleanup_stats *out);
+
 /* Where a save and a load spend their time on the host side, accumulated since the engine was
  * created: seconds and number of samples per phase.  Phases that the reference traces carry its
  * span names (pf_engine_phase_name: "save.resolve_metadata", "save.hash_filter",

@@ -192,6 +192,13 @@ _sig("pf_stream_wait_event", C.c_int, vp, vp)
 _sig("pf_engine_save_layers_async", C.c_int, vp, C.c_char_p, sz, sz, C.c_int, sz, P(LayerSave), vp)
 _sig("pf_engine_peer_load", C.c_int, vp, C.c_char_p, C.c_int, C.c_char_p, C.c_int, sz, P(sz), P(sz))
 _sig("pf_engine_get_metrics", C.c_int, vp, P(EngineMetrics))
+
+
+class CacheCleanupStats(C.Structure):
+    _fields_ = [("evicted_blocks", u64), ("evicted_bytes", u64), ("reclaimed_bytes", u64), ("still_referenced_blocks", u64)]
+
+
+_sig("pf_engine_cleanup_memory_cache", C.c_int, vp, P(CacheCleanupStats))
 _sig("pf_engine_get_phase_times", C.c_int, vp, P(PhaseTimes))
 _sig("pf_engine_phase_name", C.c_char_p, C.c_int)
 _sig("pf_load_state_new", C.c_int, P(vp))

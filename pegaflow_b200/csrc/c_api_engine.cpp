@@ -417,6 +417,13 @@ int pf_engine_get_metrics(pf_engine *engine, pf_engine_metrics *out) {
   });
 }
 
+int pf_engine_cleanup_memory_cache(pf_engine *engine, pf_cache_cleanup_stats *out) {
+  return guarded([&] {
+    if (!engine || !out) throw Error::invalid("null argument");
+    engine->impl.cleanup_memory_cache(out);
+  });
+}
+
 // ---- LoadState -------------------------------------------------------------------------------------
 int pf_load_state_new(pf_load_state **out) {
   return guarded([&] {

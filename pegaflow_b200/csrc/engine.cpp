@@ -116,6 +116,16 @@ size_t ReadCache::evict_lru(size_t n) {
   return dropped.size();
 }
 
+std::vector<BlockRef> ReadCache::remove_all() {
+  std::vector<BlockRef> out;
+  std::lock_guard<std::mutex> g(mu_);
+  out.reserve(map_.size());
+  for (auto &kv : map_) out.push_back(std::move(kv.second.block));
+  map_.clear();
+  lru_.clear();
+  return out;
+}
+
 size_t ReadCache::size() {
   std::lock_guard<std::mutex> g(mu_);
   return map_.size();
@@ -1418,6 +1428,25 @@ void Engine::peer_load(const std::string &src_instance, int src_device, const st
     }
   });
   finished.get();
+}
+
+// storage/mod.rs:395-445: every resident block leaves the cache; one that a lease, a load in
+// flight or a caller's handle still holds keeps its pool memory until that holder lets go.
+void Engine::cleanup_memory_cache(pf_cache_cleanup_stats *out) {
+  memset(out, 0, sizeof *out);
+  uint64_t used_before = 0, used_after = 0, total = 0;
+  allocator_->usage(&used_before, &total);
+  std::vector<BlockRef> removed = cache_.remove_all();
+  if (removed.empty()) return;
+  for (const BlockRef &b : removed) {
+    out->evicted_bytes += b->footprint;
+    if (b.use_count() > 1) ++out->still_referenced_blocks;
+  }
+  out->evicted_blocks = removed.size();
+  evicted_.fetch_add(removed.size());
+  removed.clear();  // frees the pool memory of the blocks nobody else holds
+  allocator_->usage(&used_after, &total);
+  out->reclaimed_bytes = used_before > used_after ? used_before - used_after : 0;
 }
 
 void Engine::metrics(pf_engine_metrics *out) {

@@ -112,6 +112,8 @@ class ReadCache {
   bool insert(const BlockKey &key, BlockRef block);
   // Drops up to n least recently used blocks; returns how many were dropped.
   size_t evict_lru(size_t n);
+  // Takes every resident block out of the cache, held by someone else or not.
+  std::vector<BlockRef> remove_all();
   size_t size();
 
  private:
@@ -284,6 +286,7 @@ class Engine {
   void peer_load(const std::string &src_instance, int src_device, const std::string &dst_instance, int dst_device,
                  const std::vector<size_t> &src_ids, const std::vector<size_t> &dst_ids);
   void metrics(pf_engine_metrics *out);
+  void cleanup_memory_cache(pf_cache_cleanup_stats *out);
   void phase_times(pf_engine_phase_times *out);
 
  private:

@@ -392,6 +392,14 @@ class PegaEngine:
         out["transfer"] = {f: getattr(m.transfer, f) for f, _ in N.BackendStats._fields_}
         return out
 
+    def cleanup_memory_cache(self) -> dict:
+        """Drop every resident block from the cache (lib.rs:636-639): evicted_blocks, evicted_bytes,
+        reclaimed_bytes (what the pool got back at once) and still_referenced_blocks (held by a lease, a
+        load in flight or a caller's handle: their memory follows when the holder lets go)."""
+        s = N.CacheCleanupStats()
+        N.check(N.lib.pf_engine_cleanup_memory_cache(self._h, C.byref(s)))
+        return {f: int(getattr(s, f)) for f, _ in N.CacheCleanupStats._fields_}
+
     def phase_times(self) -> dict:
         """{phase name: (seconds, samples)} accumulated since the engine was created; phases the
         reference traces carry its span names (``save.pinned_alloc``, ``gpu.save_task``, ...)."""

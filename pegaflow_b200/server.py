@@ -375,7 +375,8 @@ def prometheus_text(metrics: dict) -> str:
 
 class HttpEndpoints:
     """pegaflow-server/src/http_server.rs:22-196: `GET /health`, `GET /metrics` (when enabled),
-    `GET /instances`, `POST /instances/cleanup[?id=<instance_id>]`, on a thread of their own."""
+    `GET /instances`, `POST /instances/cleanup[?id=<instance_id>]`, `POST /cache/memory/cleanup`, on a thread of
+    their own."""
 
     def __init__(self, service: EngineService, address: str = "127.0.0.1:0", enable_prometheus: bool = True):
         import json
@@ -410,6 +411,12 @@ class HttpEndpoints:
 
             def do_POST(self):
                 url = urlsplit(self.path)
+                if url.path == "/cache/memory/cleanup":
+                    try:
+                        self._json(200, service.engine.cleanup_memory_cache())
+                    except Exception as e:
+                        self._send(500, str(e))
+                    return
                 if url.path != "/instances/cleanup":
                     self._send(404, "not found")
                     return

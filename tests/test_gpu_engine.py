@@ -357,6 +357,45 @@ def test_leased_blocks_survive_eviction_pressure(pf):
         eng.close()
 
 
+def test_cleanup_memory_cache_drops_every_resident_block(pf):
+    """storage/mod.rs:395-445 and its test (:662-681): every resident block leaves the cache; the ones a lease
+    still holds are counted as still referenced and keep their pool memory until the lease has been used or
+    released; a second clean-up finds nothing."""
+    eng, mem, L = _eviction_env(pf, "inst-clean")
+    try:
+        fill = sc.fill_pattern(4, 4096)
+        mem.write(L.buf, fill)
+        held, free = sc.make_block_hashes(2, 30), sc.make_block_hashes(2, 31)
+        eng.batch_save("inst-clean", 0, 0, 0, [("layer_0", [0, 1], held)])      # two saves: two pool allocations
+        eng.batch_save("inst-clean", 0, 0, 0, [("layer_0", [2, 3], free)])
+        eng.flush_saves()
+        used = eng.metrics()["pool_used_bytes"]
+        assert used > 0 and eng.metrics()["cache_blocks"] == 4
+        blocks, missing = eng.query_prefix("inst-clean", held)
+        assert missing == 0
+        lease = eng.create_query_lease("inst-clean", blocks)
+        del blocks
+        stats = eng.cleanup_memory_cache()
+        assert stats["evicted_blocks"] == 4 and stats["still_referenced_blocks"] == 2
+        assert stats["evicted_bytes"] == 4 * 4096 and stats["reclaimed_bytes"] == used // 2
+        m = eng.metrics()
+        assert m["cache_blocks"] == 0 and m["pool_used_bytes"] == used - stats["reclaimed_bytes"]
+        assert len(eng.query_prefix("inst-clean", held)[0]) == 0 and len(eng.query_prefix("inst-clean", free)[0]) == 0
+        assert eng.cleanup_memory_cache() == {"evicted_blocks": 0, "evicted_bytes": 0, "reclaimed_bytes": 0,
+                                              "still_referenced_blocks": 0}
+        # the lease still loads what it pinned, and its memory goes back once it has been consumed
+        got = _load_and_read(eng, mem, L, "inst-clean", lease, 2)
+        assert np.array_equal(got[:2 * 4096], fill[:2 * 4096])
+        import time
+
+        deadline = time.time() + 5          # the load task lets go of its blocks just after it has reported
+        while eng.metrics()["pool_used_bytes"] and time.time() < deadline:
+            time.sleep(0.01)
+        assert eng.metrics()["pool_used_bytes"] == 0
+    finally:
+        eng.close()
+
+
 def test_load_state_shm_completion_and_failure(pf):
     """lib.rs:654-680 + sync_state.rs: a cross-process style load completes through the
     shared-memory word; a pre-submit error flips it to ERROR."""

@@ -262,6 +262,10 @@ def test_http_health_metrics_and_instance_management(sidecar):
         assert json.loads(get("/instances")[1]) == {"instances": ["b"]}
         assert json.loads(post("/instances/cleanup")[1]) == {"removed_instances": ["b"], "removed_tensors": 3}
         assert json.loads(get("/instances")[1]) == {"instances": []} and registry.contexts == {}
+        engine.cleanup_memory_cache = lambda: {"evicted_blocks": 3, "evicted_bytes": 6144, "reclaimed_bytes": 4096,
+                                               "still_referenced_blocks": 1}
+        assert json.loads(post("/cache/memory/cleanup")[1]) == {"evicted_blocks": 3, "evicted_bytes": 6144,
+                                                                "reclaimed_bytes": 4096, "still_referenced_blocks": 1}
         with pytest.raises(urllib.error.HTTPError):
             get("/nothing")
     finally:
