@@ -2242,6 +2242,16 @@ def run_pool_coldstart(args):
                       "host_cores": os.cpu_count(), "rows": rows}))
 
 
+def keep_stdout_for_the_json_line():
+    """Libraries write to file descriptor 1 on their own (NCCL prints its version there when a communicator is
+    created): point descriptor 1 at stderr and keep the original for Python's `print`, so that standard output
+    carries the bench line and nothing else."""
+    sys.stdout.flush()
+    ours = os.fdopen(os.dup(1), "w", buffering=1)
+    os.dup2(2, 1)
+    sys.stdout = ours
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -2294,6 +2304,11 @@ def main():
     ap.add_argument("--probe-wide-gib", type=int, default=24,
                     help="GiB every rank fills to find chunks far apart in guest-physical memory (0 = skip)")
     args = ap.parse_args()
+    world_env = int(os.environ.get("WORLD_SIZE", "1"))
+    single_process_mode = args.peer or args.ttft or args.vllm_ttft or args.transfer_grid or args.pool_coldstart or args.pair_overhead
+    relaunch = not single_process_mode and args.gpus != world_env and world_env == 1 and args.gpus > 1
+    if not relaunch:      # the relaunched ranks do this themselves; their descriptors are this process's
+        keep_stdout_for_the_json_line()
     if args.peer:
         run_peer(args)
         return
@@ -2312,8 +2327,7 @@ def main():
     if args.pair_overhead:
         run_pair_overhead(args)
         return
-    world_env = int(os.environ.get("WORLD_SIZE", "1"))
-    if args.gpus != world_env and world_env == 1 and args.gpus > 1:
+    if relaunch:
         # convenience: relaunch under torchrun
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
                "--master-addr", "127.0.0.1", "--master-port", "29531", os.path.abspath(__file__)] + sys.argv[1:]
