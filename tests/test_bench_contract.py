@@ -65,3 +65,19 @@ def test_sweep_chunk_reports_where_it_lies_and_releases_its_mapping():
     assert (w.median_gib in w.frames_gib) if w.frames_gib else w.median_gib == -1.0
     w.close()
     assert w.view is None and w.map.closed
+
+
+def test_standard_output_is_kept_for_the_json_line():
+    """What a library writes to file descriptor 1 on its own (NCCL's version banner) must not share standard
+    output with the bench line."""
+    import subprocess
+    import sys
+
+    code = ("import importlib.util, os\n"
+            f"spec = importlib.util.spec_from_file_location('b', {os.path.join(ROOT, 'bench.py')!r})\n"
+            "b = importlib.util.module_from_spec(spec); spec.loader.exec_module(b)\n"
+            "b.keep_stdout_for_the_json_line()\n"
+            "os.write(1, b'library banner\\n')\n"
+            "print('{\"metric\": 1}')\n")
+    p = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=120)
+    assert p.returncode == 0 and p.stdout == '{"metric": 1}\n' and p.stderr.endswith("library banner\n")
