@@ -367,6 +367,13 @@ int pf_engine_register_context_layer_batch_strided(
     const size_t *block_stride_bytes, const uint32_t *layer_group_ids, int transfer_mode, int page_first);
 /* lib.rs:443-460 `unregister_instance`. */
 int pf_engine_unregister_instance(pf_engine *engine, const char *instance_id);
+/* lib.rs:459-489 `unregister_all_instances`, `list_instance_ids`, `instance_namespace`.  Text results
+ * are written NUL-terminated into buf when cap suffices (an empty string otherwise); *needed is the
+ * size that does, terminator included.  Instance ids come one per line, sorted; the first of the
+ * three returns the ids it removed. */
+int pf_engine_unregister_all_instances(pf_engine *engine, char *buf, size_t cap, size_t *needed);
+int pf_engine_list_instances(pf_engine *engine, char *buf, size_t cap, size_t *needed);
+int pf_engine_instance_namespace(pf_engine *engine, const char *instance_id, char *buf, size_t cap, size_t *needed);
 
 /* block.rs:22-26 `LayerSave`: hashes are passed as one byte string per block. */
 typedef struct pf_layer_save {

@@ -191,6 +191,9 @@ _sig("pf_engine_layer_load_event", C.c_int, vp, C.c_char_p, C.c_int, C.c_char_p,
 _sig("pf_stream_wait_event", C.c_int, vp, vp)
 _sig("pf_engine_save_layers_async", C.c_int, vp, C.c_char_p, sz, sz, C.c_int, sz, P(LayerSave), vp)
 _sig("pf_engine_peer_load", C.c_int, vp, C.c_char_p, C.c_int, C.c_char_p, C.c_int, sz, P(sz), P(sz))
+_sig("pf_engine_list_instances", C.c_int, vp, C.c_char_p, sz, P(sz))
+_sig("pf_engine_unregister_all_instances", C.c_int, vp, C.c_char_p, sz, P(sz))
+_sig("pf_engine_instance_namespace", C.c_int, vp, C.c_char_p, C.c_char_p, sz, P(sz))
 _sig("pf_engine_get_metrics", C.c_int, vp, P(EngineMetrics))
 
 

@@ -222,6 +222,41 @@ int pf_engine_unregister_instance(pf_engine *engine, const char *instance_id) {
   });
 }
 
+namespace {
+// Writes `text` (NUL-terminated) into buf when it fits; *needed is its size with the terminator.
+void copy_out(const std::string &text, char *buf, size_t cap, size_t *needed) {
+  if (needed) *needed = text.size() + 1;
+  if (buf && cap > text.size()) memcpy(buf, text.c_str(), text.size() + 1);
+  else if (buf && cap) buf[0] = 0;
+}
+std::string join_lines(const std::vector<std::string> &ids) {
+  std::string out;
+  for (size_t i = 0; i < ids.size(); ++i) out += (i ? "\n" : "") + ids[i];
+  return out;
+}
+}  // namespace
+
+int pf_engine_list_instances(pf_engine *engine, char *buf, size_t cap, size_t *needed) {
+  return guarded([&] {
+    if (!engine) throw Error::invalid("null argument");
+    copy_out(join_lines(engine->impl.list_instance_ids()), buf, cap, needed);
+  });
+}
+
+int pf_engine_unregister_all_instances(pf_engine *engine, char *buf, size_t cap, size_t *needed) {
+  return guarded([&] {
+    if (!engine) throw Error::invalid("null argument");
+    copy_out(join_lines(engine->impl.unregister_all_instances()), buf, cap, needed);
+  });
+}
+
+int pf_engine_instance_namespace(pf_engine *engine, const char *instance_id, char *buf, size_t cap, size_t *needed) {
+  return guarded([&] {
+    if (!engine || !instance_id) throw Error::invalid("null argument");
+    copy_out(engine->impl.instance_namespace(instance_id), buf, cap, needed);
+  });
+}
+
 int pf_engine_batch_save(pf_engine *engine, const char *instance_id, size_t tp_rank, size_t pp_rank, int device_id,
                          size_t n_layers, const pf_layer_save *saves) {
   return guarded([&] {

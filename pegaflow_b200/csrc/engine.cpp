@@ -576,6 +576,41 @@ void Engine::unregister_instance(const std::string &instance_id) {
   inst.reset();  // last reference: joins the instance's GPU workers
 }
 
+// lib.rs:459-475
+std::vector<std::string> Engine::unregister_all_instances() {
+  std::vector<std::shared_ptr<InstanceContext>> gone;
+  std::vector<std::string> ids;
+  {
+    std::lock_guard<std::mutex> g(instances_mu_);
+    for (auto &kv : instances_) {
+      ids.push_back(kv.first);
+      gone.push_back(std::move(kv.second));
+    }
+    instances_.clear();
+  }
+  {
+    std::lock_guard<std::mutex> g(leases_mu_);
+    leases_.clear();  // every lease belongs to an instance that is gone now
+  }
+  gone.clear();  // last references: joins the instances' GPU workers
+  std::sort(ids.begin(), ids.end());
+  return ids;
+}
+
+// lib.rs:477-484
+std::vector<std::string> Engine::list_instance_ids() {
+  std::vector<std::string> ids;
+  {
+    std::lock_guard<std::mutex> g(instances_mu_);
+    for (auto &kv : instances_) ids.push_back(kv.first);
+  }
+  std::sort(ids.begin(), ids.end());
+  return ids;
+}
+
+// lib.rs:487-489
+std::string Engine::instance_namespace(const std::string &instance_id) { return get_instance(instance_id)->ns; }
+
 // storage/mod.rs:294-330: allocate, evicting least recently used blocks until it fits.
 std::shared_ptr<PinnedAllocation> Engine::allocate(uint64_t bytes, int numa_node, const char *what) {
   for (;;) {

@@ -264,6 +264,9 @@ class Engine {
                                             const size_t *segments, const size_t *block_stride_bytes,
                                             const uint32_t *layer_group_ids, int transfer_mode, bool page_first);
   void unregister_instance(const std::string &instance_id);
+  std::vector<std::string> unregister_all_instances();
+  std::vector<std::string> list_instance_ids();
+  std::string instance_namespace(const std::string &instance_id);
 
   // ready_event == nullptr && !async: blocking save (offload.rs:293).  async: returns after the
   // pinned allocation; the copy, its completion wait and the cache insert run on the save worker.

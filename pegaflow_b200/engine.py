@@ -228,6 +228,27 @@ class PegaEngine:
     def unregister_instance(self, instance_id):
         N.check(N.lib.pf_engine_unregister_instance(self._h, instance_id.encode()))
 
+    def list_instance_ids(self):
+        """lib.rs:477-484; sorted."""
+        buf, need = C.create_string_buffer(1 << 16), N.sz()
+        N.check(N.lib.pf_engine_list_instances(self._h, buf, len(buf), C.byref(need)))
+        if need.value > len(buf):
+            buf = C.create_string_buffer(need.value)
+            N.check(N.lib.pf_engine_list_instances(self._h, buf, len(buf), C.byref(need)))
+        return [s for s in buf.value.decode().split("\n") if s]
+
+    def unregister_all_instances(self):
+        """lib.rs:459-475: removes every instance (their leases go with them) and returns the ids."""
+        buf, need = C.create_string_buffer(1 << 20), N.sz()
+        N.check(N.lib.pf_engine_unregister_all_instances(self._h, buf, len(buf), C.byref(need)))
+        return [s for s in buf.value.decode().split("\n") if s]
+
+    def instance_namespace(self, instance_id):
+        """lib.rs:487-489."""
+        buf, need = C.create_string_buffer(4096), N.sz()
+        N.check(N.lib.pf_engine_instance_namespace(self._h, instance_id.encode(), buf, len(buf), C.byref(need)))
+        return buf.value.decode()
+
     def _layer_saves(self, saves):
         n = len(saves)
         arr = (N.LayerSave * max(1, n))()

@@ -190,6 +190,11 @@ class EngineService:
         return removed
 
     def instance_ids(self) -> List[str]:
+        """The engine's registered instances (lib.rs:477-484); an engine without that call is
+        represented by what this service registered itself."""
+        lister = getattr(self.engine, "list_instance_ids", None)
+        if lister is not None:
+            return list(lister())
         with self._instances_lock:
             return list(self._instances)
 

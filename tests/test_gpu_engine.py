@@ -357,6 +357,35 @@ def test_leased_blocks_survive_eviction_pressure(pf):
         eng.close()
 
 
+def test_instance_listing_namespace_and_unregister_all(pf):
+    """lib.rs:459-489: list_instance_ids, instance_namespace, unregister_all_instances."""
+    eng = pf.PegaEngine(4 << 20, enable_numa_affinity=False)
+    mem = CudaMem(0)
+    try:
+        assert eng.list_instance_ids() == [] and eng.unregister_all_instances() == []
+        layers = []
+        for name, ns in (("inst-b", "ns-1"), ("inst-a", "ns-2")):
+            L = sc.Layer("layer_0", 4, 4096)
+            layers.append(L)
+            sc.register(eng, mem, name, ns, [L])
+        assert eng.list_instance_ids() == ["inst-a", "inst-b"]
+        assert eng.instance_namespace("inst-a") == "ns-2" and eng.instance_namespace("inst-b") == "ns-1"
+        with pytest.raises(pf.PegaFlowError, match="instance nobody not found"):
+            eng.instance_namespace("nobody")
+        h = sc.make_block_hashes(2, 40)
+        eng.batch_save("inst-a", 0, 0, 0, [("layer_0", [0, 1], h)])
+        eng.flush_saves()
+        blocks, _ = eng.query_prefix("inst-a", h)
+        lease = eng.create_query_lease("inst-a", blocks)
+        del blocks
+        assert eng.unregister_all_instances() == ["inst-a", "inst-b"]
+        assert eng.list_instance_ids() == [] and eng.release_query_lease(lease) is False   # leases went with the instances
+        with pytest.raises(pf.PegaFlowError, match="instance inst-a not found"):
+            eng.batch_save("inst-a", 0, 0, 0, [("layer_0", [0, 1], h)])
+    finally:
+        eng.close()
+
+
 def test_cleanup_memory_cache_drops_every_resident_block(pf):
     """storage/mod.rs:395-445 and its test (:662-681): every resident block leaves the cache; the ones a lease
     still holds are counted as still referenced and keep their pool memory until the lease has been used or

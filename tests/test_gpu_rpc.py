@@ -110,6 +110,10 @@ def test_worker_and_sidecar_in_two_processes():
         assert int(metrics["pegaflow_save_bytes_total"]) >= moved and int(metrics["pegaflow_load_bytes_total"]) == moved
         assert int(metrics["pegaflow_load_failures_total"]) == 0 and int(metrics["pegaflow_pool_capacity_bytes"]) >= 60 << 20
         assert 0 < int(metrics["pegaflow_pool_used_bytes"]) <= int(metrics["pegaflow_pool_capacity_bytes"])
+        cleanup = urllib.request.Request(http_base + "/cache/memory/cleanup", data=b"", method="POST")
+        stats = json.loads(urllib.request.urlopen(cleanup, timeout=10).read())
+        assert stats["evicted_blocks"] == 5 and stats["still_referenced_blocks"] == 0 and stats["reclaimed_bytes"] > 0
+        assert client.query_prefetch("w", hashes, "after-cleanup").num_hit_blocks == 0
         # this process "dies": the stream closes and the server lets the instance and its mappings go
         client.close()
         probe = EngineRpcClient(f"http://127.0.0.1:{int(line.split()[-1])}", timeout=60)
