@@ -455,3 +455,18 @@ def test_page_layout_and_unit_size_match_the_oracle_on_random_topologies():
         pool = int(rng.integers(1, 1 << 46))
         hint = int(rng.choice([0, 1, 511, 512, 513, 4096, 73728, int(rng.integers(1, 1 << 24))]))
         assert N.lib.pf_pool_unit_size(pool, hint) == po.pool_unit_size(pool, hint or None)
+
+
+def test_engine_entry_points_reject_a_null_engine_without_a_gpu():
+    """Every engine-level call added beside the reference's own (instance listing, namespace, cache clean-up,
+    metrics, phase times) checks its arguments before it touches anything: InvalidArgument, message kept."""
+    buf, need = C.create_string_buffer(16), N.sz()
+    assert N.lib.pf_engine_list_instances(None, buf, len(buf), C.byref(need)) == 3
+    assert b"null argument" in N.lib.pf_last_error()
+    assert N.lib.pf_engine_unregister_all_instances(None, buf, len(buf), C.byref(need)) == 3
+    assert N.lib.pf_engine_instance_namespace(None, b"x", buf, len(buf), C.byref(need)) == 3
+    assert N.lib.pf_engine_cleanup_memory_cache(None, C.byref(N.CacheCleanupStats())) == 3
+    assert N.lib.pf_engine_get_metrics(None, C.byref(N.EngineMetrics())) == 3
+    assert N.lib.pf_engine_get_phase_times(None, C.byref(N.PhaseTimes())) == 3
+    assert N.lib.pf_engine_phase_name(-1) is None and N.lib.pf_engine_phase_name(N.PHASE_COUNT) is None
+    assert N.lib.pf_engine_phase_name(0) == b"save.resolve_metadata"
