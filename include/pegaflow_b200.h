@@ -504,6 +504,12 @@ typedef struct pf_cache_cleanup_stats {
 } pf_cache_cleanup_stats;
 int pf_engine_cleanup_memory_cache(pf_engine *engine, pf_cache_cleanup_stats *out);
 
+/* `gc_stale_inflight` (lib.rs:938-948; the server calls it every 60 s with 300 s,
+ * pegaflow-server/src/lib.rs:612-648): drop the blocks that have been waiting longer than
+ * max_age_seconds for slots that never came (a TP rank or a layer that did not save) and give their
+ * pool memory back.  *cleaned = number of blocks dropped. */
+int pf_engine_gc_stale_inflight(pf_engine *engine, double max_age_seconds, size_t *cleaned);
+
 /* Where a save and a load spend their time on the host side, accumulated since the engine was
  * created: seconds and number of samples per phase.  Phases that the reference traces carry its
  * span names (pf_engine_phase_name: "save.resolve_metadata", "save.hash_filter",

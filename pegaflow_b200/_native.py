@@ -202,6 +202,7 @@ class CacheCleanupStats(C.Structure):
 
 
 _sig("pf_engine_cleanup_memory_cache", C.c_int, vp, P(CacheCleanupStats))
+_sig("pf_engine_gc_stale_inflight", C.c_int, vp, C.c_double, P(sz))
 _sig("pf_engine_get_phase_times", C.c_int, vp, P(PhaseTimes))
 _sig("pf_engine_phase_name", C.c_char_p, C.c_int)
 _sig("pf_load_state_new", C.c_int, P(vp))

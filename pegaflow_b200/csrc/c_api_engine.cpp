@@ -452,6 +452,14 @@ int pf_engine_get_metrics(pf_engine *engine, pf_engine_metrics *out) {
   });
 }
 
+int pf_engine_gc_stale_inflight(pf_engine *engine, double max_age_seconds, size_t *cleaned) {
+  return guarded([&] {
+    if (!engine || !cleaned) throw Error::invalid("null argument");
+    if (!(max_age_seconds >= 0)) throw Error::invalid("max_age_seconds must be >= 0");
+    *cleaned = engine->impl.gc_stale_inflight(max_age_seconds);
+  });
+}
+
 int pf_engine_cleanup_memory_cache(pf_engine *engine, pf_cache_cleanup_stats *out) {
   return guarded([&] {
     if (!engine || !out) throw Error::invalid("null argument");

@@ -576,6 +576,24 @@ void Engine::unregister_instance(const std::string &instance_id) {
   inst.reset();  // last reference: joins the instance's GPU workers
 }
 
+// lib.rs:938-948, storage/write_path.rs: the background sweep of blocks that never got all their slots.
+size_t Engine::gc_stale_inflight(double max_age_seconds) {
+  std::vector<Inflight> stale;  // destroyed outside the lock (frees pool memory)
+  {
+    const auto now = std::chrono::steady_clock::now();
+    std::lock_guard<std::mutex> g(inflight_mu_);
+    for (auto it = inflight_.begin(); it != inflight_.end();) {
+      if (std::chrono::duration<double>(now - it->second.created).count() > max_age_seconds) {
+        stale.push_back(std::move(it->second));
+        it = inflight_.erase(it);
+      } else {
+        ++it;
+      }
+    }
+  }
+  return stale.size();
+}
+
 // lib.rs:459-475
 std::vector<std::string> Engine::unregister_all_instances() {
   std::vector<std::shared_ptr<InstanceContext>> gone;
@@ -1049,6 +1067,7 @@ void Engine::insert_loop() {
 
 // storage/write_path.rs:119-254 + offload.rs:70-151.
 void Engine::process_insert(RawSaveBatch &batch) {
+  std::lock_guard<std::mutex> inflight_guard(inflight_mu_);
   if (!batch.sealed.empty()) {
     // sealed by the save itself while its copy ran: publish
     const auto &hashes = *batch.sealed_hashes;

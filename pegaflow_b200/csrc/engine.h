@@ -290,6 +290,9 @@ class Engine {
                  const std::vector<size_t> &src_ids, const std::vector<size_t> &dst_ids);
   void metrics(pf_engine_metrics *out);
   void cleanup_memory_cache(pf_cache_cleanup_stats *out);
+  // Drops blocks that have waited for their missing slots longer than max_age_seconds (a rank or a
+  // layer that never saved); returns how many.  Their pool memory goes back.
+  size_t gc_stale_inflight(double max_age_seconds);
   void phase_times(pf_engine_phase_times *out);
 
  private:
@@ -316,6 +319,7 @@ class Engine {
     size_t total_slots;
     size_t filled = 0;
     std::vector<std::optional<RawBlock>> slots;
+    std::chrono::steady_clock::time_point created = std::chrono::steady_clock::now();
   };
   struct Lease {
     std::string instance_id;
@@ -361,6 +365,7 @@ class Engine {
   bool insert_stop_ = false;
   bool trace_ = false;       // PEGAFLOW_B200_TRACE=1: per-save phase timings on stderr
   std::string async_error_;  // first failure of an asynchronous save since the last flush
+  std::mutex inflight_mu_;  // the insert thread and gc_stale_inflight
   std::unordered_map<BlockKey, Inflight, BlockKeyHash> inflight_;
 
   // metrics (metrics.rs:325-349)

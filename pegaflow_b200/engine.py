@@ -421,6 +421,13 @@ class PegaEngine:
         N.check(N.lib.pf_engine_cleanup_memory_cache(self._h, C.byref(s)))
         return {f: int(getattr(s, f)) for f, _ in N.CacheCleanupStats._fields_}
 
+    def gc_stale_inflight(self, max_age_seconds: float) -> int:
+        """Drop blocks that have waited longer than `max_age_seconds` for slots that never came (lib.rs:938-948);
+        returns how many."""
+        n = N.sz()
+        N.check(N.lib.pf_engine_gc_stale_inflight(self._h, float(max_age_seconds), C.byref(n)))
+        return int(n.value)
+
     def phase_times(self) -> dict:
         """{phase name: (seconds, samples)} accumulated since the engine was created; phases the
         reference traces carry its span names (``save.pinned_alloc``, ``gpu.save_task``, ...)."""

@@ -378,6 +378,30 @@ def prometheus_text(metrics: dict) -> str:
     return "\n".join(out) + "\n"
 
 
+class InflightSweeper:
+    """pegaflow-server/src/lib.rs:612-648: every `interval` seconds drop the blocks that have been waiting longer
+    than `max_age` for slots that never came (a rank or a layer that did not save).  The reference's constants:
+    60 s and 300 s."""
+
+    def __init__(self, engine, interval: float = 60.0, max_age: float = 300.0):
+        self.engine, self.interval, self.max_age = engine, interval, max_age
+        self.cleaned = 0
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, name="pf-inflight-gc", daemon=True)
+        self._thread.start()
+
+    def _run(self):
+        while not self._stop.wait(self.interval):
+            try:
+                self.cleaned += int(self.engine.gc_stale_inflight(self.max_age))
+            except Exception:
+                pass            # the engine is going away; the next tick finds the stop flag
+
+    def stop(self):
+        self._stop.set()
+        self._thread.join(2.0)
+
+
 class HttpEndpoints:
     """pegaflow-server/src/http_server.rs:22-196: `GET /health`, `GET /metrics` (when enabled),
     `GET /instances`, `POST /instances/cleanup[?id=<instance_id>]`, `POST /cache/memory/cleanup`, on a thread of
@@ -475,12 +499,14 @@ def main(argv=None):
     engine = PegaEngine(pool, args.use_hugepages)
     server = serve(engine, args.addr)
     http = HttpEndpoints(server.service, args.http_addr, args.enable_prometheus == "true")
+    sweeper = InflightSweeper(engine)
     print(f"pegaflow_b200 engine server listening on port {server.port}", flush=True)
     print(f"pegaflow_b200 HTTP endpoints on port {http.port}", flush=True)
     try:
         server.wait_for_shutdown_request()
     except KeyboardInterrupt:
         pass
+    sweeper.stop()
     http.stop()
     server.stop()
     engine.close()

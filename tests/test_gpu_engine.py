@@ -357,6 +357,34 @@ def test_leased_blocks_survive_eviction_pressure(pf):
         eng.close()
 
 
+def test_stale_inflight_blocks_are_swept_and_their_memory_returned(pf):
+    """lib.rs:938-948: blocks that wait for slots which never come (here: the second layer is never saved) are
+    dropped by the sweep once they are older than the age given, and nothing younger is."""
+    import time
+
+    eng, mem, _, _ = _pair(pf)
+    try:
+        layers = [sc.Layer("layer_0", 4, 1024), sc.Layer("layer_1", 4, 1024)]
+        sc.register(eng, mem, "gc", "ns", layers)
+        assert eng.gc_stale_inflight(0.0) == 0
+        hashes = sc.make_block_hashes(4, 77)
+        eng.batch_save("gc", 0, 0, 0, [("layer_0", [0, 1, 2, 3], hashes)])
+        eng.flush_saves()
+        assert len(eng.query_prefix("gc", hashes)[0]) == 0 and eng.metrics()["pool_used_bytes"] > 0
+        assert eng.gc_stale_inflight(300.0) == 0, "a block younger than the age limit was swept"
+        time.sleep(0.05)
+        assert eng.gc_stale_inflight(0.01) == 4
+        assert eng.metrics()["pool_used_bytes"] == 0 and eng.gc_stale_inflight(0.0) == 0
+        # the same blocks can be saved again, completely this time
+        eng.batch_save("gc", 0, 0, 0, [("layer_0", [0, 1, 2, 3], hashes), ("layer_1", [0, 1, 2, 3], hashes)])
+        eng.flush_saves()
+        assert len(eng.query_prefix("gc", hashes)[0]) == 4
+        with pytest.raises(pf.PegaFlowError, match="max_age_seconds"):
+            eng.gc_stale_inflight(-1.0)
+    finally:
+        eng.close()
+
+
 def test_instance_listing_namespace_and_unregister_all(pf):
     """lib.rs:459-489: list_instance_ids, instance_namespace, unregister_all_instances."""
     eng = pf.PegaEngine(4 << 20, enable_numa_affinity=False)

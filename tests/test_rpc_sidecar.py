@@ -296,3 +296,27 @@ def test_rpc_client_surface_matches_the_reference_stub():
         want = [tuple(x) for x in params]
         assert got[:len(want)] == want, f"EngineRpcClient.{method}: {got} != {want}"
         assert all(has_default for _, has_default in got[len(want):]), f"{method}: extra parameters must be optional"
+
+
+def test_inflight_sweeper_calls_the_engine_until_stopped():
+    """pegaflow-server/src/lib.rs:612-648: a background sweep with the maximum age it was given."""
+    from pegaflow_b200.server import InflightSweeper
+
+    class Engine:
+        def __init__(self):
+            self.ages = []
+
+        def gc_stale_inflight(self, max_age):
+            self.ages.append(max_age)
+            return 2
+
+    engine = Engine()
+    sweeper = InflightSweeper(engine, interval=0.02, max_age=300.0)
+    deadline = time.time() + 5
+    while len(engine.ages) < 3 and time.time() < deadline:
+        time.sleep(0.01)
+    sweeper.stop()
+    seen = len(engine.ages)
+    assert seen >= 3 and set(engine.ages) == {300.0} and sweeper.cleaned == 2 * seen
+    time.sleep(0.1)
+    assert len(engine.ages) == seen, "the sweep went on after stop()"
