@@ -153,3 +153,22 @@ def test_pre_touch_worker_count_follows_the_reference_rule():
 def test_read_hugepage_size():
     assert N.lib.pf_huge_page_size() > 0                         # pinned_mem.rs:432-436
     assert N.lib.pf_huge_page_size() % 4096 == 0
+
+
+def test_parse_cpulist_round_trips_any_set_of_cpus():
+    """Property: whatever set of CPUs the kernel's list syntax spells - runs as ranges, singletons, in any order,
+    overlapping - the parser gives back exactly that set, sorted."""
+    from hypothesis import given, settings
+    from hypothesis import strategies as st
+
+    @settings(max_examples=200, deadline=None)
+    @given(st.lists(st.tuples(st.integers(0, 240), st.integers(0, 12)), min_size=0, max_size=12), st.randoms())
+    def check(runs, rnd):
+        want, parts = set(), []
+        for start, extra in runs:
+            want.update(range(start, start + extra + 1))
+            parts.append(str(start) if extra == 0 and rnd.random() < 0.7 else f"{start}-{start + extra}")
+        rnd.shuffle(parts)
+        assert parse(",".join(parts)) == sorted(want)
+
+    check()
