@@ -18,6 +18,7 @@ allocator); parity is defined on GPU bytes after a load and on each stored block
 from __future__ import annotations
 
 import os
+import time
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -197,6 +198,7 @@ class OracleEngine:
         self.instances: Dict[str, _Instance] = {}
         self.read_cache: Dict[Tuple[str, bytes], SealedBlock] = {}
         self.inflight: Dict[Tuple[str, bytes], Tuple[int, Dict[int, _RawBlock]]] = {}
+        self.inflight_born: Dict[Tuple[str, bytes], float] = {}
         self.leases: Dict[bytes, list] = {}
 
     # -- registration: lib.rs:302-440 ----------------------------------------------------------
@@ -325,6 +327,40 @@ class OracleEngine:
         if self.instances.pop(instance_id, None) is None:
             raise EngineError("InstanceMissing", instance_id)
         self.leases = {k: v for k, v in self.leases.items() if v[0] != instance_id}
+
+    # lib.rs:459-489
+    def unregister_all_instances(self) -> List[str]:
+        ids = sorted(self.instances)
+        self.instances.clear()
+        self.leases.clear()
+        return ids
+
+    def list_instance_ids(self) -> List[str]:
+        return sorted(self.instances)
+
+    def instance_namespace(self, instance_id) -> str:
+        return self._instance(instance_id).namespace
+
+    def cleanup_memory_cache(self) -> Dict[str, int]:
+        """storage/mod.rs:395-445: every resident block leaves the cache; the ones a lease still holds are counted.
+        `reclaimed_bytes` depends on how the pool's allocations were grouped, which the model does not track."""
+        held = {id(b) for ent in self.leases.values() for b in ent[1]}
+        removed = list(self.read_cache.values())
+        self.read_cache.clear()
+        footprint = sum(seg.size for b in removed for raw in b.slots if raw is not None for seg in raw.segments)
+        return {"evicted_blocks": len(removed), "evicted_bytes": footprint,
+                "still_referenced_blocks": sum(1 for b in removed if id(b) in held)}
+
+    def gc_stale_inflight(self, max_age_seconds: float) -> int:
+        """lib.rs:938-948: drop the blocks that have waited longer than `max_age_seconds` for slots that never came."""
+        if not max_age_seconds >= 0:
+            raise _invalid("max_age_seconds must be >= 0")
+        now = time.monotonic()
+        stale = [k for k, born in self.inflight_born.items() if now - born > max_age_seconds]
+        for k in stale:
+            self.inflight.pop(k, None)
+            del self.inflight_born[k]
+        return len(stale)
 
     def _instance(self, instance_id) -> _Instance:
         if instance_id not in self.instances:
@@ -464,6 +500,8 @@ class OracleEngine:
         if key in self.read_cache:
             self._release(raw)
             return
+        if key not in self.inflight:
+            self.inflight_born[key] = time.monotonic()
         total, slots = self.inflight.setdefault(key, (total_slots, {}))
         if total != total_slots:
             return
@@ -473,6 +511,7 @@ class OracleEngine:
         slots[slot] = raw
         if len(slots) == total:
             del self.inflight[key]
+            self.inflight_born.pop(key, None)
             self.read_cache[key] = SealedBlock([slots[i] for i in range(total)])
 
     def _release(self, raw: _RawBlock):

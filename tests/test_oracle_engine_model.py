@@ -134,3 +134,51 @@ def test_layer_ids_follow_bytewise_name_order():
     sc.register(eng, mem, "ord", "ns", layers)
     topo = eng.instances["ord"].topology
     assert [topo.layer_id(n) for n in names] == [1, 2, 0]
+
+
+def test_cleanup_memory_cache_counts_what_leaves_and_what_is_still_held():
+    """storage/mod.rs:662-681: two resident blocks, one of them held elsewhere -> evicted 2, still referenced 1;
+    a second clean-up finds nothing."""
+    eng, mem = _engine(), sc.NumpyMem()
+    L = sc.Layer("layer_0", 4, 1024)
+    sc.register(eng, mem, "clean", "ns", [L])
+    held, free = sc.make_block_hashes(1, 60), sc.make_block_hashes(1, 61)
+    eng.batch_save("clean", 0, 0, 0, [("layer_0", [0], held)])
+    eng.batch_save("clean", 0, 0, 0, [("layer_0", [1], free)])
+    blocks, _ = eng.query_prefix("clean", held)
+    lease = eng.create_query_lease("clean", blocks)
+    assert eng.cleanup_memory_cache() == {"evicted_blocks": 2, "evicted_bytes": 2048, "still_referenced_blocks": 1}
+    assert eng.query_prefix("clean", held) == ([], 1) and eng.query_prefix("clean", free) == ([], 1)
+    assert eng.cleanup_memory_cache() == {"evicted_blocks": 0, "evicted_bytes": 0, "still_referenced_blocks": 0}
+    assert eng.release_query_lease(lease) is True        # the lease outlives the cache entry
+
+
+def test_stale_inflight_sweep_and_instance_listing():
+    """lib.rs:938-948 (blocks whose missing slots never came are dropped after an age limit) and lib.rs:459-489
+    (list, namespace, unregister all; leases go with the instances)."""
+    import time
+
+    eng, mem = _engine(), sc.NumpyMem()
+    assert eng.list_instance_ids() == [] and eng.unregister_all_instances() == [] and eng.gc_stale_inflight(0.0) == 0
+    layers = [sc.Layer("layer_0", 4, 1024), sc.Layer("layer_1", 4, 1024)]
+    sc.register(eng, mem, "inst-b", "ns-1", layers)
+    other = [sc.Layer("layer_0", 4, 1024)]
+    sc.register(eng, mem, "inst-a", "ns-2", other)
+    assert eng.list_instance_ids() == ["inst-a", "inst-b"] and eng.instance_namespace("inst-b") == "ns-1"
+    with pytest.raises(EngineError) as e:
+        eng.instance_namespace("nobody")
+    assert e.value.kind == "InstanceMissing"
+    hashes = sc.make_block_hashes(4, 77)
+    eng.batch_save("inst-b", 0, 0, 0, [("layer_0", [0, 1, 2, 3], hashes)])     # layer_1 never comes
+    assert eng.query_prefix("inst-b", hashes) == ([], 4)
+    assert eng.gc_stale_inflight(300.0) == 0
+    time.sleep(0.02)
+    assert eng.gc_stale_inflight(0.01) == 4 and eng.gc_stale_inflight(0.0) == 0
+    eng.batch_save("inst-b", 0, 0, 0, [("layer_0", [0, 1, 2, 3], hashes), ("layer_1", [0, 1, 2, 3], hashes)])
+    blocks, missing = eng.query_prefix("inst-b", hashes)
+    assert missing == 0
+    lease = eng.create_query_lease("inst-b", blocks)
+    with pytest.raises(EngineError):
+        eng.gc_stale_inflight(-1.0)
+    assert eng.unregister_all_instances() == ["inst-a", "inst-b"] and eng.list_instance_ids() == []
+    assert eng.release_query_lease(lease) is False
