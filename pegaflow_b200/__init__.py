@@ -8,4 +8,4 @@ from ._native import PegaFlowError, PegaflowInternal, PegaflowInvalidArgument  #
 from .backend import (HostRun, LayerXfer, PinnedPool, TransferBackend, enable_peer_access,  # noqa: F401
                       numa_node_of_device, save_blocks_noalloc)
 from .engine import Block, Completion, PegaEngine, PyLoadState  # noqa: F401
-from .connector import InProcEngineClient, QueryLoading, QueryReady  # noqa: F401,E402
+from .connector import InProcEngineClient, QueryLoading, QueryReady, TransferStats  # noqa: F401,E402

@@ -298,6 +298,66 @@ class _PendingLoad:
     started: float = 0.0
 
 
+class TransferStats:
+    """What the worker reports about its transfers between two readings, under the keys of the
+    reference's ``PegaKVConnectorStats`` (connector_metrics.py:115-260): per-operation durations
+    (seconds) and block counts as lists, success and failure counters, and the number of requests
+    whose saves are still pending.  ``aggregate`` adds another reading to this one, ``reduce`` gives
+    the summary the reference logs."""
+
+    LISTS = ("load_duration", "load_blocks", "save_duration", "save_blocks")
+    COUNTERS = ("load_success_count", "load_failure_count", "save_success_count", "save_failure_count")
+
+    def __init__(self):
+        self.reset()
+
+    def reset(self):
+        self.data = {"pending_save_requests": 0}
+        self.data.update({k: [] for k in self.LISTS})
+        self.data.update({k: 0 for k in self.COUNTERS})
+
+    def _record(self, kind: str, seconds: float, blocks: int, ok: bool):
+        self.data[f"{kind}_duration"].append(float(seconds))
+        self.data[f"{kind}_blocks"].append(int(blocks))
+        self.data[f"{kind}_{'success' if ok else 'failure'}_count"] += 1
+
+    def record_load(self, duration_seconds: float, num_blocks: int, success: bool):
+        self._record("load", duration_seconds, num_blocks, success)
+
+    def record_save(self, duration_seconds: float, num_blocks: int, success: bool):
+        self._record("save", duration_seconds, num_blocks, success)
+
+    def is_empty(self) -> bool:
+        return not self.data["pending_save_requests"] and not any(self.data[k] for k in self.LISTS + self.COUNTERS)
+
+    def aggregate(self, other: "TransferStats") -> "TransferStats":
+        self.data["pending_save_requests"] = other.data.get("pending_save_requests", 0)    # a gauge: the latest
+        for k in self.COUNTERS:
+            self.data[k] += other.data.get(k, 0)
+        for k in self.LISTS:
+            self.data[k].extend(other.data.get(k, []))
+        return self
+
+    def reduce(self) -> dict:
+        out = {"pending_save_requests": self.data["pending_save_requests"]}
+        for kind in ("load", "save"):
+            seconds, blocks = self.data[f"{kind}_duration"], self.data[f"{kind}_blocks"]
+            if seconds:
+                out[f"num_{kind}s"] = len(seconds)
+                out[f"avg_{kind}_duration_ms"] = round(sum(seconds) / len(seconds) * 1000, 3)
+                out[f"total_{kind}_blocks"] = sum(blocks)
+                out[f"avg_{kind}_blocks"] = round(sum(blocks) / len(seconds), 1)
+            out[f"{kind}_success_count"] = self.data[f"{kind}_success_count"]
+            out[f"{kind}_failure_count"] = self.data[f"{kind}_failure_count"]
+        return out
+
+    def clone_and_reset(self) -> "TransferStats":
+        old = TransferStats()
+        old.data = self.data
+        self.reset()
+        return old
+
+
 class PegaWorkerConnector:
     """Worker-side hooks on the transfer path for one GPU of one instance."""
 
@@ -325,6 +385,7 @@ class PegaWorkerConnector:
         self._load_errors: set = set()
         self._rejected_loads: List[str] = []      # requests whose load could not even be submitted
         self.load_history: List[Tuple[float, int, bool]] = []   # (seconds, blocks, ok) per finished load task
+        self.stats = TransferStats()                             # worker.py:242
         self._saves_in_flight = 0
 
     # worker.py:261-412
@@ -391,6 +452,7 @@ class PegaWorkerConnector:
                     pass
             self._load_errors.update(pending.block_ids)
             self._rejected_loads.extend(pending.request_ids)
+            self.stats.record_load(time.perf_counter() - pending.started, len(pending.block_ids), False)   # worker.py:741-753
             self.state_manager.mark_unavailable(f"load rpc failed: {msg}")   # worker.py:659,677
             return
         self._pending_loads.append(pending)
@@ -440,7 +502,13 @@ class PegaWorkerConnector:
                     else:
                         memo[key] = (ids, hashes)
                 cleaned.append((name,) + memo[key])
-            ok, msg = self.client.save(self.instance_id, self.tp_rank, self.pp_rank, self.device_id, cleaned)
+            started = time.perf_counter()
+            try:
+                ok, msg = self.client.save(self.instance_id, self.tp_rank, self.pp_rank, self.device_id, cleaned)
+            except Exception:
+                self.stats.record_save(time.perf_counter() - started, sum(len(ids) for _, ids, _ in cleaned), False)
+                raise
+            self.stats.record_save(time.perf_counter() - started, sum(len(ids) for _, ids, _ in cleaned), ok)   # worker.py:925-926
             if not ok:
                 raise RuntimeError(f"save failed: {msg}")
         ok, msg = self.client.flush_saves()
@@ -554,6 +622,7 @@ class PegaWorkerConnector:
                 self._load_errors.update(p.block_ids)
             timed_out = timed_out or st == 0
             self.load_history.append((now - p.started, len(p.block_ids), st == 1))
+            self.stats.record_load(now - p.started, len(p.block_ids), st == 1)            # worker.py:525-528
         self._pending_loads = still
         del self.load_history[:-1024]
         if timed_out:
@@ -564,6 +633,13 @@ class PegaWorkerConnector:
             raise RuntimeError("PegaFlow HMA load failed; vLLM cannot recover failed loads for multiple cache groups: "
                                f"{hma_failure}")
         return done, failed
+
+    def get_stats(self) -> Optional[TransferStats]:
+        """worker.py:1039-1047: what happened since the last reading, or None when nothing did."""
+        self.stats.data["pending_save_requests"] = self._saves_in_flight
+        if self.stats.is_empty():
+            return None
+        return self.stats.clone_and_reset()
 
     def get_block_ids_with_load_errors(self) -> set:
         out, self._load_errors = self._load_errors, set()

@@ -104,3 +104,65 @@ def test_a_group_load_that_fails_later_ends_the_step_like_the_reference(how):
     assert worker.get_block_ids_with_load_errors() == set()
     assert worker._pending_loads == [] and worker.get_finished() == ([], [])   # reported once
     assert worker.load_history[-1][2] is False
+
+
+def test_transfer_stats_have_the_reference_shape():
+    """connector_metrics.py:115-260: keys, counters, list extension on aggregate, the logged summary, reset on read."""
+    from pegaflow_b200.connector import TransferStats
+
+    a, b = TransferStats(), TransferStats()
+    assert a.is_empty() and a.reduce() == {"pending_save_requests": 0, "load_success_count": 0, "load_failure_count": 0,
+                                          "save_success_count": 0, "save_failure_count": 0}
+    a.record_load(0.010, 64, True)
+    a.record_load(0.030, 16, False)
+    b.record_save(0.002, 8, True)
+    b.data["pending_save_requests"] = 3
+    assert not a.is_empty() and not b.is_empty()
+    merged = a.aggregate(b)
+    assert merged is a and a.data["load_duration"] == [0.010, 0.030] and a.data["save_blocks"] == [8]
+    assert a.reduce() == {"pending_save_requests": 3, "num_loads": 2, "avg_load_duration_ms": 20.0, "total_load_blocks": 80,
+                          "avg_load_blocks": 40.0, "load_success_count": 1, "load_failure_count": 1, "num_saves": 1,
+                          "avg_save_duration_ms": 2.0, "total_save_blocks": 8, "avg_save_blocks": 8.0,
+                          "save_success_count": 1, "save_failure_count": 0}
+    old = a.clone_and_reset()
+    assert a.is_empty() and old.data["load_success_count"] == 1 and old.data["save_duration"] == [0.002]
+
+
+def test_worker_records_its_loads_and_saves():
+    """worker.py:525-528, 741-753, 925-926, 1039-1047: finished loads, loads that could not be submitted and batch
+    saves each leave a record; a reading hands them out and starts afresh."""
+    from pegaflow_b200.connector import PegaWorkerConnector
+
+    class Client:
+        def __init__(self):
+            self.accept_loads = True
+
+        def health(self):
+            return True, ""
+
+        def load(self, *a):
+            return (True, "") if self.accept_loads else (False, "no")
+
+        def release(self, lease):
+            pass
+
+        def save(self, instance_id, tp_rank, pp_rank, device_id, saves):
+            return True, ""
+
+        def flush_saves(self):
+            return True, ""
+
+    client = Client()
+    w = PegaWorkerConnector(client, None, instance_id="i", namespace="n", device_id=0, block_size=16)
+    w.registered_layers = ["layer_0", "layer_1"]
+    assert w.get_stats() is None
+    w.start_load_kv([("req-a", b"L" * 16, [4, None, 9])])
+    w._pending_loads[0].state.set_completed()
+    assert w.get_finished() == (["req-a"], [])
+    client.accept_loads = False
+    w.start_load_kv([("req-b", b"M" * 16, [1, 2, 3])])
+    w.wait_for_save([("layer_0", [0, 5, 6], [b"z", b"a", b"b"]), ("layer_1", [5, 6], [b"a", b"b"])])
+    got = w.get_stats()
+    assert got.data["load_blocks"] == [2, 3] and got.data["load_success_count"] == 1 and got.data["load_failure_count"] == 1
+    assert got.data["save_blocks"] == [4] and got.data["save_success_count"] == 1      # block 0 is vLLM's null block
+    assert w.get_stats() is None
